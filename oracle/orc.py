@@ -1,0 +1,232 @@
+"""ctypes/numpy front end of the CPU oracle (``liborc.so``).  TEST INFRASTRUCTURE ONLY.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg may import this module; the
+product package never does.  The functions mirror the reference's CPU path one to one and
+cite the reference file:line they restate (see ``oracle_core.cpp`` for the arithmetic).
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+QK = 128
+PQ2_BYTES = 34
+PTQ1_BYTES = 28
+Q8_0_BYTES = 34
+PQ2_0, PTQ1_0 = 0, 1
+Q8_0, Q6_K = 0, 1
+GGML, F32 = 0, 1
+
+
+def build(force=False):
+    so = os.path.join(_HERE, "liborc.so")
+    srcs = [os.path.join(_HERE, f) for f in os.listdir(_HERE) if f.endswith((".cpp", ".h"))]
+    if force or not os.path.exists(so) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs):
+        subprocess.run(["make", "-C", _HERE, "liborc.so"], check=True, capture_output=True)
+    return so
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        so = os.path.join(_HERE, "liborc.so")
+        if not os.path.exists(so):
+            build()
+        _LIB = C.CDLL(so)
+        _LIB.orc_packed2_dot_q8k.restype = C.c_float
+        _LIB.orc_packed2_dot_f32.restype = C.c_float
+        _LIB.orc_argmax.restype = C.c_uint32
+        _LIB.orc_greedy_mtp.restype = C.c_int64
+        _LIB.orc_max_threads.restype = C.c_int
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def max_threads():
+    return int(lib().orc_max_threads())
+
+
+# ---- weight decode -----------------------------------------------------------------------
+def _dequant(fn, raw, block_bytes, block_elems):
+    raw = _c(raw, np.uint8)
+    nb = raw.size // block_bytes
+    out = np.empty(nb * block_elems, np.float32)
+    fn(_p(raw), C.c_int64(nb), _p(out))
+    return out
+
+
+def dequant_pq2_0(raw):   # src/quant.rs:51
+    return _dequant(lib().orc_dequant_pq2_0, raw, 34, 128)
+
+
+def dequant_ptq1_0(raw):  # src/quant.rs:58
+    return _dequant(lib().orc_dequant_ptq1_0, raw, 28, 128)
+
+
+def dequant_q8_0(raw):    # src/quant.rs:188
+    return _dequant(lib().orc_dequant_q8_0, raw, 34, 32)
+
+
+def dequant_q6_k(raw):    # src/quant.rs:192
+    return _dequant(lib().orc_dequant_q6_k, raw, 210, 256)
+
+
+def dequant_q4_k(raw):    # src/quant.rs:215
+    return _dequant(lib().orc_dequant_q4_k, raw, 144, 256)
+
+
+def packed2_from_ggml(ty, raw, rows, cols):  # src/quant.rs:100
+    raw = _c(raw, np.uint8)
+    words = np.empty(rows * cols // 16, np.uint32)
+    scales = np.empty(rows * cols // 128, np.float32)
+    lib().orc_packed2_from_ggml(C.c_int(ty), _p(raw), C.c_int64(rows), C.c_int64(cols), _p(words), _p(scales))
+    return words, scales
+
+
+def packed2_row_f32(words, scales, cols, r):  # src/quant.rs:121
+    out = np.empty(cols, np.float32)
+    lib().orc_packed2_row_f32(_p(words), _p(scales), C.c_int64(cols), C.c_int64(r), _p(out))
+    return out
+
+
+def quantize_q8k(x):  # src/quant.rs:75
+    x = _c(x, np.float32)
+    n = x.size
+    assert n % 256 == 0
+    d = np.empty(n // 256, np.float32)
+    qs = np.empty(n, np.int8)
+    s = np.empty(n // 128, np.int32)
+    lib().orc_quantize_q8k(_p(x), C.c_int64(n), _p(d), _p(qs), _p(s))
+    return d, qs, s
+
+
+def packed2_dot_q8k(words, scales, cols, r, q):  # src/quant.rs:132
+    d, qs, s = q
+    return np.float32(lib().orc_packed2_dot_q8k(_p(words), _p(scales), C.c_int64(cols), C.c_int64(r), _p(d), _p(qs), _p(s)))
+
+
+def packed2_dot_f32(words, scales, cols, r, x):  # src/quant.rs:150
+    x = _c(x, np.float32)
+    return np.float32(lib().orc_packed2_dot_f32(_p(words), _p(scales), C.c_int64(cols), C.c_int64(r), _p(x)))
+
+
+def matvec_ternary(raw, rows, cols, x, numerics=GGML, ty=PQ2_0, nthreads=0, want_sumi=False):
+    """cpu::matvec ternary arm (src/cpu.rs:25-35) on raw PQ2_0 / PTQ1_0 row data."""
+    raw = _c(raw, np.uint8)
+    x = _c(x, np.float32)
+    assert x.size == cols
+    y = np.empty(rows, np.float32)
+    sumi = np.empty((rows, cols // 128), np.int32) if want_sumi else None
+    lib().orc_matvec_ternary(C.c_int(ty), _p(raw), C.c_int64(rows), C.c_int64(cols), _p(x), C.c_int(numerics), _p(y),
+                             C.c_int(nthreads), _p(sumi) if want_sumi else None)
+    return (y, sumi) if want_sumi else y
+
+
+def q8g16_from_ggml(ty, raw, rows, cols):  # src/quant.rs:235
+    raw = _c(raw, np.uint8)
+    words = np.empty(rows * cols // 4, np.uint32)
+    scales = np.empty(rows * cols // 16, np.float32)
+    lib().orc_q8g16_from_ggml(C.c_int(ty), _p(raw), C.c_int64(rows), C.c_int64(cols), _p(words), _p(scales))
+    return words, scales
+
+
+def q8g16_row_f32(words, scales, cols, r):
+    out = np.empty(cols, np.float32)
+    lib().orc_q8g16_row_f32(_p(words), _p(scales), C.c_int64(cols), C.c_int64(r), _p(out))
+    return out
+
+
+def mvq(words, scales, rows, cols, x, nthreads=0):  # src/mtp.rs:93 + src/quant.rs:266
+    x = _c(x, np.float32)
+    y = np.empty(rows, np.float32)
+    lib().orc_mvq(_p(words), _p(scales), C.c_int64(rows), C.c_int64(cols), _p(x), _p(y), C.c_int(nthreads))
+    return y
+
+
+# ---- Hadamard ----------------------------------------------------------------------------
+def fwht_blocks(x, block):  # src/hadamard.rs:7
+    y = _c(x, np.float32).copy()
+    lib().orc_fwht_blocks(_p(y), C.c_int64(y.size), C.c_int64(block))
+    return y
+
+
+def gdn_group_perm(x, hd, nk, rep):  # src/hadamard.rs:23
+    x = _c(x, np.float32)
+    o = np.empty_like(x)
+    lib().orc_gdn_group_perm(_p(x), _p(o), C.c_int64(hd), C.c_int64(nk), C.c_int64(rep))
+    return o
+
+
+def hadamard_forward(x, block=1024, signs=None, perm=None):  # src/hadamard.rs:35 (+ src/cpu.rs:239)
+    x = _c(x, np.float32)
+    y = np.empty_like(x)
+    hd, nk, rep = perm if perm else (0, 0, 0)
+    sg = _c(signs, np.float32) if signs is not None else None
+    lib().orc_hadamard_forward(_p(x), _p(y), C.c_int64(x.size), C.c_int64(block), _p(sg) if sg is not None else None,
+                               C.c_int64(hd), C.c_int64(nk), C.c_int64(rep))
+    return y
+
+
+def hadamard_inverse(z, block=1024, signs=None):  # src/hadamard.rs:41
+    z = _c(z, np.float32)
+    y = np.empty_like(z)
+    sg = _c(signs, np.float32) if signs is not None else None
+    lib().orc_hadamard_inverse(_p(z), _p(y), C.c_int64(z.size), C.c_int64(block), _p(sg) if sg is not None else None)
+    return y
+
+
+def argmax(v):  # src/sampling.rs:50
+    v = _c(v, np.float32)
+    return int(lib().orc_argmax(_p(v), C.c_int64(v.size)))
+
+
+# ---- speculative loop ----------------------------------------------------------------------
+class _Backend(C.Structure):
+    _fields_ = [("user", C.c_void_p),
+                ("prefill", C.CFUNCTYPE(C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32), C.c_int64)),
+                ("single", C.CFUNCTYPE(C.c_uint32, C.c_void_p, C.c_uint32)),
+                ("draft", C.CFUNCTYPE(C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32), C.c_int64)),
+                ("verify", C.CFUNCTYPE(None, C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32))),
+                ("reject", C.CFUNCTYPE(None, C.c_void_p)),
+                ("reset_all", C.CFUNCTYPE(None, C.c_void_p))]
+
+
+STAT_NAMES = ("drafted", "accepted", "steps", "draft_calls", "verify_calls", "single_forwards",
+              "timed_decode_forwards", "rejected", "terminal_rollbacks")
+
+
+def greedy_mtp(backend, prompt, n, is_eog=lambda t: False, on_tok=lambda t: True):
+    """greedy_mtp (src/mtp.rs:166-204) over a Python backend object with the MtpBackend methods."""
+    F = dict(_Backend._fields_)
+
+    def _verify(_, x, d, a0, a1):
+        r = backend.mtp_verify(x, d)
+        a0[0], a1[0] = r[0], r[1]
+    be = _Backend(None,
+                  F["prefill"](lambda _, p, k: backend.mtp_prefill([p[i] for i in range(k)])),
+                  F["single"](lambda _, x: backend.mtp_single(x)),
+                  F["draft"](lambda _, p, k: backend.mtp_draft([p[i] for i in range(k)])),
+                  F["verify"](_verify),
+                  F["reject"](lambda _: backend.mtp_reject()),
+                  F["reset_all"](lambda _: backend.reset_all()))
+    CB = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32)
+    eog = CB(lambda _, t: int(bool(is_eog(t))))
+    tok = CB(lambda _, t: int(bool(on_tok(t))))
+    pr = np.asarray(prompt, np.uint32)
+    out = np.zeros(max(n, 1) + 2, np.uint32)
+    stats = np.zeros(9, np.int64)
+    k = lib().orc_greedy_mtp(C.byref(be), _p(pr), C.c_int64(pr.size), C.c_int64(n), eog, tok, None, _p(out), _p(stats))
+    if k < 0:
+        raise ValueError("empty MTP prompt")
+    return [int(t) for t in out[:k]], dict(zip(STAT_NAMES, (int(s) for s in stats)))
