@@ -1,0 +1,126 @@
+/* irontimber_cuda.h - C ABI of the B200 (sm_100a) backend for IronTimber's ternary hot path.
+ *
+ * The reference has no FFI today: its GPU work goes through the private dispatchers of
+ * `VkEngine` (src/vk/mod.rs).  Each entry point below names the reference interface it
+ * stands in for (file:line inside the reference project), so that a `--backend cuda` arm
+ * can bind it one to one.
+ *
+ * Conventions
+ *  - every function returns 0 on success or a negative IT_E* code; `it_last_error()` gives
+ *    the message of the last failure on the calling thread.  Arguments are validated before
+ *    anything is launched (the reference validates before touching the device,
+ *    src/vk/mod.rs:494-503); nothing aborts.
+ *  - one context = one device = one host thread = one compute stream (the reference is
+ *    strictly single threaded, src/server.rs:4).  Op launches are stream ordered and do not
+ *    block; `it_sync` or any read-back waits.
+ *  - activations live in one f32 arena addressed by element offsets, exactly like the
+ *    reference's arena (shaders/common.glsl:5, push constants [M,K,ntok,xo,xs,yo,ys,accum]).
+ *  - handles are opaque; the caller releases them with the matching destroy call, children
+ *    (matrices, q8 buffers) before the context.
+ */
+#ifndef IRONTIMBER_CUDA_H
+#define IRONTIMBER_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IT_OK 0
+#define IT_EINVAL (-1)   /* bad argument (shape, alignment, null, out of range) */
+#define IT_ECUDA (-2)    /* a CUDA runtime call failed */
+#define IT_ENOMEM (-3)   /* device allocation failed */
+#define IT_ESTATE (-4)   /* call not valid in the current state */
+#define IT_ETIMEOUT (-5) /* a bounded device-side wait ran out */
+
+typedef struct it_ctx it_ctx;
+typedef struct it_mat it_mat;   /* ternary (2-bit code) matrix, device resident      */
+typedef struct it_qmat it_qmat; /* int8-group matrix (ggml Q8_0 source)             */
+typedef struct it_q8 it_q8;     /* q8k-quantised activation rows, device resident    */
+
+const char* it_last_error(void);
+int it_version(void);
+
+/* ---- context and arena ---------------------------------------------------------------
+ * Replaces Ctx::new_with + the arena allocation of VkEngine (src/vk/mod.rs:267, :567-576). */
+int it_ctx_create(int device, size_t arena_floats, it_ctx** out);
+void it_ctx_destroy(it_ctx* ctx);
+int it_sync(it_ctx* ctx);                                   /* Ctx::submit_wait, src/vk/mod.rs:380 */
+void* it_ctx_stream(it_ctx* ctx);                           /* the cudaStream_t every op is launched on */
+float* it_arena_ptr(it_ctx* ctx);                           /* device pointer of arena element 0 */
+size_t it_arena_floats(it_ctx* ctx);
+int it_arena_write(it_ctx* ctx, size_t off, const void* host, size_t n_floats); /* Ctx::upload,   src/vk/mod.rs:427 */
+int it_arena_read(it_ctx* ctx, size_t off, void* host, size_t n_floats);        /* Ctx::download */
+int it_arena_zero(it_ctx* ctx, size_t off, size_t n_floats);                    /* zero_state,    src/vk/mod.rs:645 */
+
+/* Hadamard sign vector for activations of width n (prism.hadamard.sign_values; src/model.rs:48-60,
+ * uploaded into the params buffer by the reference, src/vk/mod.rs:536).  Values must be +1 or -1. */
+int it_signs_set(it_ctx* ctx, size_t n, const float* signs);
+
+/* ---- weights -----------------------------------------------------------------------------
+ * Replaces the `mat` upload closure and DevMat (src/vk/mod.rs:459, :579-599).  Accepts either raw
+ * PQ2_0 rows (34-byte blocks, src/quant.rs:5-6,21-29) or the reference's Packed2 pair
+ * (src/quant.rs:92-119).  cols must be a multiple of 128; any row count is accepted. */
+int it_matrix_upload_pq2(it_ctx* ctx, const uint8_t* raw, size_t rows, size_t cols, it_mat** out);
+int it_matrix_upload_packed2(it_ctx* ctx, const uint32_t* words, const float* scales, size_t rows, size_t cols, it_mat** out);
+/* Synthetic matrix generated on the device: codes uniform over {0,1,2} (or {0,1,2,3} when
+ * four_codes != 0), f16 scales uniform in [0.01, 0.05], from a counter hash of (seed, index). */
+int it_matrix_synth(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, it_mat** out);
+/* Decodes the device layout back to raw PQ2_0 rows (rows*cols/128*34 bytes). */
+int it_matrix_download_pq2(it_ctx* ctx, const it_mat* m, uint8_t* raw);
+size_t it_matrix_rows(const it_mat* m);
+size_t it_matrix_cols(const it_mat* m);
+size_t it_matrix_device_bytes(const it_mat* m);
+void it_matrix_destroy(it_mat* m);
+
+/* Int8-group matrices of the MTP head: ggml Q8_0 rows (34-byte blocks of 32; src/quant.rs:188-191),
+ * what Q8G16::from_ggml consumes (src/quant.rs:235-244).  cols % 32 == 0. */
+int it_qmatrix_upload_q8_0(it_ctx* ctx, const uint8_t* raw, size_t rows, size_t cols, it_qmat** out);
+int it_qmatrix_synth(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, it_qmat** out);
+int it_qmatrix_download_q8_0(it_ctx* ctx, const it_qmat* m, uint8_t* raw);
+size_t it_qmatrix_rows(const it_qmat* m);
+size_t it_qmatrix_cols(const it_qmat* m);
+void it_qmatrix_destroy(it_qmat* m);
+
+/* ---- q8k activation rows ------------------------------------------------------------------
+ * Device form of Q8K (src/quant.rs:68-71): per row int8 qs[n], f32 d[n/256], i32 sum128[n/128]. */
+int it_q8_create(it_ctx* ctx, size_t max_n, size_t max_tok, it_q8** out);
+void it_q8_destroy(it_q8* q);
+int it_q8_read(it_ctx* ctx, const it_q8* q, size_t tok, int8_t* qs, float* d, int32_t* sum128);
+
+/* ---- ops -------------------------------------------------------------------------------------
+ * Fused forward Hadamard (per 1024-block: optional GDN head permutation, sign multiply, 10 butterfly
+ * stages, 1/32) + quantize_row_q8_K: replaces VkEngine::had (src/vk/mod.rs:749-753, shaders/hadamard.comp)
+ * followed by quantize_q8k (src/quant.rs:75-90), i.e. Model::prep + the first line of cpu::matvec
+ * (src/cpu.rs:115-117, :30).  Reads ntok rows of n floats at x_off + t*x_stride, writes rows 0..ntok-1
+ * of `out`.  use_signs != 0 multiplies by the sign vector registered for width n.  perm_hd == 0 means
+ * no permutation, otherwise source index = i0 + hd*(k + nk*r) as in shaders/hadamard.comp:13.
+ * rotate == 0 skips the transform and only quantises (weights that were not folded, src/cpu.rs:116). */
+int it_hadamard_q8(it_ctx* ctx, size_t n, size_t ntok, size_t x_off, size_t x_stride, int rotate, int use_signs,
+                   size_t perm_hd, size_t perm_nk, size_t perm_rep, it_q8* out);
+/* Plain f32 transform into the arena, forward or inverse (VkEngine::had with an f32 destination). */
+int it_hadamard_f32(it_ctx* ctx, size_t n, size_t ntok, size_t in_off, size_t in_stride, size_t out_off, size_t out_stride,
+                    int use_signs, size_t perm_hd, size_t perm_nk, size_t perm_rep, int inverse);
+
+/* Ternary matvec / matmul on q8k activations: y[t, r] (+)= sum_b (d_w[r,b] * d_x[t,b/2]) * (sum_j code*q - sum128)
+ * in ascending block order, f32, no fused multiply-add - the arithmetic of cpu::matvec's ternary arm with
+ * Numerics::Ggml (src/cpu.rs:25-35, :48-63; src/quant.rs:132-147).  Replaces VkEngine::mv (src/vk/mod.rs:653-704)
+ * and the kernels it selects (matvec_t2_1, matvec_c8/c8x2, matvec_t2, matmul_t2s, matmul_t2).  Rows 0..ntok-1
+ * of x are used; y is written at y_off + t*y_stride + r.  accum != 0 adds into y (residual adds). */
+int it_matvec_t2(it_ctx* ctx, const it_mat* w, size_t ntok, const it_q8* x, size_t y_off, size_t y_stride, int accum);
+/* Same launch, additionally stores the integer accumulators (sum_j code*q - sum128) per (t, r, block)
+ * into sumi[ntok][rows][cols/128] (device memory owned by the caller).  Used by parity tests. */
+int it_matvec_t2_sumi(it_ctx* ctx, const it_mat* w, size_t ntok, const it_q8* x, int32_t* sumi_dev);
+
+/* Int8-group matvec with f32 activations: y[t, r] (+)= sum_g scale[r,g] * sum_{j<16} q[r,16g+j] * x[t,16g+j].
+ * Replaces VkEngine::mvq (src/vk/mod.rs:742-745, shaders/matvec_q8.comp); CPU twin mtp::mv (src/mtp.rs:93). */
+int it_matvec_q8(it_ctx* ctx, const it_qmat* w, size_t ntok, size_t x_off, size_t x_stride, size_t y_off, size_t y_stride, int accum);
+
+/* Greedy pick: index of the first maximum of n logits at logits_off; the u32 result is stored bit-cast
+ * in arena element dst_off (shaders/argmax.comp, src/sampling.rs:50; dispatch at src/vk/mod.rs:866,875). */
+int it_argmax(it_ctx* ctx, size_t logits_off, size_t n, size_t dst_off);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

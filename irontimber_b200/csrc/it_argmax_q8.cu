@@ -1,0 +1,152 @@
+// Greedy argmax over the logits and the int8-group matvec of the MTP head.
+#include "it_internal.h"
+
+namespace {
+
+// ---------------------------------------------------------------- argmax
+// First index of the maximum (src/sampling.rs:50: strict '>' scan from index 0; shaders/argmax.comp:
+// ties resolve to the lowest index).  Two levels: every CTA scans a contiguous slice and publishes
+// its (value, index); the CTA that finishes last folds the partials and resets the counter, so the
+// scratch is ready for the next launch.  NaN never wins a comparison, as in the reference shader.
+// Algorithmic traffic: 4n bytes.
+struct Pick { float v; unsigned i; };
+__device__ __forceinline__ Pick pick_better(Pick a, Pick b) { return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a; }
+__device__ __forceinline__ unsigned long long pick_pack(Pick p) { return ((unsigned long long)__float_as_uint(p.v) << 32) | p.i; }
+__device__ __forceinline__ Pick pick_unpack(unsigned long long u) { return Pick{ __uint_as_float((unsigned)(u >> 32)), (unsigned)u }; }
+
+__device__ __forceinline__ Pick block_reduce(Pick p, Pick* sh) {
+    const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (unsigned m = 16; m > 0; m >>= 1) { Pick o{ __shfl_xor_sync(0xffffffffu, p.v, m), __shfl_xor_sync(0xffffffffu, p.i, m) }; p = pick_better(p, o); }
+    if (lane == 0) sh[warp] = p;
+    __syncthreads();
+    if (warp == 0) {
+        p = lane < (blockDim.x >> 5) ? sh[lane] : Pick{ -INFINITY, 0xffffffffu };
+#pragma unroll
+        for (unsigned m = 16; m > 0; m >>= 1) { Pick o{ __shfl_xor_sync(0xffffffffu, p.v, m), __shfl_xor_sync(0xffffffffu, p.i, m) }; p = pick_better(p, o); }
+    }
+    return p;   // valid in warp 0
+}
+
+__global__ void __launch_bounds__(256)
+k_argmax(const float* __restrict__ v, unsigned n, unsigned per_block, unsigned long long* partials, unsigned* counter, float* dst) {
+    __shared__ Pick sh[8];
+    __shared__ bool is_last;
+    const unsigned begin = blockIdx.x * per_block, end = min(n, begin + per_block);   // per_block % 4 == 0
+    Pick p{ -INFINITY, 0xffffffffu };
+    for (unsigned i = begin + 4 * threadIdx.x; i < end; i += 4 * blockDim.x) {
+        if (i + 4 <= end) {
+            float4 x = *reinterpret_cast<const float4*>(v + i);
+            p = pick_better(p, Pick{ x.x, i }); p = pick_better(p, Pick{ x.y, i + 1 }); p = pick_better(p, Pick{ x.z, i + 2 }); p = pick_better(p, Pick{ x.w, i + 3 });
+        } else {
+            for (unsigned k = i; k < end; k++) p = pick_better(p, Pick{ v[k], k });
+        }
+    }
+    p = block_reduce(p, sh);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = pick_pack(p);
+        __threadfence();
+        is_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    Pick q{ -INFINITY, 0xffffffffu };
+    for (unsigned b = threadIdx.x; b < gridDim.x; b += blockDim.x) q = pick_better(q, pick_unpack(__ldcg(partials + b)));
+    __syncthreads();
+    q = block_reduce(q, sh);
+    if (threadIdx.x == 0) { *dst = __uint_as_float(q.i == 0xffffffffu ? 0u : q.i); *counter = 0; }
+}
+
+// ---------------------------------------------------------------- int8-group matvec (f32 activations)
+// y[t, r] (+)= sum_g d[r, g/2] * (sum_{j<16} q[r,16g+j] * x[t,16g+j])   (src/quant.rs:266-270, shaders/matvec_q8.comp)
+// One warp per four rows: a lane takes 16 weights of each row per step (one 128-bit load per row) and
+// reuses its 16 activations for the four rows.  HBM-bound: rows*cols*(1 + 2/32) bytes of weights.
+constexpr int QROWS = 4;
+template <int NT>
+__global__ void __launch_bounds__(256)
+k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, int rows, int cols,
+            const float* x, size_t x_stride, float* y, size_t y_stride, int ntok, int accum) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r0 = (blockIdx.x * 8 + warp) * QROWS;
+    if (r0 >= rows) return;
+    const int groups = cols / 16;
+    float acc[QROWS][NT];
+#pragma unroll
+    for (int r = 0; r < QROWS; r++)
+#pragma unroll
+        for (int t = 0; t < NT; t++) acc[r][t] = 0.f;
+    for (int g = lane; g < groups; g += 32) {
+        uint4 w[QROWS]; float d[QROWS];
+#pragma unroll
+        for (int r = 0; r < QROWS; r++) {
+            const int row = min(r0 + r, rows - 1);
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[r].x), "=r"(w[r].y), "=r"(w[r].z), "=r"(w[r].w)
+                         : "l"(wq + (size_t)row * cols + 16 * g));
+            d[r] = __half2float(wd[(size_t)row * (cols / 32) + (g >> 1)]);
+        }
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            if (t < ntok) {
+                const float4* xp = reinterpret_cast<const float4*>(x + t * x_stride + 16 * g);
+                const float4 x0 = xp[0], x1 = xp[1], x2 = xp[2], x3 = xp[3];
+                const float xv[16] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w, x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w };
+#pragma unroll
+                for (int r = 0; r < QROWS; r++) {
+                    const uint32_t ww[4] = { w[r].x, w[r].y, w[r].z, w[r].w };
+                    float s = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 16; k++) s = fmaf((float)(int8_t)(ww[k >> 2] >> (8 * (k & 3))), xv[k], s);
+                    acc[r][t] = fmaf(s, d[r], acc[r][t]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < QROWS; r++)
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            float s = acc[r][t];
+#pragma unroll
+            for (unsigned m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+            if (lane == 0 && t < ntok && r0 + r < rows) { float* dst = y + t * y_stride + r0 + r; *dst = accum ? *dst + s : s; }
+        }
+}
+
+}  // namespace
+
+IT_API int it_argmax(it_ctx* c, size_t logits_off, size_t n, size_t dst_off) {
+    IT_CHECK_ARG(c, "it_argmax: null context");
+    IT_CHECK_ARG(n > 0 && n < 0xffffffffull, "it_argmax: bad length %zu", n);
+    IT_CHECK_ARG(logits_off % 4 == 0, "it_argmax: logits offset must be 4-float aligned");
+    IT_CHECK_ARG(logits_off <= c->arena_floats && n <= c->arena_floats - logits_off && dst_off < c->arena_floats, "it_argmax: range outside the arena");
+    IT_CHECK_ARG(dst_off < logits_off || dst_off >= logits_off + n, "it_argmax: the result slot overlaps the logits");
+    unsigned blocks = (unsigned)((n + 4095) / 4096);
+    const unsigned cap = (unsigned)(c->sm_count * 2 < IT_ARGMAX_MAX_BLOCKS ? c->sm_count * 2 : IT_ARGMAX_MAX_BLOCKS);
+    if (blocks > cap) blocks = cap;
+    unsigned per_block = (unsigned)((n + blocks - 1) / blocks); per_block = (per_block + 3) & ~3u;
+    blocks = (unsigned)((n + per_block - 1) / per_block);
+    k_argmax<<<blocks, 256, 0, c->stream>>>(c->arena + logits_off, (unsigned)n, per_block, c->argmax_partials, c->argmax_counter, c->arena + dst_off);
+    IT_LAUNCH_CHECK("argmax");
+    return IT_OK;
+}
+
+IT_API int it_matvec_q8(it_ctx* c, const it_qmat* w, size_t ntok, size_t x_off, size_t x_stride, size_t y_off, size_t y_stride, int accum) {
+    IT_CHECK_ARG(c && w, "it_matvec_q8: null argument");
+    IT_CHECK_ARG(w->ctx == c, "it_matvec_q8: matrix belongs to another context");
+    IT_CHECK_ARG(ntok > 0 && ntok <= 65535, "it_matvec_q8: bad row count %zu", ntok);
+    IT_CHECK_ARG(x_off % 4 == 0 && (ntok == 1 || x_stride % 4 == 0), "it_matvec_q8: activation offsets must be 4-float aligned");
+    IT_CHECK_ARG(x_off <= c->arena_floats && (ntok - 1) * x_stride + w->cols <= c->arena_floats - x_off, "it_matvec_q8: input rows fall outside the arena");
+    IT_CHECK_ARG(ntok == 1 || y_stride >= w->rows, "it_matvec_q8: output stride shorter than a row of results");
+    IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->rows <= c->arena_floats - y_off, "it_matvec_q8: output rows fall outside the arena");
+    const unsigned grid = (unsigned)((w->rows + 8 * QROWS - 1) / (8 * QROWS));
+    for (size_t t0 = 0; t0 < ntok; t0 += 4) {
+        const int nt = (int)((ntok - t0) < 4 ? (ntok - t0) : 4);
+        const float* x = c->arena + x_off + t0 * x_stride; float* y = c->arena + y_off + t0 * y_stride;
+        if (nt == 1) k_matvec_q8<1><<<grid, 256, 0, c->stream>>>(w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
+        else if (nt == 2) k_matvec_q8<2><<<grid, 256, 0, c->stream>>>(w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
+        else k_matvec_q8<4><<<grid, 256, 0, c->stream>>>(w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
+        IT_LAUNCH_CHECK("matvec_q8");
+    }
+    return IT_OK;
+}

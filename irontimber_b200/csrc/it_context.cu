@@ -1,0 +1,335 @@
+// Context, arena, weight upload / repack and q8 activation buffers of libirontimber_cuda.so.
+#include "it_internal.h"
+#include <cstring>
+#include <vector>
+
+static thread_local char g_err[512] = "";
+
+int it_fail(int code, const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt); vsnprintf(g_err, sizeof g_err, fmt, ap); va_end(ap);
+    return code;
+}
+IT_API const char* it_last_error(void) { return g_err; }
+IT_API int it_version(void) { return 1; }
+
+// ---------------------------------------------------------------- synthetic data rule
+// hash(seed, i) is the i-th output of splitmix64 seeded with `seed` (the reference's RNG family,
+// src/sampling.rs:43).  Codes: one hash per two elements, 32 bits each, code = v % 3 (or v % 4).
+// Scales: u = top 24 bits of hash(seed ^ 0x5ca1e5, block) / 2^24, d = f16(0.01 + 0.04*u) with
+// separately rounded multiply and add.
+__host__ __device__ static inline uint64_t it_mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull; z = (z ^ (z >> 27)) * 0x94d049bb133111ebull; return z ^ (z >> 31);
+}
+__host__ __device__ static inline uint64_t it_hash(uint64_t seed, uint64_t i) { return it_mix64(seed + 0x9e3779b97f4a7c15ull * (i + 1)); }
+
+__global__ void k_synth_pq2(uint64_t seed, size_t rows, size_t cols, int four, uint8_t* raw) {
+    size_t bpr = cols / 128, nblk = rows * bpr;
+    for (size_t blk = blockIdx.x * (size_t)blockDim.x + threadIdx.x; blk < nblk; blk += (size_t)gridDim.x * blockDim.x) {
+        uint8_t* o = raw + blk * 34;
+        float u = (float)(it_hash(seed ^ 0x5ca1e5ull, blk) >> 40) * (1.0f / 16777216.0f);
+        __half d = __float2half_rn(__fadd_rn(0.01f, __fmul_rn(0.04f, u)));
+        unsigned short db = __half_as_ushort(d);
+        o[0] = (uint8_t)(db & 0xff); o[1] = (uint8_t)(db >> 8);
+        size_t e0 = blk * 128;   // global element index of the block's first element (row-major)
+        for (int q = 0; q < 32; q++) {
+            uint64_t h0 = it_hash(seed, (e0 + 4 * q) / 2), h1 = it_hash(seed, (e0 + 4 * q) / 2 + 1);
+            uint32_t v[4] = { (uint32_t)h0, (uint32_t)(h0 >> 32), (uint32_t)h1, (uint32_t)(h1 >> 32) };
+            uint8_t byte = 0;
+            for (int c = 0; c < 4; c++) byte |= (uint8_t)((four ? (v[c] & 3u) : (v[c] % 3u)) << (2 * c));
+            o[2 + q] = byte;
+        }
+    }
+}
+int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, uint8_t* raw_dev) {
+    k_synth_pq2<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, rows, cols, four_codes, raw_dev);
+    IT_LAUNCH_CHECK("synth_pq2"); return IT_OK;
+}
+
+// Q8_0 synthetic rule: q = (hash(seed, e/2) 32-bit half) % 255 - 127, d = f16(0.002 + 0.004*u) per 32-block.
+__global__ void k_synth_q8_0(uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d) {
+    size_t n = rows * cols;
+    for (size_t p = blockIdx.x * (size_t)blockDim.x + threadIdx.x; p < n / 2; p += (size_t)gridDim.x * blockDim.x) {
+        uint64_t h = it_hash(seed, p);
+        q[2 * p] = (int8_t)((int)((uint32_t)h % 255u) - 127);
+        q[2 * p + 1] = (int8_t)((int)((uint32_t)(h >> 32) % 255u) - 127);
+        if (p % 16 == 0) {
+            float u = (float)(it_hash(seed ^ 0x5ca1e5ull, p / 16) >> 40) * (1.0f / 16777216.0f);
+            d[p / 16] = __float2half_rn(__fadd_rn(0.002f, __fmul_rn(0.004f, u)));
+        }
+    }
+}
+int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d) {
+    k_synth_q8_0<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, rows, cols, q, d);
+    IT_LAUNCH_CHECK("synth_q8_0"); return IT_OK;
+}
+
+// ---------------------------------------------------------------- PQ2_0 <-> tile layout
+// One thread per 32-bit code word of the tile layout (see it_internal.h).
+__global__ void k_repack_pq2(const uint8_t* __restrict__ raw, size_t rows, size_t cols, uint8_t* __restrict__ tiles) {
+    size_t nb = cols / 128, rgs = (rows + 31) / 32;
+    size_t nwords = rgs * nb * 256;   // 8 words per lane, 32 lanes
+    for (size_t w = blockIdx.x * (size_t)blockDim.x + threadIdx.x; w < nwords; w += (size_t)gridDim.x * blockDim.x) {
+        size_t tile = w / 256; int r = (int)(w % 256);
+        int half = r / 128, lane = (r % 128) / 4, slot = r % 4;     // byte offset = 512*half + 16*lane + 4*slot
+        int j = half * 2 + slot / 2, h = slot % 2, g = lane >> 2, t = lane & 3;
+        size_t rg = tile / nb, b = tile % nb;
+        uint32_t word = 0;
+        for (int i = 0; i < 4; i++) {
+            size_t row = rg * 32 + g + 8 * i;
+            if (row >= rows) { word |= 0x01010101u << (2 * i); continue; }   // padding rows decode to 0
+            const uint8_t* qs = raw + (row * nb + b) * 34 + 2;
+            int k0 = 32 * t + 8 * j + 4 * h;                                   // k0 % 4 == 0: one source byte
+            uint32_t src = qs[k0 / 4];
+            for (int c = 0; c < 4; c++) word |= ((src >> (2 * c)) & 3u) << (8 * c + 2 * i);
+        }
+        *(uint32_t*)(tiles + tile * IT_TILE_BYTES + 512 * half + 16 * lane + 4 * slot) = word;
+        if (r < 32) {   // 32 threads of the tile also copy the 32 scales
+            int gg = r >> 2, ii = r & 3; size_t row = rg * 32 + gg + 8 * ii;
+            unsigned short sb = 0;
+            if (row < rows) { const uint8_t* blk = raw + (row * nb + b) * 34; sb = (unsigned short)(blk[0] | (blk[1] << 8)); }
+            *(unsigned short*)(tiles + tile * IT_TILE_BYTES + 1024 + 8 * gg + 2 * ii) = sb;
+        }
+    }
+}
+int it_launch_repack_pq2(it_ctx* ctx, const uint8_t* raw_dev, size_t rows, size_t cols, uint8_t* tiles) {
+    k_repack_pq2<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(raw_dev, rows, cols, tiles);
+    IT_LAUNCH_CHECK("repack_pq2"); return IT_OK;
+}
+
+// One thread per raw PQ2_0 block: gathers its 128 codes back out of the tile layout.
+__global__ void k_unpack_pq2(const uint8_t* __restrict__ tiles, size_t rows, size_t cols, uint8_t* __restrict__ raw) {
+    size_t nb = cols / 128, nblk = rows * nb;
+    for (size_t blk = blockIdx.x * (size_t)blockDim.x + threadIdx.x; blk < nblk; blk += (size_t)gridDim.x * blockDim.x) {
+        size_t row = blk / nb, b = blk % nb, rg = row / 32; int rr = (int)(row % 32), g = rr % 8, i = rr / 8;
+        const uint8_t* tile = tiles + (rg * nb + b) * IT_TILE_BYTES;
+        uint8_t* o = raw + blk * 34;
+        unsigned short sb = *(const unsigned short*)(tile + 1024 + 8 * g + 2 * i);
+        o[0] = (uint8_t)(sb & 0xff); o[1] = (uint8_t)(sb >> 8);
+        for (int q = 0; q < 32; q++) {          // source byte q holds columns 4q..4q+3
+            int k0 = 4 * q, t = k0 / 32, j = (k0 % 32) / 8, h = (k0 % 8) / 4, lane = 4 * g + t;
+            uint32_t word = *(const uint32_t*)(tile + 512 * (j / 2) + 16 * lane + 4 * ((j % 2) * 2 + h));
+            uint8_t byte = 0;
+            for (int c = 0; c < 4; c++) byte |= (uint8_t)(((word >> (8 * c + 2 * i)) & 3u) << (2 * c));
+            o[2 + q] = byte;
+        }
+    }
+}
+int it_launch_unpack_pq2(it_ctx* ctx, const uint8_t* tiles, size_t rows, size_t cols, uint8_t* raw_dev) {
+    k_unpack_pq2<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(tiles, rows, cols, raw_dev);
+    IT_LAUNCH_CHECK("unpack_pq2"); return IT_OK;
+}
+
+// ---------------------------------------------------------------- context
+IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
+    IT_CHECK_ARG(out != nullptr, "it_ctx_create: out is null");
+    *out = nullptr;
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0) return it_fail(IT_ECUDA, "no CUDA device is visible: %s", cudaGetErrorString(e));
+    IT_CHECK_ARG(device >= 0 && device < ndev, "it_ctx_create: device %d out of range (%d visible)", device, ndev);
+    IT_CHECK_ARG(arena_floats > 0 && arena_floats % 64 == 0, "it_ctx_create: arena size must be a positive multiple of 64 floats");
+    IT_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop; IT_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return it_fail(IT_ESTATE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    it_ctx* c = new it_ctx(); c->device = device; c->arena = nullptr; c->arena_floats = arena_floats; c->sm_count = prop.multiProcessorCount;
+    c->argmax_partials = nullptr; c->argmax_counter = nullptr; c->stream = nullptr;
+    cudaError_t e1 = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_floats * sizeof(float)) : e1;
+    cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc(&c->argmax_partials, IT_ARGMAX_MAX_BLOCKS * sizeof(unsigned long long)) : e2;
+    cudaError_t e4 = e3 == cudaSuccess ? cudaMalloc(&c->argmax_counter, 256) : e3;
+    if (e4 != cudaSuccess) { it_ctx_destroy(c); return it_fail(e4 == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_ctx_create: %s", cudaGetErrorString(e4)); }
+    cudaMemsetAsync(c->arena, 0, arena_floats * sizeof(float), c->stream);
+    cudaMemsetAsync(c->argmax_counter, 0, 256, c->stream);
+    IT_CUDA(cudaStreamSynchronize(c->stream));
+    *out = c; return IT_OK;
+}
+IT_API void it_ctx_destroy(it_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    for (auto& kv : c->signs) cudaFree(kv.second);
+    if (c->argmax_counter) cudaFree(c->argmax_counter);
+    if (c->argmax_partials) cudaFree(c->argmax_partials);
+    if (c->arena) cudaFree(c->arena);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+IT_API int it_sync(it_ctx* c) { IT_CHECK_ARG(c, "it_sync: null context"); IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK; }
+IT_API void* it_ctx_stream(it_ctx* c) { return c ? (void*)c->stream : nullptr; }
+IT_API float* it_arena_ptr(it_ctx* c) { return c ? c->arena : nullptr; }
+IT_API size_t it_arena_floats(it_ctx* c) { return c ? c->arena_floats : 0; }
+
+static int arena_range(it_ctx* c, size_t off, size_t n, const char* who) {
+    IT_CHECK_ARG(c, "%s: null context", who);
+    IT_CHECK_ARG(off <= c->arena_floats && n <= c->arena_floats - off, "%s: range [%zu, +%zu) outside the arena (%zu floats)", who, off, n, c->arena_floats);
+    return IT_OK;
+}
+IT_API int it_arena_write(it_ctx* c, size_t off, const void* host, size_t n) {
+    int r = arena_range(c, off, n, "it_arena_write"); if (r) return r;
+    IT_CHECK_ARG(host || n == 0, "it_arena_write: null host pointer");
+    if (n == 0) return IT_OK;
+    IT_CUDA(cudaMemcpyAsync(c->arena + off, host, n * 4, cudaMemcpyHostToDevice, c->stream));
+    IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
+}
+IT_API int it_arena_read(it_ctx* c, size_t off, void* host, size_t n) {
+    int r = arena_range(c, off, n, "it_arena_read"); if (r) return r;
+    IT_CHECK_ARG(host || n == 0, "it_arena_read: null host pointer");
+    if (n == 0) return IT_OK;
+    IT_CUDA(cudaMemcpyAsync(host, c->arena + off, n * 4, cudaMemcpyDeviceToHost, c->stream));
+    IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
+}
+IT_API int it_arena_zero(it_ctx* c, size_t off, size_t n) {
+    int r = arena_range(c, off, n, "it_arena_zero"); if (r) return r;
+    if (n) IT_CUDA(cudaMemsetAsync(c->arena + off, 0, n * 4, c->stream));
+    return IT_OK;
+}
+IT_API int it_signs_set(it_ctx* c, size_t n, const float* signs) {
+    IT_CHECK_ARG(c && signs, "it_signs_set: null argument");
+    IT_CHECK_ARG(n > 0 && n % 1024 == 0, "it_signs_set: width %zu is not a multiple of the 1024 Hadamard block", n);
+    for (size_t i = 0; i < n; i++) IT_CHECK_ARG(signs[i] == 1.0f || signs[i] == -1.0f, "it_signs_set: sign %zu is %g, not +-1", i, (double)signs[i]);
+    IT_CUDA(cudaSetDevice(c->device));
+    float*& d = c->signs[n];
+    if (!d) IT_CUDA(cudaMalloc(&d, n * 4));
+    IT_CUDA(cudaMemcpyAsync(d, signs, n * 4, cudaMemcpyHostToDevice, c->stream));
+    IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
+}
+
+// ---------------------------------------------------------------- ternary matrices
+static int mat_alloc(it_ctx* c, size_t rows, size_t cols, it_mat** out, const char* who) {
+    IT_CHECK_ARG(c && out, "%s: null argument", who);
+    *out = nullptr;
+    IT_CHECK_ARG(rows > 0 && cols > 0, "%s: empty matrix %zux%zu", who, rows, cols);
+    IT_CHECK_ARG(cols % 128 == 0, "%s: cols %zu is not a multiple of the 128-element PQ2_0 block", who, cols);
+    IT_CHECK_ARG(rows <= (1u << 30) && cols <= (1u << 24), "%s: matrix %zux%zu too large", who, rows, cols);
+    IT_CUDA(cudaSetDevice(c->device));
+    it_mat* m = new it_mat(); m->ctx = c; m->rows = rows; m->cols = cols; m->row_groups = (rows + 31) / 32;
+    m->bytes = m->row_groups * (cols / 128) * IT_TILE_BYTES; m->tiles = nullptr;
+    cudaError_t e = cudaMalloc(&m->tiles, m->bytes);
+    if (e != cudaSuccess) { delete m; return it_fail(IT_ENOMEM, "%s: cudaMalloc(%zu): %s", who, m->bytes, cudaGetErrorString(e)); }
+    *out = m; return IT_OK;
+}
+static int mat_from_raw_host(it_ctx* c, const uint8_t* raw, size_t rows, size_t cols, it_mat** out, const char* who) {
+    int r = mat_alloc(c, rows, cols, out, who); if (r) return r;
+    size_t nbytes = rows * (cols / 128) * 34; uint8_t* tmp = nullptr;
+    cudaError_t e = cudaMalloc(&tmp, nbytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(tmp, raw, nbytes, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) { r = it_launch_repack_pq2(c, tmp, rows, cols, (*out)->tiles); if (r == IT_OK) e = cudaStreamSynchronize(c->stream); }
+    if (tmp) cudaFree(tmp);
+    if (e != cudaSuccess || r != IT_OK) { it_matrix_destroy(*out); *out = nullptr; return r ? r : it_fail(IT_ECUDA, "%s: %s", who, cudaGetErrorString(e)); }
+    return IT_OK;
+}
+IT_API int it_matrix_upload_pq2(it_ctx* c, const uint8_t* raw, size_t rows, size_t cols, it_mat** out) {
+    IT_CHECK_ARG(raw, "it_matrix_upload_pq2: null data");
+    return mat_from_raw_host(c, raw, rows, cols, out, "it_matrix_upload_pq2");
+}
+IT_API int it_matrix_upload_packed2(it_ctx* c, const uint32_t* words, const float* scales, size_t rows, size_t cols, it_mat** out) {
+    IT_CHECK_ARG(words && scales, "it_matrix_upload_packed2: null data");
+    IT_CHECK_ARG(rows > 0 && cols > 0 && cols % 128 == 0, "it_matrix_upload_packed2: bad shape %zux%zu", rows, cols);
+    size_t nblk = rows * (cols / 128);
+    std::vector<uint8_t> raw(nblk * 34);
+    for (size_t i = 0; i < nblk; i++) {
+        __half h = __float2half_rn(scales[i]);
+        IT_CHECK_ARG(__half2float(h) == scales[i], "it_matrix_upload_packed2: scale %zu (%g) is not an f16 value", i, (double)scales[i]);
+        unsigned short hb; memcpy(&hb, &h, 2);
+        raw[i * 34] = (uint8_t)(hb & 0xff); raw[i * 34 + 1] = (uint8_t)(hb >> 8);
+        memcpy(&raw[i * 34 + 2], words + i * 8, 32);   // Packed2 words are the PQ2_0 qs bytes read as little-endian u32
+    }
+    return mat_from_raw_host(c, raw.data(), rows, cols, out, "it_matrix_upload_packed2");
+}
+IT_API int it_matrix_synth(it_ctx* c, uint64_t seed, size_t rows, size_t cols, int four_codes, it_mat** out) {
+    int r = mat_alloc(c, rows, cols, out, "it_matrix_synth"); if (r) return r;
+    size_t nbytes = rows * (cols / 128) * 34; uint8_t* tmp = nullptr;
+    cudaError_t e = cudaMalloc(&tmp, nbytes);
+    if (e == cudaSuccess) { r = it_launch_synth_pq2(c, seed, rows, cols, four_codes, tmp); if (r == IT_OK) r = it_launch_repack_pq2(c, tmp, rows, cols, (*out)->tiles);
+        if (r == IT_OK) e = cudaStreamSynchronize(c->stream); }
+    if (tmp) cudaFree(tmp);
+    if (e != cudaSuccess || r != IT_OK) { it_matrix_destroy(*out); *out = nullptr; return r ? r : it_fail(e == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_matrix_synth: %s", cudaGetErrorString(e)); }
+    return IT_OK;
+}
+IT_API int it_matrix_download_pq2(it_ctx* c, const it_mat* m, uint8_t* raw) {
+    IT_CHECK_ARG(c && m && raw, "it_matrix_download_pq2: null argument");
+    IT_CUDA(cudaSetDevice(c->device));
+    size_t nbytes = m->rows * (m->cols / 128) * 34; uint8_t* tmp = nullptr;
+    IT_CUDA(cudaMalloc(&tmp, nbytes));
+    int r = it_launch_unpack_pq2(c, m->tiles, m->rows, m->cols, tmp);
+    cudaError_t e = r == IT_OK ? cudaMemcpyAsync(raw, tmp, nbytes, cudaMemcpyDeviceToHost, c->stream) : cudaSuccess;
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    cudaFree(tmp);
+    if (r) return r;
+    if (e != cudaSuccess) return it_fail(IT_ECUDA, "it_matrix_download_pq2: %s", cudaGetErrorString(e));
+    return IT_OK;
+}
+IT_API size_t it_matrix_rows(const it_mat* m) { return m ? m->rows : 0; }
+IT_API size_t it_matrix_cols(const it_mat* m) { return m ? m->cols : 0; }
+IT_API size_t it_matrix_device_bytes(const it_mat* m) { return m ? m->bytes : 0; }
+IT_API void it_matrix_destroy(it_mat* m) { if (!m) return; cudaSetDevice(m->ctx->device); if (m->tiles) cudaFree(m->tiles); delete m; }
+
+// ---------------------------------------------------------------- int8-group matrices
+static int qmat_alloc(it_ctx* c, size_t rows, size_t cols, it_qmat** out, const char* who) {
+    IT_CHECK_ARG(c && out, "%s: null argument", who);
+    *out = nullptr;
+    IT_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "%s: bad shape %zux%zu (cols must be a multiple of 32)", who, rows, cols);
+    IT_CUDA(cudaSetDevice(c->device));
+    it_qmat* m = new it_qmat(); m->ctx = c; m->rows = rows; m->cols = cols; m->q = nullptr; m->d = nullptr;
+    m->bytes = rows * cols + rows * (cols / 32) * 2;
+    cudaError_t e = cudaMalloc(&m->q, rows * cols);
+    if (e == cudaSuccess) e = cudaMalloc(&m->d, rows * (cols / 32) * 2);
+    if (e != cudaSuccess) { it_qmatrix_destroy(m); return it_fail(IT_ENOMEM, "%s: cudaMalloc: %s", who, cudaGetErrorString(e)); }
+    *out = m; return IT_OK;
+}
+IT_API int it_qmatrix_upload_q8_0(it_ctx* c, const uint8_t* raw, size_t rows, size_t cols, it_qmat** out) {
+    IT_CHECK_ARG(raw, "it_qmatrix_upload_q8_0: null data");
+    int r = qmat_alloc(c, rows, cols, out, "it_qmatrix_upload_q8_0"); if (r) return r;
+    size_t nblk = rows * cols / 32;
+    std::vector<int8_t> q(rows * cols); std::vector<unsigned short> d(nblk);
+    for (size_t i = 0; i < nblk; i++) { const uint8_t* b = raw + i * 34; d[i] = (unsigned short)(b[0] | (b[1] << 8)); memcpy(&q[i * 32], b + 2, 32); }
+    cudaError_t e = cudaMemcpyAsync((*out)->q, q.data(), q.size(), cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync((*out)->d, d.data(), d.size() * 2, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { it_qmatrix_destroy(*out); *out = nullptr; return it_fail(IT_ECUDA, "it_qmatrix_upload_q8_0: %s", cudaGetErrorString(e)); }
+    return IT_OK;
+}
+IT_API int it_qmatrix_synth(it_ctx* c, uint64_t seed, size_t rows, size_t cols, it_qmat** out) {
+    int r = qmat_alloc(c, rows, cols, out, "it_qmatrix_synth"); if (r) return r;
+    r = it_launch_synth_q8_0(c, seed, rows, cols, (*out)->q, (*out)->d);
+    cudaError_t e = r == IT_OK ? cudaStreamSynchronize(c->stream) : cudaSuccess;
+    if (r || e != cudaSuccess) { it_qmatrix_destroy(*out); *out = nullptr; return r ? r : it_fail(IT_ECUDA, "it_qmatrix_synth: %s", cudaGetErrorString(e)); }
+    return IT_OK;
+}
+IT_API int it_qmatrix_download_q8_0(it_ctx* c, const it_qmat* m, uint8_t* raw) {
+    IT_CHECK_ARG(c && m && raw, "it_qmatrix_download_q8_0: null argument");
+    size_t nblk = m->rows * m->cols / 32;
+    std::vector<int8_t> q(m->rows * m->cols); std::vector<unsigned short> d(nblk);
+    IT_CUDA(cudaMemcpyAsync(q.data(), m->q, q.size(), cudaMemcpyDeviceToHost, c->stream));
+    IT_CUDA(cudaMemcpyAsync(d.data(), m->d, d.size() * 2, cudaMemcpyDeviceToHost, c->stream));
+    IT_CUDA(cudaStreamSynchronize(c->stream));
+    for (size_t i = 0; i < nblk; i++) { uint8_t* b = raw + i * 34; b[0] = (uint8_t)(d[i] & 0xff); b[1] = (uint8_t)(d[i] >> 8); memcpy(b + 2, &q[i * 32], 32); }
+    return IT_OK;
+}
+IT_API size_t it_qmatrix_rows(const it_qmat* m) { return m ? m->rows : 0; }
+IT_API size_t it_qmatrix_cols(const it_qmat* m) { return m ? m->cols : 0; }
+IT_API void it_qmatrix_destroy(it_qmat* m) { if (!m) return; cudaSetDevice(m->ctx->device); if (m->q) cudaFree(m->q); if (m->d) cudaFree(m->d); delete m; }
+
+// ---------------------------------------------------------------- q8 activation rows
+IT_API int it_q8_create(it_ctx* c, size_t max_n, size_t max_tok, it_q8** out) {
+    IT_CHECK_ARG(c && out, "it_q8_create: null argument");
+    *out = nullptr;
+    IT_CHECK_ARG(max_n > 0 && max_n % 256 == 0, "it_q8_create: width %zu is not a multiple of the 256-element q8k block", max_n);
+    IT_CHECK_ARG(max_tok > 0 && max_tok <= 65535, "it_q8_create: bad row count %zu", max_tok);
+    IT_CUDA(cudaSetDevice(c->device));
+    it_q8* q = new it_q8(); q->ctx = c; q->max_n = max_n; q->max_tok = max_tok; q->n = 0; q->qs = nullptr; q->d = nullptr; q->sum128 = nullptr;
+    cudaError_t e = cudaMalloc(&q->qs, max_n * max_tok);
+    if (e == cudaSuccess) e = cudaMalloc(&q->d, max_n / 256 * max_tok * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&q->sum128, max_n / 128 * max_tok * 4);
+    if (e != cudaSuccess) { it_q8_destroy(q); return it_fail(IT_ENOMEM, "it_q8_create: %s", cudaGetErrorString(e)); }
+    *out = q; return IT_OK;
+}
+IT_API void it_q8_destroy(it_q8* q) { if (!q) return; cudaSetDevice(q->ctx->device); if (q->qs) cudaFree(q->qs); if (q->d) cudaFree(q->d); if (q->sum128) cudaFree(q->sum128); delete q; }
+IT_API int it_q8_read(it_ctx* c, const it_q8* q, size_t tok, int8_t* qs, float* d, int32_t* sum128) {
+    IT_CHECK_ARG(c && q, "it_q8_read: null argument");
+    IT_CHECK_ARG(q->n > 0 && tok < q->max_tok, "it_q8_read: nothing written yet or row %zu out of range", tok);
+    if (qs) IT_CUDA(cudaMemcpyAsync(qs, q->qs + tok * q->max_n, q->n, cudaMemcpyDeviceToHost, c->stream));
+    if (d) IT_CUDA(cudaMemcpyAsync(d, q->d + tok * (q->max_n / 256), q->n / 256 * 4, cudaMemcpyDeviceToHost, c->stream));
+    if (sum128) IT_CUDA(cudaMemcpyAsync(sum128, q->sum128 + tok * (q->max_n / 128), q->n / 128 * 4, cudaMemcpyDeviceToHost, c->stream));
+    IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
+}

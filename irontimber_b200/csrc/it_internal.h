@@ -1,0 +1,83 @@
+// Internal declarations shared by the translation units of libirontimber_cuda.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include <map>
+#include <string>
+#include "../../include/irontimber_cuda.h"
+
+#define IT_API extern "C" __attribute__((visibility("default")))
+
+// ---- error plumbing -------------------------------------------------------------------------
+int it_fail(int code, const char* fmt, ...);
+#define IT_CHECK_ARG(cond, ...) do { if (!(cond)) return it_fail(IT_EINVAL, __VA_ARGS__); } while (0)
+#define IT_CUDA(expr) do { cudaError_t e__ = (expr); if (e__ != cudaSuccess) \
+    return it_fail(e__ == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "%s: %s", #expr, cudaGetErrorString(e__)); } while (0)
+#define IT_LAUNCH_CHECK(name) do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) \
+    return it_fail(IT_ECUDA, "launch %s: %s", name, cudaGetErrorString(e__)); } while (0)
+
+// ---- device layout of a ternary matrix ----------------------------------------------------------
+// Rows are grouped by 32 and columns by 128 (one PQ2_0 block).  Tile (rg, b) covers rows
+// 32*rg .. 32*rg+31 and columns 128*b .. 128*b+127 and is IT_TILE_BYTES long; tiles of one row
+// group are contiguous in ascending b, so a warp streams a row group front to back.
+//
+// Inside a tile, with lane = 4*g + t (g = 0..7, t = 0..3) as in the mma.m16n8k32 fragments:
+//   bytes [ 16*lane      , +16): words (j=0,h=0) (0,1) (1,0) (1,1)
+//   bytes [ 512 + 16*lane, +16): words (j=2,h=0) (2,1) (3,0) (3,1)
+//   word (j,h), byte c, bit pair i holds the 2-bit code of row 32*rg + g + 8*i, column
+//   128*b + 32*t + 8*j + 4*h + c.  Masking a word with 0x03030303 << 2*i therefore yields the
+//   four int8 operands (scaled by 4^i) of matrix row g + 8*i for one mma A register.
+//   bytes [1024 + 8*g, +8): f16 scales of rows g, g+8, g+16, g+24 (block b).
+// 32 bytes of codes + 2 bytes of scale per 128 weights: the density of PQ2_0 itself.
+#define IT_TILE_ROWS 32
+#define IT_TILE_BYTES 1088
+
+struct it_mat {
+    it_ctx* ctx;
+    size_t rows, cols;      // logical shape
+    size_t row_groups;      // ceil(rows / 32)
+    uint8_t* tiles;         // [row_groups][cols/128][IT_TILE_BYTES]
+    size_t bytes;
+};
+
+// Int8-group matrix: row-major int8 q[rows][cols] and f16 d[rows][cols/32] (Q8_0 density).
+struct it_qmat {
+    it_ctx* ctx;
+    size_t rows, cols;
+    int8_t* q;
+    __half* d;
+    size_t bytes;
+};
+
+struct it_q8 {
+    it_ctx* ctx;
+    size_t max_n, max_tok;
+    size_t n;               // width of the rows currently held
+    int8_t* qs;             // [max_tok][max_n]  (row stride = n of the last write)
+    float* d;               // [max_tok][max_n/256]
+    int32_t* sum128;        // [max_tok][max_n/128]
+};
+
+struct it_ctx {
+    int device;
+    cudaStream_t stream;
+    float* arena;
+    size_t arena_floats;
+    std::map<size_t, float*> signs;   // width -> device sign vector
+    // argmax scratch: per-block partial (value, index) pairs + a completion counter
+    unsigned long long* argmax_partials;
+    unsigned int* argmax_counter;
+    int sm_count;
+};
+
+#define IT_ARGMAX_MAX_BLOCKS 1024
+
+// ---- launchers implemented in the kernel translation units ------------------------------------------
+int it_launch_repack_pq2(it_ctx* ctx, const uint8_t* raw_dev, size_t rows, size_t cols, uint8_t* tiles);
+int it_launch_repack_packed2(it_ctx* ctx, const uint32_t* words_dev, const float* scales_dev, size_t rows, size_t cols, uint8_t* tiles);
+int it_launch_unpack_pq2(it_ctx* ctx, const uint8_t* tiles, size_t rows, size_t cols, uint8_t* raw_dev);
+int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, uint8_t* raw_dev);
+int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d);

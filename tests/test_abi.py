@@ -1,0 +1,43 @@
+"""CPU-only checks of the drop-in boundary: the library loads, exports every symbol the header
+declares, and rejects bad calls before touching a device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from irontimber_b200 import build, _lib
+    build.build()
+    return _lib.load()
+
+
+def header_symbols():
+    src = open(os.path.join(ROOT, "include", "irontimber_cuda.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(it_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    from irontimber_b200 import _lib
+    names = header_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes table and header disagree"
+
+
+def test_calls_fail_cleanly_without_a_device_or_with_bad_arguments(lib):
+    h = C.c_void_p()
+    assert lib.it_ctx_create(0, 1000, C.byref(h)) != 0          # not a multiple of 64, or no device: never a crash
+    assert lib.it_last_error()
+    assert lib.it_ctx_create(0, 1024, None) == -1
+    assert lib.it_sync(None) == -1
+    assert lib.it_argmax(None, 0, 1, 2) == -1
+    assert lib.it_matvec_t2(None, None, 1, None, 0, 0, 0) == -1
+    assert lib.it_arena_write(None, 0, None, 0) == -1
+    lib.it_ctx_destroy(None); lib.it_matrix_destroy(None); lib.it_qmatrix_destroy(None); lib.it_q8_destroy(None)
