@@ -37,6 +37,7 @@ typedef struct it_ctx it_ctx;
 typedef struct it_mat it_mat;   /* ternary (2-bit code) matrix, device resident      */
 typedef struct it_qmat it_qmat; /* int8-group matrix (ggml Q8_0 source)             */
 typedef struct it_q8 it_q8;     /* q8k-quantised activation rows, device resident    */
+typedef struct it_graph it_graph; /* a recorded sequence of op launches                */
 
 const char* it_last_error(void);
 int it_version(void);
@@ -52,6 +53,15 @@ size_t it_arena_floats(it_ctx* ctx);
 int it_arena_write(it_ctx* ctx, size_t off, const void* host, size_t n_floats); /* Ctx::upload,   src/vk/mod.rs:427 */
 int it_arena_read(it_ctx* ctx, size_t off, void* host, size_t n_floats);        /* Ctx::download */
 int it_arena_zero(it_ctx* ctx, size_t off, size_t n_floats);                    /* zero_state,    src/vk/mod.rs:645 */
+
+/* Record the ops issued between begin and end into a CUDA graph and replay them with one launch.
+ * Stands where the reference records one command buffer per chunk and submits it once
+ * (Ctx::begin / submit_wait, src/vk/mod.rs:363-394).  Calls that wait (it_sync, arena read/write,
+ * uploads) are not allowed while recording. */
+int it_capture_begin(it_ctx* ctx);
+int it_capture_end(it_ctx* ctx, it_graph** out);
+int it_graph_launch(it_ctx* ctx, it_graph* g);
+void it_graph_destroy(it_graph* g);
 
 /* Hadamard sign vector for activations of width n (prism.hadamard.sign_values; src/model.rs:48-60,
  * uploaded into the params buffer by the reference, src/vk/mod.rs:536).  Values must be +1 or -1. */

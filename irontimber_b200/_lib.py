@@ -24,6 +24,10 @@ SIGNATURES = {
     "it_arena_write": (C.c_int, [P, c_size, P, c_size]),
     "it_arena_read": (C.c_int, [P, c_size, P, c_size]),
     "it_arena_zero": (C.c_int, [P, c_size, c_size]),
+    "it_capture_begin": (C.c_int, [P]),
+    "it_capture_end": (C.c_int, [P, C.POINTER(P)]),
+    "it_graph_launch": (C.c_int, [P, P]),
+    "it_graph_destroy": (None, [P]),
     "it_signs_set": (C.c_int, [P, c_size, P]),
     "it_matrix_upload_pq2": (C.c_int, [P, P, c_size, c_size, C.POINTER(P)]),
     "it_matrix_upload_packed2": (C.c_int, [P, P, P, c_size, c_size, C.POINTER(P)]),

@@ -121,6 +121,21 @@ class CudaBackend:
     def arena_ptr(self):
         return self.L.it_arena_ptr(self.ctx)
 
+    # ---- graphs (one recorded command sequence, replayed with one launch) -------------------------
+    def capture_begin(self):
+        _lib.check(self.L.it_capture_begin(self.ctx))
+
+    def capture_end(self):
+        h = C.c_void_p()
+        _lib.check(self.L.it_capture_end(self.ctx, C.byref(h)))
+        return h
+
+    def graph_launch(self, g):
+        _lib.check(self.L.it_graph_launch(self.ctx, g))
+
+    def graph_destroy(self, g):
+        self.L.it_graph_destroy(g)
+
     # ---- weights -------------------------------------------------------------------------------
     def mat(self, raw_pq2, rows, cols):
         raw = np.ascontiguousarray(raw_pq2, np.uint8)

@@ -25,18 +25,20 @@ __host__ __device__ static inline uint64_t it_hash(uint64_t seed, uint64_t i) { 
 __global__ void k_synth_pq2(uint64_t seed, size_t rows, size_t cols, int four, uint8_t* raw) {
     size_t bpr = cols / 128, nblk = rows * bpr;
     for (size_t blk = blockIdx.x * (size_t)blockDim.x + threadIdx.x; blk < nblk; blk += (size_t)gridDim.x * blockDim.x) {
-        uint8_t* o = raw + blk * 34;
-        float u = (float)(it_hash(seed ^ 0x5ca1e5ull, blk) >> 40) * (1.0f / 16777216.0f);
-        __half d = __float2half_rn(__fadd_rn(0.01f, __fmul_rn(0.04f, u)));
-        unsigned short db = __half_as_ushort(d);
-        o[0] = (uint8_t)(db & 0xff); o[1] = (uint8_t)(db >> 8);
+        unsigned short* o = reinterpret_cast<unsigned short*>(raw + blk * 34);   // 34-byte blocks are 2-byte aligned
+        const uint64_t hs = it_hash(seed ^ 0x5ca1e5ull, blk);
+        const float u = __fmul_rn((float)(uint32_t)(hs >> 40), 1.0f / 16777216.0f);
+        o[0] = __half_as_ushort(__float2half_rn(__fadd_rn(0.01f, __fmul_rn(0.04f, u))));
         size_t e0 = blk * 128;   // global element index of the block's first element (row-major)
-        for (int q = 0; q < 32; q++) {
-            uint64_t h0 = it_hash(seed, (e0 + 4 * q) / 2), h1 = it_hash(seed, (e0 + 4 * q) / 2 + 1);
-            uint32_t v[4] = { (uint32_t)h0, (uint32_t)(h0 >> 32), (uint32_t)h1, (uint32_t)(h1 >> 32) };
-            uint8_t byte = 0;
-            for (int c = 0; c < 4; c++) byte |= (uint8_t)((four ? (v[c] & 3u) : (v[c] % 3u)) << (2 * c));
-            o[2 + q] = byte;
+        for (int q = 0; q < 16; q++) {   // 8 elements = 2 code bytes per step
+            uint32_t packed = 0;
+            for (int p = 0; p < 4; p++) {
+                const uint64_t h = it_hash(seed, (e0 + 8 * q) / 2 + p);
+                const uint32_t lo = (uint32_t)h, hi = (uint32_t)(h >> 32);
+                packed |= (four ? (lo & 3u) : (lo % 3u)) << (4 * p);
+                packed |= (four ? (hi & 3u) : (hi % 3u)) << (4 * p + 2);
+            }
+            o[1 + q] = (unsigned short)packed;
         }
     }
 }
@@ -132,7 +134,7 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     cudaDeviceProp prop; IT_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10) return it_fail(IT_ESTATE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
     it_ctx* c = new it_ctx(); c->device = device; c->arena = nullptr; c->arena_floats = arena_floats; c->sm_count = prop.multiProcessorCount;
-    c->argmax_partials = nullptr; c->argmax_counter = nullptr; c->stream = nullptr;
+    c->argmax_partials = nullptr; c->argmax_counter = nullptr; c->stream = nullptr; c->capturing = false;
     cudaError_t e1 = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_floats * sizeof(float)) : e1;
     cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc(&c->argmax_partials, IT_ARGMAX_MAX_BLOCKS * sizeof(unsigned long long)) : e2;
@@ -154,7 +156,35 @@ IT_API void it_ctx_destroy(it_ctx* c) {
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
-IT_API int it_sync(it_ctx* c) { IT_CHECK_ARG(c, "it_sync: null context"); IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK; }
+IT_API int it_sync(it_ctx* c) {
+    IT_CHECK_ARG(c, "it_sync: null context");
+    if (c->capturing) return it_fail(IT_ESTATE, "it_sync: not allowed while recording a graph");
+    IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
+}
+IT_API int it_capture_begin(it_ctx* c) {
+    IT_CHECK_ARG(c, "it_capture_begin: null context");
+    if (c->capturing) return it_fail(IT_ESTATE, "it_capture_begin: already recording");
+    IT_CUDA(cudaSetDevice(c->device));
+    IT_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    c->capturing = true; return IT_OK;
+}
+IT_API int it_capture_end(it_ctx* c, it_graph** out) {
+    IT_CHECK_ARG(c && out, "it_capture_end: null argument");
+    *out = nullptr;
+    if (!c->capturing) return it_fail(IT_ESTATE, "it_capture_end: not recording");
+    c->capturing = false;
+    cudaGraph_t g = nullptr;
+    IT_CUDA(cudaStreamEndCapture(c->stream, &g));
+    cudaGraphExec_t ex = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(g); return it_fail(IT_ECUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+    it_graph* r = new it_graph(); r->ctx = c; r->graph = g; r->exec = ex; *out = r; return IT_OK;
+}
+IT_API int it_graph_launch(it_ctx* c, it_graph* g) {
+    IT_CHECK_ARG(c && g && g->ctx == c, "it_graph_launch: null argument or foreign graph");
+    IT_CUDA(cudaGraphLaunch(g->exec, c->stream)); return IT_OK;
+}
+IT_API void it_graph_destroy(it_graph* g) { if (!g) return; cudaSetDevice(g->ctx->device); cudaGraphExecDestroy(g->exec); cudaGraphDestroy(g->graph); delete g; }
 IT_API void* it_ctx_stream(it_ctx* c) { return c ? (void*)c->stream : nullptr; }
 IT_API float* it_arena_ptr(it_ctx* c) { return c ? c->arena : nullptr; }
 IT_API size_t it_arena_floats(it_ctx* c) { return c ? c->arena_floats : 0; }
@@ -166,6 +196,7 @@ static int arena_range(it_ctx* c, size_t off, size_t n, const char* who) {
 }
 IT_API int it_arena_write(it_ctx* c, size_t off, const void* host, size_t n) {
     int r = arena_range(c, off, n, "it_arena_write"); if (r) return r;
+    if (c->capturing) return it_fail(IT_ESTATE, "it_arena_write: not allowed while recording a graph");
     IT_CHECK_ARG(host || n == 0, "it_arena_write: null host pointer");
     if (n == 0) return IT_OK;
     IT_CUDA(cudaMemcpyAsync(c->arena + off, host, n * 4, cudaMemcpyHostToDevice, c->stream));
@@ -173,6 +204,7 @@ IT_API int it_arena_write(it_ctx* c, size_t off, const void* host, size_t n) {
 }
 IT_API int it_arena_read(it_ctx* c, size_t off, void* host, size_t n) {
     int r = arena_range(c, off, n, "it_arena_read"); if (r) return r;
+    if (c->capturing) return it_fail(IT_ESTATE, "it_arena_read: not allowed while recording a graph");
     IT_CHECK_ARG(host || n == 0, "it_arena_read: null host pointer");
     if (n == 0) return IT_OK;
     IT_CUDA(cudaMemcpyAsync(host, c->arena + off, n * 4, cudaMemcpyDeviceToHost, c->stream));

@@ -61,6 +61,8 @@ struct it_q8 {
     int32_t* sum128;        // [max_tok][max_n/128]
 };
 
+struct it_graph { it_ctx* ctx; cudaGraph_t graph; cudaGraphExec_t exec; };
+
 struct it_ctx {
     int device;
     cudaStream_t stream;
@@ -71,6 +73,7 @@ struct it_ctx {
     unsigned long long* argmax_partials;
     unsigned int* argmax_counter;
     int sm_count;
+    bool capturing;
 };
 
 #define IT_ARGMAX_MAX_BLOCKS 1024

@@ -6,7 +6,9 @@
 // rounded separately to f32.
 //
 // Mapping.  One CTA per 32-row group; its warps split the 128-column blocks of the row group into
-// contiguous ranges and stream the tile layout of it_internal.h front to back with 128-bit loads.
+// contiguous ranges and stream the tile layout of it_internal.h front to back with 128-bit loads,
+// several tiles in flight per warp; each warp stages its slice of the q8 activation rows into shared
+// memory with cp.async while the weight loads are in flight.
 // Per tile a warp issues eight mma.sync.m16n8k32 (u8 x s8 -> s32): the A operand is produced from
 // the packed 2-bit words by one AND per register (codes scaled by 1, 4, 16, 64 for the four rows a
 // word holds; the accumulators are shifted back, which is exact), the B operand is the q8 row of
@@ -21,14 +23,12 @@
 
 namespace {
 
-constexpr int WARPS = 8;          // warps per CTA
-constexpr int PIPE = 4;           // tiles in flight per warp
 constexpr int TERM_PAD = 4;       // floats of padding between token planes in shared memory
+constexpr int XROW_PAD = 16;      // bytes of padding between staged activation rows
 
 struct Stage {
     uint4 wa, wb;                 // 32 bytes of packed codes
     uint2 sc;                     // four f16 scales (rows g, g+8, g+16, g+24)
-    uint4 xa, xb;                 // 32 bytes of q8 activations of token g, columns 32t .. 32t+31 of the block
     float dx0, dx1;               // q8k scale of tokens 2t, 2t+1 for this block
     int s0, s1;                   // sum128 of tokens 2t, 2t+1 for this block
 };
@@ -43,24 +43,33 @@ __device__ __forceinline__ uint2 ldg_stream2(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
 }
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, bool SUMI>
-__global__ void __launch_bounds__(WARPS * 32, 2)
+// MT: activation rows per launch (columns of the mma B operand in use); WARPS: warps per CTA, which
+// split the blocks of the row group; PIPE: tiles each warp keeps in flight; MINB: CTAs per SM the
+// register budget is set for.
+template <int MT, int WARPS, int PIPE, int MINB, bool SUMI>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows,
             const int8_t* __restrict__ xq, const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
             float* y, size_t y_stride, int accum, int32_t* __restrict__ sumi_out) {
-    extern __shared__ float terms[];                 // [MT][nb*32 + TERM_PAD]
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     const int plane = nb * 32 + TERM_PAD;
+    const int xrow = nb * 128 + XROW_PAD;
+    float* terms = reinterpret_cast<float*>(smem_raw);                                   // [MT][plane]
+    int8_t* xs = reinterpret_cast<int8_t*>(smem_raw) + (SUMI ? 0 : (size_t)MT * plane * 4);   // [MT][xrow]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int rg = blockIdx.x;
     const int b0 = (warp * nb) / WARPS, b1 = ((warp + 1) * nb) / WARPS, nblk = b1 - b0;
     const uint8_t* tp = tiles + ((size_t)rg * nb) * IT_TILE_BYTES;
     const bool x_lane = g < ntok && g < MT;          // this lane feeds column g of the B operand
-    const int8_t* xrow = xq + (size_t)g * x_stride + 32 * t;
     const int c0 = 2 * t, c1 = 2 * t + 1;            // token columns this lane receives from the mma
     const bool v0 = c0 < MT && c0 < ntok, v1 = c1 < MT && c1 < ntok;
     const int dstride = x_stride / 256, sstride = x_stride / 128;
@@ -71,15 +80,18 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows,
         s.wa = ldg_stream(tile + 16 * lane);
         s.wb = ldg_stream(tile + 512 + 16 * lane);
         s.sc = ldg_stream2(tile + 1024 + 8 * g);
-        if (x_lane) { s.xa = __ldg(reinterpret_cast<const uint4*>(xrow + 128 * b)); s.xb = __ldg(reinterpret_cast<const uint4*>(xrow + 128 * b + 16)); }
-        else { s.xa = make_uint4(0, 0, 0, 0); s.xb = make_uint4(0, 0, 0, 0); }
         s.dx0 = v0 ? __ldg(xd + c0 * dstride + (b >> 1)) : 0.f; s.s0 = v0 ? __ldg(xs128 + c0 * sstride + b) : 0;
         if (MT > 1) { s.dx1 = v1 ? __ldg(xd + c1 * dstride + (b >> 1)) : 0.f; s.s1 = v1 ? __ldg(xs128 + c1 * sstride + b) : 0; }
     };
     auto compute = [&](const Stage& s, int b) {
         int cx[4] = {0, 0, 0, 0}, cy[4] = {0, 0, 0, 0};
         const uint32_t w[8] = { s.wa.x, s.wa.y, s.wa.z, s.wa.w, s.wb.x, s.wb.y, s.wb.z, s.wb.w };
-        const uint32_t xb[8] = { s.xa.x, s.xa.y, s.xa.z, s.xa.w, s.xb.x, s.xb.y, s.xb.z, s.xb.w };
+        uint4 xa = make_uint4(0, 0, 0, 0), xb4 = make_uint4(0, 0, 0, 0);
+        if (x_lane) {
+            const uint4* xp = reinterpret_cast<const uint4*>(xs + g * xrow + 128 * b + 32 * t);
+            xa = xp[0]; xb4 = xp[1];
+        }
+        const uint32_t xb[8] = { xa.x, xa.y, xa.z, xa.w, xb4.x, xb4.y, xb4.z, xb4.w };
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint32_t lo = w[2 * j], hi = w[2 * j + 1];
@@ -109,8 +121,21 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows,
         }
     };
 
+    // weights first (they come from HBM), then this warp's slice of the activation rows into shared memory
 #pragma unroll
     for (int p = 0; p < PIPE; p++) if (p < nblk) load(st[p], b0 + p);
+    {
+        const int chunks = nblk * 8;                 // 16-byte pieces per activation row in this warp's range
+        for (int m = 0; m < MT; m++) {
+            if (m < ntok) {
+                const int8_t* src = xq + (size_t)m * x_stride + 128 * b0;
+                int8_t* dst = xs + m * xrow + 128 * b0;
+                for (int ch = lane; ch < chunks; ch += 32) cp_async16(dst + 16 * ch, src + 16 * ch);
+            }
+        }
+        cp_async_wait_all();
+        __syncwarp();
+    }
     for (int i = 0; i < nblk; i += PIPE) {
 #pragma unroll
         for (int p = 0; p < PIPE; p++) {
@@ -128,6 +153,7 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows,
         if (c < ntok && row < rows) {
             const float* tcol = terms + c * plane + r;
             float sum = 0.f;
+#pragma unroll 8
             for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
             float* dst = y + (size_t)c * y_stride + row;
             *dst = accum ? __fadd_rn(*dst, sum) : sum;
@@ -135,15 +161,15 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows,
     }
 }
 
-template <int MT, bool SUMI>
-int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
+template <int MT>
+size_t smem_bytes(int nb, bool sumi) { return (sumi ? 0 : (size_t)MT * (nb * 32 + TERM_PAD) * 4) + (size_t)MT * (nb * 128 + XROW_PAD); }
+
+template <int MT, int WARPS, int PIPE, int MINB, bool SUMI>
+int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
     const int nb = (int)(w->cols / 128);
-    const size_t smem = SUMI ? 0 : (size_t)MT * (nb * 32 + TERM_PAD) * sizeof(float);
-    auto kern = k_matvec_t2<MT, SUMI>;
-    if (smem > 48 * 1024) {
-        if (smem > 200 * 1024) return it_fail(IT_EINVAL, "it_matvec_t2: %d rows of width %zu need %zu bytes of shared memory", MT, w->cols, smem);
-        IT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
+    const size_t smem = smem_bytes<MT>(nb, SUMI);
+    auto kern = k_matvec_t2<MT, WARPS, PIPE, MINB, SUMI>;
+    if (smem > 48 * 1024) IT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<(unsigned)w->row_groups, WARPS * 32, smem, c->stream>>>(w->tiles, nb, (int)w->rows,
         x->qs + xrow0 * x->max_n, x->d + xrow0 * (x->max_n / 256), x->sum128 + xrow0 * (x->max_n / 128), (int)x->max_n, ntok,
         y, y_stride, accum, sumi);
@@ -151,11 +177,27 @@ int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, f
     return IT_OK;
 }
 
+// Shape policy: few blocks per row group -> small CTAs, several per SM, so that a whole matrix of the
+// model's wide-output shapes is resident in one wave; many blocks per row group (the long-K shapes have
+// few rows) -> 32 warps per CTA to keep enough bytes in flight.
+template <int MT, bool SUMI>
+int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
+    const int nb = (int)(w->cols / 128);
+    if (MT == 1 && nb <= 48) return launch_cfg<MT, 8, 3, 4, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi);
+    if (nb <= 48) return launch_cfg<MT, 16, 3, 2, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi);
+    return launch_cfg<MT, 32, 3, 1, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi);
+}
+
 template <bool SUMI>
 int dispatch(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, float* y, size_t y_stride, int accum, int32_t* sumi) {
-    // rows of activations are processed in groups of up to eight (one mma N tile)
-    for (size_t t0 = 0; t0 < ntok; t0 += 8) {
-        const int nt = (int)((ntok - t0) < 8 ? (ntok - t0) : 8);
+    // activation rows are processed in groups of up to eight (one mma N tile); wide matrices use smaller
+    // groups so that the staged rows and the per-block terms fit in shared memory
+    const int nb = (int)(w->cols / 128);
+    size_t group = 8;
+    while (group > 1 && (group == 8 ? smem_bytes<8>(nb, SUMI) : group == 4 ? smem_bytes<4>(nb, SUMI) : smem_bytes<2>(nb, SUMI)) > 160 * 1024) group /= 2;
+    if (smem_bytes<1>(nb, SUMI) > 200 * 1024) return it_fail(IT_EINVAL, "it_matvec_t2: %zu columns exceed the shared-memory budget", w->cols);
+    for (size_t t0 = 0; t0 < ntok; t0 += group) {
+        const int nt = (int)((ntok - t0) < group ? (ntok - t0) : group);
         float* yy = y ? y + t0 * y_stride : nullptr;
         int32_t* ss = sumi ? sumi + t0 * w->rows * (w->cols / 128) : nullptr;
         int r;
