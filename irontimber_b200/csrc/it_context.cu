@@ -135,10 +135,16 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     if (prop.major != 10) return it_fail(IT_ESTATE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
     it_ctx* c = new it_ctx(); c->device = device; c->arena = nullptr; c->arena_floats = arena_floats; c->sm_count = prop.multiProcessorCount;
     c->argmax_partials = nullptr; c->argmax_counter = nullptr; c->stream = nullptr; c->capturing = false;
+    c->splitk_terms = nullptr; c->splitk_counters = nullptr; c->error_flag_host = nullptr; c->error_flag_dev = nullptr;
     cudaError_t e1 = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_floats * sizeof(float)) : e1;
     cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc(&c->argmax_partials, IT_ARGMAX_MAX_BLOCKS * sizeof(unsigned long long)) : e2;
     cudaError_t e4 = e3 == cudaSuccess ? cudaMalloc(&c->argmax_counter, 256) : e3;
+    if (e4 == cudaSuccess) e4 = cudaMalloc(&c->splitk_terms, (size_t)c->sm_count * IT_SPLITK_SLOT_BYTES);
+    if (e4 == cudaSuccess) e4 = cudaMalloc(&c->splitk_counters, (size_t)c->sm_count * sizeof(unsigned));
+    if (e4 == cudaSuccess) e4 = cudaMemsetAsync(c->splitk_counters, 0, (size_t)c->sm_count * sizeof(unsigned), c->stream);
+    if (e4 == cudaSuccess) e4 = cudaHostAlloc(&c->error_flag_host, sizeof(int), cudaHostAllocMapped);
+    if (e4 == cudaSuccess) { *c->error_flag_host = 0; e4 = cudaHostGetDevicePointer(&c->error_flag_dev, c->error_flag_host, 0); }
     if (e4 != cudaSuccess) { it_ctx_destroy(c); return it_fail(e4 == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_ctx_create: %s", cudaGetErrorString(e4)); }
     cudaMemsetAsync(c->arena, 0, arena_floats * sizeof(float), c->stream);
     cudaMemsetAsync(c->argmax_counter, 0, 256, c->stream);
@@ -150,6 +156,9 @@ IT_API void it_ctx_destroy(it_ctx* c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     for (auto& kv : c->signs) cudaFree(kv.second);
+    if (c->splitk_terms) cudaFree(c->splitk_terms);
+    if (c->splitk_counters) cudaFree(c->splitk_counters);
+    if (c->error_flag_host) cudaFreeHost(c->error_flag_host);
     if (c->argmax_counter) cudaFree(c->argmax_counter);
     if (c->argmax_partials) cudaFree(c->argmax_partials);
     if (c->arena) cudaFree(c->arena);
@@ -159,7 +168,16 @@ IT_API void it_ctx_destroy(it_ctx* c) {
 IT_API int it_sync(it_ctx* c) {
     IT_CHECK_ARG(c, "it_sync: null context");
     if (c->capturing) return it_fail(IT_ESTATE, "it_sync: not allowed while recording a graph");
-    IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
+    IT_CUDA(cudaStreamSynchronize(c->stream));
+    return it_check_device_error(c, "it_sync");
+}
+// After a synchronisation: reports (and clears) the flag a kernel raises when a bounded wait ran out.
+int it_check_device_error(it_ctx* c, const char* who) {
+    if (c->error_flag_host && *(volatile int*)c->error_flag_host) {
+        *(volatile int*)c->error_flag_host = 0;
+        return it_fail(IT_ETIMEOUT, "%s: a kernel gave up on a bounded wait; its results are not valid", who);
+    }
+    return IT_OK;
 }
 IT_API int it_capture_begin(it_ctx* c) {
     IT_CHECK_ARG(c, "it_capture_begin: null context");
@@ -208,7 +226,8 @@ IT_API int it_arena_read(it_ctx* c, size_t off, void* host, size_t n) {
     IT_CHECK_ARG(host || n == 0, "it_arena_read: null host pointer");
     if (n == 0) return IT_OK;
     IT_CUDA(cudaMemcpyAsync(host, c->arena + off, n * 4, cudaMemcpyDeviceToHost, c->stream));
-    IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
+    IT_CUDA(cudaStreamSynchronize(c->stream));
+    return it_check_device_error(c, "it_arena_read");
 }
 IT_API int it_arena_zero(it_ctx* c, size_t off, size_t n) {
     int r = arena_range(c, off, n, "it_arena_zero"); if (r) return r;

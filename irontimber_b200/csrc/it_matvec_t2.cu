@@ -5,17 +5,25 @@
 // with S = sum_j code(r, 128b+j) * q(t, 128b+j) an exact integer, every product and the running sum
 // rounded separately to f32.
 //
-// Mapping.  One CTA per 32-row group; its warps split the 128-column blocks of the row group into
-// contiguous ranges and stream the tile layout of it_internal.h front to back with 128-bit loads,
-// several tiles in flight per warp; each warp stages its slice of the q8 activation rows into shared
-// memory with cp.async while the weight loads are in flight.
-// Per tile a warp issues eight mma.sync.m16n8k32 (u8 x s8 -> s32): the A operand is produced from
-// the packed 2-bit words by one AND per register (codes scaled by 1, 4, 16, 64 for the four rows a
-// word holds; the accumulators are shifted back, which is exact), the B operand is the q8 row of
-// token n in column n, so up to eight activation rows share every weight load.  The per-block terms
-// (d_w*d_x)*float(S - sum128) go to shared memory; after a CTA barrier one thread per (row, token)
-// adds them in ascending block order.  No float partial sums are ever combined out of order, and
-// K is split across warps only at the level of exact integers.
+// Mapping.  In the tile layout of it_internal.h a 32-row group is one contiguous run of bytes.  A
+// persistent grid of a few CTAs per SM shares out the row groups round robin (CTA i takes i, i+grid,
+// ...).  In each CTA a producer thread streams its row groups, chunk by chunk (eight 128-column tiles),
+// into a shared-memory ring with bulk asynchronous copies (cp.async.bulk, completion counted on an
+// mbarrier), as far ahead as the ring is deep and across row-group boundaries, so the HBM request
+// stream does not drain between row groups.  Consumer warps, in groups of eight, take one tile each
+// per chunk.  Per tile a warp issues eight mma.sync.m16n8k32 (u8 x s8 -> s32): the A operand comes
+// from the packed 2-bit words by one AND per register (codes scaled by 1, 4, 16, 64 for the four rows
+// a word holds; the accumulators are shifted back, which is exact), the B operand is the q8 row of
+// token n in column n, so up to eight activation rows share every weight load.  The q8 rows, their
+// scales and block sums are staged in shared memory once per CTA.
+//
+// The per-block terms (d_w*d_x)*float(S - sum128) go to a shared array; after a barrier per row group
+// one thread per (row, token) adds them in ascending block order while the other warps go on with the
+// next row group (second terms buffer).  Float partial sums are never combined out of order; K is
+// split across warps only at the level of exact integers, and never across CTAs.
+//
+// Every wait on an mbarrier is bounded; when one runs out the CTA raises a flag that the host reads
+// after the stream is synchronised (IT_ETIMEOUT), drains its copies and leaves.
 //
 // Algorithmic bytes per launch: rows*cols/128*34 (codes + f16 scales) + ntok*(cols + 4*cols/256)
 // + 4*ntok*rows (x2 when accumulating).  The kernel is HBM-bound.
@@ -23,179 +31,270 @@
 
 namespace {
 
-constexpr int TERM_PAD = 4;       // floats of padding between token planes in shared memory
-constexpr int XROW_PAD = 16;      // bytes of padding between staged activation rows
+constexpr int CWARPS = 8;                         // warps per consumer group = tiles per chunk
+constexpr int CHUNK_BYTES = CWARPS * IT_TILE_BYTES;
+constexpr int TERM_PAD = 4;                       // floats of padding between token planes
+constexpr int XROW_PAD = 16;                      // bytes of padding between staged activation rows
+constexpr long long WAIT_CLOCKS = 1ll << 31;      // about one second
+constexpr int SM_SMEM = 227 * 1024;               // shared memory one SM can give to CTAs
 
-struct Stage {
-    uint4 wa, wb;                 // 32 bytes of packed codes
-    uint2 sc;                     // four f16 scales (rows g, g+8, g+16, g+24)
-    float dx0, dx1;               // q8k scale of tokens 2t, 2t+1 for this block
-    int s0, s1;                   // sum128 of tokens 2t, 2t+1 for this block
-};
-
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_arrive(unsigned bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
 }
-__device__ __forceinline__ uint2 ldg_stream2(const void* p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
+// Bounded wait: gives up after WAIT_CLOCKS, or as soon as another thread of the CTA has given up.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag) {
+    if (mbar_test(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; i++) if (mbar_test(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CLOCKS) { *abort_flag = 1; atomicExch(error_flag, 1); return false; }
+    }
+}
+__device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(smem)), "l"(gmem));
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
+template <int NTHREADS> __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" :: "n"(NTHREADS) : "memory"); }
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// MT: activation rows per launch (columns of the mma B operand in use); WARPS: warps per CTA, which
-// split the blocks of the row group; PIPE: tiles each warp keeps in flight; MINB: CTAs per SM the
-// register budget is set for.
-template <int MT, int WARPS, int PIPE, int MINB, bool SUMI>
-__global__ void __launch_bounds__(WARPS * 32, MINB)
-k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows,
+struct Smem {   // byte offsets into dynamic shared memory
+    int ring, x, dx, s128, terms, bars, flag, total, plane, xrow;
+};
+__host__ __device__ inline Smem smem_layout(int MT, int nb, int slots, int nbuf) {
+    Smem L; int o = 0;
+    L.plane = nb * 32 + TERM_PAD; L.xrow = nb * 128 + XROW_PAD;
+    L.ring = o; o += slots * CHUNK_BYTES;
+    L.x = o; o += MT * L.xrow;
+    L.dx = o; o += MT * (nb / 2) * 4;
+    L.s128 = o; o += MT * nb * 4;
+    L.terms = o; o += nbuf * MT * L.plane * 4;
+    o = (o + 15) & ~15;
+    L.bars = o; o += 2 * slots * 8;
+    L.flag = o; o += 16;
+    L.total = o;
+    return L;
+}
+
+// MT: activation rows per launch (columns of the mma B operand in use).  NG: consumer groups of eight
+// warps; group j takes the chunks k of the CTA's stream with k % NG == j.  MINB: CTAs per SM the
+// register budget allows.  nbuf: terms buffers (0 for the integer-accumulator variant, 1 when every CTA
+// has a single row group, else 2).
+template <int MT, int NG, int MINB, bool SUMI>
+__global__ void __launch_bounds__((NG * CWARPS + 1) * 32, MINB)
+k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int slots, int nbuf,
             const int8_t* __restrict__ xq, const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
-            float* y, size_t y_stride, int accum, int32_t* __restrict__ sumi_out) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int plane = nb * 32 + TERM_PAD;
-    const int xrow = nb * 128 + XROW_PAD;
-    float* terms = reinterpret_cast<float*>(smem_raw);                                   // [MT][plane]
-    int8_t* xs = reinterpret_cast<int8_t*>(smem_raw) + (SUMI ? 0 : (size_t)MT * plane * 4);   // [MT][xrow]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int rg = blockIdx.x;
-    const int b0 = (warp * nb) / WARPS, b1 = ((warp + 1) * nb) / WARPS, nblk = b1 - b0;
-    const uint8_t* tp = tiles + ((size_t)rg * nb) * IT_TILE_BYTES;
-    const bool x_lane = g < ntok && g < MT;          // this lane feeds column g of the B operand
-    const int c0 = 2 * t, c1 = 2 * t + 1;            // token columns this lane receives from the mma
-    const bool v0 = c0 < MT && c0 < ntok, v1 = c1 < MT && c1 < ntok;
-    const int dstride = x_stride / 256, sstride = x_stride / 128;
+            float* y, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag) {
+    constexpr int NCONS = NG * CWARPS;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const Smem L = smem_layout(MT, nb, slots, nbuf);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.flag);
+    const unsigned bars = smem_u32(smem + L.bars);             // full[s] at bars + 8*s, empty[s] at bars + 8*(slots + s)
+    const int cpr = (nb + CWARPS - 1) / CWARPS;                 // chunks per row group
+    const int my_rgs = row_groups > (int)blockIdx.x ? (row_groups - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-    Stage st[PIPE];
-    auto load = [&](Stage& s, int b) {
-        const uint8_t* tile = tp + (size_t)b * IT_TILE_BYTES;
-        s.wa = ldg_stream(tile + 16 * lane);
-        s.wb = ldg_stream(tile + 512 + 16 * lane);
-        s.sc = ldg_stream2(tile + 1024 + 8 * g);
-        s.dx0 = v0 ? __ldg(xd + c0 * dstride + (b >> 1)) : 0.f; s.s0 = v0 ? __ldg(xs128 + c0 * sstride + b) : 0;
-        if (MT > 1) { s.dx1 = v1 ? __ldg(xd + c1 * dstride + (b >> 1)) : 0.f; s.s1 = v1 ? __ldg(xs128 + c1 * sstride + b) : 0; }
-    };
-    auto compute = [&](const Stage& s, int b) {
-        int cx[4] = {0, 0, 0, 0}, cy[4] = {0, 0, 0, 0};
-        const uint32_t w[8] = { s.wa.x, s.wa.y, s.wa.z, s.wa.w, s.wb.x, s.wb.y, s.wb.z, s.wb.w };
-        uint4 xa = make_uint4(0, 0, 0, 0), xb4 = make_uint4(0, 0, 0, 0);
-        if (x_lane) {
-            const uint4* xp = reinterpret_cast<const uint4*>(xs + g * xrow + 128 * b + 32 * t);
-            xa = xp[0]; xb4 = xp[1];
-        }
-        const uint32_t xb[8] = { xa.x, xa.y, xa.z, xa.w, xb4.x, xb4.y, xb4.z, xb4.w };
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint32_t lo = w[2 * j], hi = w[2 * j + 1];
-            mma_u8s8(cx, lo & 0x03030303u, lo & 0x0c0c0c0cu, hi & 0x03030303u, hi & 0x0c0c0c0cu, xb[2 * j], xb[2 * j + 1]);
-            mma_u8s8(cy, lo & 0x30303030u, lo & 0xc0c0c0c0u, hi & 0x30303030u, hi & 0xc0c0c0c0u, xb[2 * j], xb[2 * j + 1]);
-        }
-        // rows g, g+8, g+16, g+24 of the tile; accumulators carry the factors 1, 4, 16, 64
-        const int S0[4] = { cx[0], cx[2] >> 2, cy[0] >> 4, cy[2] >> 6 };   // token c0
-        const int S1[4] = { cx[1], cx[3] >> 2, cy[1] >> 4, cy[3] >> 6 };   // token c1
-        const __half2 h01 = *reinterpret_cast<const __half2*>(&s.sc.x), h23 = *reinterpret_cast<const __half2*>(&s.sc.y);
-        const float dw[4] = { __low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23) };
-        if (v0) {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int sumi = S0[i] - s.s0;
-                if (SUMI) { const int row = rg * 32 + g + 8 * i; if (row < rows) sumi_out[((size_t)c0 * rows + row) * nb + b] = sumi; }
-                else terms[c0 * plane + b * 32 + g + 8 * i] = __fmul_rn(__fmul_rn(dw[i], s.dx0), (float)sumi);
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < slots; s++) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (slots + s), CWARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == NCONS) {
+        // ---------------- producer: one thread keeps the ring full
+        if (lane == 0) {
+            int issued = 0, s = 0; unsigned ph = 0;
+            for (int i = 0; i < my_rgs && !*abort_flag; i++) {
+                const uint8_t* src = tiles + ((size_t)((int)blockIdx.x + i * (int)gridDim.x) * nb) * IT_TILE_BYTES;
+                for (int cq = 0; cq < cpr; cq++) {
+                    if (!mbar_wait(bars + 8 * (slots + s), ph ^ 1u, abort_flag, error_flag)) break;
+                    const int ntile = min(CWARPS, nb - cq * CWARPS);
+                    const unsigned bytes = (unsigned)ntile * IT_TILE_BYTES;
+                    mbar_expect_tx(bars + 8 * s, bytes);
+                    bulk_load(smem_u32(smem + L.ring + s * CHUNK_BYTES), src + (size_t)cq * CHUNK_BYTES, bytes, bars + 8 * s);
+                    issued++;
+                    if (++s == slots) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (*abort_flag) {
+                // leave only after every copy this thread started has landed (each wait bounded by the clock limit)
+                const int first = issued > slots ? issued - slots : 0;
+                for (int k = first; k < issued; k++) {
+                    const long long t0 = clock64();
+                    while (!mbar_test(bars + 8 * (k % slots), (unsigned)(k / slots) & 1u) && clock64() - t0 < WAIT_CLOCKS) { }
+                }
             }
         }
-        if (MT > 1 && v1) {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int sumi = S1[i] - s.s1;
-                if (SUMI) { const int row = rg * 32 + g + 8 * i; if (row < rows) sumi_out[((size_t)c1 * rows + row) * nb + b] = sumi; }
-                else terms[c1 * plane + b * 32 + g + 8 * i] = __fmul_rn(__fmul_rn(dw[i], s.dx1), (float)sumi);
-            }
-        }
-    };
+        return;
+    }
 
-    // weights first (they come from HBM), then this warp's slice of the activation rows into shared memory
-#pragma unroll
-    for (int p = 0; p < PIPE; p++) if (p < nblk) load(st[p], b0 + p);
-    {
-        const int chunks = nblk * 8;                 // 16-byte pieces per activation row in this warp's range
+    // ---------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    int8_t* xs = reinterpret_cast<int8_t*>(smem + L.x);
+    float* dxs = reinterpret_cast<float*>(smem + L.dx);
+    int* sss = reinterpret_cast<int*>(smem + L.s128);
+    float* terms = reinterpret_cast<float*>(smem + L.terms);
+    {   // stage the activation rows, their q8k scales and block sums once per CTA
+        const int pieces = nb * 8;
         for (int m = 0; m < MT; m++) {
             if (m < ntok) {
-                const int8_t* src = xq + (size_t)m * x_stride + 128 * b0;
-                int8_t* dst = xs + m * xrow + 128 * b0;
-                for (int ch = lane; ch < chunks; ch += 32) cp_async16(dst + 16 * ch, src + 16 * ch);
+                const int8_t* src = xq + (size_t)m * x_stride;
+                for (int ch = tid; ch < pieces; ch += NCONS * 32) cp_async16(xs + m * L.xrow + 16 * ch, src + 16 * ch);
+                for (int i = tid; i < nb / 2; i += NCONS * 32) dxs[m * (nb / 2) + i] = xd[m * (x_stride / 256) + i];
+                for (int i = tid; i < nb; i += NCONS * 32) sss[m * nb + i] = xs128[m * (x_stride / 128) + i];
             }
         }
         cp_async_wait_all();
-        __syncwarp();
+        consumer_barrier<NCONS * 32>();
     }
-    for (int i = 0; i < nblk; i += PIPE) {
+    const bool x_lane = g < ntok && g < MT;          // this lane feeds column g of the B operand
+    const int c0 = 2 * t, c1 = 2 * t + 1;            // token columns this lane receives from the mma
+    const bool v0 = c0 < MT && c0 < ntok, v1 = c1 < MT && c1 < ntok;
+    const int group = warp / CWARPS, wi = warp % CWARPS;   // consumer group and tile index inside a chunk
+
+    int s = 0; unsigned ph = 0; int kg = 0;           // ring slot, its phase, and (chunk index) % NG
+    for (int i = 0; i < my_rgs; i++) {
+        const int rg = (int)blockIdx.x + i * (int)gridDim.x;
+        float* tbuf = terms + (size_t)(nbuf > 1 ? (i & 1) : 0) * MT * L.plane;
+        for (int cq = 0; cq < cpr; cq++) {
+            const bool mine = NG == 1 || kg == group;
+            const int cs = s; const unsigned cph = ph;
+            if (++s == slots) { s = 0; ph ^= 1u; }
+            if (NG > 1 && ++kg == NG) kg = 0;
+            if (!mine) continue;
+            const bool ready = mbar_wait(bars + 8 * cs, cph, abort_flag, error_flag);
+            const int b = cq * CWARPS + wi;
+            if (ready && b < nb) {
+                const unsigned char* tile = smem + L.ring + cs * CHUNK_BYTES + wi * IT_TILE_BYTES;
+                const uint4 wa = *reinterpret_cast<const uint4*>(tile + 16 * lane);
+                const uint4 wb = *reinterpret_cast<const uint4*>(tile + 512 + 16 * lane);
+                const uint2 sc = *reinterpret_cast<const uint2*>(tile + 1024 + 8 * g);
+                uint4 xa = make_uint4(0, 0, 0, 0), xb4 = make_uint4(0, 0, 0, 0);
+                if (x_lane) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(xs + g * L.xrow + 128 * b + 32 * t);
+                    xa = xp[0]; xb4 = xp[1];
+                }
+                int cx[4] = {0, 0, 0, 0}, cy[4] = {0, 0, 0, 0};
+                const uint32_t w[8] = { wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w };
+                const uint32_t xb[8] = { xa.x, xa.y, xa.z, xa.w, xb4.x, xb4.y, xb4.z, xb4.w };
 #pragma unroll
-        for (int p = 0; p < PIPE; p++) {
-            if (i + p < nblk) {
-                compute(st[p], b0 + i + p);
-                if (i + p + PIPE < nblk) load(st[p], b0 + i + p + PIPE);
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t lo = w[2 * j], hi = w[2 * j + 1];
+                    mma_u8s8(cx, lo & 0x03030303u, lo & 0x0c0c0c0cu, hi & 0x03030303u, hi & 0x0c0c0c0cu, xb[2 * j], xb[2 * j + 1]);
+                    mma_u8s8(cy, lo & 0x30303030u, lo & 0xc0c0c0c0u, hi & 0x30303030u, hi & 0xc0c0c0c0u, xb[2 * j], xb[2 * j + 1]);
+                }
+                // rows g, g+8, g+16, g+24 of the tile; accumulators carry the factors 1, 4, 16, 64
+                const int S0[4] = { cx[0], cx[2] >> 2, cy[0] >> 4, cy[2] >> 6 };   // token c0
+                const int S1[4] = { cx[1], cx[3] >> 2, cy[1] >> 4, cy[3] >> 6 };   // token c1
+                const __half2 h01 = *reinterpret_cast<const __half2*>(&sc.x), h23 = *reinterpret_cast<const __half2*>(&sc.y);
+                const float dw[4] = { __low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23) };
+                if (v0) {
+                    const float dx = dxs[c0 * (nb / 2) + (b >> 1)]; const int s128 = sss[c0 * nb + b];
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const int sumi = S0[r] - s128;
+                        if (SUMI) { const int row = rg * 32 + g + 8 * r; if (row < rows) sumi_out[((size_t)c0 * rows + row) * nb + b] = sumi; }
+                        else tbuf[c0 * L.plane + b * 32 + g + 8 * r] = __fmul_rn(__fmul_rn(dw[r], dx), (float)sumi);
+                    }
+                }
+                if (MT > 1 && v1) {
+                    const float dx = dxs[c1 * (nb / 2) + (b >> 1)]; const int s128 = sss[c1 * nb + b];
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const int sumi = S1[r] - s128;
+                        if (SUMI) { const int row = rg * 32 + g + 8 * r; if (row < rows) sumi_out[((size_t)c1 * rows + row) * nb + b] = sumi; }
+                        else tbuf[c1 * L.plane + b * 32 + g + 8 * r] = __fmul_rn(__fmul_rn(dw[r], dx), (float)sumi);
+                    }
+                }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + 8 * (slots + cs));     // the slot may be refilled
         }
-    }
-    if (SUMI) return;
-    __syncthreads();
-    // ordered f32 accumulation: thread (row r, token c) walks the blocks front to back
-    for (int idx = tid; idx < 32 * MT; idx += WARPS * 32) {
-        const int c = idx >> 5, r = idx & 31, row = rg * 32 + r;
-        if (c < ntok && row < rows) {
-            const float* tcol = terms + c * plane + r;
-            float sum = 0.f;
+        if (SUMI) continue;
+        consumer_barrier<NCONS * 32>();                              // every term of this row group is in shared memory
+        // ordered f32 accumulation: warp c (token c), lane r (row r) walks the blocks front to back while the
+        // remaining warps go on with the next row group (whose terms go to the other buffer)
+        if (warp < MT && warp < ntok) {
+            const int row = rg * 32 + lane;
+            if (row < rows) {
+                const float* tcol = tbuf + warp * L.plane + lane;
+                float sum = 0.f;
 #pragma unroll 8
-            for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
-            float* dst = y + (size_t)c * y_stride + row;
-            *dst = accum ? __fadd_rn(*dst, sum) : sum;
+                for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
+                float* dst = y + (size_t)warp * y_stride + row;
+                *dst = accum ? __fadd_rn(*dst, sum) : sum;
+            }
         }
     }
 }
 
-template <int MT>
-size_t smem_bytes(int nb, bool sumi) { return (sumi ? 0 : (size_t)MT * (nb * 32 + TERM_PAD) * 4) + (size_t)MT * (nb * 128 + XROW_PAD); }
-
-template <int MT, int WARPS, int PIPE, int MINB, bool SUMI>
-int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
+template <int MT, int NG, int MINB, bool SUMI>
+int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi,
+               int slots, int nbuf, int grid) {
     const int nb = (int)(w->cols / 128);
-    const size_t smem = smem_bytes<MT>(nb, SUMI);
-    auto kern = k_matvec_t2<MT, WARPS, PIPE, MINB, SUMI>;
-    if (smem > 48 * 1024) IT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)w->row_groups, WARPS * 32, smem, c->stream>>>(w->tiles, nb, (int)w->rows,
+    const Smem L = smem_layout(MT, nb, slots, nbuf);
+    auto kern = k_matvec_t2<MT, NG, MINB, SUMI>;
+    static bool attr_set[16] = {};
+    if (!attr_set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM - 1024)); attr_set[c->device & 15] = true; }
+    kern<<<grid, (NG * CWARPS + 1) * 32, L.total, c->stream>>>(w->tiles, nb, (int)w->rows, (int)w->row_groups, slots, nbuf,
         x->qs + xrow0 * x->max_n, x->d + xrow0 * (x->max_n / 256), x->sum128 + xrow0 * (x->max_n / 128), (int)x->max_n, ntok,
-        y, y_stride, accum, sumi);
+        y, y_stride, accum, sumi, c->error_flag_dev);
     IT_LAUNCH_CHECK("matvec_t2");
     return IT_OK;
 }
 
-// Shape policy: few blocks per row group -> small CTAs, several per SM, so that a whole matrix of the
-// model's wide-output shapes is resident in one wave; many blocks per row group (the long-K shapes have
-// few rows) -> 32 warps per CTA to keep enough bytes in flight.
+// Largest ring (up to `want` chunks) that fits `per_cta` bytes of shared memory; 0 if not even `need` fit.
+int ring_slots(int MT, int nb, int nbuf, int per_cta, int want, int need) {
+    int slots = want;
+    while (slots >= need && smem_layout(MT, nb, slots, nbuf).total > per_cta) slots--;
+    return slots >= need ? slots : 0;
+}
+
+// Shape policy.  Short rows (K <= 8192): one consumer group, up to three CTAs per SM, each with a ring that
+// holds a whole row group, so a matrix of the model's wide-output shapes is in flight almost at once.  Long
+// rows: two consumer groups per CTA (a row group is long, the per-warp chain must stay short) and up to two
+// CTAs per SM.  CTAs per SM drop when the staged activation rows and the terms leave no room for the ring.
 template <int MT, bool SUMI>
 int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
-    const int nb = (int)(w->cols / 128);
-    if (MT == 1 && nb <= 48) return launch_cfg<MT, 8, 3, 4, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi);
-    if (nb <= 48) return launch_cfg<MT, 16, 3, 2, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi);
-    return launch_cfg<MT, 32, 3, 1, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi);
+    const int nb = (int)(w->cols / 128), cpr = (nb + CWARPS - 1) / CWARPS, rgs = (int)w->row_groups;
+    const bool long_rows = nb > 64;
+    for (int per_sm = long_rows ? 2 : 3; per_sm >= 1; per_sm--) {
+        const int grid = rgs < per_sm * c->sm_count ? rgs : per_sm * c->sm_count;
+        const int nbuf = SUMI ? 0 : (grid == rgs ? 1 : 2);
+        const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / per_sm - 1024, cpr + 2 < 16 ? (cpr + 2 > 4 ? cpr + 2 : 4) : 16, cpr < 4 ? cpr : 4);
+        if (!slots) continue;
+        if (!long_rows) {
+            if (SUMI || per_sm == 1) return launch_cfg<MT, 1, 1, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
+            if (per_sm == 2) return launch_cfg<MT, 1, 2, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+            return launch_cfg<MT, 1, 3, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        }
+        if (SUMI || per_sm == 1) return launch_cfg<MT, SUMI ? 1 : 2, 1, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
+        return launch_cfg<MT, 2, 2, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+    }
+    return it_fail(IT_EINVAL, "it_matvec_t2: %d rows of width %zu exceed the shared-memory budget", MT, w->cols);
 }
 
 template <bool SUMI>
 int dispatch(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, float* y, size_t y_stride, int accum, int32_t* sumi) {
     // activation rows are processed in groups of up to eight (one mma N tile); wide matrices use smaller
-    // groups so that the staged rows and the per-block terms fit in shared memory
+    // groups so that the staged rows, the per-block terms and a ring of at least four chunks fit one SM
     const int nb = (int)(w->cols / 128);
     size_t group = 8;
-    while (group > 1 && (group == 8 ? smem_bytes<8>(nb, SUMI) : group == 4 ? smem_bytes<4>(nb, SUMI) : smem_bytes<2>(nb, SUMI)) > 160 * 1024) group /= 2;
-    if (smem_bytes<1>(nb, SUMI) > 200 * 1024) return it_fail(IT_EINVAL, "it_matvec_t2: %zu columns exceed the shared-memory budget", w->cols);
+    while (group > 1 && smem_layout((int)group, nb, 4, SUMI ? 0 : 2).total > SM_SMEM - 1024) group /= 2;
     for (size_t t0 = 0; t0 < ntok; t0 += group) {
         const int nt = (int)((ntok - t0) < group ? (ntok - t0) : group);
         float* yy = y ? y + t0 * y_stride : nullptr;
