@@ -121,6 +121,7 @@ IT_API int it_argmax(it_ctx* c, size_t logits_off, size_t n, size_t dst_off) {
     IT_CHECK_ARG(logits_off % 4 == 0, "it_argmax: logits offset must be 4-float aligned");
     IT_CHECK_ARG(logits_off <= c->arena_floats && n <= c->arena_floats - logits_off && dst_off < c->arena_floats, "it_argmax: range outside the arena");
     IT_CHECK_ARG(dst_off < logits_off || dst_off >= logits_off + n, "it_argmax: the result slot overlaps the logits");
+    it_note_op(c);
     unsigned blocks = (unsigned)((n + 4095) / 4096);
     const unsigned cap = (unsigned)(c->sm_count * 2 < IT_ARGMAX_MAX_BLOCKS ? c->sm_count * 2 : IT_ARGMAX_MAX_BLOCKS);
     if (blocks > cap) blocks = cap;
@@ -139,6 +140,7 @@ IT_API int it_matvec_q8(it_ctx* c, const it_qmat* w, size_t ntok, size_t x_off, 
     IT_CHECK_ARG(x_off <= c->arena_floats && (ntok - 1) * x_stride + w->cols <= c->arena_floats - x_off, "it_matvec_q8: input rows fall outside the arena");
     IT_CHECK_ARG(ntok == 1 || y_stride >= w->rows, "it_matvec_q8: output stride shorter than a row of results");
     IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->rows <= c->arena_floats - y_off, "it_matvec_q8: output rows fall outside the arena");
+    it_note_op(c);
     const unsigned grid = (unsigned)((w->rows + 8 * QROWS - 1) / (8 * QROWS));
     for (size_t t0 = 0; t0 < ntok; t0 += 4) {
         const int nt = (int)((ntok - t0) < 4 ? (ntok - t0) : 4);

@@ -135,7 +135,7 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     if (prop.major != 10) return it_fail(IT_ESTATE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
     it_ctx* c = new it_ctx(); c->device = device; c->arena = nullptr; c->arena_floats = arena_floats; c->sm_count = prop.multiProcessorCount;
     c->argmax_partials = nullptr; c->argmax_counter = nullptr; c->stream = nullptr; c->capturing = false;
-    c->splitk_terms = nullptr; c->splitk_counters = nullptr; c->error_flag_host = nullptr; c->error_flag_dev = nullptr;
+    c->pdl_safe_q8 = nullptr; c->splitk_terms = nullptr; c->splitk_counters = nullptr; c->error_flag_host = nullptr; c->error_flag_dev = nullptr;
     cudaError_t e1 = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_floats * sizeof(float)) : e1;
     cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc(&c->argmax_partials, IT_ARGMAX_MAX_BLOCKS * sizeof(unsigned long long)) : e2;
@@ -183,6 +183,7 @@ IT_API int it_capture_begin(it_ctx* c) {
     IT_CHECK_ARG(c, "it_capture_begin: null context");
     if (c->capturing) return it_fail(IT_ESTATE, "it_capture_begin: already recording");
     IT_CUDA(cudaSetDevice(c->device));
+    it_note_op(c);
     IT_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     c->capturing = true; return IT_OK;
 }
@@ -190,7 +191,7 @@ IT_API int it_capture_end(it_ctx* c, it_graph** out) {
     IT_CHECK_ARG(c && out, "it_capture_end: null argument");
     *out = nullptr;
     if (!c->capturing) return it_fail(IT_ESTATE, "it_capture_end: not recording");
-    c->capturing = false;
+    c->capturing = false; it_note_op(c);
     cudaGraph_t g = nullptr;
     IT_CUDA(cudaStreamEndCapture(c->stream, &g));
     cudaGraphExec_t ex = nullptr;
@@ -200,6 +201,7 @@ IT_API int it_capture_end(it_ctx* c, it_graph** out) {
 }
 IT_API int it_graph_launch(it_ctx* c, it_graph* g) {
     IT_CHECK_ARG(c && g && g->ctx == c, "it_graph_launch: null argument or foreign graph");
+    it_note_op(c);
     IT_CUDA(cudaGraphLaunch(g->exec, c->stream)); return IT_OK;
 }
 IT_API void it_graph_destroy(it_graph* g) { if (!g) return; cudaSetDevice(g->ctx->device); cudaGraphExecDestroy(g->exec); cudaGraphDestroy(g->graph); delete g; }
@@ -217,6 +219,7 @@ IT_API int it_arena_write(it_ctx* c, size_t off, const void* host, size_t n) {
     if (c->capturing) return it_fail(IT_ESTATE, "it_arena_write: not allowed while recording a graph");
     IT_CHECK_ARG(host || n == 0, "it_arena_write: null host pointer");
     if (n == 0) return IT_OK;
+    it_note_op(c);
     IT_CUDA(cudaMemcpyAsync(c->arena + off, host, n * 4, cudaMemcpyHostToDevice, c->stream));
     IT_CUDA(cudaStreamSynchronize(c->stream)); return IT_OK;
 }
@@ -231,6 +234,7 @@ IT_API int it_arena_read(it_ctx* c, size_t off, void* host, size_t n) {
 }
 IT_API int it_arena_zero(it_ctx* c, size_t off, size_t n) {
     int r = arena_range(c, off, n, "it_arena_zero"); if (r) return r;
+    it_note_op(c);
     if (n) IT_CUDA(cudaMemsetAsync(c->arena + off, 0, n * 4, c->stream));
     return IT_OK;
 }

@@ -140,6 +140,7 @@ IT_API int it_hadamard_q8(it_ctx* c, size_t n, size_t ntok, size_t x_off, size_t
     const float* signs; int r = check_common(c, n, ntok, x_off, x_stride, use_signs, hd, nk, rep, &signs, "it_hadamard_q8"); if (r) return r;
     IT_CHECK_ARG(out && out->ctx == c, "it_hadamard_q8: q8 buffer is null or belongs to another context");
     IT_CHECK_ARG(n <= out->max_n && ntok <= out->max_tok, "it_hadamard_q8: %zu rows of %zu do not fit the q8 buffer (%zu x %zu)", ntok, n, out->max_tok, out->max_n);
+    it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
     k_hadamard<true><<<grid, 256, 0, c->stream>>>(c->arena, x_off, x_stride, nullptr, 0, 0, signs, rotate, 0,
         (unsigned)hd, (unsigned)nk, (unsigned)rep, out->qs, out->d, out->sum128, out->max_n);
@@ -155,6 +156,7 @@ IT_API int it_hadamard_f32(it_ctx* c, size_t n, size_t ntok, size_t in_off, size
     IT_CHECK_ARG(!(hd && in_off == out_off), "it_hadamard_f32: a permuted transform cannot run in place");
     IT_CHECK_ARG(out_off % 4 == 0 && (ntok == 1 || out_stride % 4 == 0), "it_hadamard_f32: output offsets must be 4-float aligned");
     IT_CHECK_ARG(out_off <= c->arena_floats && (ntok - 1) * out_stride + n <= c->arena_floats - out_off, "it_hadamard_f32: output rows fall outside the arena");
+    it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
     k_hadamard<false><<<grid, 256, 0, c->stream>>>(c->arena, in_off, in_stride, c->arena, out_off, out_stride, signs, 1, inverse,
         (unsigned)hd, (unsigned)nk, (unsigned)rep, nullptr, nullptr, nullptr, 0);

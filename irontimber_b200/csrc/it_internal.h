@@ -82,7 +82,12 @@ struct it_ctx {
     // costs nothing on the normal path
     int* error_flag_host;
     int* error_flag_dev;
+    // Programmatic-dependent-launch bookkeeping: the q8 buffer whose contents are known to be complete by the
+    // time the most recently enqueued kernel lets its dependents start (null after any op that is not a matvec).
+    const it_q8* pdl_safe_q8;
 };
+// Every entry point that enqueues device work other than the ternary matvec calls this.
+static inline void it_note_op(it_ctx* c) { c->pdl_safe_q8 = nullptr; }
 
 // bytes of split-K terms per slot: enough for 8 activation rows of width 17408 (8 * 136 blocks * 32 rows * 4)
 #define IT_SPLITK_SLOT_BYTES (8 * 136 * 32 * 4)

@@ -93,11 +93,13 @@ __host__ __device__ inline Smem smem_layout(int MT, int nb, int slots, int nbuf)
 // warps; group j takes the chunks k of the CTA's stream with k % NG == j.  MINB: CTAs per SM the
 // register budget allows.  nbuf: terms buffers (0 for the integer-accumulator variant, 1 when every CTA
 // has a single row group, else 2).
-template <int MT, int NG, int MINB, bool SUMI>
-__global__ void __launch_bounds__((NG * CWARPS + 1) * 32, MINB)
+// ONESHOT: the grid has one CTA per row group and the ring holds a whole row group: thread 0 issues every
+// copy at once, there is no producer warp and no slot is ever refilled.
+template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI>
+__global__ void __launch_bounds__((NG * CWARPS + (ONESHOT ? 0 : 1)) * 32, MINB)
 k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int slots, int nbuf,
             const int8_t* __restrict__ xq, const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
-            float* y, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag) {
+            float* y, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag, int wait_early) {
     constexpr int NCONS = NG * CWARPS;
     extern __shared__ __align__(128) unsigned char smem[];
     const Smem L = smem_layout(MT, nb, slots, nbuf);
@@ -111,10 +113,26 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
         *abort_flag = 0;
         for (int s = 0; s < slots; s++) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (slots + s), CWARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (ONESHOT) {
+            // the weights do not depend on the kernel before this one: request them all right away
+            const uint8_t* src = tiles + ((size_t)blockIdx.x * nb) * IT_TILE_BYTES;
+            for (int cq = 0; cq < cpr; cq++) {
+                const unsigned bytes = (unsigned)min(CWARPS, nb - cq * CWARPS) * IT_TILE_BYTES;
+                mbar_expect_tx(bars + 8 * cq, bytes);
+                bulk_load(smem_u32(smem + L.ring + cq * CHUNK_BYTES), src + (size_t)cq * CHUNK_BYTES, bytes, bars + 8 * cq);
+            }
+        }
     }
     __syncthreads();
+    // Programmatic dependent launch.  The weights never depend on an earlier kernel, so they are requested
+    // above without waiting.  When the kernel before this one produced our activation rows (wait_early) we
+    // wait for it here, and only then let the next kernel start: a kernel that follows us may read the same
+    // rows without waiting, so they must be complete by the time it is allowed to run.  Otherwise the rows
+    // are known to be complete already and the only wait is the one in front of the store of y.
+    if (wait_early) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (warp == NCONS) {
+    if (!ONESHOT && warp == NCONS) {
         // ---------------- producer: one thread keeps the ring full
         if (lane == 0) {
             int issued = 0, s = 0; unsigned ph = 0;
@@ -221,8 +239,10 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                     }
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bars + 8 * (slots + cs));     // the slot may be refilled
+            if (!ONESHOT) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + 8 * (slots + cs)); // the slot may be refilled
+            }
         }
         if (SUMI) continue;
         consumer_barrier<NCONS * 32>();                              // every term of this row group is in shared memory
@@ -236,24 +256,33 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
 #pragma unroll 8
                 for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
                 float* dst = y + (size_t)warp * y_stride + row;
+                if (!wait_early) asm volatile("griddepcontrol.wait;" ::: "memory");   // y may be read or written by the kernel before us
                 *dst = accum ? __fadd_rn(*dst, sum) : sum;
             }
         }
     }
 }
 
-template <int MT, int NG, int MINB, bool SUMI>
+template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI>
 int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi,
                int slots, int nbuf, int grid) {
     const int nb = (int)(w->cols / 128);
     const Smem L = smem_layout(MT, nb, slots, nbuf);
-    auto kern = k_matvec_t2<MT, NG, MINB, SUMI>;
+    auto kern = k_matvec_t2<MT, NG, MINB, ONESHOT, SUMI>;
     static bool attr_set[16] = {};
     if (!attr_set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM - 1024)); attr_set[c->device & 15] = true; }
-    kern<<<grid, (NG * CWARPS + 1) * 32, L.total, c->stream>>>(w->tiles, nb, (int)w->rows, (int)w->row_groups, slots, nbuf,
-        x->qs + xrow0 * x->max_n, x->d + xrow0 * (x->max_n / 256), x->sum128 + xrow0 * (x->max_n / 128), (int)x->max_n, ntok,
-        y, y_stride, accum, sumi, c->error_flag_dev);
-    IT_LAUNCH_CHECK("matvec_t2");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((NG * CWARPS + (ONESHOT ? 0 : 1)) * 32); cfg.dynamicSmemBytes = (size_t)L.total; cfg.stream = c->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    // the activation rows are safe to read without waiting only if the previous op was a matvec on the same rows
+    const int wait_early = (SUMI || c->pdl_safe_q8 != x) ? 1 : 0;
+    const int nb_ = nb, rows_ = (int)w->rows, rgs_ = (int)w->row_groups, xs_ = (int)x->max_n;
+    IT_CUDA(cudaLaunchKernelEx(&cfg, kern, (const uint8_t*)w->tiles, nb_, rows_, rgs_, slots, nbuf,
+        (const int8_t*)(x->qs + xrow0 * x->max_n), (const float*)(x->d + xrow0 * (x->max_n / 256)), (const int32_t*)(x->sum128 + xrow0 * (x->max_n / 128)), xs_, ntok,
+        y, y_stride, accum, sumi, c->error_flag_dev, wait_early));
+    c->pdl_safe_q8 = x;
     return IT_OK;
 }
 
@@ -264,26 +293,38 @@ int ring_slots(int MT, int nb, int nbuf, int per_cta, int want, int need) {
     return slots >= need ? slots : 0;
 }
 
-// Shape policy.  Short rows (K <= 8192): one consumer group, up to three CTAs per SM, each with a ring that
-// holds a whole row group, so a matrix of the model's wide-output shapes is in flight almost at once.  Long
-// rows: two consumer groups per CTA (a row group is long, the per-warp chain must stay short) and up to two
-// CTAs per SM.  CTAs per SM drop when the staged activation rows and the terms leave no room for the ring.
+// Shape policy.
+//  - Short rows (K <= 8192) whose row groups all fit on the GPU at once: one CTA of eight warps per row group,
+//    the ring holds the whole row group and is requested in one go (up to four CTAs per SM).
+//  - Otherwise a persistent grid with a producer warp: one consumer group and up to three CTAs per SM for short
+//    rows, three consumer groups and one CTA per SM for long rows (a row group is long, so the per-warp chain
+//    must stay short and the ring deep).
+// CTAs per SM drop when the staged activation rows and the terms leave no room for the ring.
 template <int MT, bool SUMI>
 int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
     const int nb = (int)(w->cols / 128), cpr = (nb + CWARPS - 1) / CWARPS, rgs = (int)w->row_groups;
     const bool long_rows = nb > 64;
-    for (int per_sm = long_rows ? 2 : 3; per_sm >= 1; per_sm--) {
+    if (!long_rows && !SUMI) {
+        const int total = smem_layout(MT, nb, cpr, 1).total;
+        for (int per_sm = 4; per_sm >= 1; per_sm--) {
+            if (total > SM_SMEM / per_sm - 1024) continue;
+            if (rgs > per_sm * c->sm_count) break;
+            if (per_sm == 4) return launch_cfg<MT, 1, 4, true, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, cpr, 1, rgs);
+            if (per_sm == 3) return launch_cfg<MT, 1, 3, true, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, cpr, 1, rgs);
+            return launch_cfg<MT, 1, 2, true, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, cpr, 1, rgs);
+        }
+    }
+    for (int per_sm = long_rows ? 1 : 3; per_sm >= 1; per_sm--) {
         const int grid = rgs < per_sm * c->sm_count ? rgs : per_sm * c->sm_count;
         const int nbuf = SUMI ? 0 : (grid == rgs ? 1 : 2);
-        const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / per_sm - 1024, cpr + 2 < 16 ? (cpr + 2 > 4 ? cpr + 2 : 4) : 16, cpr < 4 ? cpr : 4);
+        const int want = long_rows ? 16 : (cpr + 2 > 4 ? cpr + 2 : 4);
+        const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / per_sm - 1024, want, cpr < 4 ? cpr : 4);
         if (!slots) continue;
-        if (!long_rows) {
-            if (SUMI || per_sm == 1) return launch_cfg<MT, 1, 1, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
-            if (per_sm == 2) return launch_cfg<MT, 1, 2, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
-            return launch_cfg<MT, 1, 3, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
-        }
-        if (SUMI || per_sm == 1) return launch_cfg<MT, SUMI ? 1 : 2, 1, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
-        return launch_cfg<MT, 2, 2, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (SUMI) return launch_cfg<MT, 1, 1, false, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
+        if (long_rows) return launch_cfg<MT, 3, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (per_sm == 1) return launch_cfg<MT, 1, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (per_sm == 2) return launch_cfg<MT, 1, 2, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        return launch_cfg<MT, 1, 3, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
     }
     return it_fail(IT_EINVAL, "it_matvec_t2: %d rows of width %zu exceed the shared-memory budget", MT, w->cols);
 }
