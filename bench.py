@@ -25,6 +25,9 @@ if ROOT not in sys.path:
 ROWS, COLS = 17408, 5120
 N_WEIGHTS = 12
 METRIC = "matvec_t2_hbm_gbs"
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_t2 launch on this workload, from the ncu capture
+# summarised in profiles/matvec_t2_config1_K5120_N17408.md
+NCU_DRAM_BYTES_PER_LAUNCH = 23698944
 
 
 def algorithmic_bytes(rows, cols, ntok=1, accum=False):
@@ -222,7 +225,7 @@ def main():
            "e2e": {"value": abytes / e2e_s / 1e9 * world, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4 * N_WEIGHTS, "d2h_bytes_per_step": ROWS * 4 * N_WEIGHTS,
                    "us_per_call": e2e_s * 1e6},
            "roofline": {"bound": "hbm", "kernel": "k_matvec_t2<1>", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                        "peak_kind": peak_kind, "algorithmic_bytes_per_launch": abytes, "us_per_launch": per_launch_s * 1e6, "traffic": None}}
+                        "peak_kind": peak_kind, "algorithmic_bytes_per_launch": abytes, "us_per_launch": per_launch_s * 1e6, "traffic": NCU_DRAM_BYTES_PER_LAUNCH}}
     if rank == 0:
         cb, _ = cpu_arm(10 ** 9, 1, False)
         out["cpu_baseline"] = cb
