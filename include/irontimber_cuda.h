@@ -130,6 +130,22 @@ int it_matvec_q8(it_ctx* ctx, const it_qmat* w, size_t ntok, size_t x_off, size_
  * in arena element dst_off (shaders/argmax.comp, src/sampling.rs:50; dispatch at src/vk/mod.rs:866,875). */
 int it_argmax(it_ctx* ctx, size_t logits_off, size_t n, size_t dst_off);
 
+/* Greedy pick for callers that must not allocate device memory.  No counterpart in the reference: it exists
+ * for hosts that hand all of HBM to their own pool at start-up (weights, KV cache, activation arena) and for
+ * code paths where the implicit device-wide synchronisation of cudaMalloc / cudaFree is not acceptable, e.g. a
+ * sampling step called from inside a serving loop.  Such callers cannot create an it_ctx (which owns an arena
+ * and scratch), so this entry point takes raw device pointers and a stream instead and keeps its scratch
+ * (8.4 KB: per-CTA partial results and an arrival counter) in a fixed array inside the library image.
+ *  - logits_dev: n f32 values, 16-byte aligned; index_dev: one u32 (the first index of the maximum, same rule
+ *    as it_argmax); stream: a cudaStream_t of the current device (may be NULL for the default stream).
+ *  - n may not exceed 16,777,216 (2^24); larger inputs are refused with IT_EINVAL.
+ *  - The call runs on the device that is current in the calling thread.  The first call on each device looks
+ *    up the scratch array's device address; make that first call outside any stream capture.
+ *  - It calls neither cudaMalloc nor cudaFree nor any allocating library routine.
+ *  - All calls on one device share the one scratch array: two calls whose kernels overlap on the GPU (different
+ *    streams, no dependency) race on it and give wrong results.  Calls on one stream are safe back to back. */
+int it_argmax_static(void* stream, const float* logits_dev, size_t n, uint32_t* index_dev);
+
 #ifdef __cplusplus
 }
 #endif

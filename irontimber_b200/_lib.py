@@ -52,6 +52,7 @@ SIGNATURES = {
     "it_matvec_t2_sumi": (C.c_int, [P, P, c_size, P, P]),
     "it_matvec_q8": (C.c_int, [P, P, c_size, c_size, c_size, c_size, c_size, C.c_int]),
     "it_argmax": (C.c_int, [P, c_size, c_size, c_size]),
+    "it_argmax_static": (C.c_int, [P, P, c_size, P]),
 }
 
 _lib = None

@@ -152,3 +152,46 @@ IT_API int it_matvec_q8(it_ctx* c, const it_qmat* w, size_t ntok, size_t x_off, 
     }
     return IT_OK;
 }
+
+// ---------------------------------------------------------------- argmax without any allocation
+// Scratch of it_argmax_static: the per-CTA (value, index) partials followed by the arrival counter.  It is
+// part of the library image, so every GPU that loads the library carries these bytes until the process ends.
+#define IT_ARGMAX_STATIC_MAX_N (1u << 24)
+#define IT_ARGMAX_STATIC_MAX_DEVICES 64
+static __device__ __align__(256) unsigned long long g_argmax_static_scratch[IT_ARGMAX_MAX_BLOCKS + 32];
+// Device address of the array above, one per GPU.  The array's name is only a host-side handle in host code;
+// the address a kernel can use has to be asked for, on each device, with that device current.
+static unsigned long long* g_argmax_static_ptr[IT_ARGMAX_STATIC_MAX_DEVICES] = {};
+static int g_argmax_static_sms[IT_ARGMAX_STATIC_MAX_DEVICES] = {};
+
+IT_API int it_argmax_static(void* stream, const float* logits_dev, size_t n, uint32_t* index_dev) {
+    IT_CHECK_ARG(logits_dev && index_dev, "it_argmax_static: null pointer");
+    IT_CHECK_ARG(((uintptr_t)logits_dev & 15) == 0 && ((uintptr_t)index_dev & 3) == 0, "it_argmax_static: logits must be 16-byte aligned, the result 4-byte aligned");
+    IT_CHECK_ARG(n > 0, "it_argmax_static: empty input");
+    IT_CHECK_ARG(n <= IT_ARGMAX_STATIC_MAX_N, "it_argmax_static: %zu logits exceed the built-in scratch limit of %u", n, IT_ARGMAX_STATIC_MAX_N);
+    int dev = -1;
+    IT_CUDA(cudaGetDevice(&dev));
+    IT_CHECK_ARG(dev >= 0 && dev < IT_ARGMAX_STATIC_MAX_DEVICES, "it_argmax_static: device index %d not supported", dev);
+    if (!g_argmax_static_ptr[dev]) {
+        // first call on this device: resolve the scratch address and the SM count (no allocation involved)
+        unsigned long long* p = nullptr;
+        IT_CUDA(cudaGetSymbolAddress((void**)&p, g_argmax_static_scratch));
+        int sms = 0;
+        IT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        g_argmax_static_sms[dev] = sms;
+        g_argmax_static_ptr[dev] = p;
+    }
+    unsigned long long* partials = g_argmax_static_ptr[dev];
+    unsigned* counter = reinterpret_cast<unsigned*>(partials + IT_ARGMAX_MAX_BLOCKS);
+    cudaStream_t st = (cudaStream_t)stream;
+    // the counter must start at zero; the kernel leaves it at zero, but a launch that failed earlier may not have
+    IT_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned), st));
+    unsigned blocks = (unsigned)((n + 4095) / 4096);
+    const unsigned cap = (unsigned)(g_argmax_static_sms[dev] * 2 < IT_ARGMAX_MAX_BLOCKS ? g_argmax_static_sms[dev] * 2 : IT_ARGMAX_MAX_BLOCKS);
+    if (blocks > cap) blocks = cap;
+    unsigned per_block = (unsigned)((n + blocks - 1) / blocks); per_block = (per_block + 3) & ~3u;
+    blocks = (unsigned)((n + per_block - 1) / per_block);
+    k_argmax<<<blocks, 256, 0, st>>>(logits_dev, (unsigned)n, per_block, partials, counter, reinterpret_cast<float*>(index_dev));
+    IT_LAUNCH_CHECK("argmax_static");
+    return IT_OK;
+}
