@@ -130,6 +130,81 @@ int it_matvec_q8(it_ctx* ctx, const it_qmat* w, size_t ntok, size_t x_off, size_
  * in arena element dst_off (shaders/argmax.comp, src/sampling.rs:50; dispatch at src/vk/mod.rs:866,875). */
 int it_argmax(it_ctx* ctx, size_t logits_off, size_t n, size_t dst_off);
 
+/* ---- engine: the decoder behind the reference's backend traits ---------------------------------------
+ * Model description: the fields of Config (src/model.rs:7-15) that the forward pass uses, plus the context
+ * capacity (VkEngine's ctx_len, src/vk/mod.rs:208).  Every ternary matrix is taken to be Hadamard-folded with
+ * block 1024, which is what the reference's GPU schedule assumes (src/vk/mod.rs:536, :783-871). */
+typedef struct it_model_config {
+    int32_t n_layer, n_embd, n_ff, n_vocab, n_head, n_head_kv, head_dim, n_rot;
+    float rope_base; int32_t rope_sections[4]; float eps;
+    int32_t conv_k, ssm_state, ssm_groups, ssm_vheads, ssm_inner, full_attn_interval, gdn_v_grouped, ctx_len;
+} it_model_config;
+
+/* Tensor ids (layer_names, src/model.rs:93-102; MTP head tensors, src/mtp.rs:51-52).  Ids below IT_T_TOK_EMBD
+ * are per layer; the others are global and are addressed with layer = -1. */
+enum {
+    IT_T_ATTN_NORM = 0, IT_T_POST_NORM, IT_T_FFN_GATE, IT_T_FFN_UP, IT_T_FFN_DOWN,
+    IT_T_QKV, IT_T_GATE, IT_T_CONV, IT_T_DT, IT_T_A, IT_T_BETA, IT_T_ALPHA, IT_T_SSM_NORM, IT_T_SSM_OUT,
+    IT_T_Q, IT_T_K, IT_T_V, IT_T_O, IT_T_Q_NORM, IT_T_K_NORM,
+    IT_T_TOK_EMBD, IT_T_OUTPUT_NORM, IT_T_OUTPUT,
+    IT_T_MTP_EH, IT_T_MTP_Q, IT_T_MTP_K, IT_T_MTP_V, IT_T_MTP_O, IT_T_MTP_GATE, IT_T_MTP_UP, IT_T_MTP_DOWN,
+    IT_T_MTP_ENORM, IT_T_MTP_HNORM, IT_T_MTP_ATTN_NORM, IT_T_MTP_POST_NORM, IT_T_MTP_Q_NORM, IT_T_MTP_K_NORM, IT_T_MTP_HEAD_NORM,
+    IT_T_COUNT
+};
+
+typedef struct it_engine it_engine;
+
+/* Builds an engine with random-init weights of the given architecture generated on the device (ternary matrices as
+ * it_matrix_synth, Q8_0 head matrices as it_qmatrix_synth, f32 vectors uniform in fixed ranges, all from counter hashes
+ * of `seed`).  with_mtp != 0 adds a NextN head.  Stands where VkEngine::new_with_mtp stands (src/vk/mod.rs:494-631);
+ * geometry is validated before the device is touched (validate_geometry, src/vk/mod.rs:207). */
+int it_engine_create_synth(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, it_engine** out);
+void it_engine_destroy(it_engine* e);
+it_ctx* it_engine_ctx(it_engine* e);
+/* Read-back of weights and state for parity tests.  Ternary / Q8_0 tensors come back as raw ggml rows, f32 tensors as f32. */
+int it_engine_tensor_bytes(it_engine* e, int layer, int tensor, size_t* nbytes);
+int it_engine_tensor_read(it_engine* e, int layer, int tensor, void* host);
+int it_engine_signs_read(it_engine* e, size_t width, float* host);
+/* which: 0 conv state, 1 ssm state, 2 K cache, 3 V cache (active positions, decoded to f32), 4 MTP K, 5 MTP V. */
+int it_engine_state_read(it_engine* e, int layer, int which, float* host, size_t max_floats, size_t* n_floats);
+int it_engine_hidden_read(it_engine* e, size_t row, float* host);   /* output-normed hidden row of the last pass (h_nextn) */
+int it_engine_position(it_engine* e);
+
+/* Engine trait (src/engine.rs:8-15).  eval: feed tokens, optionally return the last token's logits (n_vocab floats).
+ * eval_argmax: feed tokens and return the greedy pick of the last one, reading back 4 bytes (src/vk/mod.rs:900). */
+int it_engine_eval(it_engine* e, const uint32_t* toks, size_t n, float* logits_or_null);
+int it_engine_eval_argmax(it_engine* e, const uint32_t* toks, size_t n, uint32_t* next);
+int it_engine_reset(it_engine* e);
+/* generate_inner's greedy path (src/engine.rs:151-174): prefill, then n_predict greedy tokens (stops early on `eos`
+ * unless eos is UINT32_MAX).  The decode steps run as one recorded graph per token. */
+int it_engine_generate(it_engine* e, const uint32_t* prompt, size_t n_prompt, size_t n_predict, uint32_t eos, uint32_t* out, size_t* n_out);
+
+/* MtpBackend trait (src/mtp.rs:150-163), one to one. */
+int it_engine_mtp_prefill(it_engine* e, const uint32_t* prompt, size_t n, uint32_t* next);
+int it_engine_mtp_single(it_engine* e, uint32_t x, uint32_t* next);
+int it_engine_mtp_draft(it_engine* e, const uint32_t* toks, size_t n, uint32_t* draft);
+int it_engine_mtp_verify(it_engine* e, uint32_t x, uint32_t d, uint32_t* a0, uint32_t* a1);
+int it_engine_mtp_reject(it_engine* e);
+int it_engine_mtp_reset_all(it_engine* e);
+
+/* greedy_mtp (src/mtp.rs:166-204) over any backend given as a table of callbacks; is_eog / on_tok as in the reference
+ * (on_tok returning 0 stops).  stats: drafted, accepted, steps, draft_calls, verify_calls, single_forwards,
+ * timed_decode_forwards, rejected, terminal_rollbacks.  Returns the number of tokens written to out, or a negative code. */
+typedef struct it_mtp_backend {
+    void* user;
+    uint32_t (*prefill)(void* user, const uint32_t* prompt, size_t n);
+    uint32_t (*single)(void* user, uint32_t x);
+    uint32_t (*draft)(void* user, const uint32_t* toks, size_t n);
+    void (*verify)(void* user, uint32_t x, uint32_t d, uint32_t* a0, uint32_t* a1);
+    void (*reject)(void* user);
+    void (*reset_all)(void* user);
+} it_mtp_backend;
+int64_t it_greedy_mtp(const it_mtp_backend* b, const uint32_t* prompt, size_t n_prompt, size_t n_predict,
+                      int (*is_eog)(void* user, uint32_t tok), int (*on_tok)(void* user, uint32_t tok), void* cb_user,
+                      uint32_t* out, int64_t stats[9]);
+/* generate_mtp (src/engine.rs:180-191): greedy_mtp over this engine's own MtpBackend. */
+int64_t it_engine_generate_mtp(it_engine* e, const uint32_t* prompt, size_t n_prompt, size_t n_predict, uint32_t eos, uint32_t* out, int64_t stats[9]);
+
 /* Greedy pick for callers that must not allocate device memory.  No counterpart in the reference: it exists
  * for hosts that hand all of HBM to their own pool at start-up (weights, KV cache, activation arena) and for
  * code paths where the implicit device-wide synchronisation of cudaMalloc / cudaFree is not acceptable, e.g. a

@@ -53,6 +53,27 @@ SIGNATURES = {
     "it_matvec_q8": (C.c_int, [P, P, c_size, c_size, c_size, c_size, c_size, C.c_int]),
     "it_argmax": (C.c_int, [P, c_size, c_size, c_size]),
     "it_argmax_static": (C.c_int, [P, P, c_size, P]),
+    "it_engine_create_synth": (C.c_int, [C.c_int, P, C.c_uint64, C.c_int, C.POINTER(P)]),
+    "it_engine_destroy": (None, [P]),
+    "it_engine_ctx": (P, [P]),
+    "it_engine_tensor_bytes": (C.c_int, [P, C.c_int, C.c_int, C.POINTER(c_size)]),
+    "it_engine_tensor_read": (C.c_int, [P, C.c_int, C.c_int, P]),
+    "it_engine_signs_read": (C.c_int, [P, c_size, P]),
+    "it_engine_state_read": (C.c_int, [P, C.c_int, C.c_int, P, c_size, C.POINTER(c_size)]),
+    "it_engine_hidden_read": (C.c_int, [P, c_size, P]),
+    "it_engine_position": (C.c_int, [P]),
+    "it_engine_eval": (C.c_int, [P, P, c_size, P]),
+    "it_engine_eval_argmax": (C.c_int, [P, P, c_size, C.POINTER(C.c_uint32)]),
+    "it_engine_reset": (C.c_int, [P]),
+    "it_engine_generate": (C.c_int, [P, P, c_size, c_size, C.c_uint32, P, C.POINTER(c_size)]),
+    "it_engine_mtp_prefill": (C.c_int, [P, P, c_size, C.POINTER(C.c_uint32)]),
+    "it_engine_mtp_single": (C.c_int, [P, C.c_uint32, C.POINTER(C.c_uint32)]),
+    "it_engine_mtp_draft": (C.c_int, [P, P, c_size, C.POINTER(C.c_uint32)]),
+    "it_engine_mtp_verify": (C.c_int, [P, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "it_engine_mtp_reject": (C.c_int, [P]),
+    "it_engine_mtp_reset_all": (C.c_int, [P]),
+    "it_greedy_mtp": (C.c_int64, [P, P, c_size, c_size, P, P, P, P, P]),
+    "it_engine_generate_mtp": (C.c_int64, [P, P, c_size, c_size, C.c_uint32, P, P]),
 }
 
 _lib = None

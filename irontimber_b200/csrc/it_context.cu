@@ -17,11 +17,6 @@ IT_API int it_version(void) { return 1; }
 // src/sampling.rs:43).  Codes: one hash per two elements, 32 bits each, code = v % 3 (or v % 4).
 // Scales: u = top 24 bits of hash(seed ^ 0x5ca1e5, block) / 2^24, d = f16(0.01 + 0.04*u) with
 // separately rounded multiply and add.
-__host__ __device__ static inline uint64_t it_mix64(uint64_t z) {
-    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull; z = (z ^ (z >> 27)) * 0x94d049bb133111ebull; return z ^ (z >> 31);
-}
-__host__ __device__ static inline uint64_t it_hash(uint64_t seed, uint64_t i) { return it_mix64(seed + 0x9e3779b97f4a7c15ull * (i + 1)); }
-
 __global__ void k_synth_pq2(uint64_t seed, size_t rows, size_t cols, int four, uint8_t* raw) {
     size_t bpr = cols / 128, nblk = rows * bpr;
     for (size_t blk = blockIdx.x * (size_t)blockDim.x + threadIdx.x; blk < nblk; blk += (size_t)gridDim.x * blockDim.x) {

@@ -1,0 +1,63 @@
+// The decoder engine: weights, state and arena layout shared by it_engine.cu (construction, read-back) and
+// it_engine_run.cu (forward passes, MTP hooks, generation loops).
+#pragma once
+#include "it_internal.h"
+#include <vector>
+
+#define IT_MAXT 8     // activation rows per pass (one mma N tile)
+#define IT_MAXCK 3    // recurrent-state checkpoints per pass (rows 0..2 of a verification pass)
+
+struct it_layer {
+    bool recurrent;
+    float *attn_norm, *post_norm;
+    it_mat *ffn_gate, *ffn_up, *ffn_down;
+    // Gated DeltaNet layers
+    it_mat *qkv, *gate, *ssm_out;
+    float *conv_w, *dt, *a, *beta, *alpha, *ssm_norm;
+    float *conv_st, *ssm_st, *ck_conv, *ck_ssm;     // state and its checkpoints [IT_MAXCK][...]
+    // attention layers
+    it_mat *q, *k, *v, *o;
+    float *q_norm, *k_norm;
+    __half *kc, *vc;                                 // [ctx_len][n_head_kv * head_dim]
+};
+
+struct it_arena_layout {   // element offsets into the context's f32 arena; every row buffer holds IT_MAXT rows
+    size_t x, xn, big1, big2, conv, kcur, vcur, o, beta, alpha, hrow, hprev, mh, me, mcat, mx, logits, amx, total;
+    size_t big1_stride, big2_stride, o_stride, logits_stride;
+};
+
+struct it_engine {
+    it_ctx* ctx;
+    it_model_config cfg;
+    uint64_t seed;
+    bool has_mtp;
+    std::vector<it_layer> layers;
+    float *tok_embd, *output_norm;
+    it_mat* output;
+    // MTP head (src/mtp.rs:22-27)
+    it_qmat *m_eh, *m_q, *m_k, *m_v, *m_o, *m_gate, *m_up, *m_down;
+    float *m_enorm, *m_hnorm, *m_attn_norm, *m_post_norm, *m_q_norm, *m_k_norm, *m_head_norm;
+    float *mkc, *mvc;                                // f32 [ctx_len][kvd], slot = position - 1 (src/mtp.rs:95)
+    it_q8* q8;
+    uint32_t* toks_dev;                              // IT_MAXT token ids of the current pass
+    int* pos_dev;                                    // position read by the recorded decode step
+    it_arena_layout lay;
+    float theta_scale;
+    std::vector<void*> owned;                        // plain device allocations to free
+    int pos, mpos;                                   // trunk position; next MTP position (src/vk/mod.rs: pos, mpos)
+    size_t hp_off; int hp_n;                         // pending h rows for the next draft (arena offset, count)
+    it_graph* step_graph;                            // recorded single-token greedy step
+    uint32_t* host_pin;                              // pinned staging for token ids / picks
+};
+
+// derived sizes (src/model.rs:40-43)
+static inline int it_cfg_qk(const it_model_config& c) { return c.ssm_state * c.ssm_groups; }
+static inline int it_cfg_conv_dim(const it_model_config& c) { return 2 * it_cfg_qk(c) + c.ssm_inner; }
+static inline bool it_cfg_recurrent(const it_model_config& c, int il) { return (il + 1) % c.full_attn_interval != 0; }
+
+#define IT_TRY(expr) do { int r__ = (expr); if (r__) return r__; } while (0)
+
+// Runs one pass over nt <= IT_MAXT tokens (run_chunk_v, src/vk/mod.rs:763-892).  logit_rows: 0 none, 1 last row, 2 every
+// row; nck: recurrent-state checkpoints to take (after rows 0..nck-1); from_dev: token ids are already in toks_dev and the
+// position is read from pos_dev (recorded decode step).
+int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_rows, int nck, bool from_dev);

@@ -95,6 +95,12 @@ int it_check_device_error(it_ctx* ctx, const char* who);
 
 #define IT_ARGMAX_MAX_BLOCKS 1024
 
+// ---- synthetic data: hash(seed, i) is the i-th output of splitmix64 seeded with `seed` (src/sampling.rs:43) ----
+__host__ __device__ static inline uint64_t it_mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull; z = (z ^ (z >> 27)) * 0x94d049bb133111ebull; return z ^ (z >> 31);
+}
+__host__ __device__ static inline uint64_t it_hash(uint64_t seed, uint64_t i) { return it_mix64(seed + 0x9e3779b97f4a7c15ull * (i + 1)); }
+
 // ---- launchers implemented in the kernel translation units ------------------------------------------
 int it_launch_repack_pq2(it_ctx* ctx, const uint8_t* raw_dev, size_t rows, size_t cols, uint8_t* tiles);
 int it_launch_repack_packed2(it_ctx* ctx, const uint32_t* words_dev, const float* scales_dev, size_t rows, size_t cols, uint8_t* tiles);

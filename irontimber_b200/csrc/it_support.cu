@@ -1,0 +1,281 @@
+// Decoder support ops around the ternary matvecs: rmsnorm, rope, causal conv, delta rule, attention, ...
+//
+// These follow the reference's CPU forward pass (src/cpu.rs:14-22, :145-164, :194-274) operation for operation
+// and in its order of additions, so that results are bit-identical to that code, with three exceptions that are
+// stated where they occur: the width-n_embd rmsnorm adds its squares in a fixed lane/tree order (a sequential
+// sum of 5120 terms is a 10 us dependency chain), dense f32 rows are summed lane-strided in f64, and exp / log /
+// sin / cos come from it_math.h.  None of these kernels is on the HBM roofline; they are sized for latency.
+#include "it_internal.h"
+#include "it_support.h"
+#include "it_math.h"
+
+namespace {
+
+// x[t] = table[tok[t]]  (Model::embed, src/cpu.rs:118-122; the reference computes this on the host, src/vk/mod.rs:766-769)
+__global__ void k_embed(const uint32_t* __restrict__ toks, const float* __restrict__ table, int e, float* x) {
+    const int t = blockIdx.y; const size_t row = toks[t];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < e / 4; i += gridDim.x * blockDim.x)
+        reinterpret_cast<float4*>(x + (size_t)t * e)[i] = reinterpret_cast<const float4*>(table + row * e)[i];
+}
+
+// rmsnorm over the embedding width (src/cpu.rs:14-18), one CTA of 256 threads per row.  Sum of squares: thread i
+// adds x[i]^2, x[i+256]^2, ... in ascending order; each warp folds with a butterfly (offsets 16..1); the eight warp
+// sums are added in ascending order.  out = (x * s) * w with s = 1 / sqrt(ss / n + eps), no fused multiply-add.
+__global__ void __launch_bounds__(256) k_rmsnorm_wide(const float* x, size_t x_stride, const float* __restrict__ w, int n, float eps, float* out, size_t out_stride) {
+    __shared__ float wsum[8];
+    const float* xr = x + blockIdx.x * x_stride; float* o = out + blockIdx.x * out_stride;
+    float s = 0.f;
+    for (int j = threadIdx.x; j < n; j += 256) s = it_add(s, it_mul(xr[j], xr[j]));
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) s = it_add(s, __shfl_xor_sync(0xffffffffu, s, m));
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float t = wsum[0];
+#pragma unroll
+    for (int k = 1; k < 8; k++) t = it_add(t, wsum[k]);
+    const float sc = it_div(1.0f, it_sqrt(it_add(it_div(t, (float)n), eps)));
+    for (int j = threadIdx.x; j < n; j += 256) o[j] = it_mul(it_mul(xr[j], sc), w[j]);
+}
+
+// Per-head norms of width n <= 256, one warp per (head, row), the squares added sequentially as on the CPU.
+// mode 0: rmsnorm with weight (q_norm / k_norm, src/cpu.rs:252-256); mode 1: rmsnorm with weight, then * silu(z)
+// (gated ssm_norm, src/cpu.rs:233-237); mode 2: l2norm, x / max(sqrt(sum), eps) (src/cpu.rs:164, :214).
+__global__ void __launch_bounds__(128) k_norm_head(const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts,
+                                                   int n, int nheads, const float* __restrict__ w, int mode, float eps, const float* z, size_t z_hs, size_t z_ts) {
+    __shared__ float buf[4][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x * 4 + warp, t = blockIdx.y;
+    if (head >= nheads) return;
+    const float* x = in + t * in_ts + head * in_hs;
+    for (int i = lane; i < n; i += 32) buf[warp][i] = x[i];
+    __syncwarp();
+    float s = 0.f;
+    if (lane == 0) {
+#pragma unroll 8
+        for (int i = 0; i < n; i++) s = it_add(s, it_mul(buf[warp][i], buf[warp][i]));
+    }
+    s = __shfl_sync(0xffffffffu, s, 0);
+    const float sc = mode == 2 ? it_div(1.0f, fmaxf(it_sqrt(s), eps)) : it_div(1.0f, it_sqrt(it_add(it_div(s, (float)n), eps)));
+    float* o = out + t * out_ts + head * out_hs;
+    for (int i = lane; i < n; i += 32) {
+        float v = it_mul(buf[warp][i], sc);
+        if (mode != 2) v = it_mul(v, w[i]);
+        if (mode == 1) v = it_mul(v, it_silu(z[t * z_ts + head * z_hs + i]));
+        o[i] = v;
+    }
+}
+
+// (I)MRoPE for text positions on the first n_rot dims of each head (src/cpu.rs:145-162): the angle of pair i is the
+// position multiplied i times by theta_scale, one rounding per step exactly as the CPU's running product.
+__global__ void k_rope(float* x, size_t hs, size_t ts, int nheads, int pos0, const int* pos_ptr, int n_rot, float theta_scale, int s0, int s1, int s2, int s3) {
+    const int half = n_rot / 2, t = blockIdx.y;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= nheads * half) return;
+    const int head = idx / half, i = idx % half;
+    if (pos_ptr) pos0 += *pos_ptr;
+    float theta = (float)(pos0 + t);
+    for (int k = 0; k < i; k++) theta = it_mul(theta, theta_scale);
+    const int sect = s0 + s1 + s2 + s3, sector = sect > 0 ? i % sect : 0;
+    const bool use_e = sect > 0 && !((sector % 3 == 1 && sector < 3 * s1) || (sector % 3 == 2 && sector < 3 * s2) || (sector % 3 == 0 && sector < 3 * s0));
+    float s, c; it_sincosf(use_e ? 0.0f : theta, &s, &c);
+    float* h = x + t * ts + head * hs;
+    const float x0 = h[i], x1 = h[i + half];
+    h[i] = it_sub(it_mul(x0, c), it_mul(x1, s));
+    h[i + half] = it_add(it_mul(x0, s), it_mul(x1, c));
+}
+
+// Causal depthwise conv + SiLU + state shift, token after token (src/cpu.rs:203-212).  One thread per channel; the
+// state after token t is copied to checkpoint t when one is given (MTP rollback, src/vk/mod.rs:794).
+__global__ void k_conv(const float* mixed, size_t m_ts, const float* __restrict__ w, float* state, float* out, size_t o_ts, int cd, int kk, int nt,
+                       float* ck, size_t ck_stride, int nck) {
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= cd) return;
+    float st[8];
+    for (int i = 0; i < kk - 1; i++) st[i] = state[(size_t)i * cd + ch];
+    for (int t = 0; t < nt; t++) {
+        const float m = mixed[t * m_ts + ch];
+        float s = 0.f;
+        for (int i = 0; i < kk; i++) s = it_add(s, it_mul(i < kk - 1 ? st[i] : m, w[ch * kk + i]));
+        out[t * o_ts + ch] = it_silu(s);
+        for (int i = 0; i < kk - 2; i++) st[i] = st[i + 1];
+        st[kk - 2] = m;
+        if (t < nck) for (int i = 0; i < kk - 1; i++) ck[t * ck_stride + (size_t)i * cd + ch] = st[i];
+    }
+    for (int i = 0; i < kk - 1; i++) state[(size_t)i * cd + ch] = st[i];
+}
+
+// Dense f32 rows (ssm_beta / ssm_alpha; cpu::matvec's f32 arm under Numerics::Ggml, src/cpu.rs:36-43: f32 products,
+// f64 accumulation).  One warp per row: lane l adds the products i = l, l+32, ... in f64, then a butterfly.
+__global__ void k_dense_rows(const float* __restrict__ w, int rows, int cols, const float* x, size_t x_ts, float* y, size_t y_ts) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31, t = blockIdx.y;
+    if (row >= rows) return;
+    const float* wr = w + (size_t)row * cols; const float* xr = x + t * x_ts;
+    double s = 0.0;
+    for (int i = lane; i < cols; i += 32) s += (double)it_mul(wr[i], xr[i]);
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+    if (lane == 0) y[t * y_ts + row] = (float)s;
+}
+
+// Gated delta rule, token after token (src/cpu.rs:215-232).  One warp per 32 rows of a head's state matrix; every
+// row is updated by one thread with the CPU's two sequential passes.  The tile goes through shared memory so that
+// global accesses stay coalesced.  State layout [head][j][i] as on the CPU (src/cpu.rs:132).
+__global__ void __launch_bounds__(32) k_gdn(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
+                                            float* state, float* o, size_t o_ts, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
+    extern __shared__ float tile[];            // [32][sd + 1] rows, then q[sd], k[sd]
+    const int h = blockIdx.x, j0 = blockIdx.y * 32, lane = threadIdx.x, kh = h % nk, ld = sd + 1;
+    float* qs = tile + 32 * ld; float* ks = qs + sd;
+    float* m = state + ((size_t)h * sd + j0) * sd;
+    for (int r = 0; r < 32; r++) for (int i = lane; i < sd; i += 32) tile[r * ld + i] = m[(size_t)r * sd + i];
+    float* row = tile + lane * ld;
+    const float scale = it_div(1.0f, it_sqrt((float)sd));
+    for (int t = 0; t < nt; t++) {
+        const float* c = co + t * co_ts;
+        __syncwarp();
+        for (int i = lane; i < sd; i += 32) { qs[i] = c[kh * sd + i]; ks[i] = c[qk + kh * sd + i]; }
+        __syncwarp();
+        const float v = c[2 * qk + h * sd + j0 + lane];
+        const float bt = it_sigmoid(beta[t * ba_ts + h]);
+        const float g = it_mul(it_softplus(it_add(alpha[t * ba_ts + h], dt[h])), a[h]);
+        const float eg = it_expf(g);
+        float s = 0.f;
+        for (int i = 0; i < sd; i++) { const float r = it_mul(row[i], eg); row[i] = r; s = it_add(s, it_mul(r, ks[i])); }
+        const float delta = it_mul(it_sub(v, s), bt);
+        float acc = 0.f;
+        for (int i = 0; i < sd; i++) { const float r = it_add(row[i], it_mul(ks[i], delta)); row[i] = r; acc = it_add(acc, it_mul(r, qs[i])); }
+        o[t * o_ts + h * sd + j0 + lane] = it_mul(acc, scale);
+        if (t < nck) {
+            __syncwarp();
+            float* cm = ck + t * ck_stride + ((size_t)h * sd + j0) * sd;
+            for (int r = 0; r < 32; r++) for (int i = lane; i < sd; i += 32) cm[(size_t)r * sd + i] = tile[r * ld + i];
+        }
+    }
+    __syncwarp();
+    for (int r = 0; r < 32; r++) for (int i = lane; i < sd; i += 32) m[(size_t)r * sd + i] = tile[r * ld + i];
+}
+
+// act = silu(g) * u (src/cpu.rs:183)
+__global__ void k_silu_mul(const float* g, const float* u, float* out, size_t n) {
+    const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (i < n) out[i] = it_mul(it_silu(g[i]), u[i]);
+}
+
+// New K / V rows into the cache: f16 round-to-nearest-even for the trunk (src/cpu.rs:22, :258), f32 for the MTP head.
+template <typename T> __device__ __forceinline__ T kv_pack(float v);
+template <> __device__ __forceinline__ __half kv_pack<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float kv_pack<float>(float v) { return v; }
+__device__ __forceinline__ float kv_get(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ float kv_get(const float* p) { return *p; }
+
+template <typename T>
+__global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* vc, int kvd, int slot0, const int* pos_ptr) {
+    if (pos_ptr) slot0 += *pos_ptr;
+    const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= kvd) return;
+    kc[(size_t)(slot0 + t) * kvd + i] = kv_pack<T>(k[t * ts + i]);
+    vc[(size_t)(slot0 + t) * kvd + i] = kv_pack<T>(v[t * ts + i]);
+}
+
+// Causal gated attention for one (head, row) per CTA in the CPU's order (src/cpu.rs:262-272): every score is a
+// sequential dot over the head dimension, the exponentials are added in ascending position order by one thread,
+// every output element accumulates w[p] * v[p][j] in ascending position order, then * sigmoid(gate).
+template <typename T>
+__global__ void __launch_bounds__(256) k_attention(const float* q, size_t q_hs, size_t q_ts, const float* gate, const T* __restrict__ kc, const T* __restrict__ vc,
+                                                   int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, float* out, size_t o_ts) {
+    extern __shared__ float sc[];              // [n] scores, then q[hd]
+    __shared__ float red[8]; __shared__ float s_sum;
+    if (pos_ptr) slot0 += *pos_ptr;
+    const int h = blockIdx.x, t = blockIdx.y, n = slot0 + t + 1, kh = h / (nh / nkv), tid = threadIdx.x;
+    float* qs = sc + ((n + 3) & ~3);
+    const float* qh = q + t * q_ts + h * q_hs;
+    for (int j = tid; j < hd; j += 256) qs[j] = qh[j];
+    __syncthreads();
+    const float scale = it_div(1.0f, it_sqrt((float)hd));
+    float mx = -INFINITY;
+    for (int p = tid; p < n; p += 256) {
+        const T* kp = kc + (size_t)p * kvd + kh * hd;
+        float s = 0.f;
+        for (int j = 0; j < hd; j++) s = it_add(s, it_mul(qs[j], kv_get(kp + j)));
+        s = it_mul(s, scale); sc[p] = s; mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int k = 1; k < 8; k++) mx = fmaxf(mx, red[k]);
+    for (int p = tid; p < n; p += 256) sc[p] = it_expf(it_sub(sc[p], mx));
+    __syncthreads();
+    if (tid == 0) { float s = 0.f;
+#pragma unroll 8
+        for (int p = 0; p < n; p++) s = it_add(s, sc[p]);
+        s_sum = s; }
+    __syncthreads();
+    const float sum = s_sum;
+    for (int p = tid; p < n; p += 256) sc[p] = it_div(sc[p], sum);
+    __syncthreads();
+    for (int j = tid; j < hd; j += 256) {
+        const T* vp = vc + kh * hd + j;
+        float acc = 0.f;
+#pragma unroll 4
+        for (int p = 0; p < n; p++) acc = it_add(acc, it_mul(sc[p], kv_get(vp + (size_t)p * kvd)));
+        out[t * o_ts + h * hd + j] = it_mul(acc, it_sigmoid(gate[t * q_ts + h * q_hs + j]));
+    }
+}
+
+#define KCHK(name) do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return it_fail(IT_ECUDA, "launch %s: %s", name, cudaGetErrorString(e__)); } while (0)
+
+}  // namespace
+
+int it_sup_embed(it_ctx* c, const uint32_t* toks_dev, const float* table, int e, int nt, float* x) {
+    it_note_op(c); k_embed<<<dim3(4, nt), 256, 0, c->stream>>>(toks_dev, table, e, x); KCHK("embed"); return IT_OK;
+}
+int it_sup_rmsnorm_wide(it_ctx* c, const float* x, size_t xs, const float* w, int n, float eps, float* out, size_t os, int nt) {
+    it_note_op(c); k_rmsnorm_wide<<<nt, 256, 0, c->stream>>>(x, xs, w, n, eps, out, os); KCHK("rmsnorm_wide"); return IT_OK;
+}
+int it_sup_norm_head(it_ctx* c, const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts, int n, int nheads, const float* w, int mode, float eps,
+                     const float* z, size_t z_hs, size_t z_ts, int nt) {
+    if (n > 256) return it_fail(IT_EINVAL, "head norm width %d exceeds 256", n);
+    it_note_op(c); k_norm_head<<<dim3((nheads + 3) / 4, nt), 128, 0, c->stream>>>(in, in_hs, in_ts, out, out_hs, out_ts, n, nheads, w, mode, eps, z, z_hs, z_ts); KCHK("norm_head"); return IT_OK;
+}
+int it_sup_rope(it_ctx* c, float* x, size_t hs, size_t ts, int nheads, int nt, int pos0, const int* pos_ptr, int n_rot, float theta_scale, const int* sec) {
+    it_note_op(c); const int n = nheads * (n_rot / 2);
+    k_rope<<<dim3((n + 127) / 128, nt), 128, 0, c->stream>>>(x, hs, ts, nheads, pos0, pos_ptr, n_rot, theta_scale, sec[0], sec[1], sec[2], sec[3]); KCHK("rope"); return IT_OK;
+}
+int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, float* state, float* out, size_t o_ts, int cd, int kk, int nt, float* ck, size_t ck_stride, int nck) {
+    if (kk < 2 || kk > 9) return it_fail(IT_EINVAL, "conv kernel size %d not supported", kk);
+    it_note_op(c); k_conv<<<(cd + 127) / 128, 128, 0, c->stream>>>(mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
+}
+int it_sup_dense_rows(it_ctx* c, const float* w, int rows, int cols, const float* x, size_t x_ts, float* y, size_t y_ts, int nt) {
+    it_note_op(c); k_dense_rows<<<dim3((rows + 3) / 4, nt), 128, 0, c->stream>>>(w, rows, cols, x, x_ts, y, y_ts); KCHK("dense_rows"); return IT_OK;
+}
+int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
+               int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
+    if (sd % 32 != 0) return it_fail(IT_EINVAL, "ssm state size %d is not a multiple of 32", sd);
+    it_note_op(c); const size_t smem = (32 * (sd + 1) + 2 * sd) * sizeof(float);
+    k_gdn<<<dim3(nv, sd / 32), 32, smem, c->stream>>>(co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck); KCHK("gdn"); return IT_OK;
+}
+int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n) {
+    it_note_op(c); k_silu_mul<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(g, u, out, n); KCHK("silu_mul"); return IT_OK;
+}
+int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int slot0, const int* pos_ptr, int nt, int f16) {
+    it_note_op(c);
+    if (f16) k_kv_store<__half><<<dim3((kvd + 255) / 256, nt), 256, 0, c->stream>>>(k, v, ts, (__half*)kc, (__half*)vc, kvd, slot0, pos_ptr);
+    else k_kv_store<float><<<dim3((kvd + 255) / 256, nt), 256, 0, c->stream>>>(k, v, ts, (float*)kc, (float*)vc, kvd, slot0, pos_ptr);
+    KCHK("kv_store"); return IT_OK;
+}
+int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16) {
+    it_note_op(c);
+    // shared memory is sized for the longest row of scores this launch can meet (max_pos when the position is read on the device)
+    const size_t smem = (((size_t)(pos_ptr ? max_pos : slot0 + nt) + 3) / 4 * 4 + hd) * sizeof(float);
+    if (smem > 200 * 1024) return it_fail(IT_EINVAL, "attention over %d positions exceeds the shared-memory budget", slot0 + nt);
+    if (f16) {
+        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+        k_attention<__half><<<dim3(nh, nt), 256, smem, c->stream>>>(q, q_hs, q_ts, gate, (const __half*)kc, (const __half*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
+    } else {
+        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+        k_attention<float><<<dim3(nh, nt), 256, smem, c->stream>>>(q, q_hs, q_ts, gate, (const float*)kc, (const float*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
+    }
+    KCHK("attention"); return IT_OK;
+}

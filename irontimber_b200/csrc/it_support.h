@@ -1,0 +1,17 @@
+// Launchers of the decoder support kernels (it_support.cu), used by the engine.
+#pragma once
+#include "it_internal.h"
+
+int it_sup_embed(it_ctx* c, const uint32_t* toks_dev, const float* table, int e, int nt, float* x);
+int it_sup_rmsnorm_wide(it_ctx* c, const float* x, size_t xs, const float* w, int n, float eps, float* out, size_t os, int nt);
+int it_sup_norm_head(it_ctx* c, const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts, int n, int nheads, const float* w, int mode, float eps,
+                     const float* z, size_t z_hs, size_t z_ts, int nt);
+int it_sup_rope(it_ctx* c, float* x, size_t hs, size_t ts, int nheads, int nt, int pos0, const int* pos_ptr, int n_rot, float theta_scale, const int* sections);
+int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, float* state, float* out, size_t o_ts, int cd, int kk, int nt, float* ck, size_t ck_stride, int nck);
+int it_sup_dense_rows(it_ctx* c, const float* w, int rows, int cols, const float* x, size_t x_ts, float* y, size_t y_ts, int nt);
+int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
+               int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck);
+int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n);
+int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int slot0, const int* pos_ptr, int nt, int f16);
+int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0,
+                     const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16);

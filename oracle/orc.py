@@ -24,7 +24,7 @@ GGML, F32 = 0, 1
 
 def build(force=False):
     so = os.path.join(_HERE, "liborc.so")
-    srcs = [os.path.join(_HERE, f) for f in os.listdir(_HERE) if f.endswith((".cpp", ".h"))]
+    srcs = [os.path.join(_HERE, f) for f in os.listdir(_HERE) if f.endswith((".cpp", ".h", ".inc"))]
     if force or not os.path.exists(so) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs):
         subprocess.run(["make", "-C", _HERE, "liborc.so"], check=True, capture_output=True)
     return so
@@ -230,3 +230,164 @@ def greedy_mtp(backend, prompt, n, is_eog=lambda t: False, on_tok=lambda t: True
     if k < 0:
         raise ValueError("empty MTP prompt")
     return [int(t) for t in out[:k]], dict(zip(STAT_NAMES, (int(s) for s in stats)))
+
+
+# ---- decoder model (oracle_model.cpp) --------------------------------------------------------
+REFERENCE_ORDER, DEVICE_ORDER = 0, 1
+
+TENSORS = ("attn_norm", "post_norm", "ffn_gate", "ffn_up", "ffn_down",
+           "qkv", "gate", "conv", "dt", "a", "beta", "alpha", "ssm_norm", "ssm_out",
+           "q", "k", "v", "o", "q_norm", "k_norm",
+           "tok_embd", "output_norm", "output",
+           "mtp_eh", "mtp_q", "mtp_k", "mtp_v", "mtp_o", "mtp_gate", "mtp_up", "mtp_down",
+           "mtp_enorm", "mtp_hnorm", "mtp_attn_norm", "mtp_post_norm", "mtp_q_norm", "mtp_k_norm", "mtp_head_norm")
+TENSOR_ID = {n: i for i, n in enumerate(TENSORS)}
+
+
+class ModelConfig(C.Structure):
+    """Field-for-field mirror of it_model_config (include/irontimber_cuda.h); Config of src/model.rs:7-15."""
+    _fields_ = [("n_layer", C.c_int32), ("n_embd", C.c_int32), ("n_ff", C.c_int32), ("n_vocab", C.c_int32),
+                ("n_head", C.c_int32), ("n_head_kv", C.c_int32), ("head_dim", C.c_int32), ("n_rot", C.c_int32),
+                ("rope_base", C.c_float), ("rope_sections", C.c_int32 * 4), ("eps", C.c_float),
+                ("conv_k", C.c_int32), ("ssm_state", C.c_int32), ("ssm_groups", C.c_int32), ("ssm_vheads", C.c_int32),
+                ("ssm_inner", C.c_int32), ("full_attn_interval", C.c_int32), ("gdn_v_grouped", C.c_int32), ("ctx_len", C.c_int32)]
+
+    def is_recurrent(self, il):
+        return (il + 1) % self.full_attn_interval != 0
+
+    @property
+    def qk_dim(self):
+        return self.ssm_state * self.ssm_groups
+
+    @property
+    def conv_dim(self):
+        return 2 * self.qk_dim + self.ssm_inner
+
+
+class Model:
+    """Host-memory decoder for the oracle: set tensors by name, then run forward_token / mtp_step."""
+
+    def __init__(self, cfg, nthreads=0):
+        L = lib()
+        L.orc_model_new.restype = C.c_void_p
+        L.orc_state_new.restype = C.c_void_p
+        L.orc_state_clone.restype = C.c_void_p
+        L.orc_mtp_state_new.restype = C.c_void_p
+        L.orc_state_read.restype = C.c_int64
+        assert L.orc_model_config_bytes() == C.sizeof(ModelConfig)
+        self.cfg = cfg
+        self.h = C.c_void_p(L.orc_model_new(C.byref(cfg), C.c_int(nthreads)))
+
+    def set(self, name, data, layer=-1):
+        a = np.ascontiguousarray(data)
+        lib().orc_model_set(self.h, C.c_int(layer), C.c_int(TENSOR_ID[name]), _p(a), C.c_int64(a.nbytes))
+
+    def set_signs(self, signs):
+        s = _c(signs, np.float32)
+        lib().orc_model_set_signs(self.h, C.c_int64(s.size), _p(s))
+
+    def new_state(self):
+        return C.c_void_p(lib().orc_state_new(self.h))
+
+    def clone_state(self, st):
+        return C.c_void_p(lib().orc_state_clone(st))
+
+    def assign_state(self, dst, src):
+        lib().orc_state_assign(dst, src)
+
+    def free_state(self, st):
+        lib().orc_state_free(st)
+
+    def state_pos(self, st):
+        return int(lib().orc_state_pos(st))
+
+    def state_h(self, st):
+        out = np.empty(self.cfg.n_embd, np.float32)
+        lib().orc_state_h(st, _p(out))
+        return out
+
+    def state_read(self, st, layer, which):
+        n = lib().orc_state_read(st, C.c_int(layer), C.c_int(which), None)
+        out = np.empty(n, np.float32)
+        lib().orc_state_read(st, C.c_int(layer), C.c_int(which), _p(out))
+        return out
+
+    def forward_token(self, st, tok, want_logits=True, mode=REFERENCE_ORDER):
+        """Model::forward_token (src/cpu.rs:168)."""
+        lg = np.empty(self.cfg.n_vocab, np.float32) if want_logits else None
+        lib().orc_forward_token(self.h, st, C.c_uint32(tok), _p(lg) if want_logits else None, C.c_int(mode))
+        return lg
+
+    def new_mtp_state(self):
+        return C.c_void_p(lib().orc_mtp_state_new())
+
+    def mtp_step(self, ms, h, tok, pos, mode=REFERENCE_ORDER):
+        """cpu_step (src/mtp.rs:100)."""
+        h = _c(h, np.float32)
+        lg = np.empty(self.cfg.n_vocab, np.float32)
+        lib().orc_mtp_step(self.h, ms, _p(h), C.c_uint32(tok), C.c_int(pos), _p(lg), C.c_int(mode))
+        return lg
+
+    def close(self):
+        if self.h:
+            lib().orc_model_free(self.h)
+            self.h = None
+
+
+class CpuMtp:
+    """CpuMtp (src/mtp.rs:207-236): the reference's CPU speculative backend over the oracle model."""
+
+    def __init__(self, model, mode=REFERENCE_ORDER):
+        self.m, self.mode = model, mode
+        self.reset_all()
+
+    def reset_all(self):
+        self.st = self.m.new_state(); self.ck = None; self.ms = self.m.new_mtp_state(); self.hpend = []; self.mpos = 1
+
+    def mtp_single(self, x):
+        return argmax(self.m.forward_token(self.st, x, True, self.mode))
+
+    def mtp_prefill(self, prompt):
+        self.reset_all()
+        hs, lg = [], None
+        for i, t in enumerate(prompt):
+            lg = self.m.forward_token(self.st, t, i + 1 == len(prompt), self.mode)
+            hs.append(self.m.state_h(self.st))
+        for q in range(1, len(prompt)):
+            self.m.mtp_step(self.ms, hs[q - 1], prompt[q], q, self.mode)
+        self.mpos = len(prompt); self.hpend = [hs[-1]]
+        return argmax(lg)
+
+    def mtp_draft(self, toks):
+        assert len(toks) == len(self.hpend)
+        lg = None
+        for i, t in enumerate(toks):
+            lg = self.m.mtp_step(self.ms, self.hpend[i], t, self.mpos, self.mode); self.mpos += 1
+        return argmax(lg)
+
+    def mtp_verify(self, x, d):
+        l0 = self.m.forward_token(self.st, x, True, self.mode); h0 = self.m.state_h(self.st)
+        self.ck = self.m.clone_state(self.st)
+        l1 = self.m.forward_token(self.st, d, True, self.mode); h1 = self.m.state_h(self.st)
+        self.hpend = [h0, h1]
+        return argmax(l0), argmax(l1)
+
+    def mtp_reject(self):
+        self.m.assign_state(self.st, self.ck); self.ck = None; self.hpend = self.hpend[:1]
+
+
+def generate_greedy(model, prompt, n, mode=REFERENCE_ORDER):
+    """generate_inner's greedy path (src/engine.rs:151-174): prefill token by token, then n greedy tokens."""
+    st = model.new_state()
+    lg = None
+    for i, t in enumerate(prompt):
+        lg = model.forward_token(st, t, i + 1 == len(prompt), mode)
+    out = []
+    for _ in range(n):
+        t = argmax(lg)
+        out.append(t)
+        if len(out) == n:
+            break
+        lg = model.forward_token(st, t, True, mode)
+    model.free_state(st)
+    return out

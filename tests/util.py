@@ -74,3 +74,73 @@ def synth_q8_0(seed, rows, cols):
     raw[:, 0:2] = d16.view(np.uint8).reshape(-1, 2)
     raw[:, 2:] = q.view(np.uint8).reshape(-1, 32)
     return raw.reshape(-1)
+
+
+# ---- small decoder models for the oracle ---------------------------------------------------------------
+def tiny_config(cls, n_layer=4, ctx_len=64, n_vocab=1000):
+    """A 4-layer model with the 27B's structure (3 delta-net layers + 1 attention layer) at small widths."""
+    import ctypes as C
+    return cls(n_layer=n_layer, n_embd=1024, n_ff=2048, n_vocab=n_vocab, n_head=4, n_head_kv=2, head_dim=256, n_rot=64,
+               rope_base=1e7, rope_sections=(C.c_int32 * 4)(11, 11, 10, 0), eps=1e-6, conv_k=4, ssm_state=128, ssm_groups=2,
+               ssm_vheads=8, ssm_inner=1024, full_attn_interval=4, gdn_v_grouped=1, ctx_len=ctx_len)
+
+
+def tensor_shapes(cfg):
+    """name -> (kind, rows, cols) with kind in {'pq2', 'q8', 'f32'}; shapes of src/cpu.rs:97-111 and src/mtp.rs:51-52."""
+    e, ff, hd, nh, nkv = cfg.n_embd, cfg.n_ff, cfg.head_dim, cfg.n_head, cfg.n_head_kv
+    qk = cfg.ssm_state * cfg.ssm_groups
+    cd, inner, nv, sd, kvd, qf = 2 * qk + cfg.ssm_inner, cfg.ssm_inner, cfg.ssm_vheads, cfg.ssm_state, nkv * hd, 2 * nh * hd
+    return {"attn_norm": ("f32", 1, e), "post_norm": ("f32", 1, e), "ffn_gate": ("pq2", ff, e), "ffn_up": ("pq2", ff, e), "ffn_down": ("pq2", e, ff),
+            "qkv": ("pq2", cd, e), "gate": ("pq2", inner, e), "conv": ("f32", cd, cfg.conv_k), "dt": ("f32", 1, nv), "a": ("f32", 1, nv),
+            "beta": ("f32", nv, e), "alpha": ("f32", nv, e), "ssm_norm": ("f32", 1, sd), "ssm_out": ("pq2", e, inner),
+            "q": ("pq2", qf, e), "k": ("pq2", kvd, e), "v": ("pq2", kvd, e), "o": ("pq2", e, nh * hd), "q_norm": ("f32", 1, hd), "k_norm": ("f32", 1, hd),
+            "tok_embd": ("f32", cfg.n_vocab, e), "output_norm": ("f32", 1, e), "output": ("pq2", cfg.n_vocab, e),
+            "mtp_eh": ("q8", e, 2 * e), "mtp_q": ("q8", qf, e), "mtp_k": ("q8", kvd, e), "mtp_v": ("q8", kvd, e), "mtp_o": ("q8", e, nh * hd),
+            "mtp_gate": ("q8", ff, e), "mtp_up": ("q8", ff, e), "mtp_down": ("q8", e, ff),
+            "mtp_enorm": ("f32", 1, e), "mtp_hnorm": ("f32", 1, e), "mtp_attn_norm": ("f32", 1, e), "mtp_post_norm": ("f32", 1, e),
+            "mtp_q_norm": ("f32", 1, hd), "mtp_k_norm": ("f32", 1, hd), "mtp_head_norm": ("f32", 1, e)}
+
+
+def random_oracle_model(orc, cfg, seed=0, with_mtp=True):
+    """An oracle model with numpy-random weights in the synthetic model's ranges (no GPU involved)."""
+    rng = np.random.default_rng(seed)
+    m = orc.Model(cfg)
+    shapes = tensor_shapes(cfg)
+
+    def make(name):
+        kind, r, c = shapes[name]
+        if kind == "pq2":
+            return make_pq2(rng, r, c)[0]
+        if kind == "q8":
+            return make_q8_0(rng, r, c)
+        lo, hi = {"conv": (-0.5, 0.5), "dt": (-0.5, 0.5), "a": (-1.1, -0.1), "beta": (-0.05, 0.05), "alpha": (-0.05, 0.05), "tok_embd": (-1, 1)}.get(name, (0.9, 1.1))
+        return rng.uniform(lo, hi, r * c).astype(np.float32)
+    for il in range(cfg.n_layer):
+        names = ("attn_norm", "post_norm", "ffn_gate", "ffn_up", "ffn_down") + (
+            ("qkv", "gate", "conv", "dt", "a", "beta", "alpha", "ssm_norm", "ssm_out") if cfg.is_recurrent(il) else ("q", "k", "v", "o", "q_norm", "k_norm"))
+        for n in names:
+            m.set(n, make(n), il)
+    for n in ("tok_embd", "output_norm", "output"):
+        m.set(n, make(n))
+    if with_mtp:
+        for n in shapes:
+            if n.startswith("mtp_"):
+                m.set(n, make(n))
+    for w in {cfg.n_embd, cfg.ssm_inner, cfg.n_head * cfg.head_dim, cfg.n_ff}:
+        m.set_signs(np.where(rng.integers(0, 2, w) == 1, 1.0, -1.0).astype(np.float32))
+    return m
+
+
+def oracle_model_from_engine(orc, eng, with_mtp):
+    """Builds the oracle's host-memory model from an engine's device weights (read back through the C ABI)."""
+    from irontimber_b200 import engine as E
+    cfg = orc.ModelConfig.from_buffer_copy(bytes(eng.cfg))
+    m = orc.Model(cfg)
+    for il in range(cfg.n_layer):
+        for n in E.COMMON_TENSORS + (E.GDN_TENSORS if cfg.is_recurrent(il) else E.ATTN_TENSORS):
+            m.set(n, eng.tensor(n, il), il)
+    for n in E.GLOBAL_TENSORS + (E.MTP_TENSORS if with_mtp else ()):
+        m.set(n, eng.tensor(n))
+    for w in {cfg.n_embd, cfg.ssm_inner, cfg.n_head * cfg.head_dim, cfg.n_ff}:
+        m.set_signs(eng.signs(w))
+    return m
