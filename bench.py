@@ -1,15 +1,21 @@
-"""Benchmark of the ternary hot path on B200.
+"""Benchmark of the ternary hot path on B200: greedy decode of the 27B-shape ternary decoder.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--prompt P] [--layers L]
 
-Workload (config 1 of the baseline): the PQ2_0 ternary matvec K=5120 -> N=17408, batch 1, on q8k
-activations; synthetic weights (codes uniform over {-1,0,+1}, f16 scales in [0.01,0.05]) and an
-N(0,1) activation vector, all seeded.  One step = one sweep of `matvec_t2` over 12 distinct weight
-matrices (285 MB, larger than the 126 MB L2, so every launch reads its weights from HBM).
+Workload (config 2 of the baseline): the 64-layer random-init ternary decoder with the reference architecture
+(48 gated-delta-net + 16 attention layers, n_embd 5120, n_ff 17408, vocab 248320, f16 KV), batch 1, greedy decode
+after a prompt of P = 512 uniform-random token ids.  One step = one decoded token = one replay of the engine's
+recorded step (about 1,300 kernel launches, 401 of them ternary matvecs streaming 6.8 GB of weights - far more
+than the 126 MB L2, so every step reads its weights from HBM).
 
-`value` is the algorithmic GB/s of the sweep with everything resident in HBM, timed with CUDA
-events on the library's stream.  `e2e` is the same metric through the public call sequence with
-host buffers: pinned-host activation -> device, Hadamard + q8k, matvec, result row -> host.
+`value`: decode tokens/s with everything resident and no read-back between steps, timed with CUDA events on the
+library's stream.  `e2e`: the same through the public call `it_engine_generate`, which takes the token ids from
+host memory and reads every pick back to the host (4 bytes per token), timed on the host clock.
+`roofline`: the dominant kernel, `k_matvec_t2`, timed alone on the baseline's config 1 (K=5120 -> N=17408, batch 1)
+as a sweep over 12 distinct weight matrices (285 MB), against the measured HBM copy bandwidth.
+`cpu_baseline` / `--impl reference`: the reference's CPU path (C++ port of src/cpu.rs forward_token, reference
+order, all host threads) on a truncated stack, extrapolated to the full depth; the sample is stated.
+With N > 1 every GPU runs an independent replica of the decode (weak scaling, no collective).
 """
 import argparse
 import json
@@ -24,15 +30,27 @@ if ROOT not in sys.path:
 
 ROWS, COLS = 17408, 5120
 N_WEIGHTS = 12
-METRIC = "matvec_t2_hbm_gbs"
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_t2 launch on this workload, from the ncu capture
+METRIC = "decode_tok_s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_t2 launch on config 1, from the ncu capture
 # summarised in profiles/matvec_t2_config1_K5120_N17408.md
 NCU_DRAM_BYTES_PER_LAUNCH = 23698944
+CPU_LAYERS = 4      # layers of the truncated stack the CPU arm runs
 
 
 def algorithmic_bytes(rows, cols, ntok=1, accum=False):
     """rows*cols/128*34 (codes + f16 scales) + ntok*(cols + 4*cols/256) (q8 row + scales) + 4*ntok*rows (output)."""
     return rows * cols // 128 * 34 + ntok * (cols + 4 * cols // 256) + 4 * ntok * rows * (2 if accum else 1)
+
+
+def step_weight_bytes(cfg):
+    """PQ2_0 bytes of every ternary matrix one decoded token streams (shapes of src/cpu.rs:97-111)."""
+    e, ff, hd, nh, nkv = cfg.n_embd, cfg.n_ff, cfg.head_dim, cfg.n_head, cfg.n_head_kv
+    cd = 2 * cfg.ssm_state * cfg.ssm_groups + cfg.ssm_inner
+    gdn = cd * e + cfg.ssm_inner * e + e * cfg.ssm_inner
+    att = 2 * nh * hd * e + 2 * nkv * hd * e + e * nh * hd
+    n_att = sum(1 for il in range(cfg.n_layer) if not cfg.is_recurrent(il))
+    weights = (cfg.n_layer - n_att) * gdn + n_att * att + cfg.n_layer * 3 * ff * e + cfg.n_vocab * e
+    return weights // 128 * 34
 
 
 class ClockSampler:
@@ -89,97 +107,153 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
-def cpu_arm(steps, warmup, as_reference):
-    """The reference's CPU path (cpu::matvec, Numerics::Ggml) restated in C++, all host threads."""
+def cpu_decode_tok_s(n_layer_full, steps):
+    """Reference CPU forward_token (oracle, reference order) on a CPU_LAYERS-deep stack of the 27B shapes with
+    numpy-random weights; the per-layer time is extrapolated to the full depth, the LM head is timed once."""
     import numpy as np
     from oracle import orc
-    from tests.util import synth_pq2
-    raw = synth_pq2(1, ROWS, COLS)
-    x = np.random.default_rng(0).standard_normal(COLS).astype(np.float32)
-    nthreads = orc.max_threads()
-    for _ in range(max(warmup, 1)):
-        orc.matvec_ternary(raw, ROWS, COLS, x, nthreads=nthreads)
-    t0 = time.perf_counter()
-    n = 0
-    while n < steps and (as_reference or time.perf_counter() - t0 < 10.0):
-        orc.matvec_ternary(raw, ROWS, COLS, x, nthreads=nthreads)
-        n += 1
-    dt = (time.perf_counter() - t0) / n
-    gbs = algorithmic_bytes(ROWS, COLS) / dt / 1e9
-    return {"value": gbs, "unit": "GB/s", "cores": nthreads, "kind": "port",
-            "sample": f"{n} calls of the {ROWS}x{COLS} matvec incl. q8k quantisation, {dt * 1e3:.2f} ms each"}, dt
+    from tests.util import make_pq2, tensor_shapes
+    from irontimber_b200.engine import config_27b
+    cfg = orc.ModelConfig.from_buffer_copy(bytes(config_27b(n_layer=CPU_LAYERS, ctx_len=64)))
+    rng = np.random.default_rng(0)
+    m = orc.Model(cfg, nthreads=orc.max_threads())
+    shapes = tensor_shapes(cfg)
+    cache = {}
+
+    def make(name):
+        kind, r, c = shapes[name]
+        if kind == "pq2":
+            if (r, c) not in cache:      # one random matrix per shape is enough for timing
+                cache[(r, c)] = make_pq2(rng, r, c)[0]
+            return cache[(r, c)]
+        lo, hi = {"conv": (-0.5, 0.5), "dt": (-0.5, 0.5), "a": (-1.1, -0.1), "beta": (-0.05, 0.05), "alpha": (-0.05, 0.05)}.get(name, (0.9, 1.1))
+        return rng.uniform(lo, hi, r * c).astype(np.float32)
+    for il in range(cfg.n_layer):
+        names = ("attn_norm", "post_norm", "ffn_gate", "ffn_up", "ffn_down") + (
+            ("qkv", "gate", "conv", "dt", "a", "beta", "alpha", "ssm_norm", "ssm_out") if cfg.is_recurrent(il) else ("q", "k", "v", "o", "q_norm", "k_norm"))
+        for n in names:
+            m.set(n, make(n), il)
+    m.set("tok_embd", rng.uniform(-1, 1, 64 * cfg.n_embd).astype(np.float32))          # token ids < 64 only
+    m.set("output_norm", make("output_norm")); m.set("output", make("output"))
+    for w in {cfg.n_embd, cfg.ssm_inner, cfg.n_head * cfg.head_dim, cfg.n_ff}:
+        m.set_signs(np.where(rng.integers(0, 2, w) == 1, 1.0, -1.0).astype(np.float32))
+    st = m.new_state()
+    m.forward_token(st, 1, True)                                                         # warm-up
+    t0 = time.perf_counter(); n = 0
+    while n < steps and (n < 2 or time.perf_counter() - t0 < 15.0):
+        m.forward_token(st, 2 + n % 60, False); n += 1
+    t_layers = (time.perf_counter() - t0) / n
+    t0 = time.perf_counter(); m.forward_token(st, 3, True); t_with_head = time.perf_counter() - t0
+    t_head = max(t_with_head - t_layers, 0.0)
+    t_full = t_layers * n_layer_full / CPU_LAYERS + t_head
+    m.close()
+    return {"value": 1.0 / t_full, "unit": "tok/s", "cores": orc.max_threads(), "kind": "port",
+            "sample": f"{n} tokens through a {CPU_LAYERS}-layer stack of the 27B shapes ({t_layers * 1e3:.0f} ms per token) + one LM head ({t_head * 1e3:.0f} ms); "
+                      f"extrapolated to {n_layer_full} layers: {t_full:.2f} s per token"}, t_full
+
+
+def matvec_roofline(torch, local_rank, steps):
+    """The dominant kernel alone: replayed sweep of k_matvec_t2 over 12 distinct 17408x5120 matrices."""
+    import numpy as np
+    from irontimber_b200.backend import CudaBackend
+    be = CudaBackend(local_rank, arena_floats=1 << 20)
+    stream = torch.cuda.ExternalStream(be.stream, device=f"cuda:{local_rank}")
+    mats = [be.mat_synth(1000 + i, ROWS, COLS) for i in range(N_WEIGHTS)]
+    rng = np.random.default_rng(0)
+    be.set_signs(np.where(rng.integers(0, 2, COLS) == 1, 1.0, -1.0).astype(np.float32))
+    q = be.q8_rows(COLS, 1)
+    be.upload(0, rng.standard_normal(COLS).astype(np.float32))
+    be.had_q8(COLS, 1, 0, COLS, q)
+    be.capture_begin()
+    for m in mats:
+        be.mv(m, 1, q, 8192, ROWS)
+    graph = be.capture_end()
+    for _ in range(5):
+        be.graph_launch(graph)
+    be.sync()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(steps):
+        be.graph_launch(graph)
+    ev1.record(stream)
+    be.sync(); torch.cuda.synchronize()
+    per_launch = ev0.elapsed_time(ev1) / 1e3 / (steps * N_WEIGHTS)
+    be.graph_destroy(graph)
+    for m in mats:
+        m.close()
+    q.close(); be.close()
+    abytes = algorithmic_bytes(ROWS, COLS)
+    peak, kind = measured_peak()
+    ach = abytes / per_launch / 1e9
+    return {"bound": "hbm", "kernel": "k_matvec_t2<1> alone on config 1 (K=5120, N=17408, batch 1), sweep of 12 matrices (285 MB > L2)",
+            "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind,
+            "algorithmic_bytes_per_launch": abytes, "us_per_launch": per_launch * 1e6, "traffic": NCU_DRAM_BYTES_PER_LAUNCH}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=64)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": f"config1: PQ2_0 ternary matvec K={COLS} N={ROWS} batch 1 on q8k activations", "rows": ROWS, "cols": COLS,
-              "l2": f"inputs larger than L2: sweep over {N_WEIGHTS} distinct weight matrices ({N_WEIGHTS * algorithmic_bytes(ROWS, COLS) // 1000000} MB)",
-              "launches_per_step": N_WEIGHTS, "sharding": "independent replicas of the sweep per GPU (rows of one matrix are not split at this size)"}
+    warmup = max(args.warmup, 3)
+    from irontimber_b200.engine import config_27b
+    cfg = config_27b(n_layer=args.layers)
+    config = {"workload": f"config2: {args.layers}-layer 27B-shape ternary decoder (3 delta-net layers per attention layer), batch 1, greedy decode "
+                          f"after a {args.prompt}-token random prompt, f16 KV, ctx 8192",
+              "prompt_tokens": args.prompt, "weights_bytes_per_token": step_weight_bytes(cfg),
+              "l2": "inputs larger than L2: every step streams its weights (6.8 GB at 64 layers) from HBM; L2 is 126 MB",
+              "sharding": "independent replica per GPU (weak scaling), no collective"}
+    base = {"metric": METRIC, "unit": "tok/s", "n_gpus": world if args.impl != "reference" else args.gpus, "steps": args.steps, "warmup": warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x 2-bit codes -> int32, f32 epilogue", "data": "synthetic", "config": config}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        cb, dt = cpu_arm(max(args.steps, 1), max(args.warmup, 1), True)
-        print(json.dumps({"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-                          "warmup": args.warmup, "ms_per_step": dt * 1e3 * N_WEIGHTS, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                          "dtype": "int8 x 2-bit codes -> int32, f32 epilogue", "data": "synthetic", "config": config, "cpu_baseline": cb,
-                          "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        cb, t_full = cpu_decode_tok_s(args.layers, max(args.steps, 2))
+        print(json.dumps(dict(base, impl="reference", value=cb["value"], ms_per_step=t_full * 1e3, cpu_baseline=cb,
+                              e2e={"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})))
         return
 
     import numpy as np
     import torch
-    from irontimber_b200.backend import CudaBackend
+    from irontimber_b200 import _lib
+    from irontimber_b200.engine import CudaEngine
 
     dist = None
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    be = CudaBackend(local_rank, arena_floats=1 << 22)
-    stream = torch.cuda.ExternalStream(be.stream, device=f"cuda:{local_rank}")
-    mats = [be.mat_synth(1000 + 17 * rank + i, ROWS, COLS) for i in range(N_WEIGHTS)]
-    rng = np.random.default_rng(rank)
-    x = rng.standard_normal(COLS).astype(np.float32)
-    signs = np.where(rng.integers(0, 2, COLS) == 1, 1.0, -1.0).astype(np.float32)
-    be.set_signs(signs)
-    q = be.q8_rows(COLS, 1)
-    XO, YO = 0, 8192
-    be.upload(XO, x)
-    be.had_q8(COLS, 1, XO, COLS, q)
-
-    def sweep():
-        for m in mats:
-            be.mv(m, 1, q, YO, ROWS)
+    eng = CudaEngine(cfg, seed=7 + rank, with_mtp=False, device=local_rank)
+    L = _lib.load()
+    ctx = L.it_engine_ctx(eng.h)
+    stream = torch.cuda.ExternalStream(L.it_ctx_stream(ctx), device=f"cuda:{local_rank}")
+    rng = np.random.default_rng(100 + rank)
+    prompt = rng.integers(0, cfg.n_vocab, args.prompt).tolist()
 
     def barrier():
-        be.sync()
+        _lib.check(L.it_sync(ctx))
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # one step = one replay of a recorded sweep (the launches are queued on the device, so the host
-    # launch path is not what is timed)
-    be.capture_begin()
-    sweep()
-    graph = be.capture_end()
-    for _ in range(max(args.warmup, 3)):
-        be.graph_launch(graph)
-    barrier()
+    t0 = time.perf_counter()
+    eng.eval_argmax(prompt)
+    prefill_s = time.perf_counter() - t0
+    eng.decode_steps(warmup)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
         ev0.record(stream)
-        for _ in range(args.steps):
-            be.graph_launch(graph)
+        eng.decode_steps(args.steps, read_last=False)
         ev1.record(stream)
         barrier()
     ms = ev0.elapsed_time(ev1)
@@ -187,54 +261,28 @@ def main():
         t = torch.tensor([ms], device=f"cuda:{local_rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    launches = args.steps * N_WEIGHTS
-    per_launch_s = ms / 1e3 / launches
-    abytes = algorithmic_bytes(ROWS, COLS)
-    achieved = abytes / per_launch_s / 1e9
-    peak, peak_kind = measured_peak()
-
-    # end to end through the public calls with host buffers (pinned): H2D x, had_q8, mv, D2H y
-    import ctypes as C
-    from irontimber_b200 import _lib
-    hx = torch.from_numpy(x).pin_memory()
-    hy = torch.empty(ROWS, dtype=torch.float32).pin_memory()
-    e2e_steps = max(args.steps // 4, 10)
-
-    def e2e_step(m):
-        _lib.check(be.L.it_arena_write(be.ctx, XO, C.c_void_p(hx.data_ptr()), COLS))
-        be.had_q8(COLS, 1, XO, COLS, q)
-        be.mv(m, 1, q, YO, ROWS)
-        _lib.check(be.L.it_arena_read(be.ctx, YO, C.c_void_p(hy.data_ptr()), ROWS))
-    for i in range(5):
-        e2e_step(mats[i % N_WEIGHTS])
+    # end to end through the public generate call: token ids from host memory, every pick read back (4 bytes)
+    eng.reset()
+    first = eng.eval_argmax(prompt)
     barrier()
     t0 = time.perf_counter()
-    for i in range(e2e_steps * N_WEIGHTS):
-        e2e_step(mats[i % N_WEIGHTS])
-    barrier()
-    e2e_s = (time.perf_counter() - t0) / (e2e_steps * N_WEIGHTS)
+    hist = eng.generate([first], args.steps)
+    e2e_s = time.perf_counter() - t0
+    assert len(hist) == args.steps
     if dist:
         t = torch.tensor([e2e_s], device=f"cuda:{local_rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-
-    out = {"metric": METRIC, "value": achieved * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-           "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-           "dtype": "int8 x 2-bit codes -> int32, f32 epilogue", "data": "synthetic", "config": config,
-           "clocks": clocks.summary(), "gpu_launches": launches,
-           "e2e": {"value": abytes / e2e_s / 1e9 * world, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4 * N_WEIGHTS, "d2h_bytes_per_step": ROWS * 4 * N_WEIGHTS,
-                   "us_per_call": e2e_s * 1e6},
-           "roofline": {"bound": "hbm", "kernel": "k_matvec_t2<1>", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                        "peak_kind": peak_kind, "algorithmic_bytes_per_launch": abytes, "us_per_launch": per_launch_s * 1e6, "traffic": NCU_DRAM_BYTES_PER_LAUNCH}}
+    n_kernels = 3 + sum(20 if cfg.is_recurrent(il) else 23 for il in range(cfg.n_layer)) + 4
+    eng.close()
+    out = dict(base, value=world * args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * n_kernels,
+               e2e={"value": world * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "ms_per_token": e2e_s / args.steps * 1e3},
+               prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 8},
+               step_weight_gbs=step_weight_bytes(cfg) * args.steps / (ms / 1e3) / 1e9)
+    out["roofline"] = matvec_roofline(torch, local_rank, 200)
     if rank == 0:
-        cb, _ = cpu_arm(10 ** 9, 1, False)
-        out["cpu_baseline"] = cb
+        out["cpu_baseline"] = cpu_decode_tok_s(args.layers, 8)[0]
         print(json.dumps(out))
-    be.graph_destroy(graph)
-    for m in mats:
-        m.close()
-    q.close()
-    be.close()
     if dist:
         dist.destroy_process_group()
 

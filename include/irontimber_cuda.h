@@ -179,6 +179,10 @@ int it_engine_reset(it_engine* e);
  * unless eos is UINT32_MAX).  The decode steps run as one recorded graph per token. */
 int it_engine_generate(it_engine* e, const uint32_t* prompt, size_t n_prompt, size_t n_predict, uint32_t eos, uint32_t* out, size_t* n_out);
 
+/* n more greedy steps chained on the device (the pick of a step is the next step's token) without reading anything back
+ * in between; continues from the last pick.  Used to time decoding with everything resident; last_pick may be NULL. */
+int it_engine_decode_steps(it_engine* e, size_t n, uint32_t* last_pick);
+
 /* MtpBackend trait (src/mtp.rs:150-163), one to one. */
 int it_engine_mtp_prefill(it_engine* e, const uint32_t* prompt, size_t n, uint32_t* next);
 int it_engine_mtp_single(it_engine* e, uint32_t x, uint32_t* next);

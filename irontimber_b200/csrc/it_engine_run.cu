@@ -166,6 +166,25 @@ IT_API int it_engine_eval_argmax(it_engine* e, const uint32_t* toks, size_t n, u
     return read_pick(e, 0, next);
 }
 
+namespace {
+// Publishes the host's position to the device and records the single-token greedy step once: pick -> token slot,
+// one pass with the position read on the device, pick -> token slot and position + 1.
+int begin_device_decode(it_engine* e) {
+    it_ctx* cx = e->ctx;
+    e->host_pin[16] = (uint32_t)e->pos;
+    IT_CUDA(cudaMemcpyAsync(e->pos_dev, e->host_pin + 16, 4, cudaMemcpyHostToDevice, cx->stream));
+    if (e->step_graph) return IT_OK;
+    IT_TRY(it_capture_begin(cx));
+    k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 0);
+    int r = it_engine_run_chunk(e, nullptr, 1, 1, 0, true);
+    k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 1);
+    it_graph* g = nullptr; int r2 = it_capture_end(cx, &g);
+    if (r || r2) { if (g) it_graph_destroy(g); return r ? r : r2; }
+    e->step_graph = g;
+    return IT_OK;
+}
+}  // namespace
+
 // generate_inner, greedy (src/engine.rs:151-174).  After the prompt, every step replays one recorded graph: the pick of
 // the previous step is moved into the token slot on the device and the position is read from device memory, so the host
 // only reads 4 bytes per token.
@@ -178,25 +197,26 @@ IT_API int it_engine_generate(it_engine* e, const uint32_t* prompt, size_t n_pro
     uint32_t t = 0; IT_TRY(read_pick(e, 0, &t));
     out[(*n_out)++] = t;
     if (t == eos || *n_out == n_predict) return IT_OK;
-    it_ctx* cx = e->ctx;
-    e->host_pin[16] = (uint32_t)e->pos;
-    IT_CUDA(cudaMemcpyAsync(e->pos_dev, e->host_pin + 16, 4, cudaMemcpyHostToDevice, cx->stream));
-    if (!e->step_graph) {
-        IT_TRY(it_capture_begin(cx));
-        k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 0);
-        int r = it_engine_run_chunk(e, nullptr, 1, 1, 0, true);
-        k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 1);
-        it_graph* g = nullptr; int r2 = it_capture_end(cx, &g);
-        if (r || r2) { if (g) it_graph_destroy(g); return r ? r : r2; }
-        e->step_graph = g;
-    }
+    IT_TRY(begin_device_decode(e));
     while (*n_out < n_predict) {
-        IT_TRY(it_graph_launch(cx, e->step_graph));
+        IT_TRY(it_graph_launch(e->ctx, e->step_graph));
         e->pos += 1;
         IT_TRY(read_pick(e, 0, &t));
         out[(*n_out)++] = t;
         if (t == eos) break;
     }
+    return IT_OK;
+}
+
+// n greedy steps chained on the device with no read-back in between: the pick of each step feeds the next one.  Continues
+// from the pick left in place by the previous eval_argmax / generate / decode_steps call.  last_pick may be null.
+IT_API int it_engine_decode_steps(it_engine* e, size_t n, uint32_t* last_pick) {
+    IT_CHECK_ARG(e, "it_engine_decode_steps: null engine");
+    if (e->pos < 1) return it_fail(IT_ESTATE, "it_engine_decode_steps: nothing has been evaluated yet");
+    if (e->pos + (long long)n > e->cfg.ctx_len) return it_fail(IT_ESTATE, "it_engine_decode_steps: context full");
+    IT_TRY(begin_device_decode(e));
+    for (size_t i = 0; i < n; i++) { IT_TRY(it_graph_launch(e->ctx, e->step_graph)); e->pos += 1; }
+    if (last_pick) return read_pick(e, 0, last_pick);
     return IT_OK;
 }
 

@@ -96,6 +96,11 @@ class CudaEngine:
         _lib.check(self.L.it_engine_generate(self.h, _p(p), p.size, n_predict, eos, _p(out), C.byref(n)))
         return [int(t) for t in out[:n.value]]
 
+    def decode_steps(self, n, read_last=True):
+        out = C.c_uint32()
+        _lib.check(self.L.it_engine_decode_steps(self.h, n, C.byref(out) if read_last else None))
+        return out.value if read_last else None
+
     # ---- MtpBackend --------------------------------------------------------------------------------
     def mtp_prefill(self, prompt):
         p = _u32(prompt); out = C.c_uint32()
