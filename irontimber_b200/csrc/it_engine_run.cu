@@ -53,8 +53,7 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
         if (l.recurrent) {
             IT_TRY(had_mv(e, l.qkv, nt, L.xn, e_, L.big1, cd, 0, true));
             IT_TRY(had_mv(e, l.gate, nt, L.xn, e_, L.big2, inner, 0, false));
-            IT_TRY(it_sup_dense_rows(cx, l.beta, nv, e_, A + L.xn, e_, A + L.beta, nv, nt));
-            IT_TRY(it_sup_dense_rows(cx, l.alpha, nv, e_, A + L.xn, e_, A + L.alpha, nv, nt));
+            IT_TRY(it_sup_dense_rows(cx, l.beta, l.alpha, nv, e_, A + L.xn, e_, A + L.beta, A + L.alpha, nv, nt));
             const size_t csz = (size_t)(c.conv_k - 1) * cd, ssz = (size_t)nv * sd * sd;
             IT_TRY(it_sup_conv(cx, A + L.big1, cd, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, nt, l.ck_conv, csz, nck));
             IT_TRY(it_sup_norm_head(cx, A + L.conv, sd, cd, A + L.conv, sd, cd, sd, 2 * nk, nullptr, 2, c.eps, nullptr, 0, 0, nt));

@@ -24,8 +24,12 @@ __global__ void k_embed(const uint32_t* __restrict__ toks, const float* __restri
 __global__ void __launch_bounds__(256) k_rmsnorm_wide(const float* x, size_t x_stride, const float* __restrict__ w, int n, float eps, float* out, size_t out_stride) {
     __shared__ float wsum[8];
     const float* xr = x + blockIdx.x * x_stride; float* o = out + blockIdx.x * out_stride;
+    float v[32];                                   // n <= 8192: all loads are issued before the first add
+#pragma unroll
+    for (int k = 0; k < 32; k++) { const int j = threadIdx.x + 256 * k; v[k] = j < n ? xr[j] : 0.f; }
     float s = 0.f;
-    for (int j = threadIdx.x; j < n; j += 256) s = it_add(s, it_mul(xr[j], xr[j]));
+#pragma unroll
+    for (int k = 0; k < 32; k++) if (threadIdx.x + 256 * k < n) s = it_add(s, it_mul(v[k], v[k]));
 #pragma unroll
     for (int m = 16; m >= 1; m >>= 1) s = it_add(s, __shfl_xor_sync(0xffffffffu, s, m));
     if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = s;
@@ -34,7 +38,8 @@ __global__ void __launch_bounds__(256) k_rmsnorm_wide(const float* x, size_t x_s
 #pragma unroll
     for (int k = 1; k < 8; k++) t = it_add(t, wsum[k]);
     const float sc = it_div(1.0f, it_sqrt(it_add(it_div(t, (float)n), eps)));
-    for (int j = threadIdx.x; j < n; j += 256) o[j] = it_mul(it_mul(xr[j], sc), w[j]);
+#pragma unroll
+    for (int k = 0; k < 32; k++) { const int j = threadIdx.x + 256 * k; if (j < n) o[j] = it_mul(it_mul(v[k], sc), w[j]); }
 }
 
 // Per-head norms of width n <= 256, one warp per (head, row), the squares added sequentially as on the CPU.
@@ -105,53 +110,70 @@ __global__ void k_conv(const float* mixed, size_t m_ts, const float* __restrict_
 }
 
 // Dense f32 rows (ssm_beta / ssm_alpha; cpu::matvec's f32 arm under Numerics::Ggml, src/cpu.rs:36-43: f32 products,
-// f64 accumulation).  One warp per row: lane l adds the products i = l, l+32, ... in f64, then a butterfly.
-__global__ void k_dense_rows(const float* __restrict__ w, int rows, int cols, const float* x, size_t x_ts, float* y, size_t y_ts) {
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31, t = blockIdx.y;
-    if (row >= rows) return;
-    const float* wr = w + (size_t)row * cols; const float* xr = x + t * x_ts;
+// f64 accumulation).  One CTA of 256 threads per row: thread i adds the products i, i+256, ... in f64, each warp folds
+// with a butterfly, the eight warp sums are added in ascending order.  Rows [0, rows) use w0 / y0, rows [rows, 2 rows) w1 / y1.
+__global__ void __launch_bounds__(256) k_dense_rows(const float* __restrict__ w0, const float* __restrict__ w1, int rows, int cols, const float* x, size_t x_ts,
+                                                    float* y0, float* y1, size_t y_ts) {
+    __shared__ double wsum[8];
+    const int r = blockIdx.x, t = blockIdx.y, row = r < rows ? r : r - rows;
+    const float* wr = (r < rows ? w0 : w1) + (size_t)row * cols; const float* xr = x + t * x_ts;
     double s = 0.0;
-    for (int i = lane; i < cols; i += 32) s += (double)it_mul(wr[i], xr[i]);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < cols; i += 256) s += (double)it_mul(wr[i], xr[i]);
 #pragma unroll
     for (int m = 16; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-    if (lane == 0) y[t * y_ts + row] = (float)s;
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double tt = wsum[0];
+        for (int k = 1; k < 8; k++) tt += wsum[k];
+        (r < rows ? y0 : y1)[t * y_ts + row] = (float)tt;
+    }
 }
 
-// Gated delta rule, token after token (src/cpu.rs:215-232).  One warp per 32 rows of a head's state matrix; every
-// row is updated by one thread with the CPU's two sequential passes.  The tile goes through shared memory so that
+// Gated delta rule, token after token (src/cpu.rs:215-232).  One CTA per 32 rows of a head's state matrix; every
+// row is updated by one thread with the CPU's two sequential passes, all threads move the tile.  The tile goes through shared memory so that
 // global accesses stay coalesced.  State layout [head][j][i] as on the CPU (src/cpu.rs:132).
-__global__ void __launch_bounds__(32) k_gdn(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
-                                            float* state, float* o, size_t o_ts, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
+__global__ void __launch_bounds__(128) k_gdn(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
+                                             float* state, float* o, size_t o_ts, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
     extern __shared__ float tile[];            // [32][sd + 1] rows, then q[sd], k[sd]
-    const int h = blockIdx.x, j0 = blockIdx.y * 32, lane = threadIdx.x, kh = h % nk, ld = sd + 1;
+    const int h = blockIdx.x, j0 = blockIdx.y * 32, tid = threadIdx.x, kh = h % nk, ld = sd + 1, nvec = 32 * sd / 4;
     float* qs = tile + 32 * ld; float* ks = qs + sd;
     float* m = state + ((size_t)h * sd + j0) * sd;
-    for (int r = 0; r < 32; r++) for (int i = lane; i < sd; i += 32) tile[r * ld + i] = m[(size_t)r * sd + i];
-    float* row = tile + lane * ld;
+    auto tile_in = [&](const float* src) {     // all 128 threads, 128-bit loads, every load in flight at once
+        for (int f = tid; f < nvec; f += 128) { const float4 v = reinterpret_cast<const float4*>(src)[f]; const int r = (4 * f) / sd, i = (4 * f) % sd;
+            float* d = tile + r * ld + i; d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w; }
+    };
+    auto tile_out = [&](float* dst) {
+        for (int f = tid; f < nvec; f += 128) { const int r = (4 * f) / sd, i = (4 * f) % sd; const float* d = tile + r * ld + i;
+            reinterpret_cast<float4*>(dst)[f] = make_float4(d[0], d[1], d[2], d[3]); }
+    };
+    tile_in(m);
+    float* row = tile + tid * ld;               // threads 0..31 own one row each
     const float scale = it_div(1.0f, it_sqrt((float)sd));
     for (int t = 0; t < nt; t++) {
         const float* c = co + t * co_ts;
-        __syncwarp();
-        for (int i = lane; i < sd; i += 32) { qs[i] = c[kh * sd + i]; ks[i] = c[qk + kh * sd + i]; }
-        __syncwarp();
-        const float v = c[2 * qk + h * sd + j0 + lane];
-        const float bt = it_sigmoid(beta[t * ba_ts + h]);
-        const float g = it_mul(it_softplus(it_add(alpha[t * ba_ts + h], dt[h])), a[h]);
-        const float eg = it_expf(g);
-        float s = 0.f;
-        for (int i = 0; i < sd; i++) { const float r = it_mul(row[i], eg); row[i] = r; s = it_add(s, it_mul(r, ks[i])); }
-        const float delta = it_mul(it_sub(v, s), bt);
-        float acc = 0.f;
-        for (int i = 0; i < sd; i++) { const float r = it_add(row[i], it_mul(ks[i], delta)); row[i] = r; acc = it_add(acc, it_mul(r, qs[i])); }
-        o[t * o_ts + h * sd + j0 + lane] = it_mul(acc, scale);
-        if (t < nck) {
-            __syncwarp();
-            float* cm = ck + t * ck_stride + ((size_t)h * sd + j0) * sd;
-            for (int r = 0; r < 32; r++) for (int i = lane; i < sd; i += 32) cm[(size_t)r * sd + i] = tile[r * ld + i];
+        __syncthreads();
+        for (int i = tid; i < sd; i += 128) { qs[i] = c[kh * sd + i]; ks[i] = c[qk + kh * sd + i]; }
+        __syncthreads();
+        if (tid < 32) {
+            const float v = c[2 * qk + h * sd + j0 + tid];
+            const float bt = it_sigmoid(beta[t * ba_ts + h]);
+            const float g = it_mul(it_softplus(it_add(alpha[t * ba_ts + h], dt[h])), a[h]);
+            const float eg = it_expf(g);
+            float s = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < sd; i++) { const float r = it_mul(row[i], eg); row[i] = r; s = it_add(s, it_mul(r, ks[i])); }
+            const float delta = it_mul(it_sub(v, s), bt);
+            float acc = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < sd; i++) { const float r = it_add(row[i], it_mul(ks[i], delta)); row[i] = r; acc = it_add(acc, it_mul(r, qs[i])); }
+            o[t * o_ts + h * sd + j0 + tid] = it_mul(acc, scale);
         }
+        if (t < nck) { __syncthreads(); tile_out(ck + t * ck_stride + ((size_t)h * sd + j0) * sd); }
     }
-    __syncwarp();
-    for (int r = 0; r < 32; r++) for (int i = lane; i < sd; i += 32) m[(size_t)r * sd + i] = tile[r * ld + i];
+    __syncthreads();
+    tile_out(m);
 }
 
 // act = silu(g) * u (src/cpu.rs:183)
@@ -247,14 +269,14 @@ int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, floa
     if (kk < 2 || kk > 9) return it_fail(IT_EINVAL, "conv kernel size %d not supported", kk);
     it_note_op(c); k_conv<<<(cd + 127) / 128, 128, 0, c->stream>>>(mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
 }
-int it_sup_dense_rows(it_ctx* c, const float* w, int rows, int cols, const float* x, size_t x_ts, float* y, size_t y_ts, int nt) {
-    it_note_op(c); k_dense_rows<<<dim3((rows + 3) / 4, nt), 128, 0, c->stream>>>(w, rows, cols, x, x_ts, y, y_ts); KCHK("dense_rows"); return IT_OK;
+int it_sup_dense_rows(it_ctx* c, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts, float* y0, float* y1, size_t y_ts, int nt) {
+    it_note_op(c); k_dense_rows<<<dim3(2 * rows, nt), 256, 0, c->stream>>>(w0, w1, rows, cols, x, x_ts, y0, y1, y_ts); KCHK("dense_rows"); return IT_OK;
 }
 int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
     if (sd % 32 != 0) return it_fail(IT_EINVAL, "ssm state size %d is not a multiple of 32", sd);
     it_note_op(c); const size_t smem = (32 * (sd + 1) + 2 * sd) * sizeof(float);
-    k_gdn<<<dim3(nv, sd / 32), 32, smem, c->stream>>>(co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck); KCHK("gdn"); return IT_OK;
+    k_gdn<<<dim3(nv, sd / 32), 128, smem, c->stream>>>(co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck); KCHK("gdn"); return IT_OK;
 }
 int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n) {
     it_note_op(c); k_silu_mul<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(g, u, out, n); KCHK("silu_mul"); return IT_OK;

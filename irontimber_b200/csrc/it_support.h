@@ -8,7 +8,7 @@ int it_sup_norm_head(it_ctx* c, const float* in, size_t in_hs, size_t in_ts, flo
                      const float* z, size_t z_hs, size_t z_ts, int nt);
 int it_sup_rope(it_ctx* c, float* x, size_t hs, size_t ts, int nheads, int nt, int pos0, const int* pos_ptr, int n_rot, float theta_scale, const int* sections);
 int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, float* state, float* out, size_t o_ts, int cd, int kk, int nt, float* ck, size_t ck_stride, int nck);
-int it_sup_dense_rows(it_ctx* c, const float* w, int rows, int cols, const float* x, size_t x_ts, float* y, size_t y_ts, int nt);
+int it_sup_dense_rows(it_ctx* c, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts, float* y0, float* y1, size_t y_ts, int nt);
 int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck);
 int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n);

@@ -126,10 +126,11 @@ void dense_matvec(const float* w, int rows, int cols, const float* x, float* y, 
     for (int r = 0; r < rows; r++) {
         const float* row = w + (size_t)r * cols;
         if (!mode) { double s = 0; for (int i = 0; i < cols; i++) s += (double)(row[i] * x[i]); y[r] = (float)s; continue; }
-        double p[32];
-        for (int l = 0; l < 32; l++) { double s = 0; for (int i = l; i < cols; i += 32) s += (double)it_mul(row[i], x[i]); p[l] = s; }
-        for (int mm = 16; mm >= 1; mm >>= 1) { double q[32]; for (int l = 0; l < 32; l++) q[l] = p[l] + p[l ^ mm]; std::memcpy(p, q, sizeof p); }
-        y[r] = (float)p[0];
+        double p[256];   // device order: thread i of 256 adds the products i, i+256, ...; warp butterflies; eight warp sums in order
+        for (int l = 0; l < 256; l++) { double s = 0; for (int i = l; i < cols; i += 256) s += (double)it_mul(row[i], x[i]); p[l] = s; }
+        for (int mm = 16; mm >= 1; mm >>= 1) { double q[256]; for (int l = 0; l < 256; l++) q[l] = p[l] + p[l ^ mm]; std::memcpy(p, q, sizeof p); }
+        double t = p[0]; for (int w = 1; w < 8; w++) t += p[32 * w];
+        y[r] = (float)t;
     }
 }
 // Int8-group rows of the MTP head on raw Q8_0 blocks.  Reference order: Q8G16::dot (src/quant.rs:266-270).  Device order:
