@@ -253,7 +253,7 @@ static int mat_alloc(it_ctx* c, size_t rows, size_t cols, it_mat** out, const ch
     IT_CHECK_ARG(rows <= (1u << 30) && cols <= (1u << 24), "%s: matrix %zux%zu too large", who, rows, cols);
     IT_CUDA(cudaSetDevice(c->device));
     it_mat* m = new it_mat(); m->ctx = c; m->rows = rows; m->cols = cols; m->row_groups = (rows + 31) / 32;
-    m->bytes = m->row_groups * (cols / 128) * IT_TILE_BYTES; m->tiles = nullptr;
+    m->bytes = m->row_groups * (cols / 128) * IT_TILE_BYTES; m->tiles = nullptr; m->owns_tiles = true;
     cudaError_t e = cudaMalloc(&m->tiles, m->bytes);
     if (e != cudaSuccess) { delete m; return it_fail(IT_ENOMEM, "%s: cudaMalloc(%zu): %s", who, m->bytes, cudaGetErrorString(e)); }
     *out = m; return IT_OK;
@@ -296,6 +296,22 @@ IT_API int it_matrix_synth(it_ctx* c, uint64_t seed, size_t rows, size_t cols, i
     if (e != cudaSuccess || r != IT_OK) { it_matrix_destroy(*out); *out = nullptr; return r ? r : it_fail(e == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_matrix_synth: %s", cudaGetErrorString(e)); }
     return IT_OK;
 }
+int it_matrix_view(it_ctx* c, size_t rows, size_t cols, uint8_t* tiles, it_mat** out) {
+    IT_CHECK_ARG(c && out && tiles && rows > 0 && cols % 128 == 0, "it_matrix_view: bad argument");
+    it_mat* m = new it_mat(); m->ctx = c; m->rows = rows; m->cols = cols; m->row_groups = (rows + 31) / 32;
+    m->bytes = m->row_groups * (cols / 128) * IT_TILE_BYTES; m->tiles = tiles; m->owns_tiles = false;
+    *out = m; return IT_OK;
+}
+int it_matrix_synth_view(it_ctx* c, uint64_t seed, size_t rows, size_t cols, uint8_t* tiles, it_mat** out) {
+    int r = it_matrix_view(c, rows, cols, tiles, out); if (r) return r;
+    size_t nbytes = rows * (cols / 128) * 34; uint8_t* tmp = nullptr;
+    cudaError_t e = cudaMalloc(&tmp, nbytes);
+    if (e == cudaSuccess) { r = it_launch_synth_pq2(c, seed, rows, cols, 0, tmp); if (r == IT_OK) r = it_launch_repack_pq2(c, tmp, rows, cols, tiles);
+        if (r == IT_OK) e = cudaStreamSynchronize(c->stream); }
+    if (tmp) cudaFree(tmp);
+    if (e != cudaSuccess || r != IT_OK) { it_matrix_destroy(*out); *out = nullptr; return r ? r : it_fail(e == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_matrix_synth_view: %s", cudaGetErrorString(e)); }
+    return IT_OK;
+}
 IT_API int it_matrix_download_pq2(it_ctx* c, const it_mat* m, uint8_t* raw) {
     IT_CHECK_ARG(c && m && raw, "it_matrix_download_pq2: null argument");
     IT_CUDA(cudaSetDevice(c->device));
@@ -312,7 +328,7 @@ IT_API int it_matrix_download_pq2(it_ctx* c, const it_mat* m, uint8_t* raw) {
 IT_API size_t it_matrix_rows(const it_mat* m) { return m ? m->rows : 0; }
 IT_API size_t it_matrix_cols(const it_mat* m) { return m ? m->cols : 0; }
 IT_API size_t it_matrix_device_bytes(const it_mat* m) { return m ? m->bytes : 0; }
-IT_API void it_matrix_destroy(it_mat* m) { if (!m) return; cudaSetDevice(m->ctx->device); if (m->tiles) cudaFree(m->tiles); delete m; }
+IT_API void it_matrix_destroy(it_mat* m) { if (!m) return; cudaSetDevice(m->ctx->device); if (m->tiles && m->owns_tiles) cudaFree(m->tiles); delete m; }
 
 // ---------------------------------------------------------------- int8-group matrices
 static int qmat_alloc(it_ctx* c, size_t rows, size_t cols, it_qmat** out, const char* who) {

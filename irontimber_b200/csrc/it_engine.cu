@@ -45,6 +45,19 @@ int synth_f32(it_engine* e, int layer, int tensor, size_t n, float** out) {
 int synth_mat(it_engine* e, int layer, int tensor, size_t rows, size_t cols, it_mat** out) {
     return it_matrix_synth(e->ctx, tensor_seed(e->seed, layer, tensor), rows, cols, 0, out);
 }
+// Several ternary matrices with the same column count, stacked row-wise in one allocation: `stack` sees all rows,
+// parts[i] is a view of tensor i.  Row counts must be multiples of 32 so that every part starts on a row group.
+int synth_stack(it_engine* e, int layer, int n, const int* tensors, const size_t* rows, size_t cols, it_mat** parts, it_mat** stack) {
+    size_t total = 0; for (int i = 0; i < n; i++) { if (rows[i] % 32) return it_fail(IT_EINVAL, "engine: stacked matrix with %zu rows is not a multiple of 32", rows[i]); total += rows[i]; }
+    uint8_t* buf = nullptr;
+    IT_TRY(dev_alloc(e, (void**)&buf, total / 32 * (cols / 128) * IT_TILE_BYTES, false));
+    size_t off = 0;
+    for (int i = 0; i < n; i++) {
+        IT_TRY(it_matrix_synth_view(e->ctx, tensor_seed(e->seed, layer, tensors[i]), rows[i], cols, buf + off / 32 * (cols / 128) * IT_TILE_BYTES, &parts[i]));
+        off += rows[i];
+    }
+    return it_matrix_view(e->ctx, total, cols, buf, stack);
+}
 int synth_qmat(it_engine* e, int tensor, size_t rows, size_t cols, it_qmat** out) {
     return it_qmatrix_synth(e->ctx, tensor_seed(e->seed, -1, tensor), rows, cols, out);
 }
@@ -62,7 +75,8 @@ size_t up64(size_t n) { return (n + 63) / 64 * 64; }
 int validate(const it_model_config* c) {
     IT_CHECK_ARG(c, "it_engine_create_synth: null config");
     IT_CHECK_ARG(c->n_layer > 0 && c->n_layer <= 1024 && c->n_vocab > 0, "engine: bad layer or vocabulary count");
-    IT_CHECK_ARG(c->n_embd > 0 && c->n_embd % 1024 == 0 && c->n_ff > 0 && c->n_ff % 1024 == 0, "engine: n_embd and n_ff must be multiples of the 1024 Hadamard block");
+    IT_CHECK_ARG(c->n_embd > 0 && c->n_embd % 1024 == 0 && c->n_embd <= 8192 && c->n_ff > 0 && c->n_ff % 1024 == 0, "engine: n_embd (<= 8192) and n_ff must be multiples of the 1024 Hadamard block");
+    IT_CHECK_ARG((c->n_head_kv * c->head_dim) % 32 == 0 && c->n_ff % 32 == 0, "engine: stacked matrices need row counts that are multiples of 32");
     IT_CHECK_ARG(c->head_dim > 0 && c->head_dim <= 256 && c->head_dim % 4 == 0, "engine: head_dim must be a multiple of 4 up to 256");
     IT_CHECK_ARG(c->n_head > 0 && c->n_head_kv > 0 && c->n_head % c->n_head_kv == 0, "engine: n_head must be a multiple of n_head_kv");
     IT_CHECK_ARG((c->n_head * c->head_dim) % 1024 == 0 && (c->n_head_kv * c->head_dim) % 4 == 0, "engine: attention width must be a multiple of 1024");
@@ -93,7 +107,7 @@ IT_API int it_engine_create_synth(int device, const it_model_config* cfg, uint64
     // arena layout
     it_arena_layout& L = e->lay; size_t o = 0;
     auto take = [&](size_t& field, size_t n) { field = o; o += up64(n); };
-    L.big1_stride = (size_t)std::max(std::max(cd, qf), ff); L.big2_stride = (size_t)std::max(inner, ff);
+    L.big1_stride = (size_t)std::max(std::max(cd + inner, qf + 2 * kvd), 2 * ff); L.big2_stride = (size_t)std::max(inner, ff);
     L.o_stride = (size_t)std::max(inner, nh * hd); L.logits_stride = up64((size_t)c.n_vocab) + 64;
     take(L.x, (size_t)IT_MAXT * e_); take(L.xn, (size_t)IT_MAXT * e_); take(L.big1, IT_MAXT * L.big1_stride); take(L.big2, IT_MAXT * L.big2_stride);
     take(L.conv, (size_t)IT_MAXT * cd); take(L.kcur, (size_t)IT_MAXT * kvd); take(L.vcur, (size_t)IT_MAXT * kvd); take(L.o, IT_MAXT * L.o_stride);
@@ -112,16 +126,22 @@ IT_API int it_engine_create_synth(int device, const it_model_config* cfg, uint64
         it_layer& l = e->layers[il]; memset(&l, 0, sizeof l);
         l.recurrent = it_cfg_recurrent(c, il);
         E_TRY(synth_f32(e, il, IT_T_ATTN_NORM, e_, &l.attn_norm)); E_TRY(synth_f32(e, il, IT_T_POST_NORM, e_, &l.post_norm));
-        E_TRY(synth_mat(e, il, IT_T_FFN_GATE, ff, e_, &l.ffn_gate)); E_TRY(synth_mat(e, il, IT_T_FFN_UP, ff, e_, &l.ffn_up)); E_TRY(synth_mat(e, il, IT_T_FFN_DOWN, e_, ff, &l.ffn_down));
+        { const int ts[2] = { IT_T_FFN_GATE, IT_T_FFN_UP }; const size_t rs[2] = { (size_t)ff, (size_t)ff }; it_mat* parts[2];
+          E_TRY(synth_stack(e, il, 2, ts, rs, e_, parts, &l.gate_up)); l.ffn_gate = parts[0]; l.ffn_up = parts[1]; }
+        E_TRY(synth_mat(e, il, IT_T_FFN_DOWN, e_, ff, &l.ffn_down));
         if (l.recurrent) {
-            E_TRY(synth_mat(e, il, IT_T_QKV, cd, e_, &l.qkv)); E_TRY(synth_mat(e, il, IT_T_GATE, inner, e_, &l.gate)); E_TRY(synth_mat(e, il, IT_T_SSM_OUT, e_, inner, &l.ssm_out));
+            { const int ts[2] = { IT_T_QKV, IT_T_GATE }; const size_t rs[2] = { (size_t)cd, (size_t)inner }; it_mat* parts[2];
+              E_TRY(synth_stack(e, il, 2, ts, rs, e_, parts, &l.in_proj)); l.qkv = parts[0]; l.gate = parts[1]; }
+            E_TRY(synth_mat(e, il, IT_T_SSM_OUT, e_, inner, &l.ssm_out));
             E_TRY(synth_f32(e, il, IT_T_CONV, (size_t)cd * c.conv_k, &l.conv_w)); E_TRY(synth_f32(e, il, IT_T_DT, nv, &l.dt)); E_TRY(synth_f32(e, il, IT_T_A, nv, &l.a));
             E_TRY(synth_f32(e, il, IT_T_BETA, (size_t)nv * e_, &l.beta)); E_TRY(synth_f32(e, il, IT_T_ALPHA, (size_t)nv * e_, &l.alpha)); E_TRY(synth_f32(e, il, IT_T_SSM_NORM, sd, &l.ssm_norm));
             const size_t csz = (size_t)(c.conv_k - 1) * cd, ssz = (size_t)nv * sd * sd;
             E_TRY(dev_alloc(e, (void**)&l.conv_st, csz * 4, true)); E_TRY(dev_alloc(e, (void**)&l.ssm_st, ssz * 4, true));
             E_TRY(dev_alloc(e, (void**)&l.ck_conv, IT_MAXCK * csz * 4, true)); E_TRY(dev_alloc(e, (void**)&l.ck_ssm, IT_MAXCK * ssz * 4, true));
         } else {
-            E_TRY(synth_mat(e, il, IT_T_Q, qf, e_, &l.q)); E_TRY(synth_mat(e, il, IT_T_K, kvd, e_, &l.k)); E_TRY(synth_mat(e, il, IT_T_V, kvd, e_, &l.v)); E_TRY(synth_mat(e, il, IT_T_O, e_, nh * hd, &l.o));
+            { const int ts[3] = { IT_T_Q, IT_T_K, IT_T_V }; const size_t rs[3] = { (size_t)qf, (size_t)kvd, (size_t)kvd }; it_mat* parts[3];
+              E_TRY(synth_stack(e, il, 3, ts, rs, e_, parts, &l.in_proj)); l.q = parts[0]; l.k = parts[1]; l.v = parts[2]; }
+            E_TRY(synth_mat(e, il, IT_T_O, e_, nh * hd, &l.o));
             E_TRY(synth_f32(e, il, IT_T_Q_NORM, hd, &l.q_norm)); E_TRY(synth_f32(e, il, IT_T_K_NORM, hd, &l.k_norm));
             E_TRY(dev_alloc(e, (void**)&l.kc, (size_t)c.ctx_len * kvd * 2, true)); E_TRY(dev_alloc(e, (void**)&l.vc, (size_t)c.ctx_len * kvd * 2, true));
         }
@@ -152,7 +172,7 @@ IT_API void it_engine_destroy(it_engine* e) {
     if (e->ctx) { cudaSetDevice(e->ctx->device); cudaStreamSynchronize(e->ctx->stream); }
     if (e->step_graph) it_graph_destroy(e->step_graph);
     for (it_layer& l : e->layers) {
-        it_mat* ms[] = { l.ffn_gate, l.ffn_up, l.ffn_down, l.qkv, l.gate, l.ssm_out, l.q, l.k, l.v, l.o };
+        it_mat* ms[] = { l.ffn_gate, l.ffn_up, l.ffn_down, l.qkv, l.gate, l.ssm_out, l.q, l.k, l.v, l.o, l.in_proj, l.gate_up };
         for (it_mat* m : ms) it_matrix_destroy(m);
     }
     it_matrix_destroy(e->output);

@@ -11,6 +11,9 @@ struct it_layer {
     bool recurrent;
     float *attn_norm, *post_norm;
     it_mat *ffn_gate, *ffn_up, *ffn_down;
+    // Matrices that multiply the same input are stacked row-wise in one allocation and run as one matvec; the
+    // individual tensors above and below are views into it.  in_proj = [qkv; gate] or [q; k; v], gate_up = [ffn_gate; ffn_up].
+    it_mat *in_proj, *gate_up;
     // Gated DeltaNet layers
     it_mat *qkv, *gate, *ssm_out;
     float *conv_w, *dt, *a, *beta, *alpha, *ssm_norm;

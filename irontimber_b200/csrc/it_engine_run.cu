@@ -47,37 +47,42 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
         IT_CUDA(cudaMemcpyAsync(e->toks_dev, e->host_pin, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
     }
     IT_TRY(it_sup_embed(cx, e->toks_dev, e->tok_embd, e_, nt, A + L.x));
+    // rmsnorm fused into the Hadamard + q8k kernel; the normed f32 row is kept only where a dense f32 op needs it
+    auto norm_had = [&](const float* w, float* xn_out) {
+        it_had_prologue p; p.mode = 2; p.w = w; p.eps = c.eps; p.n = (unsigned)e_; p.xn_out = xn_out; p.xn_stride = e_;
+        return it_sup_hadamard_q8_fused(cx, e_, nt, L.x, e_, e->q8, p);
+    };
+    const size_t s_gdn = (size_t)cd + inner, s_att = (size_t)qf + 2 * kvd, s_ffn = 2 * (size_t)ff;   // row strides of the stacked outputs
     for (int il = 0; il < c.n_layer; il++) {
         const it_layer& l = e->layers[il];
-        IT_TRY(it_sup_rmsnorm_wide(cx, A + L.x, e_, l.attn_norm, e_, c.eps, A + L.xn, e_, nt));
         if (l.recurrent) {
-            IT_TRY(had_mv(e, l.qkv, nt, L.xn, e_, L.big1, cd, 0, true));
-            IT_TRY(had_mv(e, l.gate, nt, L.xn, e_, L.big2, inner, 0, false));
+            IT_TRY(norm_had(l.attn_norm, A + L.xn));
+            IT_TRY(it_matvec_t2(cx, l.in_proj, nt, e->q8, L.big1, s_gdn, 0));                // [qkv | gate] rows
             IT_TRY(it_sup_dense_rows(cx, l.beta, l.alpha, nv, e_, A + L.xn, e_, A + L.beta, A + L.alpha, nv, nt));
             const size_t csz = (size_t)(c.conv_k - 1) * cd, ssz = (size_t)nv * sd * sd;
-            IT_TRY(it_sup_conv(cx, A + L.big1, cd, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, nt, l.ck_conv, csz, nck));
+            IT_TRY(it_sup_conv(cx, A + L.big1, s_gdn, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, nt, l.ck_conv, csz, nck));
             IT_TRY(it_sup_norm_head(cx, A + L.conv, sd, cd, A + L.conv, sd, cd, sd, 2 * nk, nullptr, 2, c.eps, nullptr, 0, 0, nt));
             IT_TRY(it_sup_gdn(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck));
-            IT_TRY(it_sup_norm_head(cx, A + L.o, sd, inner, A + L.o, sd, inner, sd, nv, l.ssm_norm, 1, c.eps, A + L.big2, sd, inner, nt));
+            IT_TRY(it_sup_norm_head(cx, A + L.o, sd, inner, A + L.o, sd, inner, sd, nv, l.ssm_norm, 1, c.eps, A + L.big1 + cd, sd, s_gdn, nt));
             if (c.gdn_v_grouped) IT_TRY(had_mv(e, l.ssm_out, nt, L.o, inner, L.x, e_, 1, true, sd, nk, nv / nk));
             else IT_TRY(had_mv(e, l.ssm_out, nt, L.o, inner, L.x, e_, 1, true));
         } else {
-            IT_TRY(had_mv(e, l.q, nt, L.xn, e_, L.big1, qf, 0, true));
-            IT_TRY(had_mv(e, l.k, nt, L.xn, e_, L.kcur, kvd, 0, false));
-            IT_TRY(had_mv(e, l.v, nt, L.xn, e_, L.vcur, kvd, 0, false));
-            IT_TRY(it_sup_norm_head(cx, A + L.big1, 2 * hd, qf, A + L.big1, 2 * hd, qf, hd, nh, l.q_norm, 0, c.eps, nullptr, 0, 0, nt));
-            IT_TRY(it_sup_norm_head(cx, A + L.kcur, hd, kvd, A + L.kcur, hd, kvd, hd, nkv, l.k_norm, 0, c.eps, nullptr, 0, 0, nt));
-            IT_TRY(it_sup_rope(cx, A + L.big1, 2 * hd, qf, nh, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
-            IT_TRY(it_sup_rope(cx, A + L.kcur, hd, kvd, nkv, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
-            IT_TRY(it_sup_kv_store(cx, A + L.kcur, A + L.vcur, kvd, l.kc, l.vc, kvd, pos0, pos_ptr, nt, 1));
-            IT_TRY(it_sup_attention(cx, A + L.big1, 2 * hd, qf, A + L.big1 + hd, l.kc, l.vc, kvd, hd, nh, nkv, pos0, pos_ptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 1));
+            float* q = A + L.big1; float* k = q + qf; float* v = k + kvd;                     // [q+gate | k | v] rows
+            IT_TRY(norm_had(l.attn_norm, nullptr));
+            IT_TRY(it_matvec_t2(cx, l.in_proj, nt, e->q8, L.big1, s_att, 0));
+            IT_TRY(it_sup_norm_head(cx, q, 2 * hd, s_att, q, 2 * hd, s_att, hd, nh, l.q_norm, 0, c.eps, nullptr, 0, 0, nt));
+            IT_TRY(it_sup_norm_head(cx, k, hd, s_att, k, hd, s_att, hd, nkv, l.k_norm, 0, c.eps, nullptr, 0, 0, nt));
+            IT_TRY(it_sup_rope(cx, q, 2 * hd, s_att, nh, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
+            IT_TRY(it_sup_rope(cx, k, hd, s_att, nkv, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
+            IT_TRY(it_sup_kv_store(cx, k, v, s_att, l.kc, l.vc, kvd, pos0, pos_ptr, nt, 1));
+            IT_TRY(it_sup_attention(cx, q, 2 * hd, s_att, q + hd, l.kc, l.vc, kvd, hd, nh, nkv, pos0, pos_ptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 1));
             IT_TRY(had_mv(e, l.o, nt, L.o, (size_t)nh * hd, L.x, e_, 1, true));
         }
-        IT_TRY(it_sup_rmsnorm_wide(cx, A + L.x, e_, l.post_norm, e_, c.eps, A + L.xn, e_, nt));
-        IT_TRY(had_mv(e, l.ffn_gate, nt, L.xn, e_, L.big1, ff, 0, true));
-        IT_TRY(had_mv(e, l.ffn_up, nt, L.xn, e_, L.big2, ff, 0, false));
-        IT_TRY(it_sup_silu_mul(cx, A + L.big1, A + L.big2, A + L.big1, (size_t)nt * ff));
-        IT_TRY(had_mv(e, l.ffn_down, nt, L.big1, ff, L.x, e_, 1, true));
+        IT_TRY(norm_had(l.post_norm, nullptr));
+        IT_TRY(it_matvec_t2(cx, l.gate_up, nt, e->q8, L.big1, s_ffn, 0));                    // [gate | up] rows
+        { it_had_prologue p; p.mode = 1; p.b = A + L.big1 + ff; p.b_stride = s_ffn;           // silu(gate) * up on the way into the Hadamard
+          IT_TRY(it_sup_hadamard_q8_fused(cx, ff, nt, L.big1, s_ffn, e->q8, p)); }
+        IT_TRY(it_matvec_t2(cx, l.ffn_down, nt, e->q8, L.x, e_, 1));
     }
     // h_nextn rows: output-normed hidden state of every token of this pass (src/vk/mod.rs:858-861, src/cpu.rs:188-189)
     IT_TRY(it_sup_rmsnorm_wide(cx, A + L.x, e_, e->output_norm, e_, c.eps, A + L.hrow, e_, nt));

@@ -12,6 +12,8 @@
 // q = min(round_half_even(iscale*x), 127); d = 1/iscale; per-128 sums of q (one warp each).
 // Algorithmic traffic per row: 4n bytes in, n + 4n/256 + 4n/128 bytes out.
 #include "it_internal.h"
+#include "it_math.h"
+#include "it_support.h"
 
 namespace {
 
@@ -28,8 +30,9 @@ k_hadamard(const float* arena_in, size_t in_off, size_t in_stride,
            float* f32_out, size_t out_off, size_t out_stride,
            const float* __restrict__ signs, int rotate, int inverse,
            unsigned perm_hd, unsigned perm_nk, unsigned perm_rep,
-           int8_t* __restrict__ qs, float* __restrict__ qd, int32_t* __restrict__ qsum, size_t q_stride) {
+           int8_t* __restrict__ qs, float* __restrict__ qd, int32_t* __restrict__ qsum, size_t q_stride, it_had_prologue pro) {
     __shared__ float4 xch[256];
+    __shared__ float wsum[8];
     __shared__ float s_amax[8]; __shared__ float s_val[8]; __shared__ unsigned s_idx[8];
     const unsigned tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned blk = blockIdx.x; const size_t tok = blockIdx.y;
@@ -37,7 +40,31 @@ k_hadamard(const float* arena_in, size_t in_off, size_t in_stride,
     const float* x = arena_in + in_off + tok * in_stride;
 
     float v[4];
-    if (perm_hd == 0) {
+    if (pro.mode == 2) {
+        // rmsnorm of the whole row first (src/cpu.rs:14-18), in the order of k_rmsnorm_wide: thread i adds x[i]^2,
+        // x[i+256]^2, ...; warp butterflies; eight warp sums in ascending order.  Every CTA of the row repeats it.
+        float xv[32];
+#pragma unroll
+        for (int k = 0; k < 32; k++) { const unsigned j = tid + 256u * k; xv[k] = j < pro.n ? x[j] : 0.f; }
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; k++) if (tid + 256u * k < pro.n) s = it_add(s, it_mul(xv[k], xv[k]));
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) s = it_add(s, __shfl_xor_sync(0xffffffffu, s, m));
+        if (lane == 0) wsum[warp] = s;
+        __syncthreads();
+        float tot = wsum[0];
+#pragma unroll
+        for (int k = 1; k < 8; k++) tot = it_add(tot, wsum[k]);
+        const float sc = it_div(1.0f, it_sqrt(it_add(it_div(tot, (float)pro.n), pro.eps)));
+        const float4 t = *reinterpret_cast<const float4*>(x + g0), w4 = *reinterpret_cast<const float4*>(pro.w + g0);
+        v[0] = it_mul(it_mul(t.x, sc), w4.x); v[1] = it_mul(it_mul(t.y, sc), w4.y); v[2] = it_mul(it_mul(t.z, sc), w4.z); v[3] = it_mul(it_mul(t.w, sc), w4.w);
+        if (pro.xn_out) *reinterpret_cast<float4*>(pro.xn_out + tok * pro.xn_stride + g0) = make_float4(v[0], v[1], v[2], v[3]);
+    } else if (pro.mode == 1) {
+        // silu(a) * b (src/cpu.rs:183) computed on the way in
+        const float4 a = *reinterpret_cast<const float4*>(x + g0), b = *reinterpret_cast<const float4*>(pro.b + tok * pro.b_stride + g0);
+        v[0] = it_mul(it_silu(a.x), b.x); v[1] = it_mul(it_silu(a.y), b.y); v[2] = it_mul(it_silu(a.z), b.z); v[3] = it_mul(it_silu(a.w), b.w);
+    } else if (perm_hd == 0) {
         float4 t = *reinterpret_cast<const float4*>(x + g0);
         v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     } else {
@@ -143,7 +170,7 @@ IT_API int it_hadamard_q8(it_ctx* c, size_t n, size_t ntok, size_t x_off, size_t
     it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
     k_hadamard<true><<<grid, 256, 0, c->stream>>>(c->arena, x_off, x_stride, nullptr, 0, 0, signs, rotate, 0,
-        (unsigned)hd, (unsigned)nk, (unsigned)rep, out->qs, out->d, out->sum128, out->max_n);
+        (unsigned)hd, (unsigned)nk, (unsigned)rep, out->qs, out->d, out->sum128, out->max_n, it_had_prologue{});
     IT_LAUNCH_CHECK("hadamard_q8");
     out->n = n;
     return IT_OK;
@@ -159,7 +186,19 @@ IT_API int it_hadamard_f32(it_ctx* c, size_t n, size_t ntok, size_t in_off, size
     it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
     k_hadamard<false><<<grid, 256, 0, c->stream>>>(c->arena, in_off, in_stride, c->arena, out_off, out_stride, signs, 1, inverse,
-        (unsigned)hd, (unsigned)nk, (unsigned)rep, nullptr, nullptr, nullptr, 0);
+        (unsigned)hd, (unsigned)nk, (unsigned)rep, nullptr, nullptr, nullptr, 0, it_had_prologue{});
     IT_LAUNCH_CHECK("hadamard_f32");
+    return IT_OK;
+}
+
+// Engine-internal: the forward transform + q8k with an elementwise prologue (see it_had_prologue in it_support.h).
+int it_sup_hadamard_q8_fused(it_ctx* c, size_t n, size_t ntok, size_t x_off, size_t x_stride, it_q8* out, const it_had_prologue& pro) {
+    const float* signs; int r = check_common(c, n, ntok, x_off, x_stride, 1, 0, 0, 0, &signs, "hadamard_q8_fused"); if (r) return r;
+    IT_CHECK_ARG(out && out->ctx == c && n <= out->max_n && ntok <= out->max_tok && (pro.mode != 2 || (n <= 8192 && pro.n == n)), "hadamard_q8_fused: bad q8 buffer or width");
+    it_note_op(c);
+    dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
+    k_hadamard<true><<<grid, 256, 0, c->stream>>>(c->arena, x_off, x_stride, nullptr, 0, 0, signs, 1, 0, 0u, 0u, 0u, out->qs, out->d, out->sum128, out->max_n, pro);
+    IT_LAUNCH_CHECK("hadamard_q8_fused");
+    out->n = n;
     return IT_OK;
 }

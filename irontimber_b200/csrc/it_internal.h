@@ -41,6 +41,7 @@ struct it_mat {
     size_t row_groups;      // ceil(rows / 32)
     uint8_t* tiles;         // [row_groups][cols/128][IT_TILE_BYTES]
     size_t bytes;
+    bool owns_tiles;        // false for a view into a larger allocation (stacked matrices)
 };
 
 // Int8-group matrix: row-major int8 q[rows][cols] and f16 d[rows][cols/32] (Q8_0 density).
@@ -106,4 +107,9 @@ int it_launch_repack_pq2(it_ctx* ctx, const uint8_t* raw_dev, size_t rows, size_
 int it_launch_repack_packed2(it_ctx* ctx, const uint32_t* words_dev, const float* scales_dev, size_t rows, size_t cols, uint8_t* tiles);
 int it_launch_unpack_pq2(it_ctx* ctx, const uint8_t* tiles, size_t rows, size_t cols, uint8_t* raw_dev);
 int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, uint8_t* raw_dev);
+// A synthetic matrix generated into caller-owned tile storage (rows must be a multiple of 32 when matrices are stacked);
+// the returned it_mat is a view that does not free the tiles.
+int it_matrix_synth_view(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, uint8_t* tiles, it_mat** out);
+// A view over `row_groups` consecutive row groups starting at `tiles` (e.g. several stacked matrices seen as one).
+int it_matrix_view(it_ctx* ctx, size_t rows, size_t cols, uint8_t* tiles, it_mat** out);
 int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d);

@@ -2,6 +2,16 @@
 #pragma once
 #include "it_internal.h"
 
+// Work done on the way into the Hadamard + q8k kernel.  mode 0: nothing.  mode 1: input = silu(x) * b (b is a device
+// pointer, rows b_stride apart).  mode 2: input = rmsnorm(x) over the whole row of width n with weight w and eps; when
+// xn_out is set the normed f32 row is also stored there (rows xn_stride apart).
+struct it_had_prologue {
+    int mode = 0;
+    const float* b = nullptr; size_t b_stride = 0;
+    const float* w = nullptr; float eps = 0.f; unsigned n = 0; float* xn_out = nullptr; size_t xn_stride = 0;
+};
+int it_sup_hadamard_q8_fused(it_ctx* c, size_t n, size_t ntok, size_t x_off, size_t x_stride, it_q8* out, const it_had_prologue& pro);
+
 int it_sup_embed(it_ctx* c, const uint32_t* toks_dev, const float* table, int e, int nt, float* x);
 int it_sup_rmsnorm_wide(it_ctx* c, const float* x, size_t xs, const float* w, int n, float eps, float* out, size_t os, int nt);
 int it_sup_norm_head(it_ctx* c, const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts, int n, int nheads, const float* w, int mode, float eps,
