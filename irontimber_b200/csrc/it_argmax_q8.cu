@@ -30,6 +30,7 @@ __device__ __forceinline__ Pick block_reduce(Pick p, Pick* sh) {
 
 __global__ void __launch_bounds__(256)
 k_argmax(const float* __restrict__ v, unsigned n, unsigned per_block, unsigned long long* partials, unsigned* counter, float* dst) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     __shared__ Pick sh[8];
     __shared__ bool is_last;
     const unsigned begin = blockIdx.x * per_block, end = min(n, begin + per_block);   // per_block % 4 == 0
@@ -67,6 +68,7 @@ template <int NT>
 __global__ void __launch_bounds__(256)
 k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, int rows, int cols,
             const float* x, size_t x_stride, float* y, size_t y_stride, int ntok, int accum) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r0 = (blockIdx.x * 8 + warp) * QROWS;
     if (r0 >= rows) return;
@@ -127,7 +129,7 @@ IT_API int it_argmax(it_ctx* c, size_t logits_off, size_t n, size_t dst_off) {
     if (blocks > cap) blocks = cap;
     unsigned per_block = (unsigned)((n + blocks - 1) / blocks); per_block = (per_block + 3) & ~3u;
     blocks = (unsigned)((n + per_block - 1) / per_block);
-    k_argmax<<<blocks, 256, 0, c->stream>>>(c->arena + logits_off, (unsigned)n, per_block, c->argmax_partials, c->argmax_counter, c->arena + dst_off);
+    it_pdl(k_argmax, dim3(blocks), dim3(256), 0, c->stream, c->arena + logits_off, (unsigned)n, per_block, c->argmax_partials, c->argmax_counter, c->arena + dst_off);
     IT_LAUNCH_CHECK("argmax");
     return IT_OK;
 }
@@ -145,9 +147,9 @@ IT_API int it_matvec_q8(it_ctx* c, const it_qmat* w, size_t ntok, size_t x_off, 
     for (size_t t0 = 0; t0 < ntok; t0 += 4) {
         const int nt = (int)((ntok - t0) < 4 ? (ntok - t0) : 4);
         const float* x = c->arena + x_off + t0 * x_stride; float* y = c->arena + y_off + t0 * y_stride;
-        if (nt == 1) k_matvec_q8<1><<<grid, 256, 0, c->stream>>>(w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
-        else if (nt == 2) k_matvec_q8<2><<<grid, 256, 0, c->stream>>>(w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
-        else k_matvec_q8<4><<<grid, 256, 0, c->stream>>>(w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
+        if (nt == 1) it_pdl(k_matvec_q8<1>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
+        else if (nt == 2) it_pdl(k_matvec_q8<2>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
+        else it_pdl(k_matvec_q8<4>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
         IT_LAUNCH_CHECK("matvec_q8");
     }
     return IT_OK;

@@ -31,6 +31,7 @@ k_hadamard(const float* arena_in, size_t in_off, size_t in_stride,
            const float* __restrict__ signs, int rotate, int inverse,
            unsigned perm_hd, unsigned perm_nk, unsigned perm_rep,
            int8_t* __restrict__ qs, float* __restrict__ qd, int32_t* __restrict__ qsum, size_t q_stride, it_had_prologue pro) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     __shared__ float4 xch[256];
     __shared__ float wsum[8];
     __shared__ float s_amax[8]; __shared__ float s_val[8]; __shared__ unsigned s_idx[8];
@@ -169,7 +170,7 @@ IT_API int it_hadamard_q8(it_ctx* c, size_t n, size_t ntok, size_t x_off, size_t
     IT_CHECK_ARG(n <= out->max_n && ntok <= out->max_tok, "it_hadamard_q8: %zu rows of %zu do not fit the q8 buffer (%zu x %zu)", ntok, n, out->max_tok, out->max_n);
     it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
-    k_hadamard<true><<<grid, 256, 0, c->stream>>>(c->arena, x_off, x_stride, nullptr, 0, 0, signs, rotate, 0,
+    it_pdl(k_hadamard<true>, dim3(grid), dim3(256), 0, c->stream, c->arena, x_off, x_stride, nullptr, 0, 0, signs, rotate, 0,
         (unsigned)hd, (unsigned)nk, (unsigned)rep, out->qs, out->d, out->sum128, out->max_n, it_had_prologue{});
     IT_LAUNCH_CHECK("hadamard_q8");
     out->n = n;
@@ -185,7 +186,7 @@ IT_API int it_hadamard_f32(it_ctx* c, size_t n, size_t ntok, size_t in_off, size
     IT_CHECK_ARG(out_off <= c->arena_floats && (ntok - 1) * out_stride + n <= c->arena_floats - out_off, "it_hadamard_f32: output rows fall outside the arena");
     it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
-    k_hadamard<false><<<grid, 256, 0, c->stream>>>(c->arena, in_off, in_stride, c->arena, out_off, out_stride, signs, 1, inverse,
+    it_pdl(k_hadamard<false>, dim3(grid), dim3(256), 0, c->stream, c->arena, in_off, in_stride, c->arena, out_off, out_stride, signs, 1, inverse,
         (unsigned)hd, (unsigned)nk, (unsigned)rep, nullptr, nullptr, nullptr, 0, it_had_prologue{});
     IT_LAUNCH_CHECK("hadamard_f32");
     return IT_OK;
@@ -197,7 +198,7 @@ int it_sup_hadamard_q8_fused(it_ctx* c, size_t n, size_t ntok, size_t x_off, siz
     IT_CHECK_ARG(out && out->ctx == c && n <= out->max_n && ntok <= out->max_tok && (pro.mode != 2 || (n <= 8192 && pro.n == n)), "hadamard_q8_fused: bad q8 buffer or width");
     it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
-    k_hadamard<true><<<grid, 256, 0, c->stream>>>(c->arena, x_off, x_stride, nullptr, 0, 0, signs, 1, 0, 0u, 0u, 0u, out->qs, out->d, out->sum128, out->max_n, pro);
+    it_pdl(k_hadamard<true>, dim3(grid), dim3(256), 0, c->stream, c->arena, x_off, x_stride, nullptr, 0, 0, signs, 1, 0, 0u, 0u, 0u, out->qs, out->d, out->sum128, out->max_n, pro);
     IT_LAUNCH_CHECK("hadamard_q8_fused");
     out->n = n;
     return IT_OK;

@@ -5,6 +5,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdarg>
+#include <cstdlib>
 #include <map>
 #include <string>
 #include "../../include/irontimber_cuda.h"
@@ -95,6 +96,24 @@ static inline void it_note_op(it_ctx* c) { c->pdl_safe_q8 = nullptr; }
 int it_check_device_error(it_ctx* ctx, const char* who);
 
 #define IT_ARGMAX_MAX_BLOCKS 1024
+
+// ---- programmatic dependent launch -----------------------------------------------------------------------------
+// Every kernel of the decode path is launched with programmatic stream serialization: it lets the kernel after it be
+// scheduled at once (IT_PDL_TRIGGER) and waits for the kernel before it to finish and flush (IT_PDL_WAIT) before it
+// touches any memory that kernel may have written.  The launch latency and prologue of a kernel then overlap the
+// kernel in front of it.  Completion is transitive: a kernel only finishes after its own wait has returned.
+#define IT_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#define IT_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+template <typename... KArgs, typename... Args>
+static inline cudaError_t it_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const int pdl_on = []{ const char* v = getenv("IT_PDL_SUPPORT"); return v ? atoi(v) : 0; }();
+    cfg.attrs = attr; cfg.numAttrs = pdl_on ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // ---- synthetic data: hash(seed, i) is the i-th output of splitmix64 seeded with `seed` (src/sampling.rs:43) ----
 __host__ __device__ static inline uint64_t it_mix64(uint64_t z) {

@@ -13,6 +13,7 @@ namespace {
 
 // x[t] = table[tok[t]]  (Model::embed, src/cpu.rs:118-122; the reference computes this on the host, src/vk/mod.rs:766-769)
 __global__ void k_embed(const uint32_t* __restrict__ toks, const float* __restrict__ table, int e, float* x) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     const int t = blockIdx.y; const size_t row = toks[t];
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < e / 4; i += gridDim.x * blockDim.x)
         reinterpret_cast<float4*>(x + (size_t)t * e)[i] = reinterpret_cast<const float4*>(table + row * e)[i];
@@ -22,6 +23,7 @@ __global__ void k_embed(const uint32_t* __restrict__ toks, const float* __restri
 // adds x[i]^2, x[i+256]^2, ... in ascending order; each warp folds with a butterfly (offsets 16..1); the eight warp
 // sums are added in ascending order.  out = (x * s) * w with s = 1 / sqrt(ss / n + eps), no fused multiply-add.
 __global__ void __launch_bounds__(256) k_rmsnorm_wide(const float* x, size_t x_stride, const float* __restrict__ w, int n, float eps, float* out, size_t out_stride) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     __shared__ float wsum[8];
     const float* xr = x + blockIdx.x * x_stride; float* o = out + blockIdx.x * out_stride;
     float v[32];                                   // n <= 8192: all loads are issued before the first add
@@ -47,6 +49,7 @@ __global__ void __launch_bounds__(256) k_rmsnorm_wide(const float* x, size_t x_s
 // (gated ssm_norm, src/cpu.rs:233-237); mode 2: l2norm, x / max(sqrt(sum), eps) (src/cpu.rs:164, :214).
 __global__ void __launch_bounds__(128) k_norm_head(const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts,
                                                    int n, int nheads, const float* __restrict__ w, int mode, float eps, const float* z, size_t z_hs, size_t z_ts) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     __shared__ float buf[4][256];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x * 4 + warp, t = blockIdx.y;
@@ -73,6 +76,7 @@ __global__ void __launch_bounds__(128) k_norm_head(const float* in, size_t in_hs
 // (I)MRoPE for text positions on the first n_rot dims of each head (src/cpu.rs:145-162): the angle of pair i is the
 // position multiplied i times by theta_scale, one rounding per step exactly as the CPU's running product.
 __global__ void k_rope(float* x, size_t hs, size_t ts, int nheads, int pos0, const int* pos_ptr, int n_rot, float theta_scale, int s0, int s1, int s2, int s3) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     const int half = n_rot / 2, t = blockIdx.y;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= nheads * half) return;
@@ -93,6 +97,7 @@ __global__ void k_rope(float* x, size_t hs, size_t ts, int nheads, int pos0, con
 // state after token t is copied to checkpoint t when one is given (MTP rollback, src/vk/mod.rs:794).
 __global__ void k_conv(const float* mixed, size_t m_ts, const float* __restrict__ w, float* state, float* out, size_t o_ts, int cd, int kk, int nt,
                        float* ck, size_t ck_stride, int nck) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     const int ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= cd) return;
     float st[8];
@@ -114,6 +119,7 @@ __global__ void k_conv(const float* mixed, size_t m_ts, const float* __restrict_
 // with a butterfly, the eight warp sums are added in ascending order.  Rows [0, rows) use w0 / y0, rows [rows, 2 rows) w1 / y1.
 __global__ void __launch_bounds__(256) k_dense_rows(const float* __restrict__ w0, const float* __restrict__ w1, int rows, int cols, const float* x, size_t x_ts,
                                                     float* y0, float* y1, size_t y_ts) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     __shared__ double wsum[8];
     const int r = blockIdx.x, t = blockIdx.y, row = r < rows ? r : r - rows;
     const float* wr = (r < rows ? w0 : w1) + (size_t)row * cols; const float* xr = x + t * x_ts;
@@ -136,6 +142,7 @@ __global__ void __launch_bounds__(256) k_dense_rows(const float* __restrict__ w0
 // global accesses stay coalesced.  State layout [head][j][i] as on the CPU (src/cpu.rs:132).
 __global__ void __launch_bounds__(128) k_gdn(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
                                              float* state, float* o, size_t o_ts, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     extern __shared__ float tile[];            // [32][sd + 1] rows, then q[sd], k[sd]
     const int h = blockIdx.x, j0 = blockIdx.y * 32, tid = threadIdx.x, kh = h % nk, ld = sd + 1, nvec = 32 * sd / 4;
     float* qs = tile + 32 * ld; float* ks = qs + sd;
@@ -178,6 +185,7 @@ __global__ void __launch_bounds__(128) k_gdn(const float* co, size_t co_ts, cons
 
 // act = silu(g) * u (src/cpu.rs:183)
 __global__ void k_silu_mul(const float* g, const float* u, float* out, size_t n) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (i < n) out[i] = it_mul(it_silu(g[i]), u[i]);
 }
@@ -191,6 +199,7 @@ __device__ __forceinline__ float kv_get(const float* p) { return *p; }
 
 template <typename T>
 __global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* vc, int kvd, int slot0, const int* pos_ptr) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     if (pos_ptr) slot0 += *pos_ptr;
     const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= kvd) return;
@@ -200,24 +209,46 @@ __global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* 
 
 // Causal gated attention for one (head, row) per CTA in the CPU's order (src/cpu.rs:262-272): every score is a
 // sequential dot over the head dimension, the exponentials are added in ascending position order by one thread,
-// every output element accumulates w[p] * v[p][j] in ascending position order, then * sigmoid(gate).
+// every output element accumulates w[p] * v[p][j] in ascending position order, then * sigmoid(gate).  Loads are
+// issued in batches ahead of the dependent additions so that the chains run at arithmetic, not memory, latency.
+template <typename T> struct KvVec;
+template <> struct KvVec<__half> { static constexpr int N = 8; using V = uint4;
+    static __device__ __forceinline__ void unpack(const V& v, float* f) { const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; } } };
+template <> struct KvVec<float> { static constexpr int N = 4; using V = float4;
+    static __device__ __forceinline__ void unpack(const V& v, float* f) { f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; } };
+
 template <typename T>
-__global__ void __launch_bounds__(256) k_attention(const float* q, size_t q_hs, size_t q_ts, const float* gate, const T* __restrict__ kc, const T* __restrict__ vc,
-                                                   int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, float* out, size_t o_ts) {
+__global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs, size_t q_ts, const float* gate, const T* __restrict__ kc, const T* __restrict__ vc,
+                                                    int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, float* out, size_t o_ts) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
     extern __shared__ float sc[];              // [n] scores, then q[hd]
-    __shared__ float red[8]; __shared__ float s_sum;
+    __shared__ float red[32]; __shared__ float s_sum;
     if (pos_ptr) slot0 += *pos_ptr;
     const int h = blockIdx.x, t = blockIdx.y, n = slot0 + t + 1, kh = h / (nh / nkv), tid = threadIdx.x;
     float* qs = sc + ((n + 3) & ~3);
     const float* qh = q + t * q_ts + h * q_hs;
-    for (int j = tid; j < hd; j += 256) qs[j] = qh[j];
+    for (int j = tid; j < hd; j += 1024) qs[j] = qh[j];
     __syncthreads();
     const float scale = it_div(1.0f, it_sqrt((float)hd));
+    constexpr int VN = KvVec<T>::N; using Vec = typename KvVec<T>::V;
+    const int nvec = hd / VN;                  // vectors per K row
     float mx = -INFINITY;
-    for (int p = tid; p < n; p += 256) {
-        const T* kp = kc + (size_t)p * kvd + kh * hd;
+    for (int p = tid; p < n; p += 1024) {
+        const Vec* kp = reinterpret_cast<const Vec*>(kc + (size_t)p * kvd + kh * hd);
         float s = 0.f;
-        for (int j = 0; j < hd; j++) s = it_add(s, it_mul(qs[j], kv_get(kp + j)));
+        for (int v0 = 0; v0 < nvec; v0 += 8) {
+            Vec buf[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) if (v0 + u < nvec) buf[u] = kp[v0 + u];
+#pragma unroll
+            for (int u = 0; u < 8; u++) if (v0 + u < nvec) {
+                float f[VN]; KvVec<T>::unpack(buf[u], f);
+#pragma unroll
+                for (int i = 0; i < VN; i++) s = it_add(s, it_mul(qs[(v0 + u) * VN + i], f[i]));
+            }
+        }
         s = it_mul(s, scale); sc[p] = s; mx = fmaxf(mx, s);
     }
 #pragma unroll
@@ -226,8 +257,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* q, size_t q_hs, 
     __syncthreads();
     mx = red[0];
 #pragma unroll
-    for (int k = 1; k < 8; k++) mx = fmaxf(mx, red[k]);
-    for (int p = tid; p < n; p += 256) sc[p] = it_expf(it_sub(sc[p], mx));
+    for (int k = 1; k < 32; k++) mx = fmaxf(mx, red[k]);
+    for (int p = tid; p < n; p += 1024) sc[p] = it_expf(it_sub(sc[p], mx));
     __syncthreads();
     if (tid == 0) { float s = 0.f;
 #pragma unroll 8
@@ -235,13 +266,18 @@ __global__ void __launch_bounds__(256) k_attention(const float* q, size_t q_hs, 
         s_sum = s; }
     __syncthreads();
     const float sum = s_sum;
-    for (int p = tid; p < n; p += 256) sc[p] = it_div(sc[p], sum);
+    for (int p = tid; p < n; p += 1024) sc[p] = it_div(sc[p], sum);
     __syncthreads();
-    for (int j = tid; j < hd; j += 256) {
+    for (int j = tid; j < hd; j += 1024) {
         const T* vp = vc + kh * hd + j;
         float acc = 0.f;
-#pragma unroll 4
-        for (int p = 0; p < n; p++) acc = it_add(acc, it_mul(sc[p], kv_get(vp + (size_t)p * kvd)));
+        for (int p0 = 0; p0 < n; p0 += 32) {
+            float vv[32];
+#pragma unroll
+            for (int u = 0; u < 32; u++) vv[u] = p0 + u < n ? kv_get(vp + (size_t)(p0 + u) * kvd) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 32; u++) if (p0 + u < n) acc = it_add(acc, it_mul(sc[p0 + u], vv[u]));
+        }
         out[t * o_ts + h * hd + j] = it_mul(acc, it_sigmoid(gate[t * q_ts + h * q_hs + j]));
     }
 }
@@ -251,40 +287,40 @@ __global__ void __launch_bounds__(256) k_attention(const float* q, size_t q_hs, 
 }  // namespace
 
 int it_sup_embed(it_ctx* c, const uint32_t* toks_dev, const float* table, int e, int nt, float* x) {
-    it_note_op(c); k_embed<<<dim3(4, nt), 256, 0, c->stream>>>(toks_dev, table, e, x); KCHK("embed"); return IT_OK;
+    it_note_op(c); it_pdl(k_embed, dim3(dim3(4, nt)), dim3(256), 0, c->stream, toks_dev, table, e, x); KCHK("embed"); return IT_OK;
 }
 int it_sup_rmsnorm_wide(it_ctx* c, const float* x, size_t xs, const float* w, int n, float eps, float* out, size_t os, int nt) {
-    it_note_op(c); k_rmsnorm_wide<<<nt, 256, 0, c->stream>>>(x, xs, w, n, eps, out, os); KCHK("rmsnorm_wide"); return IT_OK;
+    it_note_op(c); it_pdl(k_rmsnorm_wide, dim3(nt), dim3(256), 0, c->stream, x, xs, w, n, eps, out, os); KCHK("rmsnorm_wide"); return IT_OK;
 }
 int it_sup_norm_head(it_ctx* c, const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts, int n, int nheads, const float* w, int mode, float eps,
                      const float* z, size_t z_hs, size_t z_ts, int nt) {
     if (n > 256) return it_fail(IT_EINVAL, "head norm width %d exceeds 256", n);
-    it_note_op(c); k_norm_head<<<dim3((nheads + 3) / 4, nt), 128, 0, c->stream>>>(in, in_hs, in_ts, out, out_hs, out_ts, n, nheads, w, mode, eps, z, z_hs, z_ts); KCHK("norm_head"); return IT_OK;
+    it_note_op(c); it_pdl(k_norm_head, dim3(dim3((nheads + 3) / 4, nt)), dim3(128), 0, c->stream, in, in_hs, in_ts, out, out_hs, out_ts, n, nheads, w, mode, eps, z, z_hs, z_ts); KCHK("norm_head"); return IT_OK;
 }
 int it_sup_rope(it_ctx* c, float* x, size_t hs, size_t ts, int nheads, int nt, int pos0, const int* pos_ptr, int n_rot, float theta_scale, const int* sec) {
     it_note_op(c); const int n = nheads * (n_rot / 2);
-    k_rope<<<dim3((n + 127) / 128, nt), 128, 0, c->stream>>>(x, hs, ts, nheads, pos0, pos_ptr, n_rot, theta_scale, sec[0], sec[1], sec[2], sec[3]); KCHK("rope"); return IT_OK;
+    it_pdl(k_rope, dim3(dim3((n + 127) / 128, nt)), dim3(128), 0, c->stream, x, hs, ts, nheads, pos0, pos_ptr, n_rot, theta_scale, sec[0], sec[1], sec[2], sec[3]); KCHK("rope"); return IT_OK;
 }
 int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, float* state, float* out, size_t o_ts, int cd, int kk, int nt, float* ck, size_t ck_stride, int nck) {
     if (kk < 2 || kk > 9) return it_fail(IT_EINVAL, "conv kernel size %d not supported", kk);
-    it_note_op(c); k_conv<<<(cd + 127) / 128, 128, 0, c->stream>>>(mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
+    it_note_op(c); it_pdl(k_conv, dim3((cd + 127) / 128), dim3(128), 0, c->stream, mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
 }
 int it_sup_dense_rows(it_ctx* c, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts, float* y0, float* y1, size_t y_ts, int nt) {
-    it_note_op(c); k_dense_rows<<<dim3(2 * rows, nt), 256, 0, c->stream>>>(w0, w1, rows, cols, x, x_ts, y0, y1, y_ts); KCHK("dense_rows"); return IT_OK;
+    it_note_op(c); it_pdl(k_dense_rows, dim3(dim3(2 * rows, nt)), dim3(256), 0, c->stream, w0, w1, rows, cols, x, x_ts, y0, y1, y_ts); KCHK("dense_rows"); return IT_OK;
 }
 int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
     if (sd % 32 != 0) return it_fail(IT_EINVAL, "ssm state size %d is not a multiple of 32", sd);
     it_note_op(c); const size_t smem = (32 * (sd + 1) + 2 * sd) * sizeof(float);
-    k_gdn<<<dim3(nv, sd / 32), 128, smem, c->stream>>>(co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck); KCHK("gdn"); return IT_OK;
+    it_pdl(k_gdn, dim3(dim3(nv, sd / 32)), dim3(128), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck); KCHK("gdn"); return IT_OK;
 }
 int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n) {
-    it_note_op(c); k_silu_mul<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(g, u, out, n); KCHK("silu_mul"); return IT_OK;
+    it_note_op(c); it_pdl(k_silu_mul, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, c->stream, g, u, out, n); KCHK("silu_mul"); return IT_OK;
 }
 int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int slot0, const int* pos_ptr, int nt, int f16) {
     it_note_op(c);
-    if (f16) k_kv_store<__half><<<dim3((kvd + 255) / 256, nt), 256, 0, c->stream>>>(k, v, ts, (__half*)kc, (__half*)vc, kvd, slot0, pos_ptr);
-    else k_kv_store<float><<<dim3((kvd + 255) / 256, nt), 256, 0, c->stream>>>(k, v, ts, (float*)kc, (float*)vc, kvd, slot0, pos_ptr);
+    if (f16) it_pdl(k_kv_store<__half>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (__half*)kc, (__half*)vc, kvd, slot0, pos_ptr);
+    else it_pdl(k_kv_store<float>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (float*)kc, (float*)vc, kvd, slot0, pos_ptr);
     KCHK("kv_store"); return IT_OK;
 }
 int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16) {
@@ -294,10 +330,10 @@ int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const 
     if (smem > 200 * 1024) return it_fail(IT_EINVAL, "attention over %d positions exceeds the shared-memory budget", slot0 + nt);
     if (f16) {
         static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
-        k_attention<__half><<<dim3(nh, nt), 256, smem, c->stream>>>(q, q_hs, q_ts, gate, (const __half*)kc, (const __half*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
+        it_pdl(k_attention<__half>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const __half*)kc, (const __half*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
     } else {
         static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
-        k_attention<float><<<dim3(nh, nt), 256, smem, c->stream>>>(q, q_hs, q_ts, gate, (const float*)kc, (const float*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
+        it_pdl(k_attention<float>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const float*)kc, (const float*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
     }
     KCHK("attention"); return IT_OK;
 }
