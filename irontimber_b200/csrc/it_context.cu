@@ -377,6 +377,28 @@ IT_API size_t it_qmatrix_cols(const it_qmat* m) { return m ? m->cols : 0; }
 IT_API void it_qmatrix_destroy(it_qmat* m) { if (!m) return; cudaSetDevice(m->ctx->device); if (m->q) cudaFree(m->q); if (m->d) cudaFree(m->d); delete m; }
 
 // ---------------------------------------------------------------- q8 activation rows
+// Tensor map over the int8 rows for the tile kernel: boxes of 128 bytes (one 128-column block) x 64 rows, written to
+// shared memory with the 128-byte swizzle so that fragment loads are free of bank conflicts.
+static int make_q8_tensor_map(it_q8* q, size_t rows_alloc) {
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr; cudaDriverEntryPointQueryResult qres;
+        IT_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return it_fail(IT_ECUDA, "it_q8_create: the driver does not export cuTensorMapEncodeTiled");
+        encode = (encode_fn)fn;
+    }
+    const cuuint64_t dims[2] = { (cuuint64_t)q->max_n, (cuuint64_t)rows_alloc };
+    const cuuint64_t strides[1] = { (cuuint64_t)q->max_n };
+    const cuuint32_t box[2] = { 128, 64 };
+    const cuuint32_t estr[2] = { 1, 1 };
+    const CUresult r = encode(&q->tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, q->qs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return it_fail(IT_ECUDA, "it_q8_create: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return IT_OK;
+}
+
 IT_API int it_q8_create(it_ctx* c, size_t max_n, size_t max_tok, it_q8** out) {
     IT_CHECK_ARG(c && out, "it_q8_create: null argument");
     *out = nullptr;
@@ -384,10 +406,14 @@ IT_API int it_q8_create(it_ctx* c, size_t max_n, size_t max_tok, it_q8** out) {
     IT_CHECK_ARG(max_tok > 0 && max_tok <= 65535, "it_q8_create: bad row count %zu", max_tok);
     IT_CUDA(cudaSetDevice(c->device));
     it_q8* q = new it_q8(); q->ctx = c; q->max_n = max_n; q->max_tok = max_tok; q->n = 0; q->qs = nullptr; q->d = nullptr; q->sum128 = nullptr;
-    cudaError_t e = cudaMalloc(&q->qs, max_n * max_tok);
+    const size_t rows_alloc = max_tok < 64 ? 64 : max_tok;      // the tile kernel fetches boxes of 64 rows
+    cudaError_t e = cudaMalloc(&q->qs, max_n * rows_alloc);
+    if (e == cudaSuccess) e = cudaMemsetAsync(q->qs, 0, max_n * rows_alloc, c->stream);
     if (e == cudaSuccess) e = cudaMalloc(&q->d, max_n / 256 * max_tok * 4);
     if (e == cudaSuccess) e = cudaMalloc(&q->sum128, max_n / 128 * max_tok * 4);
     if (e != cudaSuccess) { it_q8_destroy(q); return it_fail(IT_ENOMEM, "it_q8_create: %s", cudaGetErrorString(e)); }
+    const int r = make_q8_tensor_map(q, rows_alloc);
+    if (r) { it_q8_destroy(q); return r; }
     *out = q; return IT_OK;
 }
 IT_API void it_q8_destroy(it_q8* q) { if (!q) return; cudaSetDevice(q->ctx->device); if (q->qs) cudaFree(q->qs); if (q->d) cudaFree(q->d); if (q->sum128) cudaFree(q->sum128); delete q; }

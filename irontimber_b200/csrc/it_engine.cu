@@ -113,7 +113,7 @@ IT_API int it_engine_create_synth(int device, const it_model_config* cfg, uint64
     take(L.conv, (size_t)IT_MAXT * cd); take(L.kcur, (size_t)IT_MAXT * kvd); take(L.vcur, (size_t)IT_MAXT * kvd); take(L.o, IT_MAXT * L.o_stride);
     take(L.beta, (size_t)IT_MAXT * nv); take(L.alpha, (size_t)IT_MAXT * nv); take(L.hrow, (size_t)IT_MAXT * e_); take(L.hprev, (size_t)e_);
     take(L.mh, (size_t)(IT_MAXT + 1) * e_); take(L.me, (size_t)IT_MAXT * e_); take(L.mcat, (size_t)IT_MAXT * 2 * e_); take(L.mx, (size_t)IT_MAXT * e_);
-    take(L.logits, IT_MAXT * L.logits_stride); take(L.amx, 64); L.total = o;
+    take(L.logits, IT_MAXLOGIT * L.logits_stride); take(L.amx, 64); L.total = o;
     int r = it_ctx_create(device, L.total, &e->ctx);
     if (r) { delete e; return r; }
     auto fail = [&](int code) { it_engine_destroy(e); return code; };
@@ -159,9 +159,9 @@ IT_API int it_engine_create_synth(int device, const it_model_config* cfg, uint64
         E_TRY(dev_alloc(e, (void**)&e->mkc, (size_t)c.ctx_len * kvd * 4, true)); E_TRY(dev_alloc(e, (void**)&e->mvc, (size_t)c.ctx_len * kvd * 4, true));
     }
     E_TRY(it_q8_create(e->ctx, (size_t)std::max(std::max(e_, ff), std::max(inner, nh * hd)), IT_MAXT, &e->q8));
-    E_TRY(dev_alloc(e, (void**)&e->toks_dev, 64 * sizeof(uint32_t), true));
+    E_TRY(dev_alloc(e, (void**)&e->toks_dev, (2 * IT_MAXT + 8) * sizeof(uint32_t), true));
     E_TRY(dev_alloc(e, (void**)&e->pos_dev, 64, true));
-    if (cudaHostAlloc((void**)&e->host_pin, 64 * sizeof(uint32_t), cudaHostAllocDefault) != cudaSuccess) return fail(it_fail(IT_ENOMEM, "engine: pinned staging allocation failed"));
+    if (cudaHostAlloc((void**)&e->host_pin, (2 * IT_MAXT + 8) * sizeof(uint32_t), cudaHostAllocDefault) != cudaSuccess) return fail(it_fail(IT_ENOMEM, "engine: pinned staging allocation failed"));
     if (cudaStreamSynchronize(e->ctx->stream) != cudaSuccess) return fail(it_fail(IT_ECUDA, "engine: weight generation failed: %s", cudaGetErrorString(cudaGetLastError())));
 #undef E_TRY
     *out = e; return IT_OK;

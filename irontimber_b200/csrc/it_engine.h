@@ -4,7 +4,8 @@
 #include "it_internal.h"
 #include <vector>
 
-#define IT_MAXT 8     // activation rows per pass (one mma N tile)
+#define IT_MAXT 64    // activation rows per pass: the prompt chunk of prefill_chunks (src/vk/mod.rs:130-134)
+#define IT_MAXLOGIT 8 // rows of a pass that can get logits and a greedy pick (verification passes)
 #define IT_MAXCK 3    // recurrent-state checkpoints per pass (rows 0..2 of a verification pass)
 
 struct it_layer {
@@ -42,7 +43,7 @@ struct it_engine {
     float *m_enorm, *m_hnorm, *m_attn_norm, *m_post_norm, *m_q_norm, *m_k_norm, *m_head_norm;
     float *mkc, *mvc;                                // f32 [ctx_len][kvd], slot = position - 1 (src/mtp.rs:95)
     it_q8* q8;
-    uint32_t* toks_dev;                              // IT_MAXT token ids of the current pass
+    uint32_t* toks_dev;                              // [0, IT_MAXT) token ids of the trunk pass, [IT_MAXT, 2*IT_MAXT) of the head pass
     int* pos_dev;                                    // position read by the recorded decode step
     it_arena_layout lay;
     float theta_scale;
@@ -50,7 +51,7 @@ struct it_engine {
     int pos, mpos;                                   // trunk position; next MTP position (src/vk/mod.rs: pos, mpos)
     size_t hp_off; int hp_n;                         // pending h rows for the next draft (arena offset, count)
     it_graph* step_graph;                            // recorded single-token greedy step
-    uint32_t* host_pin;                              // pinned staging for token ids / picks
+    uint32_t* host_pin;                              // pinned staging, laid out like toks_dev, plus the position at [2*IT_MAXT]
 };
 
 // derived sizes (src/model.rs:40-43)

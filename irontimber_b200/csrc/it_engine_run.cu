@@ -3,8 +3,8 @@
 // The schedule of one pass is the reference's run_chunk_v (src/vk/mod.rs:763-892): per layer norm -> Hadamard ->
 // grouped ternary matvecs -> delta-rule or attention block -> Hadamard -> output matvec (accumulating into the residual)
 // -> norm -> Hadamard -> gate / up -> silu*mul -> Hadamard -> down (accumulating).  Differences: the Hadamard is fused
-// with q8k quantisation (the CPU numerics), embeddings are gathered on the device, and up to eight rows share each
-// weight load in every pass, prefill included (the reference's batched tiles are a GCN-specific schedule).
+// with q8k quantisation (the CPU numerics), embeddings are gathered on the device, and a pass takes up to 64 rows (the
+// reference's prompt chunk): passes of more than eight rows run their ternary products on the tile kernel.
 #include "it_engine.h"
 #include "it_support.h"
 #include <algorithm>
@@ -39,7 +39,7 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
     float* A = cx->arena;
     const int e_ = c.n_embd, ff = c.n_ff, hd = c.head_dim, nh = c.n_head, nkv = c.n_head_kv, kvd = nkv * hd, qf = 2 * nh * hd;
     const int cd = it_cfg_conv_dim(c), inner = c.ssm_inner, nv = c.ssm_vheads, sd = c.ssm_state, nk = c.ssm_groups, qk = it_cfg_qk(c);
-    IT_CHECK_ARG(nt >= 1 && nt <= IT_MAXT && nck >= 0 && nck <= IT_MAXCK && nck < nt + 1, "engine: bad pass geometry");
+    IT_CHECK_ARG(nt >= 1 && nt <= IT_MAXT && nck >= 0 && nck <= IT_MAXCK && nck < nt + 1 && (logit_rows != 2 || nt <= IT_MAXLOGIT), "engine: bad pass geometry");
     if (e->pos + nt > c.ctx_len) return it_fail(IT_ESTATE, "engine: context full (%d + %d > %d)", e->pos, nt, c.ctx_len);   // src/vk/mod.rs:765
     const int* pos_ptr = from_dev ? e->pos_dev : nullptr; const int pos0 = from_dev ? 0 : e->pos;
     if (!from_dev) {
@@ -112,9 +112,9 @@ int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, 
     it_ctx* cx = e->ctx; const it_model_config& c = e->cfg; const it_arena_layout& L = e->lay; float* A = cx->arena;
     const int e_ = c.n_embd, ff = c.n_ff, hd = c.head_dim, nh = c.n_head, nkv = c.n_head_kv, kvd = nkv * hd, qf = 2 * nh * hd;
     IT_CHECK_ARG(nt >= 1 && nt <= IT_MAXT && pos0 >= 1 && pos0 + nt <= c.ctx_len, "engine: bad MTP pass geometry");
-    for (int t = 0; t < nt; t++) e->host_pin[32 + t] = toks[t];
-    IT_CUDA(cudaMemcpyAsync(e->toks_dev + 32, e->host_pin + 32, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
-    IT_TRY(it_sup_embed(cx, e->toks_dev + 32, e->tok_embd, e_, nt, A + L.me));
+    for (int t = 0; t < nt; t++) e->host_pin[IT_MAXT + t] = toks[t];
+    IT_CUDA(cudaMemcpyAsync(e->toks_dev + IT_MAXT, e->host_pin + IT_MAXT, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+    IT_TRY(it_sup_embed(cx, e->toks_dev + IT_MAXT, e->tok_embd, e_, nt, A + L.me));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + L.me, e_, e->m_enorm, e_, c.eps, A + L.mcat, 2 * e_, nt));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + hoff, e_, e->m_hnorm, e_, c.eps, A + L.mcat + e_, 2 * e_, nt));
     IT_TRY(it_matvec_q8(cx, e->m_eh, nt, L.mcat, 2 * e_, L.mx, e_, 0));
@@ -175,8 +175,8 @@ namespace {
 // one pass with the position read on the device, pick -> token slot and position + 1.
 int begin_device_decode(it_engine* e) {
     it_ctx* cx = e->ctx;
-    e->host_pin[16] = (uint32_t)e->pos;
-    IT_CUDA(cudaMemcpyAsync(e->pos_dev, e->host_pin + 16, 4, cudaMemcpyHostToDevice, cx->stream));
+    e->host_pin[2 * IT_MAXT] = (uint32_t)e->pos;
+    IT_CUDA(cudaMemcpyAsync(e->pos_dev, e->host_pin + 2 * IT_MAXT, 4, cudaMemcpyHostToDevice, cx->stream));
     if (e->step_graph) return IT_OK;
     IT_TRY(it_capture_begin(cx));
     k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 0);

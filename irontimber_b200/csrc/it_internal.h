@@ -1,5 +1,6 @@
 // Internal declarations shared by the translation units of libirontimber_cuda.so.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cstdint>
@@ -58,9 +59,10 @@ struct it_q8 {
     it_ctx* ctx;
     size_t max_n, max_tok;
     size_t n;               // width of the rows currently held
-    int8_t* qs;             // [max_tok][max_n]  (row stride = n of the last write)
+    int8_t* qs;             // [max_tok][max_n]  (row stride max_n whatever the current width)
     float* d;               // [max_tok][max_n/256]
     int32_t* sum128;        // [max_tok][max_n/128]
+    CUtensorMap tmap;       // qs as a 2-D byte tensor [rows][max_n], box 128 x 64, 128-byte swizzle (tile kernel)
 };
 
 struct it_graph { it_ctx* ctx; cudaGraph_t graph; cudaGraphExec_t exec; };
@@ -131,4 +133,6 @@ int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, in
 int it_matrix_synth_view(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, uint8_t* tiles, it_mat** out);
 // A view over `row_groups` consecutive row groups starting at `tiles` (e.g. several stacked matrices seen as one).
 int it_matrix_view(it_ctx* ctx, size_t rows, size_t cols, uint8_t* tiles, it_mat** out);
+// Tile kernel for more than eight activation rows (it_matmul_t2.cu); same arithmetic as the matvec kernel.
+int it_matmul_t2_launch(it_ctx* ctx, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum);
 int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d);

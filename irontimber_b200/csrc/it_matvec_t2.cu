@@ -28,6 +28,7 @@
 // Algorithmic bytes per launch: rows*cols/128*34 (codes + f16 scales) + ntok*(cols + 4*cols/256)
 // + 4*ntok*rows (x2 when accumulating).  The kernel is HBM-bound.
 #include "it_internal.h"
+#include "it_pipe.cuh"
 
 namespace {
 
@@ -35,41 +36,7 @@ constexpr int CWARPS = 8;                         // warps per consumer group = 
 constexpr int CHUNK_BYTES = CWARPS * IT_TILE_BYTES;
 constexpr int TERM_PAD = 4;                       // floats of padding between token planes
 constexpr int XROW_PAD = 16;                      // bytes of padding between staged activation rows
-constexpr long long WAIT_CLOCKS = 1ll << 31;      // about one second
 constexpr int SM_SMEM = 227 * 1024;               // shared memory one SM can give to CTAs
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count)); }
-__device__ __forceinline__ void mbar_arrive(unsigned bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory"); }
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory"); }
-__device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after WAIT_CLOCKS, or as soon as another thread of the CTA has given up.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag) {
-    if (mbar_test(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-        for (int i = 0; i < 64; i++) if (mbar_test(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CLOCKS) { *abort_flag = 1; atomicExch(error_flag, 1); return false; }
-    }
-}
-__device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(smem)), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
-template <int NTHREADS> __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" :: "n"(NTHREADS) : "memory"); }
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 struct Smem {   // byte offsets into dynamic shared memory
     int ring, x, dx, s128, terms, bars, flag, total, plane, xrow;
@@ -334,6 +301,8 @@ int dispatch(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, float* y, 
     // activation rows are processed in groups of up to eight (one mma N tile); wide matrices use smaller
     // groups so that the staged rows, the per-block terms and a ring of at least four chunks fit one SM
     const int nb = (int)(w->cols / 128);
+    // more than one mma N tile of activation rows: the tile kernel reads the weights once per 64 rows
+    if (!SUMI && ntok > 8) return it_matmul_t2_launch(c, w, (int)ntok, x, y, y_stride, accum);
     size_t group = 8;
     while (group > 1 && smem_layout((int)group, nb, 4, SUMI ? 0 : 2).total > SM_SMEM - 1024) group /= 2;
     for (size_t t0 = 0; t0 < ntok; t0 += group) {

@@ -22,7 +22,7 @@ def pair(orc):
     model.close(); eng.close()
 
 
-PROMPT = [5, 77, 901, 13, 640, 2, 999, 0, 321, 45, 600]     # 11 tokens: one full pass of 8 rows and one of 3
+PROMPT = [5, 77, 901, 13, 640, 2, 999, 0, 321, 45, 600]     # 11 tokens: one pass of 11 rows through the tile kernel
 
 
 def test_prompt_logits_and_state_bit_exact(orc, pair):
@@ -34,7 +34,7 @@ def test_prompt_logits_and_state_bit_exact(orc, pair):
         want = m.forward_token(st, t, i + 1 == len(PROMPT), orc.DEVICE_ORDER)
     assert np.array_equal(bits(lg), bits(want))
     assert eng.pos == m.state_pos(st) == len(PROMPT)
-    assert np.array_equal(bits(eng.hidden(2)), bits(m.state_h(st)))      # row 2 of the second pass = last token
+    assert np.array_equal(bits(eng.hidden(len(PROMPT) - 1)), bits(m.state_h(st)))      # last row of the pass = last token
     for il in range(eng.cfg.n_layer):
         if eng.cfg.is_recurrent(il):
             assert np.array_equal(bits(eng.state(il, 0)), bits(m.state_read(st, il, 0))), f"conv state layer {il}"
@@ -42,7 +42,7 @@ def test_prompt_logits_and_state_bit_exact(orc, pair):
         else:
             assert np.array_equal(bits(eng.state(il, 2)), bits(m.state_read(st, il, 2))), f"K cache layer {il}"
             assert np.array_equal(bits(eng.state(il, 3)), bits(m.state_read(st, il, 3))), f"V cache layer {il}"
-    # token by token gives the same bits as the 8-row passes
+    # token by token gives the same bits as the multi-row pass
     eng.reset()
     for t in PROMPT:
         lg1 = eng.eval([t])
@@ -96,6 +96,33 @@ def test_speculative_decode_equals_plain_greedy_with_oracle_counts(orc, pair):
     w._next_wrong = lambda: plain[idx[0]]
     out, st = E.greedy_mtp(w, PROMPT, 12)
     assert out == plain[:12] and st["rejected"] == 0 and st["accepted"] == st["drafted"] > 0
+
+
+def test_long_prompt_in_64_row_passes_bit_exact(orc):
+    """A 75-token prompt runs as one pass of 64 rows and one of 11 (prefill_chunks, src/vk/mod.rs:130-134): logits, the
+    greedy continuation and the speculative loop with its head catch-up across passes equal the token-by-token oracle."""
+    from irontimber_b200.engine import CudaEngine, ModelConfig
+    eng = CudaEngine(tiny_config(ModelConfig, ctx_len=128), seed=23, with_mtp=True)
+    m = oracle_model_from_engine(orc, eng, with_mtp=True)
+    try:
+        prompt = [int(t) for t in np.random.default_rng(9).integers(0, eng.cfg.n_vocab, 75)]
+        lg = eng.eval(prompt)
+        st = m.new_state()
+        for i, t in enumerate(prompt):
+            want = m.forward_token(st, t, i + 1 == len(prompt), orc.DEVICE_ORDER)
+        assert np.array_equal(bits(lg), bits(want))
+        for il in range(eng.cfg.n_layer):
+            kinds = (0, 1) if eng.cfg.is_recurrent(il) else (2, 3)
+            for kind in kinds:
+                assert np.array_equal(bits(eng.state(il, kind)), bits(m.state_read(st, il, kind))), f"state {kind} of layer {il}"
+        plain = orc.generate_greedy(m, prompt, 10, orc.DEVICE_ORDER)
+        eng.reset()
+        assert eng.generate(prompt, 10) == plain
+        want_out, want_stats = orc.greedy_mtp(orc.CpuMtp(m, orc.DEVICE_ORDER), prompt, 10)
+        out, stats = eng.generate_mtp(prompt, 10)
+        assert out == plain == want_out and stats == want_stats
+    finally:
+        m.close(); eng.close()
 
 
 def test_engine_rejects_bad_requests_without_touching_state(pair):
