@@ -52,6 +52,14 @@ float* it_arena_ptr(it_ctx* ctx);                           /* device pointer of
 size_t it_arena_floats(it_ctx* ctx);
 int it_arena_write(it_ctx* ctx, size_t off, const void* host, size_t n_floats); /* Ctx::upload,   src/vk/mod.rs:427 */
 int it_arena_read(it_ctx* ctx, size_t off, void* host, size_t n_floats);        /* Ctx::download */
+/* Peers: one process per GPU, up to 8.  it_ctx_ipc_handle writes the 64-byte CUDA IPC handle of this context's arena;
+ * the host exchanges the handles (any transport) and gives every context all of them, ordered by rank (its own entry
+ * is ignored).  Every rank must create its arena with the same size and issue the same sequence of sharded ops; a
+ * sharded op completes on a rank only when every rank's slice has arrived in its arena (bounded wait, IT_ETIMEOUT).
+ * No counterpart in the reference (single GPU). */
+int it_ctx_ipc_handle(it_ctx* ctx, void* handle64);
+int it_ctx_attach_peers(it_ctx* ctx, int rank, int world, const void* handles);
+int it_ctx_world(const it_ctx* ctx);
 int it_arena_zero(it_ctx* ctx, size_t off, size_t n_floats);                    /* zero_state,    src/vk/mod.rs:645 */
 
 /* Record the ops issued between begin and end into a CUDA graph and replay them with one launch.
@@ -76,6 +84,15 @@ int it_matrix_upload_packed2(it_ctx* ctx, const uint32_t* words, const float* sc
 /* Synthetic matrix generated on the device: codes uniform over {0,1,2} (or {0,1,2,3} when
  * four_codes != 0), f16 scales uniform in [0.01, 0.05], from a counter hash of (seed, index). */
 int it_matrix_synth(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, it_mat** out);
+/* Row shards (no counterpart in the reference, which runs on one GPU; every output row of its matvec is an independent
+ * dot with the shared activation row, src/cpu.rs:31-34, which is what makes the split exact).  it_shard_range gives the
+ * rows of rank `rank` of `world` (rows must divide evenly; pure host arithmetic).  it_matrix_set_shard marks an uploaded
+ * matrix as rows [row0, row0 + rows) of a logical matrix of total_rows rows; it_matrix_synth_rows generates exactly those
+ * rows of the matrix that it_matrix_synth would generate for (seed, total_rows, cols).  it_matvec_t2 on a shard writes
+ * its results at their positions in the full output row and pushes them into the arena of every attached peer. */
+int it_shard_range(size_t rows, int rank, int world, size_t* row0, size_t* nrows);
+int it_matrix_set_shard(it_mat* m, size_t row0, size_t total_rows);
+int it_matrix_synth_rows(it_ctx* ctx, uint64_t seed, size_t total_rows, size_t cols, int four_codes, size_t row0, size_t nrows, it_mat** out);
 /* Decodes the device layout back to raw PQ2_0 rows (rows*cols/128*34 bytes). */
 int it_matrix_download_pq2(it_ctx* ctx, const it_mat* m, uint8_t* raw);
 size_t it_matrix_rows(const it_mat* m);
@@ -159,6 +176,10 @@ typedef struct it_engine it_engine;
  * of `seed`).  with_mtp != 0 adds a NextN head.  Stands where VkEngine::new_with_mtp stands (src/vk/mod.rs:494-631);
  * geometry is validated before the device is touched (validate_geometry, src/vk/mod.rs:207). */
 int it_engine_create_synth(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, it_engine** out);
+/* The same model with the trunk matrices and the LM head split by output rows over `world` ranks (this engine holds the
+ * rows of `rank`); activations, recurrent state, KV cache and the NextN head stay replicated and every rank computes
+ * the same tokens.  Attach the peers of it_engine_ctx() before the first pass. */
+int it_engine_create_synth_sharded(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, int rank, int world, it_engine** out);
 void it_engine_destroy(it_engine* e);
 it_ctx* it_engine_ctx(it_engine* e);
 /* Read-back of weights and state for parity tests.  Ternary / Q8_0 tensors come back as raw ggml rows, f32 tensors as f32. */

@@ -32,6 +32,12 @@ SIGNATURES = {
     "it_matrix_upload_pq2": (C.c_int, [P, P, c_size, c_size, C.POINTER(P)]),
     "it_matrix_upload_packed2": (C.c_int, [P, P, P, c_size, c_size, C.POINTER(P)]),
     "it_matrix_synth": (C.c_int, [P, C.c_uint64, c_size, c_size, C.c_int, C.POINTER(P)]),
+    "it_shard_range": (C.c_int, [c_size, C.c_int, C.c_int, C.POINTER(c_size), C.POINTER(c_size)]),
+    "it_matrix_set_shard": (C.c_int, [P, c_size, c_size]),
+    "it_matrix_synth_rows": (C.c_int, [P, C.c_uint64, c_size, c_size, C.c_int, c_size, c_size, C.POINTER(P)]),
+    "it_ctx_ipc_handle": (C.c_int, [P, P]),
+    "it_ctx_attach_peers": (C.c_int, [P, C.c_int, C.c_int, P]),
+    "it_ctx_world": (C.c_int, [P]),
     "it_matrix_download_pq2": (C.c_int, [P, P, P]),
     "it_matrix_rows": (c_size, [P]),
     "it_matrix_cols": (c_size, [P]),
@@ -54,6 +60,7 @@ SIGNATURES = {
     "it_argmax": (C.c_int, [P, c_size, c_size, c_size]),
     "it_argmax_static": (C.c_int, [P, P, c_size, P]),
     "it_engine_create_synth": (C.c_int, [C.c_int, P, C.c_uint64, C.c_int, C.POINTER(P)]),
+    "it_engine_create_synth_sharded": (C.c_int, [C.c_int, P, C.c_uint64, C.c_int, C.c_int, C.c_int, C.POINTER(P)]),
     "it_engine_destroy": (None, [P]),
     "it_engine_ctx": (P, [P]),
     "it_engine_tensor_bytes": (C.c_int, [P, C.c_int, C.c_int, C.POINTER(c_size)]),

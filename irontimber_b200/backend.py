@@ -156,6 +156,23 @@ class CudaBackend:
         _lib.check(self.L.it_matrix_synth(self.ctx, seed, rows, cols, int(four_codes), C.byref(h)))
         return TernaryMatrix(self, h)
 
+    def mat_synth_rows(self, seed, total_rows, cols, row0, nrows, four_codes=False):
+        """Rows [row0, row0 + nrows) of the synthetic matrix (seed, total_rows, cols), marked as a row shard."""
+        h = C.c_void_p()
+        _lib.check(self.L.it_matrix_synth_rows(self.ctx, seed, total_rows, cols, int(four_codes), row0, nrows, C.byref(h)))
+        return TernaryMatrix(self, h)
+
+    def mat_shard(self, raw_pq2, nrows, cols, row0, total_rows):
+        """Uploaded rows [row0, row0 + nrows) of a logical matrix of total_rows rows."""
+        m = self.mat(raw_pq2, nrows, cols)
+        _lib.check(self.L.it_matrix_set_shard(m.handle, row0, total_rows))
+        return m
+
+    # ---- peers (one process per GPU) ----------------------------------------------------------------
+    def attach_peers(self, rank=0, world=1, group=None):
+        from .sharding import attach_peers
+        attach_peers(self.L, self.ctx, rank, world, group)
+
     def qmat(self, raw_q8_0, rows, cols):
         raw = np.ascontiguousarray(raw_q8_0, np.uint8)
         if raw.size != rows * (cols // 32) * 34:

@@ -17,10 +17,11 @@ IT_API int it_version(void) { return 1; }
 // src/sampling.rs:43).  Codes: one hash per two elements, 32 bits each, code = v % 3 (or v % 4).
 // Scales: u = top 24 bits of hash(seed ^ 0x5ca1e5, block) / 2^24, d = f16(0.01 + 0.04*u) with
 // separately rounded multiply and add.
-__global__ void k_synth_pq2(uint64_t seed, size_t rows, size_t cols, int four, uint8_t* raw) {
+__global__ void k_synth_pq2(uint64_t seed, size_t rows, size_t cols, int four, uint8_t* raw, size_t row0) {
     size_t bpr = cols / 128, nblk = rows * bpr;
-    for (size_t blk = blockIdx.x * (size_t)blockDim.x + threadIdx.x; blk < nblk; blk += (size_t)gridDim.x * blockDim.x) {
-        unsigned short* o = reinterpret_cast<unsigned short*>(raw + blk * 34);   // 34-byte blocks are 2-byte aligned
+    for (size_t lblk = blockIdx.x * (size_t)blockDim.x + threadIdx.x; lblk < nblk; lblk += (size_t)gridDim.x * blockDim.x) {
+        unsigned short* o = reinterpret_cast<unsigned short*>(raw + lblk * 34);   // 34-byte blocks are 2-byte aligned
+        const size_t blk = lblk + row0 * bpr;                                     // block index in the full matrix
         const uint64_t hs = it_hash(seed ^ 0x5ca1e5ull, blk);
         const float u = __fmul_rn((float)(uint32_t)(hs >> 40), 1.0f / 16777216.0f);
         o[0] = __half_as_ushort(__float2half_rn(__fadd_rn(0.01f, __fmul_rn(0.04f, u))));
@@ -37,8 +38,8 @@ __global__ void k_synth_pq2(uint64_t seed, size_t rows, size_t cols, int four, u
         }
     }
 }
-int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, uint8_t* raw_dev) {
-    k_synth_pq2<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, rows, cols, four_codes, raw_dev);
+int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, uint8_t* raw_dev, size_t row0) {
+    k_synth_pq2<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, rows, cols, four_codes, raw_dev, row0);
     IT_LAUNCH_CHECK("synth_pq2"); return IT_OK;
 }
 
@@ -130,9 +131,10 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     if (prop.major != 10) return it_fail(IT_ESTATE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
     it_ctx* c = new it_ctx(); c->device = device; c->arena = nullptr; c->arena_floats = arena_floats; c->sm_count = prop.multiProcessorCount;
     c->argmax_partials = nullptr; c->argmax_counter = nullptr; c->stream = nullptr; c->capturing = false;
+    c->peers_dev = nullptr; c->rank = 0; c->world = 1; for (int i = 0; i < IT_MAX_PEERS; i++) c->peer_base[i] = nullptr;
     c->pdl_safe_q8 = nullptr; c->splitk_terms = nullptr; c->splitk_counters = nullptr; c->error_flag_host = nullptr; c->error_flag_dev = nullptr;
     cudaError_t e1 = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
-    cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_floats * sizeof(float)) : e1;
+    cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_floats * sizeof(float) + IT_ARENA_TAIL) : e1;
     cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc(&c->argmax_partials, IT_ARGMAX_MAX_BLOCKS * sizeof(unsigned long long)) : e2;
     cudaError_t e4 = e3 == cudaSuccess ? cudaMalloc(&c->argmax_counter, 256) : e3;
     if (e4 == cudaSuccess) e4 = cudaMalloc(&c->splitk_terms, (size_t)c->sm_count * IT_SPLITK_SLOT_BYTES);
@@ -141,7 +143,7 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     if (e4 == cudaSuccess) e4 = cudaHostAlloc(&c->error_flag_host, sizeof(int), cudaHostAllocMapped);
     if (e4 == cudaSuccess) { *c->error_flag_host = 0; e4 = cudaHostGetDevicePointer(&c->error_flag_dev, c->error_flag_host, 0); }
     if (e4 != cudaSuccess) { it_ctx_destroy(c); return it_fail(e4 == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_ctx_create: %s", cudaGetErrorString(e4)); }
-    cudaMemsetAsync(c->arena, 0, arena_floats * sizeof(float), c->stream);
+    cudaMemsetAsync(c->arena, 0, arena_floats * sizeof(float) + IT_ARENA_TAIL, c->stream);
     cudaMemsetAsync(c->argmax_counter, 0, 256, c->stream);
     IT_CUDA(cudaStreamSynchronize(c->stream));
     *out = c; return IT_OK;
@@ -150,6 +152,8 @@ IT_API void it_ctx_destroy(it_ctx* c) {
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    for (int i = 0; i < IT_MAX_PEERS; i++) if (c->peer_base[i]) cudaIpcCloseMemHandle(c->peer_base[i]);
+    if (c->peers_dev) cudaFree(c->peers_dev);
     for (auto& kv : c->signs) cudaFree(kv.second);
     if (c->splitk_terms) cudaFree(c->splitk_terms);
     if (c->splitk_counters) cudaFree(c->splitk_counters);
@@ -160,6 +164,47 @@ IT_API void it_ctx_destroy(it_ctx* c) {
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
+// ---------------------------------------------------------------- peers (one process per GPU)
+IT_API int it_ctx_ipc_handle(it_ctx* c, void* handle64) {
+    IT_CHECK_ARG(c && handle64, "it_ctx_ipc_handle: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are exchanged as 64-byte blobs");
+    IT_CUDA(cudaSetDevice(c->device));
+    IT_CUDA(cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle64), c->arena));
+    return IT_OK;
+}
+IT_API int it_ctx_attach_peers(it_ctx* c, int rank, int world, const void* handles) {
+    IT_CHECK_ARG(c && handles, "it_ctx_attach_peers: null argument");
+    IT_CHECK_ARG(world >= 1 && world <= IT_MAX_PEERS && rank >= 0 && rank < world, "it_ctx_attach_peers: bad rank %d of %d", rank, world);
+    if (c->peers_dev) return it_fail(IT_ESTATE, "it_ctx_attach_peers: peers are already attached");
+    if (c->capturing) return it_fail(IT_ESTATE, "it_ctx_attach_peers: not allowed while recording a graph");
+    IT_CUDA(cudaSetDevice(c->device));
+    it_peers P; memset(&P, 0, sizeof P);
+    P.rank = rank; P.world = world;
+    const size_t tail = c->arena_floats * sizeof(float);
+    for (int p = 0; p < world; p++) {
+        char* base = reinterpret_cast<char*>(c->arena);
+        if (p != rank) {
+            cudaIpcMemHandle_t h; memcpy(&h, static_cast<const char*>(handles) + 64 * p, 64);
+            void* mapped = nullptr;
+            cudaError_t e = cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                for (int q = 0; q < p; q++) if (c->peer_base[q]) { cudaIpcCloseMemHandle(c->peer_base[q]); c->peer_base[q] = nullptr; }
+                return it_fail(IT_ECUDA, "it_ctx_attach_peers: cannot map the arena of rank %d: %s", p, cudaGetErrorString(e));
+            }
+            c->peer_base[p] = mapped; base = static_cast<char*>(mapped);
+        }
+        P.arena[p] = reinterpret_cast<float*>(base);
+        P.flags[p] = reinterpret_cast<unsigned*>(base + tail);
+    }
+    P.done = P.flags[rank] + IT_MAX_PEERS; P.epoch = P.flags[rank] + IT_MAX_PEERS + 1;
+    IT_CUDA(cudaMalloc(&c->peers_dev, sizeof P));
+    IT_CUDA(cudaMemcpyAsync(c->peers_dev, &P, sizeof P, cudaMemcpyHostToDevice, c->stream));
+    IT_CUDA(cudaStreamSynchronize(c->stream));
+    c->rank = rank; c->world = world;
+    return IT_OK;
+}
+IT_API int it_ctx_world(const it_ctx* c) { return c ? c->world : 0; }
+
 IT_API int it_sync(it_ctx* c) {
     IT_CHECK_ARG(c, "it_sync: null context");
     if (c->capturing) return it_fail(IT_ESTATE, "it_sync: not allowed while recording a graph");
@@ -254,6 +299,7 @@ static int mat_alloc(it_ctx* c, size_t rows, size_t cols, it_mat** out, const ch
     IT_CUDA(cudaSetDevice(c->device));
     it_mat* m = new it_mat(); m->ctx = c; m->rows = rows; m->cols = cols; m->row_groups = (rows + 31) / 32;
     m->bytes = m->row_groups * (cols / 128) * IT_TILE_BYTES; m->tiles = nullptr; m->owns_tiles = true;
+    m->sharded = false; m->map.nseg = 0; m->out_rows = rows;
     cudaError_t e = cudaMalloc(&m->tiles, m->bytes);
     if (e != cudaSuccess) { delete m; return it_fail(IT_ENOMEM, "%s: cudaMalloc(%zu): %s", who, m->bytes, cudaGetErrorString(e)); }
     *out = m; return IT_OK;
@@ -296,17 +342,46 @@ IT_API int it_matrix_synth(it_ctx* c, uint64_t seed, size_t rows, size_t cols, i
     if (e != cudaSuccess || r != IT_OK) { it_matrix_destroy(*out); *out = nullptr; return r ? r : it_fail(e == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_matrix_synth: %s", cudaGetErrorString(e)); }
     return IT_OK;
 }
+// ---------------------------------------------------------------- row shards
+IT_API int it_shard_range(size_t rows, int rank, int world, size_t* row0, size_t* nrows) {
+    IT_CHECK_ARG(row0 && nrows, "it_shard_range: null output");
+    IT_CHECK_ARG(world >= 1 && world <= IT_MAX_PEERS && rank >= 0 && rank < world, "it_shard_range: bad rank %d of %d", rank, world);
+    IT_CHECK_ARG(rows % (size_t)world == 0, "it_shard_range: %zu rows do not split evenly over %d ranks", rows, world);
+    *nrows = rows / (size_t)world; *row0 = *nrows * (size_t)rank;
+    return IT_OK;
+}
+IT_API int it_matrix_set_shard(it_mat* m, size_t row0, size_t total_rows) {
+    IT_CHECK_ARG(m, "it_matrix_set_shard: null matrix");
+    IT_CHECK_ARG(row0 + m->rows <= total_rows && total_rows <= (1u << 30), "it_matrix_set_shard: rows [%zu, %zu) fall outside a matrix of %zu rows", row0, row0 + m->rows, total_rows);
+    m->sharded = true; m->map.nseg = 1; m->map.start[0] = 0; m->map.delta[0] = (int)row0; m->out_rows = total_rows;
+    return IT_OK;
+}
+IT_API int it_matrix_synth_rows(it_ctx* c, uint64_t seed, size_t total_rows, size_t cols, int four_codes, size_t row0, size_t nrows, it_mat** out) {
+    IT_CHECK_ARG(out, "it_matrix_synth_rows: null output");
+    *out = nullptr;
+    IT_CHECK_ARG(nrows > 0 && row0 + nrows <= total_rows, "it_matrix_synth_rows: rows [%zu, %zu) fall outside a matrix of %zu rows", row0, row0 + nrows, total_rows);
+    int r = mat_alloc(c, nrows, cols, out, "it_matrix_synth_rows"); if (r) return r;
+    size_t nbytes = nrows * (cols / 128) * 34; uint8_t* tmp = nullptr;
+    cudaError_t e = cudaMalloc(&tmp, nbytes);
+    if (e == cudaSuccess) { r = it_launch_synth_pq2(c, seed, nrows, cols, four_codes, tmp, row0); if (r == IT_OK) r = it_launch_repack_pq2(c, tmp, nrows, cols, (*out)->tiles);
+        if (r == IT_OK) e = cudaStreamSynchronize(c->stream); }
+    if (tmp) cudaFree(tmp);
+    if (e != cudaSuccess || r != IT_OK) { it_matrix_destroy(*out); *out = nullptr; return r ? r : it_fail(e == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_matrix_synth_rows: %s", cudaGetErrorString(e)); }
+    return it_matrix_set_shard(*out, row0, total_rows);
+}
+
 int it_matrix_view(it_ctx* c, size_t rows, size_t cols, uint8_t* tiles, it_mat** out) {
     IT_CHECK_ARG(c && out && tiles && rows > 0 && cols % 128 == 0, "it_matrix_view: bad argument");
     it_mat* m = new it_mat(); m->ctx = c; m->rows = rows; m->cols = cols; m->row_groups = (rows + 31) / 32;
     m->bytes = m->row_groups * (cols / 128) * IT_TILE_BYTES; m->tiles = tiles; m->owns_tiles = false;
+    m->sharded = false; m->map.nseg = 0; m->out_rows = rows;
     *out = m; return IT_OK;
 }
-int it_matrix_synth_view(it_ctx* c, uint64_t seed, size_t rows, size_t cols, uint8_t* tiles, it_mat** out) {
+int it_matrix_synth_view(it_ctx* c, uint64_t seed, size_t rows, size_t cols, uint8_t* tiles, it_mat** out, size_t row0) {
     int r = it_matrix_view(c, rows, cols, tiles, out); if (r) return r;
     size_t nbytes = rows * (cols / 128) * 34; uint8_t* tmp = nullptr;
     cudaError_t e = cudaMalloc(&tmp, nbytes);
-    if (e == cudaSuccess) { r = it_launch_synth_pq2(c, seed, rows, cols, 0, tmp); if (r == IT_OK) r = it_launch_repack_pq2(c, tmp, rows, cols, tiles);
+    if (e == cudaSuccess) { r = it_launch_synth_pq2(c, seed, rows, cols, 0, tmp, row0); if (r == IT_OK) r = it_launch_repack_pq2(c, tmp, rows, cols, tiles);
         if (r == IT_OK) e = cudaStreamSynchronize(c->stream); }
     if (tmp) cudaFree(tmp);
     if (e != cudaSuccess || r != IT_OK) { it_matrix_destroy(*out); *out = nullptr; return r ? r : it_fail(e == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_matrix_synth_view: %s", cudaGetErrorString(e)); }

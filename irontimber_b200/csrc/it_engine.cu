@@ -42,21 +42,38 @@ int synth_f32(it_engine* e, int layer, int tensor, size_t n, float** out) {
     k_synth_f32<<<e->ctx->sm_count * 4, 256, 0, e->ctx->stream>>>(tensor_seed(e->seed, layer, tensor), n, r.lo, r.hi - r.lo, *out);
     IT_LAUNCH_CHECK("synth_f32"); return IT_OK;
 }
+// Trunk matrices are split by output rows over the ranks (every row is an independent dot with the replicated
+// activations, src/cpu.rs:31-34): this engine generates and holds rows [rank*rows/world, (rank+1)*rows/world) only.
 int synth_mat(it_engine* e, int layer, int tensor, size_t rows, size_t cols, it_mat** out) {
-    return it_matrix_synth(e->ctx, tensor_seed(e->seed, layer, tensor), rows, cols, 0, out);
+    if (e->world == 1) return it_matrix_synth(e->ctx, tensor_seed(e->seed, layer, tensor), rows, cols, 0, out);
+    size_t row0, n; IT_TRY(it_shard_range(rows, e->rank, e->world, &row0, &n));
+    return it_matrix_synth_rows(e->ctx, tensor_seed(e->seed, layer, tensor), rows, cols, 0, row0, n, out);
 }
 // Several ternary matrices with the same column count, stacked row-wise in one allocation: `stack` sees all rows,
-// parts[i] is a view of tensor i.  Row counts must be multiples of 32 so that every part starts on a row group.
+// parts[i] is a view of tensor i.  Row counts (per rank) must be multiples of 32 so that every part starts on a row
+// group.  On a sharded engine the stack holds this rank's rows of every part, and its row map sends each part's rows
+// to their place in the full stacked output.
 int synth_stack(it_engine* e, int layer, int n, const int* tensors, const size_t* rows, size_t cols, it_mat** parts, it_mat** stack) {
-    size_t total = 0; for (int i = 0; i < n; i++) { if (rows[i] % 32) return it_fail(IT_EINVAL, "engine: stacked matrix with %zu rows is not a multiple of 32", rows[i]); total += rows[i]; }
+    size_t total = 0, full = 0, local[4], row0[4];
+    for (int i = 0; i < n; i++) {
+        IT_TRY(it_shard_range(rows[i], e->rank, e->world, &row0[i], &local[i]));
+        if (local[i] % 32) return it_fail(IT_EINVAL, "engine: stacked matrix with %zu rows per rank is not a multiple of 32", local[i]);
+        total += local[i]; full += rows[i];
+    }
     uint8_t* buf = nullptr;
     IT_TRY(dev_alloc(e, (void**)&buf, total / 32 * (cols / 128) * IT_TILE_BYTES, false));
     size_t off = 0;
     for (int i = 0; i < n; i++) {
-        IT_TRY(it_matrix_synth_view(e->ctx, tensor_seed(e->seed, layer, tensors[i]), rows[i], cols, buf + off / 32 * (cols / 128) * IT_TILE_BYTES, &parts[i]));
-        off += rows[i];
+        IT_TRY(it_matrix_synth_view(e->ctx, tensor_seed(e->seed, layer, tensors[i]), local[i], cols, buf + off / 32 * (cols / 128) * IT_TILE_BYTES, &parts[i], row0[i]));
+        off += local[i];
     }
-    return it_matrix_view(e->ctx, total, cols, buf, stack);
+    IT_TRY(it_matrix_view(e->ctx, total, cols, buf, stack));
+    if (e->world > 1) {
+        it_mat* m = *stack; m->sharded = true; m->out_rows = full; m->map.nseg = n;
+        size_t lo = 0, go = 0;
+        for (int i = 0; i < n; i++) { m->map.start[i] = (int)lo; m->map.delta[i] = (int)(go + row0[i]) - (int)lo; lo += local[i]; go += rows[i]; }
+    }
+    return IT_OK;
 }
 int synth_qmat(it_engine* e, int tensor, size_t rows, size_t cols, it_qmat** out) {
     return it_qmatrix_synth(e->ctx, tensor_seed(e->seed, -1, tensor), rows, cols, out);
@@ -94,14 +111,25 @@ int validate(const it_model_config* c) {
 }  // namespace
 
 IT_API int it_engine_create_synth(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, it_engine** out) {
+    return it_engine_create_synth_sharded(device, cfg, seed, with_mtp, 0, 1, out);
+}
+
+IT_API int it_engine_create_synth_sharded(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, int rank, int world, it_engine** out) {
     IT_CHECK_ARG(out, "it_engine_create_synth: out is null");
     *out = nullptr;
     IT_TRY(validate(cfg));
+    IT_CHECK_ARG(world >= 1 && world <= IT_MAX_PEERS && rank >= 0 && rank < world, "it_engine_create_synth_sharded: bad rank %d of %d", rank, world);
+    {   // every trunk matrix must split evenly, stacked ones on row-group boundaries
+        const int kvd_ = cfg->n_head_kv * cfg->head_dim, qf_ = 2 * cfg->n_head * cfg->head_dim, cd_ = it_cfg_conv_dim(*cfg);
+        const int stacked[] = { cfg->n_ff, cd_, cfg->ssm_inner, qf_, kvd_ };
+        for (int v : stacked) IT_CHECK_ARG(v % (32 * world) == 0, "engine: a stacked matrix of %d rows does not split over %d ranks on 32-row boundaries", v, world);
+        IT_CHECK_ARG(cfg->n_embd % world == 0 && cfg->n_vocab % world == 0, "engine: n_embd and n_vocab must be multiples of the rank count %d", world);
+    }
     const it_model_config& c = *cfg;
     const int e_ = c.n_embd, ff = c.n_ff, hd = c.head_dim, nh = c.n_head, nkv = c.n_head_kv, kvd = nkv * hd, qf = 2 * nh * hd;
     const int cd = it_cfg_conv_dim(c), inner = c.ssm_inner, nv = c.ssm_vheads, sd = c.ssm_state;
     it_engine* e = new it_engine();
-    e->ctx = nullptr; e->cfg = c; e->seed = seed; e->has_mtp = with_mtp != 0; e->output = nullptr; e->q8 = nullptr; e->step_graph = nullptr; e->host_pin = nullptr;
+    e->ctx = nullptr; e->cfg = c; e->seed = seed; e->has_mtp = with_mtp != 0; e->rank = rank; e->world = world; e->output = nullptr; e->q8 = nullptr; e->step_graph = nullptr; e->host_pin = nullptr;
     e->m_eh = e->m_q = e->m_k = e->m_v = e->m_o = e->m_gate = e->m_up = e->m_down = nullptr;
     e->pos = 0; e->mpos = 1; e->hp_off = 0; e->hp_n = 0;
     // arena layout

@@ -35,6 +35,7 @@ struct it_engine {
     it_model_config cfg;
     uint64_t seed;
     bool has_mtp;
+    int rank, world;                                 // row shard of the trunk matrices held by this engine (0 of 1: everything)
     std::vector<it_layer> layers;
     float *tok_embd, *output_norm;
     it_mat* output;

@@ -37,6 +37,26 @@ int it_fail(int code, const char* fmt, ...);
 #define IT_TILE_ROWS 32
 #define IT_TILE_BYTES 1088
 
+// ---- row sharding over several GPUs -----------------------------------------------------------------------------
+// A matrix may hold only some rows of a logical matrix; its results land at the rows' positions in the full output and
+// are pushed into the arena of every attached peer (one process per GPU, arenas mapped through CUDA IPC).
+#define IT_MAX_PEERS 8
+struct it_peers {                       // lives in device memory, one per attached context
+    float* arena[IT_MAX_PEERS];         // every rank's arena as mapped into this process (own arena at [rank])
+    unsigned* flags[IT_MAX_PEERS];      // every rank's flag words: flags[p][r] is written by rank r and read by rank p
+    int rank, world;
+    unsigned* done;                     // CTAs of the running sharded kernel that have finished their stores
+    unsigned* epoch;                    // sharded ops completed so far (the same sequence on every rank)
+};
+// Local row r belongs to the last segment with start[s] <= r and lands at output row r + delta[s].
+struct it_rowmap { int nseg; int start[4]; int delta[4]; };
+__host__ __device__ static inline int it_map_row(const it_rowmap& m, int r) {
+    int d = 0;
+#pragma unroll
+    for (int s = 0; s < 4; s++) if (s < m.nseg && r >= m.start[s]) d = m.delta[s];
+    return r + d;
+}
+
 struct it_mat {
     it_ctx* ctx;
     size_t rows, cols;      // logical shape
@@ -44,6 +64,9 @@ struct it_mat {
     uint8_t* tiles;         // [row_groups][cols/128][IT_TILE_BYTES]
     size_t bytes;
     bool owns_tiles;        // false for a view into a larger allocation (stacked matrices)
+    bool sharded;           // rows of a larger logical matrix: results are pushed to every peer
+    it_rowmap map;          // where the local rows land in the full output (identity when nseg == 0)
+    size_t out_rows;        // rows of the full output (== rows unless sharded)
 };
 
 // Int8-group matrix: row-major int8 q[rows][cols] and f16 d[rows][cols/32] (Q8_0 density).
@@ -89,7 +112,13 @@ struct it_ctx {
     // Programmatic-dependent-launch bookkeeping: the q8 buffer whose contents are known to be complete by the
     // time the most recently enqueued kernel lets its dependents start (null after any op that is not a matvec).
     const it_q8* pdl_safe_q8;
+    // peers (null / world 1 until it_ctx_attach_peers): device copy of the table, the mapped peer allocations, own flag words
+    it_peers* peers_dev;
+    void* peer_base[IT_MAX_PEERS];
+    int rank, world;
 };
+// The arena allocation ends with IT_ARENA_TAIL bytes of flag words: [0, IT_MAX_PEERS) arrival flags, [8] done counter, [9] epoch.
+#define IT_ARENA_TAIL 256
 // Every entry point that enqueues device work other than the ternary matvec calls this.
 static inline void it_note_op(it_ctx* c) { c->pdl_safe_q8 = nullptr; }
 
@@ -127,10 +156,11 @@ __host__ __device__ static inline uint64_t it_hash(uint64_t seed, uint64_t i) { 
 int it_launch_repack_pq2(it_ctx* ctx, const uint8_t* raw_dev, size_t rows, size_t cols, uint8_t* tiles);
 int it_launch_repack_packed2(it_ctx* ctx, const uint32_t* words_dev, const float* scales_dev, size_t rows, size_t cols, uint8_t* tiles);
 int it_launch_unpack_pq2(it_ctx* ctx, const uint8_t* tiles, size_t rows, size_t cols, uint8_t* raw_dev);
-int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, uint8_t* raw_dev);
+// rows [row0, row0 + rows) of the synthetic matrix with this seed and column count
+int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int four_codes, uint8_t* raw_dev, size_t row0 = 0);
 // A synthetic matrix generated into caller-owned tile storage (rows must be a multiple of 32 when matrices are stacked);
 // the returned it_mat is a view that does not free the tiles.
-int it_matrix_synth_view(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, uint8_t* tiles, it_mat** out);
+int it_matrix_synth_view(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, uint8_t* tiles, it_mat** out, size_t row0 = 0);
 // A view over `row_groups` consecutive row groups starting at `tiles` (e.g. several stacked matrices seen as one).
 int it_matrix_view(it_ctx* ctx, size_t rows, size_t cols, uint8_t* tiles, it_mat** out);
 // Tile kernel for more than eight activation rows (it_matmul_t2.cu); same arithmetic as the matvec kernel.

@@ -46,7 +46,7 @@ template <int WR, int WT>
 __global__ void __launch_bounds__((WR * WT + 1) * 32, 1)
 k_matmul_t2(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int stages,
             const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
-            float* y, size_t y_stride, int accum, int* error_flag) {
+            float* arena, size_t y_off, size_t y_stride, int accum, int* error_flag, const it_peers* peers, const it_rowmap map) {
     constexpr int NCW = WR * WT, NT = MM_TOK / (8 * WT);   // consumer warps; mma column tiles (8 activation rows) per warp
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -156,23 +156,27 @@ k_matmul_t2(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
         if (lane == 0) mbar_arrive(bars + 8 * (stages + s));     // the stage may be refilled
         if (++s == stages) { s = 0; ph ^= 1u; }
     }
-    if (*abort_flag || !rg_valid) return;
+    if (!*abort_flag && rg_valid) {
 #pragma unroll
-    for (int n = 0; n < NT; n++)
+        for (int n = 0; n < NT; n++)
 #pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
-            const int m = tb + 8 * n + 2 * t + cc;
-            if (m < ntv) {
+            for (int cc = 0; cc < 2; cc++) {
+                const int m = tb + 8 * n + 2 * t + cc;
+                if (m < ntv) {
 #pragma unroll
-                for (int r = 0; r < 4; r++) {
-                    const int row = (rg0 + wr) * 32 + g + 8 * r;
-                    if (row < rows) {
-                        float* dst = y + (size_t)(tok0 + m) * y_stride + row;
-                        *dst = accum ? __fadd_rn(*dst, acc[n][r][cc]) : acc[n][r][cc];
+                    for (int r = 0; r < 4; r++) {
+                        const int row = (rg0 + wr) * 32 + g + 8 * r;
+                        if (row < rows) it_result_store(peers, arena, y_off + (size_t)(tok0 + m) * y_stride + it_map_row(map, row), acc[n][r][cc], accum);
                     }
                 }
             }
-        }
+    }
+    if (peers) {
+        // sharded launch: make this CTA's pushes visible system-wide, then count the CTA as done
+        __threadfence_system();
+        consumer_barrier<NCW * 32>();
+        if (tid == 0) it_shard_finish(peers, gridDim.x * gridDim.y, error_flag);
+    }
 }
 
 template <int WR, int WT>
@@ -195,7 +199,8 @@ int mm_launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, float* y, si
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     IT_CUDA(cudaLaunchKernelEx(&cfg, kern, x->tmap, (const uint8_t*)w->tiles, nb, (int)w->rows, (int)w->row_groups, stages,
-        (const float*)x->d, (const int32_t*)x->sum128, (int)x->max_n, ntok, y, y_stride, accum, c->error_flag_dev));
+        (const float*)x->d, (const int32_t*)x->sum128, (int)x->max_n, ntok, c->arena, (size_t)(y - c->arena), y_stride, accum, c->error_flag_dev,
+        (const it_peers*)(w->sharded ? c->peers_dev : nullptr), w->map));
     c->pdl_safe_q8 = x;     // this kernel waits for its predecessor before it lets its successor start
     return IT_OK;
 }

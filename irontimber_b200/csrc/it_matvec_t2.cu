@@ -66,7 +66,8 @@ template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI>
 __global__ void __launch_bounds__((NG * CWARPS + (ONESHOT ? 0 : 1)) * 32, MINB)
 k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int slots, int nbuf,
             const int8_t* __restrict__ xq, const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
-            float* y, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag, int wait_early) {
+            float* arena, size_t y_off, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag, int wait_early,
+            const it_peers* peers, const it_rowmap map) {
     constexpr int NCONS = NG * CWARPS;
     extern __shared__ __align__(128) unsigned char smem[];
     const Smem L = smem_layout(MT, nb, slots, nbuf);
@@ -222,11 +223,16 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 float sum = 0.f;
 #pragma unroll 8
                 for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
-                float* dst = y + (size_t)warp * y_stride + row;
                 if (!wait_early) asm volatile("griddepcontrol.wait;" ::: "memory");   // y may be read or written by the kernel before us
-                *dst = accum ? __fadd_rn(*dst, sum) : sum;
+                it_result_store(peers, arena, y_off + (size_t)warp * y_stride + it_map_row(map, row), sum, accum);
             }
         }
+    }
+    if (!SUMI && peers) {
+        // sharded launch: make this CTA's pushes visible system-wide, then count the CTA as done
+        __threadfence_system();
+        consumer_barrier<NCONS * 32>();
+        if (tid == 0) it_shard_finish(peers, gridDim.x, error_flag);
     }
 }
 
@@ -248,7 +254,8 @@ int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow
     const int nb_ = nb, rows_ = (int)w->rows, rgs_ = (int)w->row_groups, xs_ = (int)x->max_n;
     IT_CUDA(cudaLaunchKernelEx(&cfg, kern, (const uint8_t*)w->tiles, nb_, rows_, rgs_, slots, nbuf,
         (const int8_t*)(x->qs + xrow0 * x->max_n), (const float*)(x->d + xrow0 * (x->max_n / 256)), (const int32_t*)(x->sum128 + xrow0 * (x->max_n / 128)), xs_, ntok,
-        y, y_stride, accum, sumi, c->error_flag_dev, wait_early));
+        c->arena, y ? (size_t)(y - c->arena) : (size_t)0, y_stride, accum, sumi, c->error_flag_dev, wait_early,
+        (const it_peers*)(w->sharded ? c->peers_dev : nullptr), w->map));
     c->pdl_safe_q8 = x;
     return IT_OK;
 }
@@ -332,8 +339,9 @@ int check(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, const char* w
 
 IT_API int it_matvec_t2(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, size_t y_off, size_t y_stride, int accum) {
     int r = check(c, w, ntok, x, "it_matvec_t2"); if (r) return r;
-    IT_CHECK_ARG(ntok == 1 || y_stride >= w->rows, "it_matvec_t2: output stride %zu is shorter than a row of %zu results", y_stride, w->rows);
-    IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->rows <= c->arena_floats - y_off, "it_matvec_t2: output rows fall outside the arena");
+    IT_CHECK_ARG(ntok == 1 || y_stride >= w->out_rows, "it_matvec_t2: output stride %zu is shorter than a row of %zu results", y_stride, w->out_rows);
+    IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->out_rows <= c->arena_floats - y_off, "it_matvec_t2: output rows fall outside the arena");
+    if (w->sharded && !c->peers_dev) return it_fail(IT_ESTATE, "it_matvec_t2: the matrix is a row shard but no peers are attached to the context");
     return dispatch<false>(c, w, ntok, x, c->arena + y_off, y_stride, accum, nullptr);
 }
 

@@ -2,6 +2,7 @@
 // copies into shared memory, and the int8 tensor-core instruction both kernels are built on.
 #pragma once
 #include <cstdint>
+#include "it_internal.h"
 
 namespace {
 
@@ -45,5 +46,41 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+
+// ---- results of a row shard: pushed into every rank's arena -----------------------------------------------------
+// Store of one result at float offset `off` of the arena: on a sharded launch (P != null) the value goes to the same
+// offset in every rank's arena (own included), plain peer stores over NVLink; accum adds to this rank's old value,
+// which is the same on every rank.
+__device__ __forceinline__ void it_result_store(const it_peers* P, float* own_arena, size_t off, float v, int accum) {
+    if (accum) v = __fadd_rn(__ldcg(own_arena + off), v);
+    if (!P) { own_arena[off] = v; return; }
+    const int world = P->world;
+    for (int p = 0; p < world; p++) P->arena[p][off] = v;
+}
+// End of a sharded kernel.  Every thread that stored results has issued __threadfence_system() and the CTA has passed
+// a barrier before ONE thread of the CTA calls this.  The last CTA to arrive publishes this rank's slice (a release
+// store of the new epoch into every peer's flag word for this rank) and then waits until every peer has published the
+// same epoch here, so that when the kernel completes the full result is in this rank's arena.  The wait is bounded;
+// when it runs out the error flag is raised and the kernel leaves.
+__device__ __forceinline__ void it_shard_finish(const it_peers* P, unsigned total_ctas, int* error_flag) {
+    const unsigned old = atomicAdd(P->done, 1u);
+    if (old != total_ctas - 1) return;
+    *P->done = 0;
+    __threadfence_system();
+    const unsigned e = *P->epoch + 1u;
+    const int rank = P->rank, world = P->world;
+    for (int p = 0; p < world; p++) if (p != rank) asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(P->flags[p] + rank), "r"(e) : "memory");
+    const long long t0 = clock64();
+    for (int q = 0; q < world; q++) {
+        if (q == rank) continue;
+        const unsigned* f = P->flags[rank] + q;
+        for (;;) {
+            unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int)(v - e) >= 0) break;
+            if (clock64() - t0 > WAIT_CLOCKS) { atomicExch(error_flag, 1); q = world; break; }
+        }
+    }
+    *P->epoch = e;
+}
 
 }  // namespace

@@ -56,13 +56,22 @@ def _p(a):
 
 
 class CudaEngine:
-    def __init__(self, cfg, seed=1, with_mtp=False, device=0):
+    def __init__(self, cfg, seed=1, with_mtp=False, device=0, rank=0, world=1, group=None):
+        """rank / world > 1: this engine holds the rows of `rank` of every trunk matrix; the arenas of all ranks (one
+        process per GPU, torch.distributed initialised) are attached to each other before the constructor returns."""
         self.L = _lib.load()
         self.cfg = cfg
         h = C.c_void_p()
-        _lib.check(self.L.it_engine_create_synth(device, C.byref(cfg), seed, int(with_mtp), C.byref(h)))
+        _lib.check(self.L.it_engine_create_synth_sharded(device, C.byref(cfg), seed, int(with_mtp), rank, world, C.byref(h)))
         self.h = h
         self.with_mtp = with_mtp
+        self.rank, self.world = rank, world
+        if world > 1:
+            from .sharding import attach_peers
+            attach_peers(self.L, self.L.it_engine_ctx(self.h), rank, world, group)
+
+    def sync(self):
+        _lib.check(self.L.it_sync(self.L.it_engine_ctx(self.h)))
 
     def close(self):
         if self.h:
