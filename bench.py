@@ -15,7 +15,12 @@ host memory and reads every pick back to the host (4 bytes per token), timed on 
 as a sweep over 12 distinct weight matrices (285 MB), against the measured HBM copy bandwidth.
 `cpu_baseline` / `--impl reference`: the reference's CPU path (C++ port of src/cpu.rs forward_token, reference
 order, all host threads) on a truncated stack, extrapolated to the full depth; the sample is stated.
-With N > 1 every GPU runs an independent replica of the decode (weak scaling, no collective).
+With N > 1 (one process per GPU, torchrun) `value` is the aggregate of N independent sequences, one full engine per
+GPU and no collective (the model is 6.8 GB, sequences are independent units: weak scaling).  The same run also decodes
+ONE sequence with the row-sharded engine (`sharded`): every trunk matrix and the LM head split by output rows over the
+ranks, each rank's matvec kernels push their result slices into every peer's arena over NVLink (8-byte value+epoch
+slots) and collect the peers' slices at the end of the kernel, everything else replicated, every rank producing the
+same tokens (strong scaling; tokens of the one sequence per second, max over ranks of the device time).
 """
 import argparse
 import json
@@ -209,7 +214,7 @@ def main():
                           f"after a {args.prompt}-token random prompt, f16 KV, ctx 8192",
               "prompt_tokens": args.prompt, "weights_bytes_per_token": step_weight_bytes(cfg),
               "l2": "inputs larger than L2: every step streams its weights (6.8 GB at 64 layers) from HBM; L2 is 126 MB",
-              "sharding": "independent replica per GPU (weak scaling), no collective"}
+              "sharding": "single GPU" if world == 1 else f"value: {world} independent sequences, one engine per GPU, no collective; sharded: one sequence, trunk matrices and LM head split by output rows over {world} GPUs"}
     base = {"metric": METRIC, "unit": "tok/s", "n_gpus": world if args.impl != "reference" else args.gpus, "steps": args.steps, "warmup": warmup,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x 2-bit codes -> int32, f32 epilogue", "data": "synthetic", "config": config}
 
@@ -231,19 +236,49 @@ def main():
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    eng = CudaEngine(cfg, seed=7 + rank, with_mtp=False, device=local_rank)
-    L = _lib.load()
-    ctx = L.it_engine_ctx(eng.h)
-    stream = torch.cuda.ExternalStream(L.it_ctx_stream(ctx), device=f"cuda:{local_rank}")
-    rng = np.random.default_rng(100 + rank)
-    prompt = rng.integers(0, cfg.n_vocab, args.prompt).tolist()
-
-    def barrier():
-        _lib.check(L.it_sync(ctx))
+    def barrier(ctx=None):
+        if ctx is not None:
+            _lib.check(L.it_sync(ctx))
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
         torch.cuda.synchronize()
+
+    L = _lib.load()
+    sharded = None
+    if world > 1:
+        # one sequence on the row-sharded engine: same seed and prompt on every rank
+        seng = CudaEngine(cfg, seed=7, with_mtp=False, device=local_rank, rank=rank, world=world)
+        sctx = L.it_engine_ctx(seng.h)
+        sstream = torch.cuda.ExternalStream(L.it_ctx_stream(sctx), device=f"cuda:{local_rank}")
+        sprompt = np.random.default_rng(100).integers(0, cfg.n_vocab, args.prompt).tolist()
+        barrier(sctx)
+        t0 = time.perf_counter()
+        seng.eval_argmax(sprompt)
+        sprefill = time.perf_counter() - t0
+        seng.decode_steps(warmup)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier(sctx)
+        s0.record(sstream)
+        seng.decode_steps(args.steps, read_last=False)
+        s1.record(sstream)
+        barrier(sctx)
+        t = torch.tensor([s0.elapsed_time(s1)], device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sms = float(t.item())
+        seng.close()
+        sharded = {"value": args.steps / (sms / 1e3), "unit": "tok/s", "ms_per_step": sms / args.steps, "scaling": "strong",
+                   "prefill_tok_s": args.prompt / sprefill,
+                   "exchange": "257 exchanges per token (4 per layer + LM head), each inside the matvec kernel: peer stores of 8-byte value+epoch slots over NVLink, no NCCL call"}
+    eng = CudaEngine(cfg, seed=7 + rank, with_mtp=True, device=local_rank)
+    ctx = L.it_engine_ctx(eng.h)
+    stream = torch.cuda.ExternalStream(L.it_ctx_stream(ctx), device=f"cuda:{local_rank}")
+    rng = np.random.default_rng(100 + rank)
+    prompt = rng.integers(0, cfg.n_vocab, args.prompt).tolist()
+    _barrier = barrier
+
+    def barrier():
+        _barrier(ctx)
 
     t0 = time.perf_counter()
     eng.eval_argmax(prompt)
@@ -273,14 +308,57 @@ def main():
         t = torch.tensor([e2e_s], device=f"cuda:{local_rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    n_kernels = 3 + sum(20 if cfg.is_recurrent(il) else 23 for il in range(cfg.n_layer)) + 4
+    # speculative decode (config 3): the library's greedy_mtp loop with the random-init NextN head (its drafts are almost
+    # never right, so this is the cost of the reject path), and the same loop with the head's draft replaced by the
+    # token plain greedy decoding produced (every draft accepted: the accept path, as the reference's scripted-draft tests do)
+    mtp = None
+    if world == 1:
+        from irontimber_b200 import engine as E
+        n_mtp = min(args.steps, 64)
+        t0 = time.perf_counter()
+        eng.mtp_prefill(prompt)
+        pre_s = time.perf_counter() - t0                    # prompt pass with the head's catch-up, common to both runs
+        t0 = time.perf_counter()
+        out_mtp, st_nat = eng.generate_mtp(prompt, n_mtp)
+        nat_s = time.perf_counter() - t0
+        eng.reset()
+        plain = eng.generate(prompt, n_mtp)
+        assert out_mtp == plain, "speculative decoding must reproduce plain greedy decoding"
+
+        class Scripted:
+            def __init__(self, e): self.e, self.i = e, 1
+            def __getattr__(self, name): return getattr(self.e, name)
+            def mtp_draft(self, toks):
+                self.e.mtp_draft(toks)                      # the head still runs; only its pick is overridden
+                return plain[min(self.i, len(plain) - 1)]
+            def mtp_verify(self, x, d):
+                r = self.e.mtp_verify(x, d); self.i += 2 if r[0] == d else 1; return r
+        eng.reset()
+        t0 = time.perf_counter()
+        out_acc, st_acc = E.greedy_mtp(Scripted(eng), prompt, n_mtp)
+        acc_s = time.perf_counter() - t0
+        assert out_acc == plain
+        keep = ("drafted", "accepted", "rejected", "steps", "verify_calls", "single_forwards")
+        mtp = {"tokens": n_mtp, "prefill_with_head_catch_up_s": pre_s, "note": "decode tok/s = (tokens - 1) / (run time - prefill time)",
+               "random_head": {"tok_s": (n_mtp - 1) / max(nat_s - pre_s, 1e-9), "run_s": nat_s, **{k: st_nat[k] for k in keep if k in st_nat}},
+               "scripted_right_drafts": {"tok_s": (n_mtp - 1) / max(acc_s - pre_s, 1e-9), "run_s": acc_s, **{k: st_acc[k] for k in keep if k in st_acc}}}
+    # launches of one recorded step: 13 per delta-net layer, 15 per attention layer, embedding, output norm, LM head
+    # (Hadamard + matvec), argmax and the two token/position updates
+    n_kernels = sum(13 if cfg.is_recurrent(il) else 15 for il in range(cfg.n_layer)) + 7
+    barrier()
     eng.close()
     out = dict(base, value=world * args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * n_kernels,
                e2e={"value": world * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "ms_per_token": e2e_s / args.steps * 1e3},
-               prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 8},
+               prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64},
                step_weight_gbs=step_weight_bytes(cfg) * args.steps / (ms / 1e3) / 1e9)
-    out["roofline"] = matvec_roofline(torch, local_rank, 200)
+    if mtp:
+        out["mtp"] = mtp
+    if sharded:
+        out["sharded"] = sharded
     if rank == 0:
+        if world > 1:
+            os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())     # torchrun pins it to 1; the CPU arm uses every host thread
+        out["roofline"] = matvec_roofline(torch, local_rank, 200)
         out["cpu_baseline"] = cpu_decode_tok_s(args.layers, 8)[0]
         print(json.dumps(out))
     if dist:

@@ -134,7 +134,9 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     c->peers_dev = nullptr; c->rank = 0; c->world = 1; for (int i = 0; i < IT_MAX_PEERS; i++) c->peer_base[i] = nullptr;
     c->pdl_safe_q8 = nullptr; c->splitk_terms = nullptr; c->splitk_counters = nullptr; c->error_flag_host = nullptr; c->error_flag_dev = nullptr;
     cudaError_t e1 = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
-    cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_floats * sizeof(float) + IT_ARENA_TAIL) : e1;
+    c->ll_slots = arena_floats < IT_LL_MAX_SLOTS ? arena_floats : IT_LL_MAX_SLOTS;
+    const size_t arena_bytes = arena_floats * sizeof(float) + IT_ARENA_TAIL + 2 * c->ll_slots * 8;
+    cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_bytes) : e1;
     cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc(&c->argmax_partials, IT_ARGMAX_MAX_BLOCKS * sizeof(unsigned long long)) : e2;
     cudaError_t e4 = e3 == cudaSuccess ? cudaMalloc(&c->argmax_counter, 256) : e3;
     if (e4 == cudaSuccess) e4 = cudaMalloc(&c->splitk_terms, (size_t)c->sm_count * IT_SPLITK_SLOT_BYTES);
@@ -143,7 +145,7 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     if (e4 == cudaSuccess) e4 = cudaHostAlloc(&c->error_flag_host, sizeof(int), cudaHostAllocMapped);
     if (e4 == cudaSuccess) { *c->error_flag_host = 0; e4 = cudaHostGetDevicePointer(&c->error_flag_dev, c->error_flag_host, 0); }
     if (e4 != cudaSuccess) { it_ctx_destroy(c); return it_fail(e4 == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_ctx_create: %s", cudaGetErrorString(e4)); }
-    cudaMemsetAsync(c->arena, 0, arena_floats * sizeof(float) + IT_ARENA_TAIL, c->stream);
+    cudaMemsetAsync(c->arena, 0, arena_bytes, c->stream);
     cudaMemsetAsync(c->argmax_counter, 0, 256, c->stream);
     IT_CUDA(cudaStreamSynchronize(c->stream));
     *out = c; return IT_OK;
@@ -195,7 +197,9 @@ IT_API int it_ctx_attach_peers(it_ctx* c, int rank, int world, const void* handl
         }
         P.arena[p] = reinterpret_cast<float*>(base);
         P.flags[p] = reinterpret_cast<unsigned*>(base + tail);
+        P.ll[p] = reinterpret_cast<unsigned long long*>(base + tail + IT_ARENA_TAIL);
     }
+    P.ll_slots = c->ll_slots;
     P.done = P.flags[rank] + IT_MAX_PEERS; P.epoch = P.flags[rank] + IT_MAX_PEERS + 1;
     IT_CUDA(cudaMalloc(&c->peers_dev, sizeof P));
     IT_CUDA(cudaMemcpyAsync(c->peers_dev, &P, sizeof P, cudaMemcpyHostToDevice, c->stream));
@@ -353,7 +357,7 @@ IT_API int it_shard_range(size_t rows, int rank, int world, size_t* row0, size_t
 IT_API int it_matrix_set_shard(it_mat* m, size_t row0, size_t total_rows) {
     IT_CHECK_ARG(m, "it_matrix_set_shard: null matrix");
     IT_CHECK_ARG(row0 + m->rows <= total_rows && total_rows <= (1u << 30), "it_matrix_set_shard: rows [%zu, %zu) fall outside a matrix of %zu rows", row0, row0 + m->rows, total_rows);
-    m->sharded = true; m->map.nseg = 1; m->map.start[0] = 0; m->map.delta[0] = (int)row0; m->out_rows = total_rows;
+    m->sharded = true; m->map.nseg = 1; m->map.start[0] = 0; m->map.delta[0] = (int)row0; m->map.shift[0] = (int)m->rows; m->out_rows = total_rows;
     return IT_OK;
 }
 IT_API int it_matrix_synth_rows(it_ctx* c, uint64_t seed, size_t total_rows, size_t cols, int four_codes, size_t row0, size_t nrows, it_mat** out) {

@@ -71,7 +71,7 @@ int synth_stack(it_engine* e, int layer, int n, const int* tensors, const size_t
     if (e->world > 1) {
         it_mat* m = *stack; m->sharded = true; m->out_rows = full; m->map.nseg = n;
         size_t lo = 0, go = 0;
-        for (int i = 0; i < n; i++) { m->map.start[i] = (int)lo; m->map.delta[i] = (int)(go + row0[i]) - (int)lo; lo += local[i]; go += rows[i]; }
+        for (int i = 0; i < n; i++) { m->map.start[i] = (int)lo; m->map.delta[i] = (int)(go + row0[i]) - (int)lo; m->map.shift[i] = (int)local[i]; lo += local[i]; go += rows[i]; }
     }
     return IT_OK;
 }

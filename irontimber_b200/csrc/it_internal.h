@@ -47,13 +47,18 @@ struct it_peers {                       // lives in device memory, one per attac
     int rank, world;
     unsigned* done;                     // CTAs of the running sharded kernel that have finished their stores
     unsigned* epoch;                    // sharded ops completed so far (the same sequence on every rank)
+    // low-latency exchange: every rank's buffer of 8-byte (value, epoch) slots, two halves of ll_slots slots used by
+    // even and odd epochs; a slot is complete as soon as its epoch tag matches, no fence or flag needed
+    unsigned long long* ll[IT_MAX_PEERS];
+    size_t ll_slots;
 };
 // Local row r belongs to the last segment with start[s] <= r and lands at output row r + delta[s].
-struct it_rowmap { int nseg; int start[4]; int delta[4]; };
-__host__ __device__ static inline int it_map_row(const it_rowmap& m, int r) {
-    int d = 0;
+struct it_rowmap { int nseg; int start[4]; int delta[4]; int shift[4]; };   // shift[s]: how far segment s moves from one rank to the next
+__host__ __device__ static inline int it_map_row(const it_rowmap& m, int r, int* shift = nullptr) {
+    int d = 0, sh = 0;
 #pragma unroll
-    for (int s = 0; s < 4; s++) if (s < m.nseg && r >= m.start[s]) d = m.delta[s];
+    for (int s = 0; s < 4; s++) if (s < m.nseg && r >= m.start[s]) { d = m.delta[s]; sh = m.shift[s]; }
+    if (shift) *shift = sh;
     return r + d;
 }
 
@@ -116,9 +121,12 @@ struct it_ctx {
     it_peers* peers_dev;
     void* peer_base[IT_MAX_PEERS];
     int rank, world;
+    size_t ll_slots;
 };
-// The arena allocation ends with IT_ARENA_TAIL bytes of flag words: [0, IT_MAX_PEERS) arrival flags, [8] done counter, [9] epoch.
+// The arena allocation continues with IT_ARENA_TAIL bytes of flag words ([0, IT_MAX_PEERS) arrival flags, [8] done
+// counter, [9] epoch) and the low-latency exchange buffer of 2 * ll_slots 8-byte slots.
 #define IT_ARENA_TAIL 256
+#define IT_LL_MAX_SLOTS ((size_t)1 << 21)
 // Every entry point that enqueues device work other than the ternary matvec calls this.
 static inline void it_note_op(it_ctx* c) { c->pdl_safe_q8 = nullptr; }
 

@@ -67,7 +67,7 @@ __global__ void __launch_bounds__((NG * CWARPS + (ONESHOT ? 0 : 1)) * 32, MINB)
 k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int slots, int nbuf,
             const int8_t* __restrict__ xq, const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
             float* arena, size_t y_off, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag, int wait_early,
-            const it_peers* peers, const it_rowmap map) {
+            const it_peers* peers, const it_rowmap map, int ll_mode, int out_rows) {
     constexpr int NCONS = NG * CWARPS;
     extern __shared__ __align__(128) unsigned char smem[];
     const Smem L = smem_layout(MT, nb, slots, nbuf);
@@ -220,19 +220,28 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
             const int row = rg * 32 + lane;
             if (row < rows) {
                 const float* tcol = tbuf + warp * L.plane + lane;
+                // y may be read or written by the kernel before us; a sharded launch waits before the additions so
+                // that the load of the epoch counter overlaps them
+                unsigned epoch = 0;
+                if (peers && ll_mode) {
+                    if (!wait_early) asm volatile("griddepcontrol.wait;" ::: "memory");
+                    epoch = *reinterpret_cast<volatile unsigned*>(peers->epoch) + 1u;
+                }
                 float sum = 0.f;
 #pragma unroll 8
                 for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
-                if (!wait_early) asm volatile("griddepcontrol.wait;" ::: "memory");   // y may be read or written by the kernel before us
-                it_result_store(peers, arena, y_off + (size_t)warp * y_stride + it_map_row(map, row), sum, accum);
+                if (!wait_early && !(peers && ll_mode)) asm volatile("griddepcontrol.wait;" ::: "memory");
+                int shift; const int grow = it_map_row(map, row, &shift);
+                if (peers && ll_mode) it_result_exchange_ll(peers, arena, y_off + (size_t)warp * y_stride, (size_t)warp * out_rows, grow, shift, sum, accum, epoch, error_flag);
+                else it_result_store(peers, arena, y_off + (size_t)warp * y_stride + grow, sum, accum);
             }
         }
     }
     if (!SUMI && peers) {
-        // sharded launch: make this CTA's pushes visible system-wide, then count the CTA as done
-        __threadfence_system();
+        // sharded launch: count the CTA as done; without the slot protocol first make its pushes visible system-wide
+        if (!ll_mode) __threadfence_system();
         consumer_barrier<NCONS * 32>();
-        if (tid == 0) it_shard_finish(peers, gridDim.x, error_flag);
+        if (tid == 0) { if (ll_mode) it_shard_finish_ll(peers, gridDim.x); else it_shard_finish(peers, gridDim.x, error_flag); }
     }
 }
 
@@ -255,7 +264,8 @@ int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow
     IT_CUDA(cudaLaunchKernelEx(&cfg, kern, (const uint8_t*)w->tiles, nb_, rows_, rgs_, slots, nbuf,
         (const int8_t*)(x->qs + xrow0 * x->max_n), (const float*)(x->d + xrow0 * (x->max_n / 256)), (const int32_t*)(x->sum128 + xrow0 * (x->max_n / 128)), xs_, ntok,
         c->arena, y ? (size_t)(y - c->arena) : (size_t)0, y_stride, accum, sumi, c->error_flag_dev, wait_early,
-        (const it_peers*)(w->sharded ? c->peers_dev : nullptr), w->map));
+        (const it_peers*)(w->sharded ? c->peers_dev : nullptr), w->map,
+        (w->sharded && (size_t)ntok * w->out_rows <= c->ll_slots) ? 1 : 0, (int)w->out_rows));
     c->pdl_safe_q8 = x;
     return IT_OK;
 }

@@ -7,6 +7,7 @@
 namespace {
 
 constexpr long long WAIT_CLOCKS = 1ll << 31;      // about one second
+constexpr long long PEER_WAIT_CLOCKS = 1ll << 33; // about four seconds: another process may be a little behind
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count)); }
@@ -77,10 +78,46 @@ __device__ __forceinline__ void it_shard_finish(const it_peers* P, unsigned tota
         for (;;) {
             unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if ((int)(v - e) >= 0) break;
-            if (clock64() - t0 > WAIT_CLOCKS) { atomicExch(error_flag, 1); q = world; break; }
+            if (clock64() - t0 > PEER_WAIT_CLOCKS) { atomicExch(error_flag, 1); q = world; break; }
         }
     }
     *P->epoch = e;
+}
+
+// Low-latency exchange of one result (the decode path, where an exchange is pure latency).  The value travels as an
+// 8-byte (value, epoch) slot written with one store, so it is complete the moment its tag matches: no fence, no flag,
+// one NVLink crossing.  The calling thread pushes its result into the slot of output row `grow` in every peer's buffer,
+// stores it into its own arena, then collects the results of the same local row of every peer (output row
+// grow + (p - rank) * shift) from its own buffer as they arrive and stores them too.  Slots of even and odd epochs
+// live in different halves, and a rank cannot run two ops ahead of a peer, so a slot is never overwritten before it was read.
+__device__ __forceinline__ void it_result_exchange_ll(const it_peers* P, float* arena, size_t row_off, size_t slot0, int grow, int shift,
+                                                      float v, int accum, unsigned e, int* error_flag) {
+    if (accum) v = __fadd_rn(__ldcg(arena + row_off + grow), v);
+    const int rank = P->rank, world = P->world;
+    const size_t half = (size_t)(e & 1u) * P->ll_slots + slot0;
+    const unsigned long long packed = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(v);
+    for (int p = 0; p < world; p++) if (p != rank) asm volatile("st.volatile.global.u64 [%0], %1;" :: "l"(P->ll[p] + half + grow), "l"(packed) : "memory");
+    arena[row_off + grow] = v;
+    const long long t0 = clock64();
+    for (int p = 0; p < world; p++) {
+        if (p == rank) continue;
+        const int gp = grow + (p - rank) * shift;
+        const unsigned long long* slot = P->ll[rank] + half + gp;
+        unsigned long long x;
+        for (;;) {
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(x) : "l"(slot) : "memory");
+            if ((unsigned)(x >> 32) == e) break;
+            if (clock64() - t0 > PEER_WAIT_CLOCKS) { atomicExch(error_flag, 1); return; }
+        }
+        arena[row_off + gp] = __uint_as_float((unsigned)x);
+    }
+}
+// End of a kernel that exchanged its results slot by slot: the last CTA moves the epoch on.  One thread per CTA, after a CTA barrier.
+__device__ __forceinline__ void it_shard_finish_ll(const it_peers* P, unsigned total_ctas) {
+    const unsigned old = atomicAdd(P->done, 1u);
+    if (old != total_ctas - 1) return;
+    *P->done = 0;
+    *P->epoch = *P->epoch + 1u;
 }
 
 }  // namespace
