@@ -280,9 +280,10 @@ int ring_slots(int MT, int nb, int nbuf, int per_cta, int want, int need) {
 // Shape policy.
 //  - Short rows (K <= 8192) whose row groups all fit on the GPU at once: one CTA of eight warps per row group,
 //    the ring holds the whole row group and is requested in one go (up to four CTAs per SM).
-//  - Otherwise a persistent grid with a producer warp: one consumer group and up to three CTAs per SM for short
-//    rows, three consumer groups and one CTA per SM for long rows (a row group is long, so the per-warp chain
-//    must stay short and the ring deep).
+//  - Otherwise a persistent grid with a producer warp: one consumer group and up to three CTAs per SM (for the
+//    160 long row groups of a 5120 x 17408 matrix that gives every row group its own CTA: 5.2 us against 8.4 us
+//    with one three-group CTA per SM, where twelve CTAs had to take a second row group); three consumer groups
+//    only when the staged activation rows leave room for a single CTA per SM.
 // CTAs per SM drop when the staged activation rows and the terms leave no room for the ring.
 template <int MT, bool SUMI>
 int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
@@ -298,17 +299,18 @@ int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, f
             return launch_cfg<MT, 1, 2, true, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, cpr, 1, rgs);
         }
     }
-    for (int per_sm = long_rows ? 1 : 3; per_sm >= 1; per_sm--) {
+    for (int per_sm = 3; per_sm >= 1; per_sm--) {
         const int grid = rgs < per_sm * c->sm_count ? rgs : per_sm * c->sm_count;
         const int nbuf = SUMI ? 0 : (grid == rgs ? 1 : 2);
         const int want = long_rows ? 16 : (cpr + 2 > 4 ? cpr + 2 : 4);
         const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / per_sm - 1024, want, cpr < 4 ? cpr : 4);
         if (!slots) continue;
         if (SUMI) return launch_cfg<MT, 1, 1, false, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
-        if (long_rows) return launch_cfg<MT, 3, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
-        if (per_sm == 1) return launch_cfg<MT, 1, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (per_sm == 3) return launch_cfg<MT, 1, 3, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
         if (per_sm == 2) return launch_cfg<MT, 1, 2, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
-        return launch_cfg<MT, 1, 3, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        // a single CTA per SM: long rows get three consumer groups so that the per-warp chain stays short
+        if (long_rows) return launch_cfg<MT, 3, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        return launch_cfg<MT, 1, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
     }
     return it_fail(IT_EINVAL, "it_matvec_t2: %d rows of width %zu exceed the shared-memory budget", MT, w->cols);
 }
@@ -349,6 +351,7 @@ int check(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, const char* w
 
 IT_API int it_matvec_t2(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, size_t y_off, size_t y_stride, int accum) {
     int r = check(c, w, ntok, x, "it_matvec_t2"); if (r) return r;
+    if (it_dbg_skip("matvec")) return IT_OK;
     IT_CHECK_ARG(ntok == 1 || y_stride >= w->out_rows, "it_matvec_t2: output stride %zu is shorter than a row of %zu results", y_stride, w->out_rows);
     IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->out_rows <= c->arena_floats - y_off, "it_matvec_t2: output rows fall outside the arena");
     if (w->sharded && !c->peers_dev) return it_fail(IT_ESTATE, "it_matvec_t2: the matrix is a row shard but no peers are attached to the context");

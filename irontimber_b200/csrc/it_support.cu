@@ -196,6 +196,8 @@ template <> __device__ __forceinline__ __half kv_pack<__half>(float v) { return 
 template <> __device__ __forceinline__ float kv_pack<float>(float v) { return v; }
 __device__ __forceinline__ float kv_get(const __half* p) { return __half2float(*p); }
 __device__ __forceinline__ float kv_get(const float* p) { return *p; }
+__device__ __forceinline__ float2 kv_get2(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+__device__ __forceinline__ float2 kv_get2(const float* p) { return *reinterpret_cast<const float2*>(p); }
 
 template <typename T>
 __global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* vc, int kvd, int slot0, const int* pos_ptr) {
@@ -231,6 +233,25 @@ __global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs,
     const float* qh = q + t * q_ts + h * q_hs;
     for (int j = tid; j < hd; j += 1024) qs[j] = qh[j];
     __syncthreads();
+    // the first V chunks are requested now and arrive while the scores are computed
+    constexpr int RING = 4, CHUNK_BYTES = 32768;
+    T* ring = reinterpret_cast<T*>(reinterpret_cast<unsigned char*>(qs + hd) + ((16u - ((unsigned)__cvta_generic_to_shared(qs + hd) & 15u)) & 15u));
+    const int cp = CHUNK_BYTES / (hd * (int)sizeof(T));              // positions per chunk
+    const int ppr = hd * (int)sizeof(T) / 16, epp = 16 / (int)sizeof(T);   // 16-byte pieces per row, elements per piece
+    const int nchunks = (n + cp - 1) / cp;
+    auto issue = [&](int c) {
+        if (c < nchunks) {
+            const int p0 = c * cp, rows = min(cp, n - p0);
+            T* dst = ring + (size_t)(c % RING) * cp * hd;
+            for (int i = tid; i < rows * ppr; i += 1024) {
+                const int r = i / ppr, k = i % ppr;
+                const unsigned d = (unsigned)__cvta_generic_to_shared(dst + r * hd + k * epp);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(d), "l"(vc + (size_t)(p0 + r) * kvd + kh * hd + k * epp));
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int c = 0; c < RING - 1; c++) issue(c);
     const float scale = it_div(1.0f, it_sqrt((float)hd));
     constexpr int VN = KvVec<T>::N; using Vec = typename KvVec<T>::V;
     const int nvec = hd / VN;                  // vectors per K row
@@ -242,11 +263,14 @@ __global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs,
             Vec buf[8];
 #pragma unroll
             for (int u = 0; u < 8; u++) if (v0 + u < nvec) buf[u] = kp[v0 + u];
+            asm volatile("" ::: "memory");       // all eight loads are in flight before the first dependent add
 #pragma unroll
             for (int u = 0; u < 8; u++) if (v0 + u < nvec) {
-                float f[VN]; KvVec<T>::unpack(buf[u], f);
+                float f[VN], qv[VN]; KvVec<T>::unpack(buf[u], f);
 #pragma unroll
-                for (int i = 0; i < VN; i++) s = it_add(s, it_mul(qs[(v0 + u) * VN + i], f[i]));
+                for (int i = 0; i < VN; i += 4) *reinterpret_cast<float4*>(qv + i) = *reinterpret_cast<const float4*>(qs + (v0 + u) * VN + i);
+#pragma unroll
+                for (int i = 0; i < VN; i++) s = it_add(s, it_mul(qv[i], f[i]));
             }
         }
         s = it_mul(s, scale); sc[p] = s; mx = fmaxf(mx, s);
@@ -268,17 +292,35 @@ __global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs,
     const float sum = s_sum;
     for (int p = tid; p < n; p += 1024) sc[p] = it_div(sc[p], sum);
     __syncthreads();
-    for (int j = tid; j < hd; j += 1024) {
-        const T* vp = vc + kh * hd + j;
-        float acc = 0.f;
-        for (int p0 = 0; p0 < n; p0 += 32) {
-            float vv[32];
+    // Output: thread j adds w[p] * v[p][j] in ascending p.  The V rows of the head stream through a ring of shared-memory
+    // chunks filled with 16-byte asynchronous copies by all threads, several chunks ahead, so the chain of additions
+    // never waits for global memory.
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int c = 0; c < nchunks; c++) {
+        issue(c + RING - 1);
+        asm volatile("cp.async.wait_group %0;" :: "n"(RING - 1) : "memory");
+        __syncthreads();
+        if (2 * tid < hd) {                                  // two outputs per thread: elements 2*tid, 2*tid + 1
+            const int p0 = c * cp, rows = min(cp, n - p0);
+            const T* src = ring + (size_t)(c % RING) * cp * hd + 2 * tid;
+            int r = 0;
+            for (; r + 4 <= rows; r += 4) {
+                const float4 w4 = *reinterpret_cast<const float4*>(sc + p0 + r);
+                const float w[4] = { w4.x, w4.y, w4.z, w4.w };
+                float2 v[4];
 #pragma unroll
-            for (int u = 0; u < 32; u++) vv[u] = p0 + u < n ? kv_get(vp + (size_t)(p0 + u) * kvd) : 0.f;
+                for (int u = 0; u < 4; u++) v[u] = kv_get2(src + (r + u) * hd);
 #pragma unroll
-            for (int u = 0; u < 32; u++) if (p0 + u < n) acc = it_add(acc, it_mul(sc[p0 + u], vv[u]));
+                for (int u = 0; u < 4; u++) { acc0 = it_add(acc0, it_mul(w[u], v[u].x)); acc1 = it_add(acc1, it_mul(w[u], v[u].y)); }
+            }
+            for (; r < rows; r++) { const float w = sc[p0 + r]; const float2 v = kv_get2(src + r * hd); acc0 = it_add(acc0, it_mul(w, v.x)); acc1 = it_add(acc1, it_mul(w, v.y)); }
         }
-        out[t * o_ts + h * hd + j] = it_mul(acc, it_sigmoid(gate[t * q_ts + h * q_hs + j]));
+        __syncthreads();
+    }
+    if (2 * tid < hd) {
+        const float* gp = gate + t * q_ts + h * q_hs + 2 * tid;
+        float* op = out + t * o_ts + h * hd + 2 * tid;
+        op[0] = it_mul(acc0, it_sigmoid(gp[0])); op[1] = it_mul(acc1, it_sigmoid(gp[1]));
     }
 }
 
@@ -287,52 +329,62 @@ __global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs,
 }  // namespace
 
 int it_sup_embed(it_ctx* c, const uint32_t* toks_dev, const float* table, int e, int nt, float* x) {
+    if (it_dbg_skip("embed")) return IT_OK;
     it_note_op(c); it_pdl(k_embed, dim3(dim3(4, nt)), dim3(256), 0, c->stream, toks_dev, table, e, x); KCHK("embed"); return IT_OK;
 }
 int it_sup_rmsnorm_wide(it_ctx* c, const float* x, size_t xs, const float* w, int n, float eps, float* out, size_t os, int nt) {
+    if (it_dbg_skip("rmsw")) return IT_OK;
     it_note_op(c); it_pdl(k_rmsnorm_wide, dim3(nt), dim3(256), 0, c->stream, x, xs, w, n, eps, out, os); KCHK("rmsnorm_wide"); return IT_OK;
 }
 int it_sup_norm_head(it_ctx* c, const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts, int n, int nheads, const float* w, int mode, float eps,
                      const float* z, size_t z_hs, size_t z_ts, int nt) {
+    if (it_dbg_skip("normhead")) return IT_OK;
     if (n > 256) return it_fail(IT_EINVAL, "head norm width %d exceeds 256", n);
     it_note_op(c); it_pdl(k_norm_head, dim3(dim3((nheads + 3) / 4, nt)), dim3(128), 0, c->stream, in, in_hs, in_ts, out, out_hs, out_ts, n, nheads, w, mode, eps, z, z_hs, z_ts); KCHK("norm_head"); return IT_OK;
 }
 int it_sup_rope(it_ctx* c, float* x, size_t hs, size_t ts, int nheads, int nt, int pos0, const int* pos_ptr, int n_rot, float theta_scale, const int* sec) {
+    if (it_dbg_skip("rope")) return IT_OK;
     it_note_op(c); const int n = nheads * (n_rot / 2);
     it_pdl(k_rope, dim3(dim3((n + 127) / 128, nt)), dim3(128), 0, c->stream, x, hs, ts, nheads, pos0, pos_ptr, n_rot, theta_scale, sec[0], sec[1], sec[2], sec[3]); KCHK("rope"); return IT_OK;
 }
 int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, float* state, float* out, size_t o_ts, int cd, int kk, int nt, float* ck, size_t ck_stride, int nck) {
+    if (it_dbg_skip("conv")) return IT_OK;
     if (kk < 2 || kk > 9) return it_fail(IT_EINVAL, "conv kernel size %d not supported", kk);
     it_note_op(c); it_pdl(k_conv, dim3((cd + 127) / 128), dim3(128), 0, c->stream, mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
 }
 int it_sup_dense_rows(it_ctx* c, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts, float* y0, float* y1, size_t y_ts, int nt) {
+    if (it_dbg_skip("dense")) return IT_OK;
     it_note_op(c); it_pdl(k_dense_rows, dim3(dim3(2 * rows, nt)), dim3(256), 0, c->stream, w0, w1, rows, cols, x, x_ts, y0, y1, y_ts); KCHK("dense_rows"); return IT_OK;
 }
 int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
+    if (it_dbg_skip("gdn")) return IT_OK;
     if (sd % 32 != 0) return it_fail(IT_EINVAL, "ssm state size %d is not a multiple of 32", sd);
     it_note_op(c); const size_t smem = (32 * (sd + 1) + 2 * sd) * sizeof(float);
     it_pdl(k_gdn, dim3(dim3(nv, sd / 32)), dim3(128), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck); KCHK("gdn"); return IT_OK;
 }
 int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n) {
+    if (it_dbg_skip("silu")) return IT_OK;
     it_note_op(c); it_pdl(k_silu_mul, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, c->stream, g, u, out, n); KCHK("silu_mul"); return IT_OK;
 }
 int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int slot0, const int* pos_ptr, int nt, int f16) {
+    if (it_dbg_skip("kvstore")) return IT_OK;
     it_note_op(c);
     if (f16) it_pdl(k_kv_store<__half>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (__half*)kc, (__half*)vc, kvd, slot0, pos_ptr);
     else it_pdl(k_kv_store<float>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (float*)kc, (float*)vc, kvd, slot0, pos_ptr);
     KCHK("kv_store"); return IT_OK;
 }
 int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16) {
+    if (it_dbg_skip("attention")) return IT_OK;
     it_note_op(c);
     // shared memory is sized for the longest row of scores this launch can meet (max_pos when the position is read on the device)
-    const size_t smem = (((size_t)(pos_ptr ? max_pos : slot0 + nt) + 3) / 4 * 4 + hd) * sizeof(float);
-    if (smem > 200 * 1024) return it_fail(IT_EINVAL, "attention over %d positions exceeds the shared-memory budget", slot0 + nt);
+    const size_t smem = (((size_t)(pos_ptr ? max_pos : slot0 + nt) + 3) / 4 * 4 + hd) * sizeof(float) + 16 + 4 * 32768;   // scores, q, ring of V chunks
+    if (smem > 220 * 1024 || hd > 1024 || (hd * (f16 ? 2 : 4)) % 16) return it_fail(IT_EINVAL, "attention over %d positions exceeds the shared-memory budget", slot0 + nt);
     if (f16) {
-        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); set = true; }
         it_pdl(k_attention<__half>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const __half*)kc, (const __half*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
     } else {
-        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); set = true; }
         it_pdl(k_attention<float>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const float*)kc, (const float*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
     }
     KCHK("attention"); return IT_OK;
