@@ -92,14 +92,6 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
         }
     }
     __syncthreads();
-    // Programmatic dependent launch.  The weights never depend on an earlier kernel, so they are requested
-    // above without waiting.  When the kernel before this one produced our activation rows (wait_early) we
-    // wait for it here, and only then let the next kernel start: a kernel that follows us may read the same
-    // rows without waiting, so they must be complete by the time it is allowed to run.  Otherwise the rows
-    // are known to be complete already and the only wait is the one in front of the store of y.
-    if (wait_early) asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
     if (!ONESHOT && warp == NCONS) {
         // ---------------- producer: one thread keeps the ring full
         if (lane == 0) {
@@ -129,6 +121,14 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
     }
 
     // ---------------- consumers
+    // Programmatic dependent launch.  The weights never depend on an earlier kernel, so the producer warp above
+    // requests them without waiting (and never triggers: its exit counts as done).  When the kernel before this one
+    // produced our activation rows (wait_early) the consumers wait for it here, and only then let the next kernel
+    // start: a kernel that follows us may read the same rows without waiting, so they must be complete by the time
+    // it is allowed to run.  Otherwise the rows are known to be complete already and the only wait is the one in
+    // front of the store of y.
+    if (wait_early) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int g = lane >> 2, t = lane & 3;
     int8_t* xs = reinterpret_cast<int8_t*>(smem + L.x);
     float* dxs = reinterpret_cast<float*>(smem + L.dx);
@@ -277,35 +277,24 @@ int ring_slots(int MT, int nb, int nbuf, int per_cta, int want, int need) {
     return slots >= need ? slots : 0;
 }
 
-// Shape policy.
-//  - Short rows (K <= 8192) whose row groups all fit on the GPU at once: one CTA of eight warps per row group,
-//    the ring holds the whole row group and is requested in one go (up to four CTAs per SM).
-//  - Otherwise a persistent grid with a producer warp: one consumer group and up to three CTAs per SM (for the
-//    160 long row groups of a 5120 x 17408 matrix that gives every row group its own CTA: 5.2 us against 8.4 us
-//    with one three-group CTA per SM, where twelve CTAs had to take a second row group); three consumer groups
-//    only when the staged activation rows leave room for a single CTA per SM.
-// CTAs per SM drop when the staged activation rows and the terms leave no room for the ring.
+// Shape policy: a persistent grid with a producer warp and one consumer group per CTA, as many CTAs per SM as the
+// staged activation rows, the terms and a ring of at least four chunks leave room for: four for short rows (K <= 8192;
+// 17408 x 5120: 6.0 us against 6.6 us for one CTA per row group that requests its whole row group at once), three
+// for long rows (the 160 row groups of a 5120 x 17408 matrix then have a CTA each: 5.2 us against 8.4 us with one
+// three-group CTA per SM, where twelve CTAs had to take a second row group).  Three consumer groups only when a
+// single CTA fits an SM and the rows are long, so that the per-warp chain stays short.
 template <int MT, bool SUMI>
 int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
     const int nb = (int)(w->cols / 128), cpr = (nb + CWARPS - 1) / CWARPS, rgs = (int)w->row_groups;
     const bool long_rows = nb > 64;
-    if (!long_rows && !SUMI) {
-        const int total = smem_layout(MT, nb, cpr, 1).total;
-        for (int per_sm = 4; per_sm >= 1; per_sm--) {
-            if (total > SM_SMEM / per_sm - 1024) continue;
-            if (rgs > per_sm * c->sm_count) break;
-            if (per_sm == 4) return launch_cfg<MT, 1, 4, true, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, cpr, 1, rgs);
-            if (per_sm == 3) return launch_cfg<MT, 1, 3, true, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, cpr, 1, rgs);
-            return launch_cfg<MT, 1, 2, true, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, cpr, 1, rgs);
-        }
-    }
-    for (int per_sm = 3; per_sm >= 1; per_sm--) {
+    for (int per_sm = long_rows ? 3 : 4; per_sm >= 1; per_sm--) {
         const int grid = rgs < per_sm * c->sm_count ? rgs : per_sm * c->sm_count;
         const int nbuf = SUMI ? 0 : (grid == rgs ? 1 : 2);
-        const int want = long_rows ? 16 : (cpr + 2 > 4 ? cpr + 2 : 4);
+        const int want = long_rows ? 16 : (per_sm == 4 ? 6 : (cpr + 2 > 4 ? cpr + 2 : 4));
         const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / per_sm - 1024, want, cpr < 4 ? cpr : 4);
         if (!slots) continue;
         if (SUMI) return launch_cfg<MT, 1, 1, false, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
+        if (per_sm == 4) return launch_cfg<MT, 1, 4, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
         if (per_sm == 3) return launch_cfg<MT, 1, 3, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
         if (per_sm == 2) return launch_cfg<MT, 1, 2, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
         // a single CTA per SM: long rows get three consumer groups so that the per-warp chain stays short
