@@ -53,28 +53,41 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
         return it_sup_hadamard_q8_fused(cx, e_, nt, L.x, e_, e->q8, p);
     };
     const size_t s_gdn = (size_t)cd + inner, s_att = (size_t)qf + 2 * kvd, s_ffn = 2 * (size_t)ff;   // row strides of the stacked outputs
+    const bool fused = nt <= 8 && cd % sd == 0 && sd <= 256 && hd <= 256;    // decode and verification passes: fewer, fused support launches
     for (int il = 0; il < c.n_layer; il++) {
         const it_layer& l = e->layers[il];
         if (l.recurrent) {
             IT_TRY(norm_had(l.attn_norm, A + L.xn));
             IT_TRY(it_matvec_t2(cx, l.in_proj, nt, e->q8, L.big1, s_gdn, 0));                // [qkv | gate] rows
-            IT_TRY(it_sup_dense_rows(cx, l.beta, l.alpha, nv, e_, A + L.xn, e_, A + L.beta, A + L.alpha, nv, nt));
             const size_t csz = (size_t)(c.conv_k - 1) * cd, ssz = (size_t)nv * sd * sd;
-            IT_TRY(it_sup_conv(cx, A + L.big1, s_gdn, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, nt, l.ck_conv, csz, nck));
-            IT_TRY(it_sup_norm_head(cx, A + L.conv, sd, cd, A + L.conv, sd, cd, sd, 2 * nk, nullptr, 2, c.eps, nullptr, 0, 0, nt));
-            IT_TRY(it_sup_gdn(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck));
-            IT_TRY(it_sup_norm_head(cx, A + L.o, sd, inner, A + L.o, sd, inner, sd, nv, l.ssm_norm, 1, c.eps, A + L.big1 + cd, sd, s_gdn, nt));
+            if (fused) {
+                // three launches instead of six: [dense beta/alpha rows | conv | l2norm of q, k], [delta rule | gated norm]
+                IT_TRY(it_sup_conv_l2_dense(cx, A + L.big1, s_gdn, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, sd, nk, nt, l.ck_conv, csz, nck, c.eps,
+                                            l.beta, l.alpha, nv, e_, A + L.xn, e_, A + L.beta, A + L.alpha, nv));
+                IT_TRY(it_sup_gdn_norm(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck,
+                                       l.ssm_norm, c.eps, A + L.big1 + cd, s_gdn));
+            } else {
+                IT_TRY(it_sup_dense_rows(cx, l.beta, l.alpha, nv, e_, A + L.xn, e_, A + L.beta, A + L.alpha, nv, nt));
+                IT_TRY(it_sup_conv(cx, A + L.big1, s_gdn, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, nt, l.ck_conv, csz, nck));
+                IT_TRY(it_sup_norm_head(cx, A + L.conv, sd, cd, A + L.conv, sd, cd, sd, 2 * nk, nullptr, 2, c.eps, nullptr, 0, 0, nt));
+                IT_TRY(it_sup_gdn(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck));
+                IT_TRY(it_sup_norm_head(cx, A + L.o, sd, inner, A + L.o, sd, inner, sd, nv, l.ssm_norm, 1, c.eps, A + L.big1 + cd, sd, s_gdn, nt));
+            }
             if (c.gdn_v_grouped) IT_TRY(had_mv(e, l.ssm_out, nt, L.o, inner, L.x, e_, 1, true, sd, nk, nv / nk));
             else IT_TRY(had_mv(e, l.ssm_out, nt, L.o, inner, L.x, e_, 1, true));
         } else {
             float* q = A + L.big1; float* k = q + qf; float* v = k + kvd;                     // [q+gate | k | v] rows
             IT_TRY(norm_had(l.attn_norm, nullptr));
             IT_TRY(it_matvec_t2(cx, l.in_proj, nt, e->q8, L.big1, s_att, 0));
-            IT_TRY(it_sup_norm_head(cx, q, 2 * hd, s_att, q, 2 * hd, s_att, hd, nh, l.q_norm, 0, c.eps, nullptr, 0, 0, nt));
-            IT_TRY(it_sup_norm_head(cx, k, hd, s_att, k, hd, s_att, hd, nkv, l.k_norm, 0, c.eps, nullptr, 0, 0, nt));
-            IT_TRY(it_sup_rope(cx, q, 2 * hd, s_att, nh, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
-            IT_TRY(it_sup_rope(cx, k, hd, s_att, nkv, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
-            IT_TRY(it_sup_kv_store(cx, k, v, s_att, l.kc, l.vc, kvd, pos0, pos_ptr, nt, 1));
+            if (fused) {
+                IT_TRY(it_sup_attn_prep(cx, q, s_att, nh, nkv, hd, l.q_norm, l.k_norm, c.eps, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections, l.kc, l.vc, nt));
+            } else {
+                IT_TRY(it_sup_norm_head(cx, q, 2 * hd, s_att, q, 2 * hd, s_att, hd, nh, l.q_norm, 0, c.eps, nullptr, 0, 0, nt));
+                IT_TRY(it_sup_norm_head(cx, k, hd, s_att, k, hd, s_att, hd, nkv, l.k_norm, 0, c.eps, nullptr, 0, 0, nt));
+                IT_TRY(it_sup_rope(cx, q, 2 * hd, s_att, nh, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
+                IT_TRY(it_sup_rope(cx, k, hd, s_att, nkv, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
+                IT_TRY(it_sup_kv_store(cx, k, v, s_att, l.kc, l.vc, kvd, pos0, pos_ptr, nt, 1));
+            }
             IT_TRY(it_sup_attention(cx, q, 2 * hd, s_att, q + hd, l.kc, l.vc, kvd, hd, nh, nkv, pos0, pos_ptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 1));
             IT_TRY(had_mv(e, l.o, nt, L.o, (size_t)nh * hd, L.x, e_, 1, true));
         }

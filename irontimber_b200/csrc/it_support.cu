@@ -209,6 +209,170 @@ __global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* 
     vc[(size_t)(slot0 + t) * kvd + i] = kv_pack<T>(v[t * ts + i]);
 }
 
+// ---------------------------------------------------------------- fused kernels of the decode path (up to 8 rows)
+// The three kernels below run the same per-element arithmetic as the separate kernels above, in the same order; they
+// only remove kernel boundaries, which dominate a decode step's support work.
+
+// Attention input block in one launch: per-head rmsnorm of q and k (src/cpu.rs:252-256), rope on both (:145-162), and the
+// new K / V rows rounded to f16 into the cache (:258).  One warp per job and row: jobs [0, nh) are q heads (q and gate
+// interleaved per head, 2*hd apart), [nh, nh + nkv) k heads, [nh + nkv, nh + 2 nkv) v heads (copy only).
+__global__ void __launch_bounds__(128) k_attn_prep(float* qkv, size_t ts, int nh, int nkv, int hd, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                                   int pos0, const int* pos_ptr, int n_rot, float theta_scale, int s0, int s1, int s2, int s3,
+                                                   __half* kc, __half* vc, int slot0) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
+    __shared__ float buf[4][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int job = blockIdx.x * 4 + warp, t = blockIdx.y, kvd = nkv * hd;
+    if (job >= nh + 2 * nkv) return;
+    if (pos_ptr) { const int p = *pos_ptr; pos0 += p; slot0 += p; }
+    float* row = qkv + t * ts;
+    if (job >= nh + nkv) {                                   // v head: into the cache as it is
+        const int kh = job - nh - nkv; const float* v = row + (size_t)nh * 2 * hd + kvd + kh * hd;
+        for (int i = lane; i < hd; i += 32) vc[(size_t)(slot0 + t) * kvd + kh * hd + i] = __float2half_rn(v[i]);
+        return;
+    }
+    const bool is_q = job < nh;
+    float* x = is_q ? row + (size_t)job * 2 * hd : row + (size_t)nh * 2 * hd + (job - nh) * hd;
+    const float* w = is_q ? q_norm : k_norm;
+    for (int i = lane; i < hd; i += 32) buf[warp][i] = x[i];
+    __syncwarp();
+    float s = 0.f;
+    if (lane == 0) {
+#pragma unroll 8
+        for (int i = 0; i < hd; i++) s = it_add(s, it_mul(buf[warp][i], buf[warp][i]));
+    }
+    s = __shfl_sync(0xffffffffu, s, 0);
+    const float sc = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)hd), eps)));
+    for (int i = lane; i < hd; i += 32) buf[warp][i] = it_mul(it_mul(buf[warp][i], sc), w[i]);
+    __syncwarp();
+    const int half = n_rot / 2, sect = s0 + s1 + s2 + s3;
+    for (int i = lane; i < half; i += 32) {
+        float theta = (float)(pos0 + t);
+        for (int k = 0; k < i; k++) theta = it_mul(theta, theta_scale);
+        const int sector = sect > 0 ? i % sect : 0;
+        const bool use_e = sect > 0 && !((sector % 3 == 1 && sector < 3 * s1) || (sector % 3 == 2 && sector < 3 * s2) || (sector % 3 == 0 && sector < 3 * s0));
+        float sn, cs; it_sincosf(use_e ? 0.0f : theta, &sn, &cs);
+        const float x0 = buf[warp][i], x1 = buf[warp][i + half];
+        buf[warp][i] = it_sub(it_mul(x0, cs), it_mul(x1, sn));
+        buf[warp][i + half] = it_add(it_mul(x0, sn), it_mul(x1, cs));
+    }
+    __syncwarp();
+    if (is_q) { for (int i = lane; i < hd; i += 32) x[i] = buf[warp][i]; }
+    else { const int kh = job - nh; for (int i = lane; i < hd; i += 32) { x[i] = buf[warp][i]; kc[(size_t)(slot0 + t) * kvd + kh * hd + i] = __float2half_rn(buf[warp][i]); } }
+}
+
+// Delta-net input block in one launch.  CTAs [0, cd/sd): causal conv + SiLU + state shift of one head-wide run of sd
+// channels (src/cpu.rs:203-212) and, for the q and k heads (the first 2*nk runs), the l2norm of the run (:214), the
+// squares added by one thread in index order.  CTAs after those: one dense f32 row of ssm_beta / ssm_alpha each
+// (src/cpu.rs:36-43, :199-200), with the accumulation order of k_dense_rows.  nt <= 8.
+__global__ void __launch_bounds__(256) k_conv_l2_dense(const float* mixed, size_t m_ts, const float* __restrict__ cw, float* state, float* out, size_t o_ts, int cd, int kk, int sd, int nk,
+                                                       int nt, float* ck, size_t ck_stride, int nck, float eps,
+                                                       const float* __restrict__ w0, const float* __restrict__ w1, int rows, int cols, const float* x, size_t x_ts,
+                                                       float* y0, float* y1, size_t y_ts) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
+    __shared__ float vals[8][256];
+    __shared__ float scs[8];
+    __shared__ double wsum[8];
+    const int nruns = cd / sd, tid = threadIdx.x;
+    if ((int)blockIdx.x >= nruns) {
+        const int job = blockIdx.x - nruns, r = job % (2 * rows), t = job / (2 * rows), rowi = r < rows ? r : r - rows;
+        const float* wr = (r < rows ? w0 : w1) + (size_t)rowi * cols; const float* xr = x + t * x_ts;
+        double s = 0.0;
+#pragma unroll 4
+        for (int i = tid; i < cols; i += 256) s += (double)it_mul(wr[i], xr[i]);
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+        if ((tid & 31) == 0) wsum[tid >> 5] = s;
+        __syncthreads();
+        if (tid == 0) { double tt = wsum[0]; for (int k = 1; k < 8; k++) tt += wsum[k]; (r < rows ? y0 : y1)[t * y_ts + rowi] = (float)tt; }
+        return;
+    }
+    const int run = blockIdx.x, ch = run * sd + tid;
+    const bool norm = run < 2 * nk;
+    if (tid < sd) {
+        float st[8];
+        for (int i = 0; i < kk - 1; i++) st[i] = state[(size_t)i * cd + ch];
+        for (int t = 0; t < nt; t++) {
+            const float m = mixed[t * m_ts + ch];
+            float s = 0.f;
+            for (int i = 0; i < kk; i++) s = it_add(s, it_mul(i < kk - 1 ? st[i] : m, cw[ch * kk + i]));
+            const float v = it_silu(s);
+            if (norm) vals[t][tid] = v; else out[t * o_ts + ch] = v;
+            for (int i = 0; i < kk - 2; i++) st[i] = st[i + 1];
+            st[kk - 2] = m;
+            if (t < nck) for (int i = 0; i < kk - 1; i++) ck[t * ck_stride + (size_t)i * cd + ch] = st[i];
+        }
+        for (int i = 0; i < kk - 1; i++) state[(size_t)i * cd + ch] = st[i];
+    }
+    if (!norm) return;
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31;
+    if (warp < nt && lane == 0) {                            // warp t: the squares of row t in index order
+        float s = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < sd; i++) s = it_add(s, it_mul(vals[warp][i], vals[warp][i]));
+        scs[warp] = it_div(1.0f, fmaxf(it_sqrt(s), eps));
+    }
+    __syncthreads();
+    if (tid < sd) for (int t = 0; t < nt; t++) out[t * o_ts + ch] = it_mul(vals[t][tid], scs[t]);
+}
+
+// Gated delta rule (src/cpu.rs:215-232) and the gated per-head norm that follows it (:233-237) in one launch: one CTA
+// per head, one thread per state row; after each token the head's outputs are normed (squares added by one thread in
+// index order), weighted and multiplied by silu(z).  State layout [head][j][i] as on the CPU.  nt <= 8.
+__global__ void __launch_bounds__(256) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
+                                                  float* state, float* o, size_t o_ts, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck,
+                                                  const float* __restrict__ nw, float eps, const float* z, size_t z_ts) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
+    extern __shared__ float tile[];            // [sd][sd + 1] rows, then q[sd], k[sd], o[sd], 1 scale
+    const int h = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x, kh = h % nk, ld = sd + 1, nvec = sd * sd / 4;
+    float* qs = tile + sd * ld; float* ks = qs + sd; float* os = ks + sd; float* scp = os + sd;
+    float* m = state + (size_t)h * sd * sd;
+    auto tile_in = [&](const float* src) {
+        for (int f = tid; f < nvec; f += nthr) { const float4 v = reinterpret_cast<const float4*>(src)[f]; const int r = (4 * f) / sd, i = (4 * f) % sd;
+            float* d = tile + r * ld + i; d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w; }
+    };
+    auto tile_out = [&](float* dst) {
+        for (int f = tid; f < nvec; f += nthr) { const int r = (4 * f) / sd, i = (4 * f) % sd; const float* d = tile + r * ld + i;
+            reinterpret_cast<float4*>(dst)[f] = make_float4(d[0], d[1], d[2], d[3]); }
+    };
+    tile_in(m);
+    float* row = tile + tid * ld;               // thread j owns row j (tid < sd)
+    const float scale = it_div(1.0f, it_sqrt((float)sd));
+    for (int t = 0; t < nt; t++) {
+        const float* c = co + t * co_ts;
+        __syncthreads();
+        for (int i = tid; i < sd; i += nthr) { qs[i] = c[kh * sd + i]; ks[i] = c[qk + kh * sd + i]; }
+        __syncthreads();
+        if (tid < sd) {
+            const float v = c[2 * qk + h * sd + tid];
+            const float bt = it_sigmoid(beta[t * ba_ts + h]);
+            const float g = it_mul(it_softplus(it_add(alpha[t * ba_ts + h], dt[h])), a[h]);
+            const float eg = it_expf(g);
+            float s = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < sd; i++) { const float r = it_mul(row[i], eg); row[i] = r; s = it_add(s, it_mul(r, ks[i])); }
+            const float delta = it_mul(it_sub(v, s), bt);
+            float acc = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < sd; i++) { const float r = it_add(row[i], it_mul(ks[i], delta)); row[i] = r; acc = it_add(acc, it_mul(r, qs[i])); }
+            os[tid] = it_mul(acc, scale);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float s = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < sd; i++) s = it_add(s, it_mul(os[i], os[i]));
+            *scp = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)sd), eps)));
+        }
+        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * sd * sd);
+        __syncthreads();
+        if (tid < sd) o[t * o_ts + h * sd + tid] = it_mul(it_mul(it_mul(os[tid], *scp), nw[tid]), it_silu(z[t * z_ts + h * sd + tid]));
+    }
+    __syncthreads();
+    tile_out(m);
+}
+
 // Causal gated attention for one (head, row) per CTA in the CPU's order (src/cpu.rs:262-272): every score is a
 // sequential dot over the head dimension, the exponentials are added in ascending position order by one thread,
 // every output element accumulates w[p] * v[p][j] in ascending position order, then * sigmoid(gate).  Loads are
@@ -388,4 +552,28 @@ int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const 
         it_pdl(k_attention<float>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const float*)kc, (const float*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
     }
     KCHK("attention"); return IT_OK;
+}
+
+int it_sup_attn_prep(it_ctx* c, float* qkv, size_t ts, int nh, int nkv, int hd, const float* q_norm, const float* k_norm, float eps, int pos0, const int* pos_ptr,
+                     int n_rot, float theta_scale, const int* sections, void* kc, void* vc, int nt) {
+    it_note_op(c);
+    it_pdl(k_attn_prep, dim3(dim3((nh + 2 * nkv + 3) / 4, nt)), dim3(128), 0, c->stream, qkv, ts, nh, nkv, hd, q_norm, k_norm, eps, pos0, pos_ptr, n_rot, theta_scale,
+           sections[0], sections[1], sections[2], sections[3], (__half*)kc, (__half*)vc, pos0);
+    KCHK("attn_prep"); return IT_OK;
+}
+int it_sup_conv_l2_dense(it_ctx* c, const float* mixed, size_t m_ts, const float* cw, float* state, float* out, size_t o_ts, int cd, int kk, int sd, int nk, int nt,
+                         float* ck, size_t ck_stride, int nck, float eps, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts,
+                         float* y0, float* y1, size_t y_ts) {
+    it_note_op(c);
+    it_pdl(k_conv_l2_dense, dim3(dim3(cd / sd + 2 * rows * nt)), dim3(256), 0, c->stream, mixed, m_ts, cw, state, out, o_ts, cd, kk, sd, nk, nt, ck, ck_stride, nck, eps,
+           w0, w1, rows, cols, x, x_ts, y0, y1, y_ts);
+    KCHK("conv_l2_dense"); return IT_OK;
+}
+int it_sup_gdn_norm(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
+                    int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck, const float* nw, float eps, const float* z, size_t z_ts) {
+    it_note_op(c);
+    const size_t smem = ((size_t)sd * (sd + 1) + 3 * sd + 4) * sizeof(float);
+    static bool set = false; if (!set) { cudaFuncSetAttribute(k_gdn_norm, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+    it_pdl(k_gdn_norm, dim3(dim3(nv)), dim3(sd < 128 ? 128 : sd), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
+    KCHK("gdn_norm"); return IT_OK;
 }
