@@ -218,8 +218,9 @@ IT_API int it_sync(it_ctx* c) {
 // After a synchronisation: reports (and clears) the flag a kernel raises when a bounded wait ran out.
 int it_check_device_error(it_ctx* c, const char* who) {
     if (c->error_flag_host && *(volatile int*)c->error_flag_host) {
+        const int code = *(volatile int*)c->error_flag_host;
         *(volatile int*)c->error_flag_host = 0;
-        return it_fail(IT_ETIMEOUT, "%s: a kernel gave up on a bounded wait; its results are not valid", who);
+        return it_fail(IT_ETIMEOUT, "%s: a kernel gave up on a bounded wait (site %d); its results are not valid", who, code);
     }
     return IT_OK;
 }

@@ -175,4 +175,6 @@ int it_matrix_synth_view(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, u
 int it_matrix_view(it_ctx* ctx, size_t rows, size_t cols, uint8_t* tiles, it_mat** out);
 // Tile kernel for more than eight activation rows (it_matmul_t2.cu); same arithmetic as the matvec kernel.
 int it_matmul_t2_launch(it_ctx* ctx, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum);
+// tcgen05 version of the tile kernel (it_matmul_tc.cu); returns a positive value when the shape does not fit it.
+int it_matmul_tc_launch(it_ctx* ctx, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum);
 int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d);

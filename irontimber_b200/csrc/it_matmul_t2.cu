@@ -212,6 +212,13 @@ int mm_launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, float* y, si
 int it_matmul_t2_launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum) {
     const long tok_tiles = (ntok + MM_TOK - 1) / MM_TOK;
     const long want = (long)c->sm_count * 6 / 10;
+    // The tensor-memory kernel (it_matmul_tc.cu) works on 128-row tiles: it takes the shapes that give such tiles to
+    // most SMs; smaller matrices keep the finer tiles of the kernel in this file.  IT_MATMUL=legacy / tc forces one.
+    const char* fv = getenv("IT_MATMUL");      // read on every call so that a test can exercise both kernels on one shape
+    const int force = !fv ? 0 : !strcmp(fv, "legacy") ? 1 : !strcmp(fv, "tc") ? 2 : 0;
+    if (force != 1 && (force == 2 || (long)((w->row_groups + 3) / 4) * tok_tiles >= want)) {
+        const int r = it_matmul_tc_launch(c, w, ntok, x, y, y_stride, accum); if (r <= 0) return r;
+    }
     if ((long)((w->row_groups + 3) / 4) * tok_tiles >= want) return mm_launch<4, 4>(c, w, ntok, x, y, y_stride, accum);
     if ((long)((w->row_groups + 1) / 2) * tok_tiles >= want) return mm_launch<2, 4>(c, w, ntok, x, y, y_stride, accum);
     return mm_launch<1, 8>(c, w, ntok, x, y, y_stride, accum);

@@ -18,14 +18,20 @@ __device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool mbar_poll(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after WAIT_CLOCKS, or as soon as another thread of the CTA has given up.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag) {
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag, int site = 1) {
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
         for (int i = 0; i < 64; i++) if (mbar_test(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CLOCKS) { *abort_flag = 1; atomicExch(error_flag, 1); return false; }
+        if (clock64() - t0 > WAIT_CLOCKS) { if (!*abort_flag) atomicExch(error_flag, site); *abort_flag = 1; return false; }
     }
 }
 __device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {

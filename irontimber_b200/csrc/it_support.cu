@@ -556,6 +556,7 @@ int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const 
 
 int it_sup_attn_prep(it_ctx* c, float* qkv, size_t ts, int nh, int nkv, int hd, const float* q_norm, const float* k_norm, float eps, int pos0, const int* pos_ptr,
                      int n_rot, float theta_scale, const int* sections, void* kc, void* vc, int nt) {
+    if (it_dbg_skip("attnprep")) return IT_OK;
     it_note_op(c);
     it_pdl(k_attn_prep, dim3(dim3((nh + 2 * nkv + 3) / 4, nt)), dim3(128), 0, c->stream, qkv, ts, nh, nkv, hd, q_norm, k_norm, eps, pos0, pos_ptr, n_rot, theta_scale,
            sections[0], sections[1], sections[2], sections[3], (__half*)kc, (__half*)vc, pos0);
@@ -564,6 +565,7 @@ int it_sup_attn_prep(it_ctx* c, float* qkv, size_t ts, int nh, int nkv, int hd, 
 int it_sup_conv_l2_dense(it_ctx* c, const float* mixed, size_t m_ts, const float* cw, float* state, float* out, size_t o_ts, int cd, int kk, int sd, int nk, int nt,
                          float* ck, size_t ck_stride, int nck, float eps, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts,
                          float* y0, float* y1, size_t y_ts) {
+    if (it_dbg_skip("convl2")) return IT_OK;
     it_note_op(c);
     it_pdl(k_conv_l2_dense, dim3(dim3(cd / sd + 2 * rows * nt)), dim3(256), 0, c->stream, mixed, m_ts, cw, state, out, o_ts, cd, kk, sd, nk, nt, ck, ck_stride, nck, eps,
            w0, w1, rows, cols, x, x_ts, y0, y1, y_ts);
@@ -571,6 +573,7 @@ int it_sup_conv_l2_dense(it_ctx* c, const float* mixed, size_t m_ts, const float
 }
 int it_sup_gdn_norm(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                     int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck, const float* nw, float eps, const float* z, size_t z_ts) {
+    if (it_dbg_skip("gdnnorm")) return IT_OK;
     it_note_op(c);
     const size_t smem = ((size_t)sd * (sd + 1) + 3 * sd + 4) * sizeof(float);
     static bool set = false; if (!set) { cudaFuncSetAttribute(k_gdn_norm, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
