@@ -53,7 +53,7 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
         return it_sup_hadamard_q8_fused(cx, e_, nt, L.x, e_, e->q8, p);
     };
     const size_t s_gdn = (size_t)cd + inner, s_att = (size_t)qf + 2 * kvd, s_ffn = 2 * (size_t)ff;   // row strides of the stacked outputs
-    const bool fused = nt <= 8 && cd % sd == 0 && sd <= 256 && hd <= 256;    // decode and verification passes: fewer, fused support launches
+    const bool fused = nt <= 8 && sd == 128 && cd % sd == 0 && hd <= 256;    // decode and verification passes: fewer, fused support launches
     for (int il = 0; il < c.n_layer; il++) {
         const it_layer& l = e->layers[il];
         if (l.recurrent) {

@@ -320,54 +320,71 @@ __global__ void __launch_bounds__(256) k_conv_l2_dense(const float* mixed, size_
 // Gated delta rule (src/cpu.rs:215-232) and the gated per-head norm that follows it (:233-237) in one launch: one CTA
 // per head, one thread per state row; after each token the head's outputs are normed (squares added by one thread in
 // index order), weighted and multiplied by silu(z).  State layout [head][j][i] as on the CPU.  nt <= 8.
-__global__ void __launch_bounds__(256) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
-                                                  float* state, float* o, size_t o_ts, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck,
-                                                  const float* __restrict__ nw, float eps, const float* z, size_t z_ts) {
+// The head's SD x SD state sits in shared memory for the whole launch, rows unpadded, the 16-byte pieces of row j
+// stored at piece index ^ (j & 7): both the coalesced 16-byte moves of the tile and the 16-byte accesses of the row
+// owners are then free of bank conflicts.
+template <int SD>
+__global__ void __launch_bounds__(SD) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
+                                                 float* state, float* o, size_t o_ts, int nk, int qk, int nt, float* ck, size_t ck_stride, int nck,
+                                                 const float* __restrict__ nw, float eps, const float* z, size_t z_ts) {
     IT_PDL_TRIGGER(); IT_PDL_WAIT();
-    extern __shared__ float tile[];            // [sd][sd + 1] rows, then q[sd], k[sd], o[sd], 1 scale
-    const int h = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x, kh = h % nk, ld = sd + 1, nvec = sd * sd / 4;
-    float* qs = tile + sd * ld; float* ks = qs + sd; float* os = ks + sd; float* scp = os + sd;
-    float* m = state + (size_t)h * sd * sd;
-    auto tile_in = [&](const float* src) {
-        for (int f = tid; f < nvec; f += nthr) { const float4 v = reinterpret_cast<const float4*>(src)[f]; const int r = (4 * f) / sd, i = (4 * f) % sd;
-            float* d = tile + r * ld + i; d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w; }
+    extern __shared__ __align__(16) float tile[];      // [SD][SD] swizzled rows, then q[SD], k[SD], o[SD], 1 scale
+    constexpr int PPR = SD / 4;                         // 16-byte pieces per row
+    const int h = blockIdx.x, tid = threadIdx.x, kh = h % nk;
+    float* qs = tile + SD * SD; float* ks = qs + SD; float* os = ks + SD; float* scp = os + SD;
+    float* m = state + (size_t)h * SD * SD;
+    auto piece = [&](int j, int c) { return reinterpret_cast<float4*>(tile + j * SD + ((c ^ (j & 7)) << 2)); };
+    auto tile_in = [&](const float* src) {   // asynchronous 16-byte copies: the whole 64 KB is in flight at once
+#pragma unroll 8
+        for (int f = tid; f < SD * PPR; f += SD)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(piece(f / PPR, f % PPR))), "l"(reinterpret_cast<const float4*>(src) + f));
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
     };
     auto tile_out = [&](float* dst) {
-        for (int f = tid; f < nvec; f += nthr) { const int r = (4 * f) / sd, i = (4 * f) % sd; const float* d = tile + r * ld + i;
-            reinterpret_cast<float4*>(dst)[f] = make_float4(d[0], d[1], d[2], d[3]); }
+#pragma unroll 8
+        for (int f = tid; f < SD * PPR; f += SD) reinterpret_cast<float4*>(dst)[f] = *piece(f / PPR, f % PPR);
     };
     tile_in(m);
-    float* row = tile + tid * ld;               // thread j owns row j (tid < sd)
-    const float scale = it_div(1.0f, it_sqrt((float)sd));
+    const float scale = it_div(1.0f, it_sqrt((float)SD));
     for (int t = 0; t < nt; t++) {
         const float* c = co + t * co_ts;
         __syncthreads();
-        for (int i = tid; i < sd; i += nthr) { qs[i] = c[kh * sd + i]; ks[i] = c[qk + kh * sd + i]; }
+        qs[tid] = c[kh * SD + tid]; ks[tid] = c[qk + kh * SD + tid];
         __syncthreads();
-        if (tid < sd) {
-            const float v = c[2 * qk + h * sd + tid];
+        {
+            const float v = c[2 * qk + h * SD + tid];
             const float bt = it_sigmoid(beta[t * ba_ts + h]);
             const float g = it_mul(it_softplus(it_add(alpha[t * ba_ts + h], dt[h])), a[h]);
             const float eg = it_expf(g);
             float s = 0.f;
-#pragma unroll 8
-            for (int i = 0; i < sd; i++) { const float r = it_mul(row[i], eg); row[i] = r; s = it_add(s, it_mul(r, ks[i])); }
+#pragma unroll 4
+            for (int cc = 0; cc < PPR; cc++) {
+                float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc);
+                r.x = it_mul(r.x, eg); r.y = it_mul(r.y, eg); r.z = it_mul(r.z, eg); r.w = it_mul(r.w, eg);
+                *rp = r;
+                s = it_add(s, it_mul(r.x, k4.x)); s = it_add(s, it_mul(r.y, k4.y)); s = it_add(s, it_mul(r.z, k4.z)); s = it_add(s, it_mul(r.w, k4.w));
+            }
             const float delta = it_mul(it_sub(v, s), bt);
             float acc = 0.f;
-#pragma unroll 8
-            for (int i = 0; i < sd; i++) { const float r = it_add(row[i], it_mul(ks[i], delta)); row[i] = r; acc = it_add(acc, it_mul(r, qs[i])); }
+#pragma unroll 4
+            for (int cc = 0; cc < PPR; cc++) {
+                float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc), q4 = *reinterpret_cast<const float4*>(qs + 4 * cc);
+                r.x = it_add(r.x, it_mul(k4.x, delta)); r.y = it_add(r.y, it_mul(k4.y, delta)); r.z = it_add(r.z, it_mul(k4.z, delta)); r.w = it_add(r.w, it_mul(k4.w, delta));
+                *rp = r;
+                acc = it_add(acc, it_mul(r.x, q4.x)); acc = it_add(acc, it_mul(r.y, q4.y)); acc = it_add(acc, it_mul(r.z, q4.z)); acc = it_add(acc, it_mul(r.w, q4.w));
+            }
             os[tid] = it_mul(acc, scale);
         }
         __syncthreads();
         if (tid == 0) {
             float s = 0.f;
 #pragma unroll 8
-            for (int i = 0; i < sd; i++) s = it_add(s, it_mul(os[i], os[i]));
-            *scp = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)sd), eps)));
+            for (int i = 0; i < SD; i++) s = it_add(s, it_mul(os[i], os[i]));
+            *scp = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)SD), eps)));
         }
-        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * sd * sd);
+        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * SD * SD);
         __syncthreads();
-        if (tid < sd) o[t * o_ts + h * sd + tid] = it_mul(it_mul(it_mul(os[tid], *scp), nw[tid]), it_silu(z[t * z_ts + h * sd + tid]));
+        o[t * o_ts + h * SD + tid] = it_mul(it_mul(it_mul(os[tid], *scp), nw[tid]), it_silu(z[t * z_ts + h * SD + tid]));
     }
     __syncthreads();
     tile_out(m);
@@ -574,9 +591,10 @@ int it_sup_conv_l2_dense(it_ctx* c, const float* mixed, size_t m_ts, const float
 int it_sup_gdn_norm(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                     int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck, const float* nw, float eps, const float* z, size_t z_ts) {
     if (it_dbg_skip("gdnnorm")) return IT_OK;
+    if (sd != 128) return it_fail(IT_EINVAL, "gdn_norm: the fused kernel is built for a state size of 128");
     it_note_op(c);
-    const size_t smem = ((size_t)sd * (sd + 1) + 3 * sd + 4) * sizeof(float);
-    static bool set = false; if (!set) { cudaFuncSetAttribute(k_gdn_norm, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
-    it_pdl(k_gdn_norm, dim3(dim3(nv)), dim3(sd < 128 ? 128 : sd), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
+    const size_t smem = ((size_t)sd * sd + 3 * sd + 4) * sizeof(float);
+    static bool set = false; if (!set) { cudaFuncSetAttribute(k_gdn_norm<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+    it_pdl(k_gdn_norm<128>, dim3(dim3(nv)), dim3(128), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
     KCHK("gdn_norm"); return IT_OK;
 }
