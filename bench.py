@@ -1,6 +1,6 @@
 """Benchmark of the ternary hot path on B200: greedy decode of the 27B-shape ternary decoder.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--prompt P] [--layers L]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--prompt P] [--layers L] [--decode-only | --roofline-only]
 
 Workload (config 2 of the baseline): the 64-layer random-init ternary decoder with the reference architecture
 (48 gated-delta-net + 16 attention layers, n_embd 5120, n_ff 17408, vocab 248320, f16 KV), batch 1, greedy decode
@@ -38,7 +38,7 @@ N_WEIGHTS = 12
 METRIC = "decode_tok_s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_t2 launch on config 1, from the ncu capture
 # summarised in profiles/matvec_t2_config1_K5120_N17408.md
-NCU_DRAM_BYTES_PER_LAUNCH = 23698944
+NCU_DRAM_BYTES_PER_LAUNCH = 23717632
 CPU_LAYERS = 4      # layers of the truncated stack the CPU arm runs
 
 
@@ -203,6 +203,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--roofline-only", action="store_true", help="only the k_matvec_t2 sweep on config 1 (the run to put under a profiler for that kernel)")
+    ap.add_argument("--decode-only", action="store_true", help="prompt + timed decode steps only (no end-to-end, speculative, roofline or CPU legs): the run to put under a profiler")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -230,6 +232,11 @@ def main():
     import torch
     from irontimber_b200 import _lib
     from irontimber_b200.engine import CudaEngine
+
+    if args.roofline_only:
+        if rank == 0:
+            print(json.dumps(dict(base, roofline=matvec_roofline(torch, local_rank, max(args.steps, 3)), roofline_only=True)))
+        return
 
     dist = None
     if world > 1:
@@ -296,6 +303,14 @@ def main():
         t = torch.tensor([ms], device=f"cuda:{local_rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    if args.decode_only:
+        eng.close()
+        if rank == 0:
+            print(json.dumps(dict(base, value=world * args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(),
+                                  prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64}, decode_only=True)))
+        if dist:
+            dist.destroy_process_group()
+        return
     # end to end through the public generate call: token ids from host memory, every pick read back (4 bytes)
     eng.reset()
     first = eng.eval_argmax(prompt)

@@ -170,7 +170,6 @@ IT_API int it_hadamard_q8(it_ctx* c, size_t n, size_t ntok, size_t x_off, size_t
     IT_CHECK_ARG(n <= out->max_n && ntok <= out->max_tok, "it_hadamard_q8: %zu rows of %zu do not fit the q8 buffer (%zu x %zu)", ntok, n, out->max_tok, out->max_n);
     it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
-    if (it_dbg_skip("had")) { out->n = n; return IT_OK; }
     it_pdl(k_hadamard<true>, dim3(grid), dim3(256), 0, c->stream, c->arena, x_off, x_stride, nullptr, 0, 0, signs, rotate, 0,
         (unsigned)hd, (unsigned)nk, (unsigned)rep, out->qs, out->d, out->sum128, out->max_n, it_had_prologue{});
     IT_LAUNCH_CHECK("hadamard_q8");
@@ -199,7 +198,6 @@ int it_sup_hadamard_q8_fused(it_ctx* c, size_t n, size_t ntok, size_t x_off, siz
     IT_CHECK_ARG(out && out->ctx == c && n <= out->max_n && ntok <= out->max_tok && (pro.mode != 2 || (n <= 8192 && pro.n == n)), "hadamard_q8_fused: bad q8 buffer or width");
     it_note_op(c);
     dim3 grid((unsigned)(n / 1024), (unsigned)ntok);
-    if (it_dbg_skip("had")) { out->n = n; return IT_OK; }
     it_pdl(k_hadamard<true>, dim3(grid), dim3(256), 0, c->stream, c->arena, x_off, x_stride, nullptr, 0, 0, signs, 1, 0, 0u, 0u, 0u, out->qs, out->d, out->sum128, out->max_n, pro);
     IT_LAUNCH_CHECK("hadamard_q8_fused");
     out->n = n;

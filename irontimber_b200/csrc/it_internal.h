@@ -127,8 +127,6 @@ struct it_ctx {
 // counter, [9] epoch) and the low-latency exchange buffer of 2 * ll_slots 8-byte slots.
 #define IT_ARENA_TAIL 256
 #define IT_LL_MAX_SLOTS ((size_t)1 << 21)
-#include <cstring>
-static inline bool it_dbg_skip(const char* name) { const char* v = getenv("IT_SKIP"); return v && strstr(v, name); }
 // Every entry point that enqueues device work other than the ternary matvec calls this.
 static inline void it_note_op(it_ctx* c) { c->pdl_safe_q8 = nullptr; }
 

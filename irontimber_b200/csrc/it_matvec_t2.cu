@@ -340,7 +340,6 @@ int check(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, const char* w
 
 IT_API int it_matvec_t2(it_ctx* c, const it_mat* w, size_t ntok, const it_q8* x, size_t y_off, size_t y_stride, int accum) {
     int r = check(c, w, ntok, x, "it_matvec_t2"); if (r) return r;
-    if (it_dbg_skip("matvec")) return IT_OK;
     IT_CHECK_ARG(ntok == 1 || y_stride >= w->out_rows, "it_matvec_t2: output stride %zu is shorter than a row of %zu results", y_stride, w->out_rows);
     IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->out_rows <= c->arena_floats - y_off, "it_matvec_t2: output rows fall outside the arena");
     if (w->sharded && !c->peers_dev) return it_fail(IT_ESTATE, "it_matvec_t2: the matrix is a row shard but no peers are attached to the context");

@@ -194,8 +194,6 @@ __global__ void k_silu_mul(const float* g, const float* u, float* out, size_t n)
 template <typename T> __device__ __forceinline__ T kv_pack(float v);
 template <> __device__ __forceinline__ __half kv_pack<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ float kv_pack<float>(float v) { return v; }
-__device__ __forceinline__ float kv_get(const __half* p) { return __half2float(*p); }
-__device__ __forceinline__ float kv_get(const float* p) { return *p; }
 __device__ __forceinline__ float2 kv_get2(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
 __device__ __forceinline__ float2 kv_get2(const float* p) { return *reinterpret_cast<const float2*>(p); }
 
@@ -510,53 +508,43 @@ __global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs,
 }  // namespace
 
 int it_sup_embed(it_ctx* c, const uint32_t* toks_dev, const float* table, int e, int nt, float* x) {
-    if (it_dbg_skip("embed")) return IT_OK;
     it_note_op(c); it_pdl(k_embed, dim3(dim3(4, nt)), dim3(256), 0, c->stream, toks_dev, table, e, x); KCHK("embed"); return IT_OK;
 }
 int it_sup_rmsnorm_wide(it_ctx* c, const float* x, size_t xs, const float* w, int n, float eps, float* out, size_t os, int nt) {
-    if (it_dbg_skip("rmsw")) return IT_OK;
     it_note_op(c); it_pdl(k_rmsnorm_wide, dim3(nt), dim3(256), 0, c->stream, x, xs, w, n, eps, out, os); KCHK("rmsnorm_wide"); return IT_OK;
 }
 int it_sup_norm_head(it_ctx* c, const float* in, size_t in_hs, size_t in_ts, float* out, size_t out_hs, size_t out_ts, int n, int nheads, const float* w, int mode, float eps,
                      const float* z, size_t z_hs, size_t z_ts, int nt) {
-    if (it_dbg_skip("normhead")) return IT_OK;
     if (n > 256) return it_fail(IT_EINVAL, "head norm width %d exceeds 256", n);
     it_note_op(c); it_pdl(k_norm_head, dim3(dim3((nheads + 3) / 4, nt)), dim3(128), 0, c->stream, in, in_hs, in_ts, out, out_hs, out_ts, n, nheads, w, mode, eps, z, z_hs, z_ts); KCHK("norm_head"); return IT_OK;
 }
 int it_sup_rope(it_ctx* c, float* x, size_t hs, size_t ts, int nheads, int nt, int pos0, const int* pos_ptr, int n_rot, float theta_scale, const int* sec) {
-    if (it_dbg_skip("rope")) return IT_OK;
     it_note_op(c); const int n = nheads * (n_rot / 2);
     it_pdl(k_rope, dim3(dim3((n + 127) / 128, nt)), dim3(128), 0, c->stream, x, hs, ts, nheads, pos0, pos_ptr, n_rot, theta_scale, sec[0], sec[1], sec[2], sec[3]); KCHK("rope"); return IT_OK;
 }
 int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, float* state, float* out, size_t o_ts, int cd, int kk, int nt, float* ck, size_t ck_stride, int nck) {
-    if (it_dbg_skip("conv")) return IT_OK;
     if (kk < 2 || kk > 9) return it_fail(IT_EINVAL, "conv kernel size %d not supported", kk);
     it_note_op(c); it_pdl(k_conv, dim3((cd + 127) / 128), dim3(128), 0, c->stream, mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
 }
 int it_sup_dense_rows(it_ctx* c, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts, float* y0, float* y1, size_t y_ts, int nt) {
-    if (it_dbg_skip("dense")) return IT_OK;
     it_note_op(c); it_pdl(k_dense_rows, dim3(dim3(2 * rows, nt)), dim3(256), 0, c->stream, w0, w1, rows, cols, x, x_ts, y0, y1, y_ts); KCHK("dense_rows"); return IT_OK;
 }
 int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck) {
-    if (it_dbg_skip("gdn")) return IT_OK;
     if (sd % 32 != 0) return it_fail(IT_EINVAL, "ssm state size %d is not a multiple of 32", sd);
     it_note_op(c); const size_t smem = (32 * (sd + 1) + 2 * sd) * sizeof(float);
     it_pdl(k_gdn, dim3(dim3(nv, sd / 32)), dim3(128), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, sd, qk, nt, ck, ck_stride, nck); KCHK("gdn"); return IT_OK;
 }
 int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n) {
-    if (it_dbg_skip("silu")) return IT_OK;
     it_note_op(c); it_pdl(k_silu_mul, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, c->stream, g, u, out, n); KCHK("silu_mul"); return IT_OK;
 }
 int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int slot0, const int* pos_ptr, int nt, int f16) {
-    if (it_dbg_skip("kvstore")) return IT_OK;
     it_note_op(c);
     if (f16) it_pdl(k_kv_store<__half>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (__half*)kc, (__half*)vc, kvd, slot0, pos_ptr);
     else it_pdl(k_kv_store<float>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (float*)kc, (float*)vc, kvd, slot0, pos_ptr);
     KCHK("kv_store"); return IT_OK;
 }
 int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16) {
-    if (it_dbg_skip("attention")) return IT_OK;
     it_note_op(c);
     // shared memory is sized for the longest row of scores this launch can meet (max_pos when the position is read on the device)
     const size_t smem = (((size_t)(pos_ptr ? max_pos : slot0 + nt) + 3) / 4 * 4 + hd) * sizeof(float) + 16 + 4 * 32768;   // scores, q, ring of V chunks
@@ -573,7 +561,6 @@ int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const 
 
 int it_sup_attn_prep(it_ctx* c, float* qkv, size_t ts, int nh, int nkv, int hd, const float* q_norm, const float* k_norm, float eps, int pos0, const int* pos_ptr,
                      int n_rot, float theta_scale, const int* sections, void* kc, void* vc, int nt) {
-    if (it_dbg_skip("attnprep")) return IT_OK;
     it_note_op(c);
     it_pdl(k_attn_prep, dim3(dim3((nh + 2 * nkv + 3) / 4, nt)), dim3(128), 0, c->stream, qkv, ts, nh, nkv, hd, q_norm, k_norm, eps, pos0, pos_ptr, n_rot, theta_scale,
            sections[0], sections[1], sections[2], sections[3], (__half*)kc, (__half*)vc, pos0);
@@ -582,7 +569,6 @@ int it_sup_attn_prep(it_ctx* c, float* qkv, size_t ts, int nh, int nkv, int hd, 
 int it_sup_conv_l2_dense(it_ctx* c, const float* mixed, size_t m_ts, const float* cw, float* state, float* out, size_t o_ts, int cd, int kk, int sd, int nk, int nt,
                          float* ck, size_t ck_stride, int nck, float eps, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts,
                          float* y0, float* y1, size_t y_ts) {
-    if (it_dbg_skip("convl2")) return IT_OK;
     it_note_op(c);
     it_pdl(k_conv_l2_dense, dim3(dim3(cd / sd + 2 * rows * nt)), dim3(256), 0, c->stream, mixed, m_ts, cw, state, out, o_ts, cd, kk, sd, nk, nt, ck, ck_stride, nck, eps,
            w0, w1, rows, cols, x, x_ts, y0, y1, y_ts);
@@ -590,7 +576,6 @@ int it_sup_conv_l2_dense(it_ctx* c, const float* mixed, size_t m_ts, const float
 }
 int it_sup_gdn_norm(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                     int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck, const float* nw, float eps, const float* z, size_t z_ts) {
-    if (it_dbg_skip("gdnnorm")) return IT_OK;
     if (sd != 128) return it_fail(IT_EINVAL, "gdn_norm: the fused kernel is built for a state size of 128");
     it_note_op(c);
     const size_t smem = ((size_t)sd * sd + 3 * sd + 4) * sizeof(float);
