@@ -93,6 +93,9 @@ int it_matrix_synth(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int fo
 int it_shard_range(size_t rows, int rank, int world, size_t* row0, size_t* nrows);
 int it_matrix_set_shard(it_mat* m, size_t row0, size_t total_rows);
 int it_matrix_synth_rows(it_ctx* ctx, uint64_t seed, size_t total_rows, size_t cols, int four_codes, size_t row0, size_t nrows, it_mat** out);
+/* The same for int8-group matrices (it_matvec_q8 on a shard pushes its rows to every peer). */
+int it_qmatrix_set_shard(it_qmat* m, size_t row0, size_t total_rows);
+int it_qmatrix_synth_rows(it_ctx* ctx, uint64_t seed, size_t total_rows, size_t cols, size_t row0, size_t nrows, it_qmat** out);
 /* Decodes the device layout back to raw PQ2_0 rows (rows*cols/128*34 bytes). */
 int it_matrix_download_pq2(it_ctx* ctx, const it_mat* m, uint8_t* raw);
 size_t it_matrix_rows(const it_mat* m);

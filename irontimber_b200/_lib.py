@@ -35,6 +35,8 @@ SIGNATURES = {
     "it_shard_range": (C.c_int, [c_size, C.c_int, C.c_int, C.POINTER(c_size), C.POINTER(c_size)]),
     "it_matrix_set_shard": (C.c_int, [P, c_size, c_size]),
     "it_matrix_synth_rows": (C.c_int, [P, C.c_uint64, c_size, c_size, C.c_int, c_size, c_size, C.POINTER(P)]),
+    "it_qmatrix_set_shard": (C.c_int, [P, c_size, c_size]),
+    "it_qmatrix_synth_rows": (C.c_int, [P, C.c_uint64, c_size, c_size, c_size, c_size, C.POINTER(P)]),
     "it_ctx_ipc_handle": (C.c_int, [P, P]),
     "it_ctx_attach_peers": (C.c_int, [P, C.c_int, C.c_int, P]),
     "it_ctx_world": (C.c_int, [P]),

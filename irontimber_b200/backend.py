@@ -181,6 +181,12 @@ class CudaBackend:
         _lib.check(self.L.it_qmatrix_upload_q8_0(self.ctx, _ptr(raw), rows, cols, C.byref(h)))
         return Q8Matrix(self, h)
 
+    def qmat_synth_rows(self, seed, total_rows, cols, row0, nrows):
+        """Rows [row0, row0 + nrows) of the synthetic int8-group matrix (seed, total_rows, cols), marked as a row shard."""
+        h = C.c_void_p()
+        _lib.check(self.L.it_qmatrix_synth_rows(self.ctx, seed, total_rows, cols, row0, nrows, C.byref(h)))
+        return Q8Matrix(self, h)
+
     def qmat_synth(self, seed, rows, cols):
         h = C.c_void_p()
         _lib.check(self.L.it_qmatrix_synth(self.ctx, seed, rows, cols, C.byref(h)))

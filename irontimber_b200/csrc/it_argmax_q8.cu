@@ -1,5 +1,6 @@
 // Greedy argmax over the logits and the int8-group matvec of the MTP head.
 #include "it_internal.h"
+#include "it_pipe.cuh"
 
 namespace {
 
@@ -67,12 +68,12 @@ constexpr int QROWS = 4;
 template <int NT>
 __global__ void __launch_bounds__(256)
 k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, int rows, int cols,
-            const float* x, size_t x_stride, float* y, size_t y_stride, int ntok, int accum) {
+            const float* x, size_t x_stride, float* arena, size_t y_off, size_t y_stride, int ntok, int accum,
+            const it_peers* peers, int row_off, int* error_flag) {
     IT_PDL_TRIGGER(); IT_PDL_WAIT();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r0 = (blockIdx.x * 8 + warp) * QROWS;
-    if (r0 >= rows) return;
-    const int groups = cols / 16;
+    const int groups = r0 < rows ? cols / 16 : 0;      // warps past the last row only take part in the end-of-kernel handshake
     float acc[QROWS][NT];
 #pragma unroll
     for (int r = 0; r < QROWS; r++)
@@ -111,8 +112,19 @@ k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, int ro
             float s = acc[r][t];
 #pragma unroll
             for (unsigned m = 16; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-            if (lane == 0 && t < ntok && r0 + r < rows) { float* dst = y + t * y_stride + r0 + r; *dst = accum ? *dst + s : s; }
+            if (lane == 0 && t < ntok && r0 + r < rows) {
+                // a row shard writes at its rows' place in the full output, into every rank's arena (the old value of an
+                // accumulating call is added with a plain f32 addition, as before)
+                const size_t off = y_off + t * y_stride + row_off + r0 + r;
+                if (accum) s = arena[off] + s;
+                it_result_store(peers, arena, off, s, 0);
+            }
         }
+    if (peers) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) it_shard_finish(peers, gridDim.x, error_flag);
+    }
 }
 
 }  // namespace
@@ -140,16 +152,18 @@ IT_API int it_matvec_q8(it_ctx* c, const it_qmat* w, size_t ntok, size_t x_off, 
     IT_CHECK_ARG(ntok > 0 && ntok <= 65535, "it_matvec_q8: bad row count %zu", ntok);
     IT_CHECK_ARG(x_off % 4 == 0 && (ntok == 1 || x_stride % 4 == 0), "it_matvec_q8: activation offsets must be 4-float aligned");
     IT_CHECK_ARG(x_off <= c->arena_floats && (ntok - 1) * x_stride + w->cols <= c->arena_floats - x_off, "it_matvec_q8: input rows fall outside the arena");
-    IT_CHECK_ARG(ntok == 1 || y_stride >= w->rows, "it_matvec_q8: output stride shorter than a row of results");
-    IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->rows <= c->arena_floats - y_off, "it_matvec_q8: output rows fall outside the arena");
+    IT_CHECK_ARG(ntok == 1 || y_stride >= w->out_rows, "it_matvec_q8: output stride shorter than a row of results");
+    IT_CHECK_ARG(y_off <= c->arena_floats && (ntok - 1) * y_stride + w->out_rows <= c->arena_floats - y_off, "it_matvec_q8: output rows fall outside the arena");
+    if (w->sharded && !c->peers_dev) return it_fail(IT_ESTATE, "it_matvec_q8: the matrix is a row shard but no peers are attached to the context");
     it_note_op(c);
     const unsigned grid = (unsigned)((w->rows + 8 * QROWS - 1) / (8 * QROWS));
+    const it_peers* peers = w->sharded ? c->peers_dev : nullptr;
     for (size_t t0 = 0; t0 < ntok; t0 += 4) {
         const int nt = (int)((ntok - t0) < 4 ? (ntok - t0) : 4);
-        const float* x = c->arena + x_off + t0 * x_stride; float* y = c->arena + y_off + t0 * y_stride;
-        if (nt == 1) it_pdl(k_matvec_q8<1>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
-        else if (nt == 2) it_pdl(k_matvec_q8<2>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
-        else it_pdl(k_matvec_q8<4>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, y, y_stride, nt, accum);
+        const float* x = c->arena + x_off + t0 * x_stride; const size_t yo = y_off + t0 * y_stride;
+        if (nt == 1) it_pdl(k_matvec_q8<1>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, c->arena, yo, y_stride, nt, accum, peers, (int)w->row0, c->error_flag_dev);
+        else if (nt == 2) it_pdl(k_matvec_q8<2>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, c->arena, yo, y_stride, nt, accum, peers, (int)w->row0, c->error_flag_dev);
+        else it_pdl(k_matvec_q8<4>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, c->arena, yo, y_stride, nt, accum, peers, (int)w->row0, c->error_flag_dev);
         IT_LAUNCH_CHECK("matvec_q8");
     }
     return IT_OK;

@@ -44,20 +44,21 @@ int it_launch_synth_pq2(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, in
 }
 
 // Q8_0 synthetic rule: q = (hash(seed, e/2) 32-bit half) % 255 - 127, d = f16(0.002 + 0.004*u) per 32-block.
-__global__ void k_synth_q8_0(uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d) {
+__global__ void k_synth_q8_0(uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d, size_t row0) {
     size_t n = rows * cols;
-    for (size_t p = blockIdx.x * (size_t)blockDim.x + threadIdx.x; p < n / 2; p += (size_t)gridDim.x * blockDim.x) {
+    for (size_t lp = blockIdx.x * (size_t)blockDim.x + threadIdx.x; lp < n / 2; lp += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = lp + row0 * cols / 2;            // pair index in the full matrix (cols is a multiple of 32)
         uint64_t h = it_hash(seed, p);
-        q[2 * p] = (int8_t)((int)((uint32_t)h % 255u) - 127);
-        q[2 * p + 1] = (int8_t)((int)((uint32_t)(h >> 32) % 255u) - 127);
+        q[2 * lp] = (int8_t)((int)((uint32_t)h % 255u) - 127);
+        q[2 * lp + 1] = (int8_t)((int)((uint32_t)(h >> 32) % 255u) - 127);
         if (p % 16 == 0) {
             float u = (float)(it_hash(seed ^ 0x5ca1e5ull, p / 16) >> 40) * (1.0f / 16777216.0f);
-            d[p / 16] = __float2half_rn(__fadd_rn(0.002f, __fmul_rn(0.004f, u)));
+            d[lp / 16] = __float2half_rn(__fadd_rn(0.002f, __fmul_rn(0.004f, u)));
         }
     }
 }
-int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d) {
-    k_synth_q8_0<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, rows, cols, q, d);
+int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d, size_t row0) {
+    k_synth_q8_0<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, rows, cols, q, d, row0);
     IT_LAUNCH_CHECK("synth_q8_0"); return IT_OK;
 }
 
@@ -416,7 +417,7 @@ static int qmat_alloc(it_ctx* c, size_t rows, size_t cols, it_qmat** out, const 
     *out = nullptr;
     IT_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "%s: bad shape %zux%zu (cols must be a multiple of 32)", who, rows, cols);
     IT_CUDA(cudaSetDevice(c->device));
-    it_qmat* m = new it_qmat(); m->ctx = c; m->rows = rows; m->cols = cols; m->q = nullptr; m->d = nullptr;
+    it_qmat* m = new it_qmat(); m->ctx = c; m->rows = rows; m->cols = cols; m->q = nullptr; m->d = nullptr; m->sharded = false; m->row0 = 0; m->out_rows = rows;
     m->bytes = rows * cols + rows * (cols / 32) * 2;
     cudaError_t e = cudaMalloc(&m->q, rows * cols);
     if (e == cudaSuccess) e = cudaMalloc(&m->d, rows * (cols / 32) * 2);
@@ -441,6 +442,22 @@ IT_API int it_qmatrix_synth(it_ctx* c, uint64_t seed, size_t rows, size_t cols, 
     cudaError_t e = r == IT_OK ? cudaStreamSynchronize(c->stream) : cudaSuccess;
     if (r || e != cudaSuccess) { it_qmatrix_destroy(*out); *out = nullptr; return r ? r : it_fail(IT_ECUDA, "it_qmatrix_synth: %s", cudaGetErrorString(e)); }
     return IT_OK;
+}
+IT_API int it_qmatrix_set_shard(it_qmat* m, size_t row0, size_t total_rows) {
+    IT_CHECK_ARG(m, "it_qmatrix_set_shard: null matrix");
+    IT_CHECK_ARG(row0 + m->rows <= total_rows && total_rows <= (1u << 30), "it_qmatrix_set_shard: rows [%zu, %zu) fall outside a matrix of %zu rows", row0, row0 + m->rows, total_rows);
+    m->sharded = true; m->row0 = row0; m->out_rows = total_rows;
+    return IT_OK;
+}
+IT_API int it_qmatrix_synth_rows(it_ctx* c, uint64_t seed, size_t total_rows, size_t cols, size_t row0, size_t nrows, it_qmat** out) {
+    IT_CHECK_ARG(out, "it_qmatrix_synth_rows: null output");
+    *out = nullptr;
+    IT_CHECK_ARG(nrows > 0 && row0 + nrows <= total_rows, "it_qmatrix_synth_rows: rows [%zu, %zu) fall outside a matrix of %zu rows", row0, row0 + nrows, total_rows);
+    int r = qmat_alloc(c, nrows, cols, out, "it_qmatrix_synth_rows"); if (r) return r;
+    r = it_launch_synth_q8_0(c, seed, nrows, cols, (*out)->q, (*out)->d, row0);
+    cudaError_t e = r == IT_OK ? cudaStreamSynchronize(c->stream) : cudaSuccess;
+    if (r || e != cudaSuccess) { it_qmatrix_destroy(*out); *out = nullptr; return r ? r : it_fail(IT_ECUDA, "it_qmatrix_synth_rows: %s", cudaGetErrorString(e)); }
+    return it_qmatrix_set_shard(*out, row0, total_rows);
 }
 IT_API int it_qmatrix_download_q8_0(it_ctx* c, const it_qmat* m, uint8_t* raw) {
     IT_CHECK_ARG(c && m && raw, "it_qmatrix_download_q8_0: null argument");

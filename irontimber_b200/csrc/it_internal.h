@@ -81,6 +81,7 @@ struct it_qmat {
     int8_t* q;
     __half* d;
     size_t bytes;
+    bool sharded; size_t row0, out_rows;   // rows [row0, row0 + rows) of a logical matrix of out_rows rows (see it_mat)
 };
 
 struct it_q8 {
@@ -175,4 +176,4 @@ int it_matrix_view(it_ctx* ctx, size_t rows, size_t cols, uint8_t* tiles, it_mat
 int it_matmul_t2_launch(it_ctx* ctx, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum);
 // tcgen05 version of the tile kernel (it_matmul_tc.cu); returns a positive value when the shape does not fit it.
 int it_matmul_tc_launch(it_ctx* ctx, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum);
-int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d);
+int it_launch_synth_q8_0(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, int8_t* q, __half* d, size_t row0 = 0);

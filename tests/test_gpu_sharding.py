@@ -53,6 +53,37 @@ def test_shards_on_one_gpu_fill_the_full_output(orc, rows, cols, ntok, acc):
         be.close()
 
 
+@pytest.mark.parametrize("rows,cols,ntok,acc", [(1000, 1024, 1, False), (4096, 5120, 3, True)])
+def test_q8_shards_on_one_gpu_equal_the_full_matrix(rows, cols, ntok, acc):
+    """Int8-group matvec (the NextN head / q8 LM head kind) on row shards: same bits as the unsharded launch."""
+    from irontimber_b200.backend import CudaBackend
+    be = CudaBackend(0, arena_floats=1 << 22)
+    try:
+        be.attach_peers(0, 1)
+        rng = np.random.default_rng(rows)
+        full = be.qmat_synth(31, rows, cols)
+        cut = rows // 2
+        parts = [be.qmat_synth_rows(31, rows, cols, 0, cut), be.qmat_synth_rows(31, rows, cols, cut, rows - cut)]
+        raw = full.download_q8_0().reshape(rows, -1)
+        assert np.array_equal(parts[0].download_q8_0().reshape(cut, -1), raw[:cut])
+        assert np.array_equal(parts[1].download_q8_0().reshape(rows - cut, -1), raw[cut:])
+        X = rng.standard_normal((ntok, cols)).astype(np.float32)
+        y0 = rng.standard_normal(ntok * rows).astype(np.float32)
+        yo = ((ntok * cols + 63) // 64) * 64
+        be.upload(0, X); be.upload(yo, y0)
+        be.mvq(full, ntok, 0, cols, yo, rows, acc=acc)
+        want = be.download(yo, ntok * rows)
+        be.upload(yo, y0)
+        for m in parts:
+            be.mvq(m, ntok, 0, cols, yo, rows, acc=acc)
+        got = be.download(yo, ntok * rows)
+        assert np.array_equal(bits(got), bits(want))
+        for m in parts + [full]:
+            m.close()
+    finally:
+        be.close()
+
+
 def test_shard_without_peers_is_refused():
     from irontimber_b200 import _lib
     from irontimber_b200.backend import CudaBackend
