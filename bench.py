@@ -1,6 +1,6 @@
 """Benchmark of the ternary hot path on B200: greedy decode of the 27B-shape ternary decoder.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--prompt P] [--layers L] [--decode-only | --roofline-only]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--prompt P] [--layers L] [--decode-only | --roofline-only | --sweep]
 
 Workload (config 2 of the baseline): the 64-layer random-init ternary decoder with the reference architecture
 (48 gated-delta-net + 16 attention layers, n_embd 5120, n_ff 17408, vocab 248320, f16 KV), batch 1, greedy decode
@@ -195,6 +195,84 @@ def matvec_roofline(torch, local_rank, steps):
             "algorithmic_bytes_per_launch": abytes, "us_per_launch": per_launch * 1e6, "traffic": NCU_DRAM_BYTES_PER_LAUNCH}
 
 
+def sweep(args, torch, np, rank, world, local_rank, base):
+    """Config 5 of the baseline: K = 5120, N in {17408, 34816, 69632}, M in {1, 4, 64, 512}, and the Q8_0 LM head
+    (N = 248320, M = 1).  With more than one rank every matrix is split by output rows and each launch ends with the
+    exchange of the result slices through peer memory; the time is the max over ranks of the device time per launch."""
+    from irontimber_b200.backend import CudaBackend
+    from irontimber_b200.sharding import shard_range
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    be = CudaBackend(local_rank, arena_floats=1 << 26)
+    if world > 1:
+        be.attach_peers(rank, world)
+    stream = torch.cuda.ExternalStream(be.stream, device=f"cuda:{local_rank}")
+    rng = np.random.default_rng(0)
+    K = COLS
+    out = []
+
+    def timed(launch, nmat):
+        launch(); be.sync()
+        if dist:
+            dist.barrier()
+        be.capture_begin(); launch(); g = be.capture_end()
+        for _ in range(3):
+            be.graph_launch(g)
+        be.sync()
+        if dist:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, args.steps // 8)
+        e0.record(stream)
+        for _ in range(reps):
+            be.graph_launch(g)
+        e1.record(stream)
+        be.sync(); torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * nmat)
+        if dist:
+            t = torch.tensor([us], device=f"cuda:{local_rank}")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+        be.graph_destroy(g)
+        return us
+
+    for N in (17408, 34816, 69632):
+        row0, n = shard_range(N, rank, world)
+        nmat = max(2, min(12, int(300e6 // (n * K * 34 / 128)) + 1))        # distinct matrices: more bytes than L2
+        mats = [be.mat_synth_rows(100 + i, N, K, row0, n) if world > 1 else be.mat_synth(100 + i, N, K) for i in range(nmat)]
+        for M in (1, 4, 64, 512):
+            q = be.q8_rows(K, M)
+            be.upload(0, rng.standard_normal((M, K)).astype(np.float32))
+            be.had_q8(K, M, 0, K, q, signs=False, rotate=False)
+            yo = ((M * K + 63) // 64) * 64
+            us = timed(lambda: [be.mv(w, M, q, yo, N) for w in mats], nmat)
+            out.append({"op": "matvec_t2" if M <= 8 else "matmul_t2", "N": N, "K": K, "M": M, "us": us,
+                        "weights_GBs": N * K * 34 / 128 / us / 1e3, "TOPs": 2 * M * N * K / us / 1e6})
+            q.close()
+        for w in mats:
+            w.close()
+    N = 248320
+    row0, n = shard_range(N, rank, world)
+    heads = [be.qmat_synth_rows(7 + i, N, K, row0, n) if world > 1 else be.qmat_synth(7 + i, N, K) for i in range(2)]
+    be.upload(0, rng.standard_normal(K).astype(np.float32))
+    us = timed(lambda: [be.mvq(h, 1, 0, K, 1 << 20, N) for h in heads], 2)
+    out.append({"op": "matvec_q8 (Q8_0 LM head)", "N": N, "K": K, "M": 1, "us": us, "weights_GBs": N * K * 34 / 32 / us / 1e3})
+    for h in heads:
+        h.close()
+    be.sync()
+    if dist:
+        dist.barrier()
+    be.close()
+    if rank == 0:
+        print(json.dumps(dict(base, metric="config5_sweep_us_per_launch", unit="us", higher_is_better=False, scaling="strong", value=out[0]["us"],
+                              sweep=out, config={"workload": "config5: ternary product K=5120, N x M grid, and the Q8_0 LM head; rows split evenly over the ranks, result slices exchanged inside the kernels"})))
+    if dist:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -204,6 +282,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--roofline-only", action="store_true", help="only the k_matvec_t2 sweep on config 1 (the run to put under a profiler for that kernel)")
+    ap.add_argument("--sweep", action="store_true", help="config 5: op-level sweep of the ternary product (N x M grid) and the q8 LM head, row-sharded over the ranks when N > 1")
     ap.add_argument("--decode-only", action="store_true", help="prompt + timed decode steps only (no end-to-end, speculative, roofline or CPU legs): the run to put under a profiler")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -233,6 +312,9 @@ def main():
     from irontimber_b200 import _lib
     from irontimber_b200.engine import CudaEngine
 
+    if args.sweep:
+        sweep(args, torch, np, rank, world, local_rank, base)
+        return
     if args.roofline_only:
         if rank == 0:
             print(json.dumps(dict(base, roofline=matvec_roofline(torch, local_rank, max(args.steps, 3)), roofline_only=True)))
