@@ -61,15 +61,19 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
             IT_TRY(it_matvec_t2(cx, l.in_proj, nt, e->q8, L.big1, s_gdn, 0));                // [qkv | gate] rows
             const size_t csz = (size_t)(c.conv_k - 1) * cd, ssz = (size_t)nv * sd * sd;
             if (fused) {
-                // three launches instead of six: [dense beta/alpha rows | conv | l2norm of q, k], [delta rule | gated norm]
+                // [dense beta/alpha rows | conv | l2norm of q, k] in one launch
                 IT_TRY(it_sup_conv_l2_dense(cx, A + L.big1, s_gdn, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, sd, nk, nt, l.ck_conv, csz, nck, c.eps,
                                             l.beta, l.alpha, nv, e_, A + L.xn, e_, A + L.beta, A + L.alpha, nv));
-                IT_TRY(it_sup_gdn_norm(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck,
-                                       l.ssm_norm, c.eps, A + L.big1 + cd, s_gdn));
             } else {
                 IT_TRY(it_sup_dense_rows(cx, l.beta, l.alpha, nv, e_, A + L.xn, e_, A + L.beta, A + L.alpha, nv, nt));
                 IT_TRY(it_sup_conv(cx, A + L.big1, s_gdn, l.conv_w, l.conv_st, A + L.conv, cd, cd, c.conv_k, nt, l.ck_conv, csz, nck));
                 IT_TRY(it_sup_norm_head(cx, A + L.conv, sd, cd, A + L.conv, sd, cd, sd, 2 * nk, nullptr, 2, c.eps, nullptr, 0, 0, nt));
+            }
+            if (sd == 128) {
+                // [delta rule | gated norm] in one launch, for any number of rows (the state stays in shared memory across the rows)
+                IT_TRY(it_sup_gdn_norm(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck,
+                                       l.ssm_norm, c.eps, A + L.big1 + cd, s_gdn));
+            } else {
                 IT_TRY(it_sup_gdn(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck));
                 IT_TRY(it_sup_norm_head(cx, A + L.o, sd, inner, A + L.o, sd, inner, sd, nv, l.ssm_norm, 1, c.eps, A + L.big1 + cd, sd, s_gdn, nt));
             }
