@@ -233,6 +233,31 @@ int64_t it_greedy_mtp(const it_mtp_backend* b, const uint32_t* prompt, size_t n_
 /* generate_mtp (src/engine.rs:180-191): greedy_mtp over this engine's own MtpBackend. */
 int64_t it_engine_generate_mtp(it_engine* e, const uint32_t* prompt, size_t n_prompt, size_t n_predict, uint32_t eos, uint32_t* out, int64_t stats[9]);
 
+/* Draft length k = 1..3.  The reference defines k = 1 only (src/mtp.rs:3-8: the head needs the trunk's hidden state of the
+ * previous position, which does not exist for a drafted position); this extension keeps its invariant (the output is
+ * plain greedy decoding).  Draft i >= 2 feeds the head its own hidden state before head_norm with draft i - 1 as the
+ * token, one position on; its KV entry is provisional.  it_engine_mtp_verify_k runs the k + 1 rows [x, d_1 .. d_k]
+ * through the trunk with a recurrent-state checkpoint after every row and returns the k + 1 picks; the caller keeps the
+ * longest prefix with pick_{i-1} == d_i and calls it_engine_mtp_rollback(keep_rows) (1 <= keep_rows <= k + 1) - always,
+ * also when every row is kept.  it_greedy_mtp_k is that loop (k = 1 reproduces it_greedy_mtp's tokens and counters;
+ * `rejected` counts discarded drafts); it_engine_generate_mtp_k runs it over this engine. */
+int it_engine_mtp_draft_k(it_engine* e, const uint32_t* toks, size_t n, size_t k, uint32_t* drafts);
+int it_engine_mtp_verify_k(it_engine* e, uint32_t x, const uint32_t* drafts, size_t k, uint32_t* picks);
+int it_engine_mtp_rollback(it_engine* e, size_t keep_rows);
+typedef struct it_mtp_backend_k {
+    void* user;
+    uint32_t (*prefill)(void* user, const uint32_t* prompt, size_t n);
+    uint32_t (*single)(void* user, uint32_t x);
+    void (*draft_k)(void* user, const uint32_t* toks, size_t n, size_t k, uint32_t* drafts);
+    void (*verify_k)(void* user, uint32_t x, const uint32_t* drafts, size_t k, uint32_t* picks);
+    void (*rollback)(void* user, size_t keep_rows);
+    void (*reset_all)(void* user);
+} it_mtp_backend_k;
+int64_t it_greedy_mtp_k(const it_mtp_backend_k* b, size_t k, const uint32_t* prompt, size_t n_prompt, size_t n_predict,
+                        int (*is_eog)(void* user, uint32_t tok), int (*on_tok)(void* user, uint32_t tok), void* cb_user,
+                        uint32_t* out, int64_t stats[9]);
+int64_t it_engine_generate_mtp_k(it_engine* e, size_t k, const uint32_t* prompt, size_t n_prompt, size_t n_predict, uint32_t eos, uint32_t* out, int64_t stats[9]);
+
 /* Greedy pick for callers that must not allocate device memory.  No counterpart in the reference: it exists
  * for hosts that hand all of HBM to their own pool at start-up (weights, KV cache, activation arena) and for
  * code paths where the implicit device-wide synchronisation of cudaMalloc / cudaFree is not acceptable, e.g. a

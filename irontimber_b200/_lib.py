@@ -84,6 +84,11 @@ SIGNATURES = {
     "it_engine_mtp_reset_all": (C.c_int, [P]),
     "it_greedy_mtp": (C.c_int64, [P, P, c_size, c_size, P, P, P, P, P]),
     "it_engine_generate_mtp": (C.c_int64, [P, P, c_size, c_size, C.c_uint32, P, P]),
+    "it_engine_mtp_draft_k": (C.c_int, [P, P, c_size, c_size, P]),
+    "it_engine_mtp_verify_k": (C.c_int, [P, C.c_uint32, P, c_size, P]),
+    "it_engine_mtp_rollback": (C.c_int, [P, c_size]),
+    "it_greedy_mtp_k": (C.c_int64, [P, c_size, P, c_size, c_size, P, P, P, P, P]),
+    "it_engine_generate_mtp_k": (C.c_int64, [P, c_size, P, c_size, c_size, C.c_uint32, P, P]),
 }
 
 _lib = None

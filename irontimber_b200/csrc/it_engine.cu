@@ -1,5 +1,6 @@
 // Engine construction (random-init weights generated on the device), teardown and read-back for parity tests.
 #include "it_engine.h"
+#include "it_support.h"
 #include <cmath>
 #include <cstring>
 
@@ -15,6 +16,14 @@ __global__ void k_synth_f32(uint64_t seed, size_t n, float lo, float span, float
 }
 template <typename T> __global__ void k_kv_decode(const T* src, float* dst, size_t n) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = (float)src[i];
+}
+// the tiled f16 K cache (it_kc_index) back to rows [pos][kvd]
+__global__ void k_kc_decode(const __half* src, float* dst, size_t n, int nkv, int hd) {
+    const size_t kvd = (size_t)nkv * hd;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t pos = i / kvd, r = i % kvd;
+        dst[i] = __half2float(src[it_kc_index(pos, (int)(r / hd), (int)(r % hd), nkv, hd)]);
+    }
 }
 
 uint64_t tensor_seed(uint64_t seed, int layer, int tensor) { return it_hash(seed, (uint64_t)(layer + 2) * 64 + (uint64_t)tensor); }
@@ -94,7 +103,7 @@ int validate(const it_model_config* c) {
     IT_CHECK_ARG(c->n_layer > 0 && c->n_layer <= 1024 && c->n_vocab > 0, "engine: bad layer or vocabulary count");
     IT_CHECK_ARG(c->n_embd > 0 && c->n_embd % 1024 == 0 && c->n_embd <= 8192 && c->n_ff > 0 && c->n_ff % 1024 == 0, "engine: n_embd (<= 8192) and n_ff must be multiples of the 1024 Hadamard block");
     IT_CHECK_ARG((c->n_head_kv * c->head_dim) % 32 == 0 && c->n_ff % 32 == 0, "engine: stacked matrices need row counts that are multiples of 32");
-    IT_CHECK_ARG(c->head_dim > 0 && c->head_dim <= 256 && c->head_dim % 4 == 0, "engine: head_dim must be a multiple of 4 up to 256");
+    IT_CHECK_ARG(c->head_dim > 0 && c->head_dim <= 256 && c->head_dim % 8 == 0, "engine: head_dim must be a multiple of 8 up to 256");
     IT_CHECK_ARG(c->n_head > 0 && c->n_head_kv > 0 && c->n_head % c->n_head_kv == 0, "engine: n_head must be a multiple of n_head_kv");
     IT_CHECK_ARG((c->n_head * c->head_dim) % 1024 == 0 && (c->n_head_kv * c->head_dim) % 4 == 0, "engine: attention width must be a multiple of 1024");
     IT_CHECK_ARG(c->n_rot > 0 && c->n_rot % 2 == 0 && c->n_rot <= c->head_dim, "engine: bad rope dimension count");
@@ -131,7 +140,7 @@ IT_API int it_engine_create_synth_sharded(int device, const it_model_config* cfg
     it_engine* e = new it_engine();
     e->ctx = nullptr; e->cfg = c; e->seed = seed; e->has_mtp = with_mtp != 0; e->rank = rank; e->world = world; e->output = nullptr; e->q8 = nullptr; e->step_graph = nullptr; e->host_pin = nullptr;
     e->m_eh = e->m_q = e->m_k = e->m_v = e->m_o = e->m_gate = e->m_up = e->m_down = nullptr;
-    e->pos = 0; e->mpos = 1; e->hp_off = 0; e->hp_n = 0;
+    e->pos = 0; e->mpos = 1; e->hp_off = 0; e->hp_n = 0; e->last_rows = 0;
     // arena layout
     it_arena_layout& L = e->lay; size_t o = 0;
     auto take = [&](size_t& field, size_t n) { field = o; o += up64(n); };
@@ -171,7 +180,8 @@ IT_API int it_engine_create_synth_sharded(int device, const it_model_config* cfg
               E_TRY(synth_stack(e, il, 3, ts, rs, e_, parts, &l.in_proj)); l.q = parts[0]; l.k = parts[1]; l.v = parts[2]; }
             E_TRY(synth_mat(e, il, IT_T_O, e_, nh * hd, &l.o));
             E_TRY(synth_f32(e, il, IT_T_Q_NORM, hd, &l.q_norm)); E_TRY(synth_f32(e, il, IT_T_K_NORM, hd, &l.k_norm));
-            E_TRY(dev_alloc(e, (void**)&l.kc, (size_t)c.ctx_len * kvd * 2, true)); E_TRY(dev_alloc(e, (void**)&l.vc, (size_t)c.ctx_len * kvd * 2, true));
+            E_TRY(dev_alloc(e, (void**)&l.kc, (size_t)((c.ctx_len + 31) / 32 * 32) * kvd * 2, true));   // tiles of 32 positions
+            E_TRY(dev_alloc(e, (void**)&l.vc, (size_t)c.ctx_len * kvd * 2, true));
         }
     }
     E_TRY(synth_f32(e, -1, IT_T_TOK_EMBD, (size_t)c.n_vocab * e_, &e->tok_embd));
@@ -291,7 +301,8 @@ IT_API int it_engine_state_read(it_engine* e, int layer, int which, float* host,
     IT_CHECK_ARG(n <= max_floats, "it_engine_state_read: buffer too small (%zu > %zu)", n, max_floats);
     if (hsrc) {   // decode f16 -> f32 on the device (decode_kv_readback, src/vk/mod.rs:965)
         float* tmp = nullptr; IT_CUDA(cudaMalloc(&tmp, n * 4));
-        k_kv_decode<__half><<<e->ctx->sm_count, 256, 0, e->ctx->stream>>>(hsrc, tmp, n);
+        if (which == 2) k_kc_decode<<<e->ctx->sm_count, 256, 0, e->ctx->stream>>>(hsrc, tmp, n, c.n_head_kv, c.head_dim);
+        else k_kv_decode<__half><<<e->ctx->sm_count, 256, 0, e->ctx->stream>>>(hsrc, tmp, n);
         cudaError_t er = cudaMemcpyAsync(host, tmp, n * 4, cudaMemcpyDeviceToHost, e->ctx->stream);
         if (er == cudaSuccess) er = cudaStreamSynchronize(e->ctx->stream);
         cudaFree(tmp);

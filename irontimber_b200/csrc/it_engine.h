@@ -51,6 +51,7 @@ struct it_engine {
     std::vector<void*> owned;                        // plain device allocations to free
     int pos, mpos;                                   // trunk position; next MTP position (src/vk/mod.rs: pos, mpos)
     size_t hp_off; int hp_n;                         // pending h rows for the next draft (arena offset, count)
+    int last_rows;                                   // rows of the last verification pass (it_engine_mtp_rollback)
     it_graph* step_graph;                            // recorded single-token greedy step
     uint32_t* host_pin;                              // pinned staging, laid out like toks_dev, plus the position at [2*IT_MAXT]
 };

@@ -90,7 +90,7 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
                 IT_TRY(it_sup_norm_head(cx, k, hd, s_att, k, hd, s_att, hd, nkv, l.k_norm, 0, c.eps, nullptr, 0, 0, nt));
                 IT_TRY(it_sup_rope(cx, q, 2 * hd, s_att, nh, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
                 IT_TRY(it_sup_rope(cx, k, hd, s_att, nkv, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
-                IT_TRY(it_sup_kv_store(cx, k, v, s_att, l.kc, l.vc, kvd, pos0, pos_ptr, nt, 1));
+                IT_TRY(it_sup_kv_store(cx, k, v, s_att, l.kc, l.vc, kvd, hd, pos0, pos_ptr, nt, 1));
             }
             IT_TRY(it_sup_attention(cx, q, 2 * hd, s_att, q + hd, l.kc, l.vc, kvd, hd, nh, nkv, pos0, pos_ptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 1));
             IT_TRY(had_mv(e, l.o, nt, L.o, (size_t)nh * hd, L.x, e_, 1, true));
@@ -144,7 +144,7 @@ int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, 
     IT_TRY(it_sup_norm_head(cx, A + L.kcur, hd, kvd, A + L.kcur, hd, kvd, hd, nkv, e->m_k_norm, 0, c.eps, nullptr, 0, 0, nt));
     if (predict) IT_TRY(it_sup_rope(cx, A + L.big1, 2 * hd, qf, nh, nt, pos0, nullptr, c.n_rot, e->theta_scale, c.rope_sections));
     IT_TRY(it_sup_rope(cx, A + L.kcur, hd, kvd, nkv, nt, pos0, nullptr, c.n_rot, e->theta_scale, c.rope_sections));
-    IT_TRY(it_sup_kv_store(cx, A + L.kcur, A + L.vcur, kvd, e->mkc, e->mvc, kvd, slot0, nullptr, nt, 0));
+    IT_TRY(it_sup_kv_store(cx, A + L.kcur, A + L.vcur, kvd, e->mkc, e->mvc, kvd, hd, slot0, nullptr, nt, 0));
     if (!predict) return IT_OK;
     IT_TRY(it_sup_attention(cx, A + L.big1, 2 * hd, qf, A + L.big1 + hd, e->mkc, e->mvc, kvd, hd, nh, nkv, slot0, nullptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 0));
     IT_TRY(it_matvec_q8(cx, e->m_o, nt, L.o, (size_t)nh * hd, L.mx, e_, 1));
@@ -172,7 +172,7 @@ IT_API int it_engine_reset(it_engine* e) {   // zero_state, src/vk/mod.rs:645-65
         IT_CUDA(cudaMemsetAsync(l.conv_st, 0, (size_t)(c.conv_k - 1) * it_cfg_conv_dim(c) * 4, st));
         IT_CUDA(cudaMemsetAsync(l.ssm_st, 0, (size_t)c.ssm_vheads * c.ssm_state * c.ssm_state * 4, st));
     }
-    e->pos = 0; e->mpos = 1; e->hp_off = 0; e->hp_n = 0;
+    e->pos = 0; e->mpos = 1; e->hp_off = 0; e->hp_n = 0; e->last_rows = 0;
     return IT_OK;
 }
 IT_API int it_engine_eval(it_engine* e, const uint32_t* toks, size_t n, float* logits) {
@@ -295,6 +295,84 @@ IT_API int it_engine_mtp_reject(it_engine* e) {   // src/vk/mod.rs:1018-1025
     return IT_OK;
 }
 
+// ---------------------------------------------------------------- draft length k (extension, see the header)
+IT_API int it_engine_mtp_draft_k(it_engine* e, const uint32_t* toks, size_t n, size_t k, uint32_t* drafts) {
+    IT_NEED_MTP(e, "it_engine_mtp_draft_k");
+    IT_CHECK_ARG(toks && drafts && (int)n == e->hp_n && n >= 1 && k >= 1 && k <= IT_MAXCK, "it_engine_mtp_draft_k: bad token count or draft length");
+    if (e->mpos + (int)n + (int)k - 1 > e->cfg.ctx_len) return it_fail(IT_ESTATE, "it_engine_mtp_draft_k: context full");
+    const size_t e_ = e->cfg.n_embd;
+    IT_TRY(mtp_pass(e, toks, (int)n, e->mpos, e->hp_off, true));
+    e->mpos += (int)n;
+    IT_TRY(read_pick(e, 0, &drafts[0]));
+    size_t hid = e->lay.mx + (n - 1) * e_;                  // the head's hidden state before head_norm, last row of the pass
+    for (size_t i = 1; i < k; i++) {                        // chained steps: provisional KV entries at positions mpos, mpos + 1, ..
+        IT_TRY(mtp_pass(e, &drafts[i - 1], 1, e->mpos + (int)i - 1, hid, true));
+        IT_TRY(read_pick(e, 0, &drafts[i]));
+        hid = e->lay.mx;
+    }
+    return IT_OK;
+}
+IT_API int it_engine_mtp_verify_k(it_engine* e, uint32_t x, const uint32_t* drafts, size_t k, uint32_t* picks) {
+    IT_NEED_MTP(e, "it_engine_mtp_verify_k");
+    IT_CHECK_ARG(drafts && picks && k >= 1 && k <= IT_MAXCK, "it_engine_mtp_verify_k: bad argument");
+    uint32_t toks[IT_MAXCK + 1]; toks[0] = x;
+    for (size_t i = 0; i < k; i++) toks[i + 1] = drafts[i];
+    IT_TRY(it_engine_run_chunk(e, toks, (int)k + 1, 2, (int)k, false));      // a pick per row, state checkpointed after rows 0 .. k - 1
+    e->hp_off = e->lay.hrow; e->hp_n = (int)k + 1; e->last_rows = (int)k + 1;
+    return it_arena_read(e->ctx, e->lay.amx, picks, k + 1);
+}
+IT_API int it_engine_mtp_rollback(it_engine* e, size_t keep_rows) {
+    IT_NEED_MTP(e, "it_engine_mtp_rollback");
+    IT_CHECK_ARG(e->last_rows >= 2 && keep_rows >= 1 && (int)keep_rows <= e->last_rows, "it_engine_mtp_rollback: no verification pass to roll back, or bad row count");
+    const int drop = e->last_rows - (int)keep_rows;
+    if (drop > 0) {
+        const it_model_config& c = e->cfg; cudaStream_t st = e->ctx->stream; it_note_op(e->ctx);
+        const size_t csz = (size_t)(c.conv_k - 1) * it_cfg_conv_dim(c), ssz = (size_t)c.ssm_vheads * c.ssm_state * c.ssm_state;
+        for (it_layer& l : e->layers) if (l.recurrent) {      // checkpoint t holds the state after row t
+            IT_CUDA(cudaMemcpyAsync(l.conv_st, l.ck_conv + (keep_rows - 1) * csz, csz * 4, cudaMemcpyDeviceToDevice, st));
+            IT_CUDA(cudaMemcpyAsync(l.ssm_st, l.ck_ssm + (keep_rows - 1) * ssz, ssz * 4, cudaMemcpyDeviceToDevice, st));
+        }
+        e->pos -= drop;
+    }
+    e->hp_off = e->lay.hrow; e->hp_n = (int)keep_rows; e->last_rows = 0;
+    return IT_OK;
+}
+
+IT_API int64_t it_greedy_mtp_k(const it_mtp_backend_k* b, size_t k, const uint32_t* prompt, size_t np, size_t n,
+                               int (*is_eog)(void*, uint32_t), int (*on_tok)(void*, uint32_t), void* cbu, uint32_t* out, int64_t* stats) {
+    if (!b || !out || !stats || !is_eog || !on_tok || k < 1 || k > IT_MAXCK) return it_fail(IT_EINVAL, "it_greedy_mtp_k: bad argument");
+    enum { DRAFTED, ACCEPTED, STEPS, DRAFT_CALLS, VERIFY_CALLS, SINGLE, TIMED, REJECTED, TERMINAL };
+    for (int i = 0; i < 9; i++) stats[i] = 0;
+    size_t no = 0;
+    auto emit = [&](uint32_t t) { out[no++] = t; const bool go = on_tok(cbu, t) != 0; return go && !is_eog(cbu, t) && no < n; };
+    if (n == 0) return 0;
+    if (np == 0 || !prompt) return it_fail(IT_EINVAL, "it_greedy_mtp_k: empty MTP prompt");
+    uint32_t x = b->prefill(b->user, prompt, np);
+    if (!emit(x)) return (int64_t)no;
+    uint32_t pending[IT_MAXCK + 1] = { x }; size_t npend = 1;
+    for (;;) {
+        if (n - no == 1) { const uint32_t a = b->single(b->user, x); stats[SINGLE]++; stats[TIMED]++; emit(a); break; }
+        const size_t kk = k < n - no - 1 ? k : n - no - 1;
+        uint32_t ds[IT_MAXCK] = {}, picks[IT_MAXCK + 1] = {};
+        b->draft_k(b->user, pending, npend, kk, ds); stats[DRAFT_CALLS]++;
+        b->verify_k(b->user, x, ds, kk, picks);
+        stats[DRAFTED] += (int64_t)kk; stats[STEPS]++; stats[VERIFY_CALLS]++; stats[TIMED] += (int64_t)kk + 1;
+        size_t nacc = 0;
+        while (nacc < kk && picks[nacc] == ds[nacc]) nacc++;
+        stats[ACCEPTED] += (int64_t)nacc; stats[REJECTED] += (int64_t)(kk - nacc);
+        bool stop = false;
+        for (size_t i = 0; i < nacc; i++)
+            if (!emit(ds[i])) { b->rollback(b->user, i + 1); stats[TERMINAL]++; stop = true; break; }
+        if (stop) break;
+        b->rollback(b->user, nacc + 1);
+        if (!emit(picks[nacc])) break;
+        x = picks[nacc];
+        for (size_t i = 0; i < nacc; i++) pending[i] = ds[i];
+        pending[nacc] = picks[nacc]; npend = nacc + 1;
+    }
+    return (int64_t)no;
+}
+
 // ---------------------------------------------------------------- greedy_mtp (src/mtp.rs:166-204)
 IT_API int64_t it_greedy_mtp(const it_mtp_backend* b, const uint32_t* prompt, size_t np, size_t n,
                              int (*is_eog)(void*, uint32_t), int (*on_tok)(void*, uint32_t), void* cbu, uint32_t* out, int64_t* stats) {
@@ -338,6 +416,21 @@ void cb_reset(void* u) { EngineCb* c = (EngineCb*)u; if (!c->err) c->err = it_en
 int cb_eog(void* u, uint32_t t) { EngineCb* c = (EngineCb*)u; return c->err != 0 || t == c->eos; }
 int cb_tok(void*, uint32_t) { return 1; }
 }  // namespace
+
+namespace {
+void cb_draft_k(void* u, const uint32_t* p, size_t n, size_t k, uint32_t* d) { EngineCb* c = (EngineCb*)u; for (size_t i = 0; i < k; i++) d[i] = 0; if (!c->err) c->err = it_engine_mtp_draft_k(c->e, p, n, k, d); }
+void cb_verify_k(void* u, uint32_t x, const uint32_t* d, size_t k, uint32_t* a) { EngineCb* c = (EngineCb*)u; for (size_t i = 0; i <= k; i++) a[i] = 0; if (!c->err) c->err = it_engine_mtp_verify_k(c->e, x, d, k, a); }
+void cb_rollback(void* u, size_t keep) { EngineCb* c = (EngineCb*)u; if (!c->err) c->err = it_engine_mtp_rollback(c->e, keep); }
+}  // namespace
+
+IT_API int64_t it_engine_generate_mtp_k(it_engine* e, size_t k, const uint32_t* prompt, size_t n_prompt, size_t n_predict, uint32_t eos, uint32_t* out, int64_t* stats) {
+    if (!e || !e->has_mtp) return it_fail(IT_ESTATE, "it_engine_generate_mtp_k: the engine has no MTP head");
+    if ((long long)n_prompt + (long long)n_predict + (long long)k > e->cfg.ctx_len) return it_fail(IT_ESTATE, "it_engine_generate_mtp_k: prompt + prediction exceed the context capacity");
+    EngineCb cb{ e, eos, 0 };
+    it_mtp_backend_k b{ &cb, cb_prefill, cb_single, cb_draft_k, cb_verify_k, cb_rollback, cb_reset };
+    const int64_t n = it_greedy_mtp_k(&b, k, prompt, n_prompt, n_predict, cb_eog, cb_tok, &cb, out, stats);
+    return cb.err ? cb.err : n;
+}
 
 IT_API int64_t it_engine_generate_mtp(it_engine* e, const uint32_t* prompt, size_t n_prompt, size_t n_predict, uint32_t eos, uint32_t* out, int64_t* stats) {
     if (!e || !e->has_mtp) return it_fail(IT_ESTATE, "it_engine_generate_mtp: the engine has no MTP head");

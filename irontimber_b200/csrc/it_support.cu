@@ -198,12 +198,13 @@ __device__ __forceinline__ float2 kv_get2(const __half* p) { return __half22floa
 __device__ __forceinline__ float2 kv_get2(const float* p) { return *reinterpret_cast<const float2*>(p); }
 
 template <typename T>
-__global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* vc, int kvd, int slot0, const int* pos_ptr) {
+__global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* vc, int kvd, int hd, int slot0, const int* pos_ptr) {
     IT_PDL_TRIGGER(); IT_PDL_WAIT();
     if (pos_ptr) slot0 += *pos_ptr;
     const int t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= kvd) return;
-    kc[(size_t)(slot0 + t) * kvd + i] = kv_pack<T>(k[t * ts + i]);
+    const size_t ki = sizeof(T) == 2 ? it_kc_index(slot0 + t, i / hd, i % hd, kvd / hd, hd) : (size_t)(slot0 + t) * kvd + i;   // the f16 K cache is tiled
+    kc[ki] = kv_pack<T>(k[t * ts + i]);
     vc[(size_t)(slot0 + t) * kvd + i] = kv_pack<T>(v[t * ts + i]);
 }
 
@@ -256,7 +257,7 @@ __global__ void __launch_bounds__(128) k_attn_prep(float* qkv, size_t ts, int nh
     }
     __syncwarp();
     if (is_q) { for (int i = lane; i < hd; i += 32) x[i] = buf[warp][i]; }
-    else { const int kh = job - nh; for (int i = lane; i < hd; i += 32) { x[i] = buf[warp][i]; kc[(size_t)(slot0 + t) * kvd + kh * hd + i] = __float2half_rn(buf[warp][i]); } }
+    else { const int kh = job - nh; for (int i = lane; i < hd; i += 32) { x[i] = buf[warp][i]; kc[it_kc_index(slot0 + t, kh, i, nkv, hd)] = __float2half_rn(buf[warp][i]); } }
 }
 
 // Delta-net input block in one launch.  CTAs [0, cd/sd): causal conv + SiLU + state shift of one head-wide run of sd
@@ -436,12 +437,14 @@ __global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs,
     const int nvec = hd / VN;                  // vectors per K row
     float mx = -INFINITY;
     for (int p = tid; p < n; p += 1024) {
-        const Vec* kp = reinterpret_cast<const Vec*>(kc + (size_t)p * kvd + kh * hd);
+        // f16 cache: tiled (piece v of 32 consecutive positions is contiguous: the loads of a warp are coalesced); f32 cache: rows
+        const Vec* kp = sizeof(T) == 2 ? reinterpret_cast<const Vec*>(kc + it_kc_index(p, kh, 0, nkv, hd)) : reinterpret_cast<const Vec*>(kc + (size_t)p * kvd + kh * hd);
+        const int vstep = sizeof(T) == 2 ? 32 : 1;     // distance between consecutive pieces of one position, in vectors
         float s = 0.f;
         for (int v0 = 0; v0 < nvec; v0 += 8) {
             Vec buf[8];
 #pragma unroll
-            for (int u = 0; u < 8; u++) if (v0 + u < nvec) buf[u] = kp[v0 + u];
+            for (int u = 0; u < 8; u++) if (v0 + u < nvec) buf[u] = kp[(v0 + u) * vstep];
             asm volatile("" ::: "memory");       // all eight loads are in flight before the first dependent add
 #pragma unroll
             for (int u = 0; u < 8; u++) if (v0 + u < nvec) {
@@ -538,10 +541,10 @@ int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, cons
 int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n) {
     it_note_op(c); it_pdl(k_silu_mul, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, c->stream, g, u, out, n); KCHK("silu_mul"); return IT_OK;
 }
-int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int slot0, const int* pos_ptr, int nt, int f16) {
+int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int hd, int slot0, const int* pos_ptr, int nt, int f16) {
     it_note_op(c);
-    if (f16) it_pdl(k_kv_store<__half>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (__half*)kc, (__half*)vc, kvd, slot0, pos_ptr);
-    else it_pdl(k_kv_store<float>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (float*)kc, (float*)vc, kvd, slot0, pos_ptr);
+    if (f16) it_pdl(k_kv_store<__half>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (__half*)kc, (__half*)vc, kvd, hd, slot0, pos_ptr);
+    else it_pdl(k_kv_store<float>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (float*)kc, (float*)vc, kvd, hd, slot0, pos_ptr);
     KCHK("kv_store"); return IT_OK;
 }
 int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16) {

@@ -2,6 +2,13 @@
 #pragma once
 #include "it_internal.h"
 
+// f16 K cache of the trunk (not the V cache, not the head's f32 caches): positions are stored in tiles of 32, and inside a
+// tile the same 16-byte piece (8 elements) of the 32 positions is contiguous, so that one thread per position reads its
+// row with fully coalesced 16-byte loads.  Element j of kv head kh at position pos:
+__host__ __device__ static inline size_t it_kc_index(size_t pos, int kh, int j, int nkv, int hd) {
+    return (((pos >> 5) * (size_t)nkv + kh) * (size_t)(hd >> 3) + (size_t)(j >> 3)) * 256 + (pos & 31) * 8 + (j & 7);
+}
+
 // Work done on the way into the Hadamard + q8k kernel.  mode 0: nothing.  mode 1: input = silu(x) * b (b is a device
 // pointer, rows b_stride apart).  mode 2: input = rmsnorm(x) over the whole row of width n with weight w and eps; when
 // xn_out is set the normed f32 row is also stored there (rows xn_stride apart).
@@ -22,7 +29,7 @@ int it_sup_dense_rows(it_ctx* c, const float* w0, const float* w1, int rows, int
 int it_sup_gdn(it_ctx* c, const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* dt, const float* a, float* state, float* o, size_t o_ts,
                int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck);
 int it_sup_silu_mul(it_ctx* c, const float* g, const float* u, float* out, size_t n);
-int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int slot0, const int* pos_ptr, int nt, int f16);
+int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* kc, void* vc, int kvd, int hd, int slot0, const int* pos_ptr, int nt, int f16);   // f16: K goes to the tiled layout
 int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0,
                      const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16);
 

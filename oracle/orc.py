@@ -328,6 +328,14 @@ class Model:
         lib().orc_mtp_step(self.h, ms, _p(h), C.c_uint32(tok), C.c_int(pos), _p(lg), C.c_int(mode))
         return lg
 
+    def mtp_step_hidden(self, ms, h, tok, pos, mode=REFERENCE_ORDER):
+        """cpu_step that also returns the head's hidden state before head_norm (input of a chained draft step)."""
+        h = _c(h, np.float32)
+        lg = np.empty(self.cfg.n_vocab, np.float32)
+        hid = np.empty(self.cfg.n_embd, np.float32)
+        lib().orc_mtp_step_hidden(self.h, ms, _p(h), C.c_uint32(tok), C.c_int(pos), _p(lg), C.c_int(mode), _p(hid))
+        return lg, hid
+
     def close(self):
         if self.h:
             lib().orc_model_free(self.h)
@@ -374,6 +382,81 @@ class CpuMtp:
 
     def mtp_reject(self):
         self.m.assign_state(self.st, self.ck); self.ck = None; self.hpend = self.hpend[:1]
+
+    # ---- draft length k > 1.  The reference defines k = 1 only (src/mtp.rs:3-8: the head consumes the trunk's hidden state
+    # of the previous position, which does not exist for a drafted position).  Extension used here and in the CUDA engine:
+    # draft i >= 2 feeds the head its OWN hidden state before head_norm, with draft i - 1 as the token, one position on; its
+    # KV entry is provisional (the next real pair at that position replaces it).  Verification runs the k + 1 rows
+    # [x, d_1 .. d_k] through the trunk with a state copy after every row; the longest prefix with pick_{i-1} == d_i is kept.
+    def mtp_draft_k(self, toks, k):
+        assert len(toks) == len(self.hpend) and k >= 1
+        lg = hid = None
+        for i, t in enumerate(toks):
+            lg, hid = self.m.mtp_step_hidden(self.ms, self.hpend[i], t, self.mpos, self.mode); self.mpos += 1
+        drafts = [argmax(lg)]
+        for i in range(1, k):
+            lg, hid = self.m.mtp_step_hidden(self.ms, hid, drafts[-1], self.mpos + i - 1, self.mode)
+            drafts.append(argmax(lg))
+        return drafts
+
+    def mtp_verify_k(self, x, drafts):
+        picks, self.hs, self.cks = [], [], []
+        for i, t in enumerate([x] + list(drafts)):
+            lg = self.m.forward_token(self.st, t, True, self.mode)
+            picks.append(argmax(lg)); self.hs.append(self.m.state_h(self.st))
+            if i < len(drafts):
+                self.cks.append(self.m.clone_state(self.st))
+        self.hpend = list(self.hs)
+        return picks
+
+    def mtp_rollback(self, keep_rows):
+        """Keeps the first keep_rows rows of the last verification (1 <= keep_rows <= k + 1)."""
+        if keep_rows <= len(self.cks):
+            self.m.assign_state(self.st, self.cks[keep_rows - 1])
+        self.hpend = self.hs[:keep_rows]
+        for ck in self.cks:
+            self.m.free_state(ck)
+        self.cks = []
+
+
+def greedy_mtp_k(backend, prompt, n, k, is_eog=lambda t: False):
+    """Speculative greedy loop with draft length k (k = 1 gives greedy_mtp's token list and counters, src/mtp.rs:166-204)."""
+    st = dict.fromkeys(STAT_NAMES, 0)
+    out = []
+    if n == 0:
+        return out, st
+    if not len(prompt):
+        raise ValueError("empty MTP prompt")
+
+    def emit(t):
+        out.append(t)
+        return not is_eog(t) and len(out) < n
+    x = backend.mtp_prefill(list(prompt))
+    if not emit(x):
+        return out, st
+    pending = [x]
+    while True:
+        if n - len(out) == 1:
+            a = backend.mtp_single(x); st["single_forwards"] += 1; st["timed_decode_forwards"] += 1; emit(a); break
+        kk = min(k, n - len(out) - 1)
+        ds = backend.mtp_draft_k(pending, kk); st["draft_calls"] += 1
+        picks = backend.mtp_verify_k(x, ds)
+        st["drafted"] += kk; st["steps"] += 1; st["verify_calls"] += 1; st["timed_decode_forwards"] += kk + 1
+        nacc = 0
+        while nacc < kk and picks[nacc] == ds[nacc]:
+            nacc += 1
+        st["accepted"] += nacc; st["rejected"] += kk - nacc
+        stop = False
+        for i in range(nacc):
+            if not emit(ds[i]):
+                backend.mtp_rollback(i + 1); st["terminal_rollbacks"] += 1; stop = True; break
+        if stop:
+            break
+        backend.mtp_rollback(nacc + 1)
+        if not emit(picks[nacc]):
+            break
+        x = picks[nacc]; pending = ds[:nacc] + [picks[nacc]]
+    return out, st
 
 
 def generate_greedy(model, prompt, n, mode=REFERENCE_ORDER):

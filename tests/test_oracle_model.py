@@ -65,3 +65,58 @@ def test_library_greedy_mtp_passes_the_reference_loop_scenarios():
     loop_scenarios(engine.greedy_mtp)
     with pytest.raises(Exception):
         engine.greedy_mtp(None, [], 3)
+
+
+class _ScriptedK:
+    """Wraps a k-draft backend: the head still runs, but the drafts are replaced by a script (true continuation or wrong ids)."""
+
+    def __init__(self, inner, plain, right, vocab):
+        self.b, self.plain, self.right, self.vocab, self.i = inner, plain, right, vocab, 1
+
+    def __getattr__(self, name):
+        return getattr(self.b, name)
+
+    def mtp_draft_k(self, toks, k):
+        self.b.mtp_draft_k(toks, k)
+        nxt = [self.plain[min(self.i + j, len(self.plain) - 1)] for j in range(k)]
+        return nxt if self.right else [(t + 1) % self.vocab for t in nxt]
+
+    def mtp_rollback(self, keep_rows):
+        self.i += keep_rows
+        return self.b.mtp_rollback(keep_rows)
+
+
+@pytest.mark.parametrize("k", [1, 2, 3])
+def test_draft_length_k_reproduces_plain_greedy(orc, tiny, k):
+    """Draft length k (k = 1: the reference's loop; k > 1: the chained-head extension): whatever the head drafts, the
+    output is plain greedy decoding; scripted right drafts are all accepted, scripted wrong ones all rejected."""
+    prompt = [9, 8, 7, 300, 2]
+    n = 12
+    plain = orc.generate_greedy(tiny, prompt, n, orc.DEVICE_ORDER)
+    out, st = orc.greedy_mtp_k(orc.CpuMtp(tiny, orc.DEVICE_ORDER), prompt, n, k)
+    assert out == plain
+    assert st["drafted"] == st["accepted"] + st["rejected"] and st["verify_calls"] == st["steps"] == st["draft_calls"]
+    if k == 1:      # same list and counters as the reference's loop
+        out1, st1 = orc.greedy_mtp(orc.CpuMtp(tiny, orc.DEVICE_ORDER), prompt, n)
+        assert out1 == out and st1 == st
+    vocab = tiny.cfg.n_vocab
+    out, st = orc.greedy_mtp_k(_ScriptedK(orc.CpuMtp(tiny, orc.DEVICE_ORDER), plain, True, vocab), prompt, n, k)
+    assert out == plain and st["rejected"] == 0 and st["accepted"] == st["drafted"] > 0
+    assert st["steps"] <= -(-(n - 1) // (k + 1)) + 1          # k + 1 tokens per step
+    out, st = orc.greedy_mtp_k(_ScriptedK(orc.CpuMtp(tiny, orc.DEVICE_ORDER), plain, False, vocab), prompt, n, k)
+    assert out == plain and st["accepted"] == 0 and st["rejected"] == st["drafted"] > 0
+
+
+def test_draft_length_k_stops_on_end_of_generation(orc, tiny):
+    prompt = [9, 8, 7, 300, 2]
+    plain = orc.generate_greedy(tiny, prompt, 12, orc.DEVICE_ORDER)
+    eog = plain[5]
+    want = plain[:plain.index(eog) + 1]
+    for right in (True, False):
+        b = _ScriptedK(orc.CpuMtp(tiny, orc.DEVICE_ORDER), plain, right, tiny.cfg.n_vocab)
+        out, _ = orc.greedy_mtp_k(b, prompt, 12, 3, is_eog=lambda t: t == eog)
+        assert out == want
+        # the trunk state holds exactly the emitted tokens but the last: one more forward gives plain greedy's next token
+        nxt = b.mtp_single(out[-1])
+        if len(want) < len(plain):
+            assert nxt == plain[len(want)]
