@@ -436,9 +436,31 @@ def main():
         acc_s = time.perf_counter() - t0
         assert out_acc == plain
         keep = ("drafted", "accepted", "rejected", "steps", "verify_calls", "single_forwards")
+        # draft length 2 and 3 (extension: chained head steps, k + 1 verification rows), scripted right drafts and the random head
+        longer = {}
+        for kd in (2, 3):
+            class ScriptedK:
+                def __init__(self, e): self.e, self.i = e, 1
+                def __getattr__(self, name): return getattr(self.e, name)
+                def mtp_draft_k(self, toks, kk):
+                    self.e.mtp_draft_k(toks, kk)
+                    return [plain[min(self.i + j, len(plain) - 1)] for j in range(kk)]
+                def mtp_rollback(self, keep_rows):
+                    self.i += keep_rows; return self.e.mtp_rollback(keep_rows)
+            t0 = time.perf_counter()
+            out_k, st_k = E.greedy_mtp_k(ScriptedK(eng), prompt, n_mtp, kd)
+            k_s = time.perf_counter() - t0
+            assert out_k == plain
+            t0 = time.perf_counter()
+            out_n, st_n = eng.generate_mtp_k(prompt, n_mtp, kd)
+            n_s = time.perf_counter() - t0
+            assert out_n == plain
+            longer[f"k{kd}"] = {"scripted_right_drafts": {"tok_s": (n_mtp - 1) / max(k_s - pre_s, 1e-9), **{q: st_k[q] for q in keep if q in st_k}},
+                                "random_head": {"tok_s": (n_mtp - 1) / max(n_s - pre_s, 1e-9), **{q: st_n[q] for q in keep if q in st_n}}}
         mtp = {"tokens": n_mtp, "prefill_with_head_catch_up_s": pre_s, "note": "decode tok/s = (tokens - 1) / (run time - prefill time)",
                "random_head": {"tok_s": (n_mtp - 1) / max(nat_s - pre_s, 1e-9), "run_s": nat_s, **{k: st_nat[k] for k in keep if k in st_nat}},
-               "scripted_right_drafts": {"tok_s": (n_mtp - 1) / max(acc_s - pre_s, 1e-9), "run_s": acc_s, **{k: st_acc[k] for k in keep if k in st_acc}}}
+               "scripted_right_drafts": {"tok_s": (n_mtp - 1) / max(acc_s - pre_s, 1e-9), "run_s": acc_s, **{k: st_acc[k] for k in keep if k in st_acc}},
+               **longer}
     # launches of one recorded step: 13 per delta-net layer, 15 per attention layer, embedding, output norm, LM head
     # (Hadamard + matvec), argmax and the two token/position updates
     n_kernels = sum(13 if cfg.is_recurrent(il) else 15 for il in range(cfg.n_layer)) + 7

@@ -146,6 +146,31 @@ class CudaEngine:
             _lib.check(int(n))
         return [int(t) for t in out[:n]], dict(zip(STAT_NAMES, (int(s) for s in stats)))
 
+    # ---- draft length k (extension; see include/irontimber_cuda.h) ---------------------------------------------
+    def mtp_draft_k(self, toks, k):
+        t = _u32(toks)
+        d = np.zeros(k, np.uint32)
+        _lib.check(self.L.it_engine_mtp_draft_k(self.h, _p(t), t.size, k, _p(d)))
+        return [int(x) for x in d]
+
+    def mtp_verify_k(self, x, drafts):
+        d = _u32(drafts)
+        a = np.zeros(d.size + 1, np.uint32)
+        _lib.check(self.L.it_engine_mtp_verify_k(self.h, x, _p(d), d.size, _p(a)))
+        return [int(v) for v in a]
+
+    def mtp_rollback(self, keep_rows):
+        _lib.check(self.L.it_engine_mtp_rollback(self.h, keep_rows))
+
+    def generate_mtp_k(self, prompt, n_predict, k, eos=NO_EOS):
+        p = _u32(prompt)
+        out = np.zeros(n_predict + 2, np.uint32)
+        stats = np.zeros(9, np.int64)
+        n = self.L.it_engine_generate_mtp_k(self.h, k, _p(p), p.size, n_predict, eos, _p(out), _p(stats))
+        if n < 0:
+            _lib.check(int(n))
+        return [int(t) for t in out[:n]], dict(zip(STAT_NAMES, (int(s) for s in stats)))
+
     # ---- read-back for parity tests ---------------------------------------------------------------------
     def tensor(self, name, layer=-1):
         nb = C.c_size_t()
@@ -203,3 +228,38 @@ def greedy_mtp(backend, prompt, n, is_eog=lambda t: False, on_tok=lambda t: True
     if k < 0:
         _lib.check(int(k))
     return [int(t) for t in out[:k]], dict(zip(STAT_NAMES, (int(s) for s in stats)))
+
+
+def greedy_mtp_k(backend, prompt, n, k, is_eog=lambda t: False, on_tok=lambda t: True):
+    """The library's speculative loop with draft length k (it_greedy_mtp_k) over any Python object with mtp_prefill,
+    mtp_single, mtp_draft_k, mtp_verify_k, mtp_rollback and reset_all."""
+    L = _lib.load()
+
+    class B(C.Structure):
+        _fields_ = [("user", C.c_void_p),
+                    ("prefill", C.CFUNCTYPE(C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32), C.c_size_t)),
+                    ("single", C.CFUNCTYPE(C.c_uint32, C.c_void_p, C.c_uint32)),
+                    ("draft_k", C.CFUNCTYPE(None, C.c_void_p, C.POINTER(C.c_uint32), C.c_size_t, C.c_size_t, C.POINTER(C.c_uint32))),
+                    ("verify_k", C.CFUNCTYPE(None, C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.c_uint32))),
+                    ("rollback", C.CFUNCTYPE(None, C.c_void_p, C.c_size_t)),
+                    ("reset_all", C.CFUNCTYPE(None, C.c_void_p))]
+    F = dict(B._fields_)
+
+    def _draft(_, p, np_, kk, out):
+        for i, d in enumerate(backend.mtp_draft_k([p[i] for i in range(np_)], kk)):
+            out[i] = d
+
+    def _verify(_, x, d, kk, out):
+        for i, a in enumerate(backend.mtp_verify_k(x, [d[i] for i in range(kk)])):
+            out[i] = a
+    be = B(None, F["prefill"](lambda _, p, m: backend.mtp_prefill([p[i] for i in range(m)])), F["single"](lambda _, x: backend.mtp_single(x)),
+           F["draft_k"](_draft), F["verify_k"](_verify), F["rollback"](lambda _, keep: backend.mtp_rollback(keep)), F["reset_all"](lambda _: backend.reset_all()))
+    CB = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32)
+    eog, tok = CB(lambda _, t: int(bool(is_eog(t)))), CB(lambda _, t: int(bool(on_tok(t))))
+    pr = _u32(prompt)
+    out = np.zeros(max(n, 1) + 2, np.uint32)
+    stats = np.zeros(9, np.int64)
+    m = L.it_greedy_mtp_k(C.byref(be), k, _p(pr), pr.size, n, eog, tok, None, _p(out), _p(stats))
+    if m < 0:
+        _lib.check(int(m))
+    return [int(t) for t in out[:m]], dict(zip(STAT_NAMES, (int(s) for s in stats)))

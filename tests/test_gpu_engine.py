@@ -125,6 +125,32 @@ def test_long_prompt_in_64_row_passes_bit_exact(orc):
         m.close(); eng.close()
 
 
+@pytest.mark.parametrize("k", [1, 2, 3])
+def test_draft_length_k_equals_plain_greedy_with_oracle_counts(orc, pair, k):
+    """Draft length k (k > 1: chained head steps, k + 1 verification rows, rollback to the first mismatch): tokens and
+    counters identical to the oracle's loop, which is plain greedy decoding; scripted right drafts are all accepted."""
+    eng, m = pair
+    n = 14
+    plain = orc.generate_greedy(m, PROMPT, n, orc.DEVICE_ORDER)
+    want_out, want_stats = orc.greedy_mtp_k(orc.CpuMtp(m, orc.DEVICE_ORDER), PROMPT, n, k)
+    assert want_out == plain
+    out, stats = eng.generate_mtp_k(PROMPT, n, k)
+    assert out == plain and stats == want_stats
+    if k == 1:
+        assert eng.generate_mtp(PROMPT, n) == (out, stats)
+
+    class Right:                                   # the head runs, its drafts are replaced by the true continuation
+        def __init__(self, e): self.e, self.i = e, 1
+        def __getattr__(self, name): return getattr(self.e, name)
+        def mtp_draft_k(self, toks, kk):
+            self.e.mtp_draft_k(toks, kk)
+            return [plain[min(self.i + j, n - 1)] for j in range(kk)]
+        def mtp_rollback(self, keep):
+            self.i += keep; return self.e.mtp_rollback(keep)
+    out, st = orc.greedy_mtp_k(Right(eng), PROMPT, n, k)
+    assert out == plain and st["rejected"] == 0 and st["accepted"] == st["drafted"] > 0
+
+
 def test_engine_rejects_bad_requests_without_touching_state(pair):
     from irontimber_b200 import _lib
     eng, _ = pair

@@ -120,3 +120,23 @@ def test_draft_length_k_stops_on_end_of_generation(orc, tiny):
         nxt = b.mtp_single(out[-1])
         if len(want) < len(plain):
             assert nxt == plain[len(want)]
+
+
+@pytest.mark.parametrize("k", [1, 2, 3])
+def test_library_loop_with_draft_length_k_matches_the_oracle_loop(orc, tiny, k):
+    """it_greedy_mtp_k (host code of the library, no GPU) over the oracle's CPU backend: same tokens and counters as the
+    oracle's own loop, with the head's drafts and with scripted ones, and with an end-of-generation token in the middle."""
+    from irontimber_b200 import engine
+    prompt = [9, 8, 7, 300, 2]
+    n = 12
+    plain = orc.generate_greedy(tiny, prompt, n, orc.DEVICE_ORDER)
+    want = orc.greedy_mtp_k(orc.CpuMtp(tiny, orc.DEVICE_ORDER), prompt, n, k)
+    assert engine.greedy_mtp_k(orc.CpuMtp(tiny, orc.DEVICE_ORDER), prompt, n, k) == want
+    for right in (True, False):
+        want = orc.greedy_mtp_k(_ScriptedK(orc.CpuMtp(tiny, orc.DEVICE_ORDER), plain, right, tiny.cfg.n_vocab), prompt, n, k)
+        got = engine.greedy_mtp_k(_ScriptedK(orc.CpuMtp(tiny, orc.DEVICE_ORDER), plain, right, tiny.cfg.n_vocab), prompt, n, k)
+        assert got == want
+    eog = plain[5]
+    want = orc.greedy_mtp_k(_ScriptedK(orc.CpuMtp(tiny, orc.DEVICE_ORDER), plain, True, tiny.cfg.n_vocab), prompt, n, k, is_eog=lambda t: t == eog)
+    got = engine.greedy_mtp_k(_ScriptedK(orc.CpuMtp(tiny, orc.DEVICE_ORDER), plain, True, tiny.cfg.n_vocab), prompt, n, k, is_eog=lambda t: t == eog)
+    assert got == want and got[0] == plain[:plain.index(eog) + 1]
