@@ -138,10 +138,12 @@ int it_check_device_error(it_ctx* ctx, const char* who);
 #define IT_ARGMAX_MAX_BLOCKS 1024
 
 // ---- programmatic dependent launch -----------------------------------------------------------------------------
-// Every kernel of the decode path is launched with programmatic stream serialization: it lets the kernel after it be
-// scheduled at once (IT_PDL_TRIGGER) and waits for the kernel before it to finish and flush (IT_PDL_WAIT) before it
-// touches any memory that kernel may have written.  The launch latency and prologue of a kernel then overlap the
-// kernel in front of it.  Completion is transitive: a kernel only finishes after its own wait has returned.
+// The ternary matvec and tile kernels are launched with programmatic stream serialization: their weight requests do not
+// depend on the kernel before them, so they start while it still runs and wait (IT_PDL_WAIT) only in front of the first
+// access to memory it may have written.  Every other kernel of the decode path triggers its dependents at once
+// (IT_PDL_TRIGGER) so that a matvec behind it can start early, but is itself launched the plain way: measured, launching
+// the small support kernels early made a decode step 3-9 % slower (IT_PDL_SUPPORT=1 turns it on for experiments).
+// Completion is transitive: a kernel only finishes after its own wait has returned.
 #define IT_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
 #define IT_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
 template <typename... KArgs, typename... Args>
