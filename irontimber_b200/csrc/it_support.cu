@@ -114,6 +114,27 @@ __global__ void k_conv(const float* mixed, size_t m_ts, const float* __restrict_
     for (int i = 0; i < kk - 1; i++) state[(size_t)i * cd + ch] = st[i];
 }
 
+// The same conv for many rows at once (prompt passes): the output of row t depends only on the inputs of rows t-kk+1 .. t
+// (the state is just the last kk-1 inputs), so rows are independent: 128 channels x 8 row lanes per CTA, every sum in the
+// tap order of k_conv.  The state is rewritten after all reads of the old one.  No checkpoints (verification passes are short).
+__global__ void __launch_bounds__(1024) k_conv_wide(const float* mixed, size_t m_ts, const float* __restrict__ w, float* state, float* out, size_t o_ts, int cd, int kk, int nt) {
+    IT_PDL_TRIGGER(); IT_PDL_WAIT();
+    const int ch = blockIdx.x * 128 + threadIdx.x;
+    const bool live = ch < cd;
+    float wt[9];
+    if (live) for (int i = 0; i < kk; i++) wt[i] = w[ch * kk + i];
+    auto input = [&](int r) { return r >= 0 ? mixed[r * m_ts + ch] : state[(size_t)(kk - 1 + r) * cd + ch]; };   // row r of this pass, or of the state
+    if (live) for (int t = threadIdx.y; t < nt; t += 8) {
+        float s = 0.f;
+        for (int i = 0; i < kk; i++) s = it_add(s, it_mul(input(t - (kk - 1) + i), wt[i]));
+        out[t * o_ts + ch] = it_silu(s);
+    }
+    float keep[8];
+    if (live && threadIdx.y == 0) for (int i = 0; i < kk - 1; i++) keep[i] = input(nt - (kk - 1) + i);
+    __syncthreads();
+    if (live && threadIdx.y == 0) for (int i = 0; i < kk - 1; i++) state[(size_t)i * cd + ch] = keep[i];
+}
+
 // Dense f32 rows (ssm_beta / ssm_alpha; cpu::matvec's f32 arm under Numerics::Ggml, src/cpu.rs:36-43: f32 products,
 // f64 accumulation).  One CTA of 256 threads per row: thread i adds the products i, i+256, ... in f64, each warp folds
 // with a butterfly, the eight warp sums are added in ascending order.  Rows [0, rows) use w0 / y0, rows [rows, 2 rows) w1 / y1.
@@ -527,7 +548,11 @@ int it_sup_rope(it_ctx* c, float* x, size_t hs, size_t ts, int nheads, int nt, i
 }
 int it_sup_conv(it_ctx* c, const float* mixed, size_t m_ts, const float* w, float* state, float* out, size_t o_ts, int cd, int kk, int nt, float* ck, size_t ck_stride, int nck) {
     if (kk < 2 || kk > 9) return it_fail(IT_EINVAL, "conv kernel size %d not supported", kk);
-    it_note_op(c); it_pdl(k_conv, dim3((cd + 127) / 128), dim3(128), 0, c->stream, mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
+    it_note_op(c);
+    if (nt > 8 && nck == 0) {   // prompt passes: rows in parallel
+        it_pdl(k_conv_wide, dim3((cd + 127) / 128), dim3(128, 8), 0, c->stream, mixed, m_ts, w, state, out, o_ts, cd, kk, nt); KCHK("conv_wide"); return IT_OK;
+    }
+    it_pdl(k_conv, dim3((cd + 127) / 128), dim3(128), 0, c->stream, mixed, m_ts, w, state, out, o_ts, cd, kk, nt, ck, ck_stride, nck); KCHK("conv"); return IT_OK;
 }
 int it_sup_dense_rows(it_ctx* c, const float* w0, const float* w1, int rows, int cols, const float* x, size_t x_ts, float* y0, float* y1, size_t y_ts, int nt) {
     it_note_op(c); it_pdl(k_dense_rows, dim3(dim3(2 * rows, nt)), dim3(256), 0, c->stream, w0, w1, rows, cols, x, x_ts, y0, y1, y_ts); KCHK("dense_rows"); return IT_OK;
