@@ -34,6 +34,11 @@ __device__ __forceinline__ void it_hadamard_block(it_had_smem& sm, const unsigne
     const unsigned g0 = blk * 1024u + 4u * tid;      // index of this thread's first element inside the row
     const float* x = arena_in + in_off + tok * in_stride;
 
+    // loads that depend on nothing computed here are issued first, so that their latency overlaps the row reduction
+    float4 sg = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (signs) sg = *reinterpret_cast<const float4*>(signs + g0);
+    float4 own = make_float4(0.f, 0.f, 0.f, 0.f), w4 = own;
+    if (pro.mode == 2) { own = *reinterpret_cast<const float4*>(x + g0); w4 = *reinterpret_cast<const float4*>(pro.w + g0); }
     float v[4];
     if (pro.mode == 2) {
         // rmsnorm of the whole row first (src/cpu.rs:14-18), in the order of k_rmsnorm_wide: thread i adds x[i]^2,
@@ -52,7 +57,7 @@ __device__ __forceinline__ void it_hadamard_block(it_had_smem& sm, const unsigne
 #pragma unroll
         for (int k = 1; k < 8; k++) tot = it_add(tot, wsum[k]);
         const float sc = it_div(1.0f, it_sqrt(it_add(it_div(tot, (float)pro.n), pro.eps)));
-        const float4 t = *reinterpret_cast<const float4*>(x + g0), w4 = *reinterpret_cast<const float4*>(pro.w + g0);
+        const float4 t = own;
         v[0] = it_mul(it_mul(t.x, sc), w4.x); v[1] = it_mul(it_mul(t.y, sc), w4.y); v[2] = it_mul(it_mul(t.z, sc), w4.z); v[3] = it_mul(it_mul(t.w, sc), w4.w);
         if (pro.xn_out) *reinterpret_cast<float4*>(pro.xn_out + tok * pro.xn_stride + g0) = make_float4(v[0], v[1], v[2], v[3]);
     } else if (pro.mode == 1) {
@@ -69,10 +74,7 @@ __device__ __forceinline__ void it_hadamard_block(it_had_smem& sm, const unsigne
             v[e] = x[i0 + perm_hd * (k + perm_nk * r)];
         }
     }
-    if (signs && !inverse) {
-        float4 s = *reinterpret_cast<const float4*>(signs + g0);
-        v[0] *= s.x; v[1] *= s.y; v[2] *= s.z; v[3] *= s.w;
-    }
+    if (signs && !inverse) { v[0] *= sg.x; v[1] *= sg.y; v[2] *= sg.z; v[3] *= sg.w; }
     if (rotate) {
         float a, b;
         a = v[0]; b = v[1]; v[0] = a + b; v[1] = a - b;      // h = 1
@@ -100,10 +102,7 @@ __device__ __forceinline__ void it_hadamard_block(it_had_smem& sm, const unsigne
 #pragma unroll
         for (int e = 0; e < 4; e++) v[e] *= 0.03125f;
     }
-    if (signs && inverse) {
-        float4 s = *reinterpret_cast<const float4*>(signs + g0);
-        v[0] *= s.x; v[1] *= s.y; v[2] *= s.z; v[3] *= s.w;
-    }
+    if (signs && inverse) { v[0] *= sg.x; v[1] *= sg.y; v[2] *= sg.z; v[3] *= sg.w; }
     if (!QUANT) {
         *reinterpret_cast<float4*>(f32_out + out_off + tok * out_stride + g0) = make_float4(v[0], v[1], v[2], v[3]);
         return;
