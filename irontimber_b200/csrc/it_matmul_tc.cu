@@ -56,7 +56,7 @@ __host__ __device__ inline TcSmem tc_layout(int nb, int wstages) {
     L.s128 = o; o += nb * TC_TOK * 4;
     L.dw = o; o += TC_NDW * TC_ROWS * 4;
     o = (o + 15) & ~15;
-    L.bars = o; o += (2 * wstages + 2 * TC_XS + 2 * TC_NA + 2 * TC_ND) * 8;
+    L.bars = o; o += (2 * wstages + TC_XS + TC_NA + 2 * TC_ND) * 8;
     L.tmem = o; o += 16;
     L.flag = o; o += 16;
     L.total = o;
@@ -100,17 +100,19 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.flag);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + L.tmem);
     const unsigned bars = smem_u32(smem + L.bars);
-    // barrier addresses: weight stages, activation boxes, expanded tiles, accumulators (full / empty each)
-    const unsigned wfull0 = bars, wempty0 = wfull0 + 8 * wstages, xfull0 = wempty0 + 8 * wstages, xempty0 = xfull0 + 8 * TC_XS,
-                   afull0 = xempty0 + 8 * TC_XS, aempty0 = afull0 + 8 * TC_NA, dfull0 = aempty0 + 8 * TC_NA, dempty0 = dfull0 + 8 * TC_ND;
+    // barrier addresses: weight stages (full / empty), activation boxes landed, expanded tiles ready, accumulators (full / empty).
+    // "Accumulator d full" is the one commit of a block: it also tells the expanders and the activation producer that the
+    // tile and the box that block read may be reused.
+    const unsigned wfull0 = bars, wempty0 = wfull0 + 8 * wstages, xfull0 = wempty0 + 8 * wstages,
+                   afull0 = xfull0 + 8 * TC_XS, dfull0 = afull0 + 8 * TC_NA, dempty0 = dfull0 + 8 * TC_ND;
     const int rg0 = (int)blockIdx.x * 4, tok0 = (int)blockIdx.y * TC_TOK;
     const int ntv = min(TC_TOK, ntok - tok0), nrg = min(4, row_groups - rg0);
 
     if (tid == 0) {
         *abort_flag = 0;
         for (int s = 0; s < wstages; s++) { mbar_init(wfull0 + 8 * s, 1); mbar_init(wempty0 + 8 * s, 4 * TC_KB); }
-        for (int s = 0; s < TC_XS; s++) { mbar_init(xfull0 + 8 * s, 1); mbar_init(xempty0 + 8 * s, 1); }
-        for (int a = 0; a < TC_NA; a++) { mbar_init(afull0 + 8 * a, 128); mbar_init(aempty0 + 8 * a, 1); }
+        for (int s = 0; s < TC_XS; s++) mbar_init(xfull0 + 8 * s, 1);
+        for (int a = 0; a < TC_NA; a++) mbar_init(afull0 + 8 * a, 128);
         for (int d = 0; d < TC_ND; d++) { mbar_init(dfull0 + 8 * d, 1); mbar_init(dempty0 + 8 * d, TC_EPI_WARPS * 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -153,13 +155,14 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
         // ---------------- activation producer: the rows come from the kernel before this one
         if (lane == 0) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            int s = 0, issued = 0; unsigned ph = 0;
+            int s = 0, issued = 0;
             for (int b = 0; b < nb; b++) {
-                if (!mbar_wait(xempty0 + 8 * s, ph ^ 1u, abort_flag, error_flag, 19)) break;
+                // the box slot was last read by block b - TC_XS: wait for that block's commit
+                if (b >= TC_XS && !mbar_wait(dfull0 + 8 * ((b - TC_XS) % TC_ND), (unsigned)((b - TC_XS) / TC_ND) & 1u, abort_flag, error_flag, 19)) break;
                 mbar_expect_tx(xfull0 + 8 * s, (unsigned)TC_X_BYTES);
                 tma_load_2d(smem_u32(smem + L.x + s * TC_X_BYTES), &xmap, b * 128, tok0, xfull0 + 8 * s);
                 issued++;
-                if (++s == TC_XS) { s = 0; ph ^= 1u; }
+                if (++s == TC_XS) s = 0;
             }
             if (*abort_flag) {
                 const int first = issued > TC_XS ? issued - TC_XS : 0;
@@ -173,12 +176,12 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
         // ---------------- MMA issuer.  Its loop is the critical path of the CTA (one thread, three barrier waits and seven
         // asynchronous instructions per block), so the waits try the non-blocking test first.
         if (lane == 0) {
-            int s = 0, a = 0, d = 0; unsigned sph = 0, aph = 0, dph = 0;
+            int s = 0, a = 0, d = 0; unsigned aph = 0;
             const unsigned long long adesc0 = tc_smem_desc(smem_u32(smem + L.a)), bdesc0 = tc_smem_desc(smem_u32(smem + L.x));
             for (int b = 0; b < nb; b++) {
-                if (!mbar_poll(afull0 + 8 * a, aph) && !mbar_wait(afull0 + 8 * a, aph, abort_flag, error_flag, 12)) break;              // expanded weights are in place
-                if (!mbar_poll(xfull0 + 8 * s, sph) && !mbar_wait(xfull0 + 8 * s, sph, abort_flag, error_flag, 13)) break;              // so is the activation box
-                if (!mbar_poll(dempty0 + 8 * d, dph ^ 1u) && !mbar_wait(dempty0 + 8 * d, dph ^ 1u, abort_flag, error_flag, 14)) break;  // the accumulator has been read out
+                // one wait per block: the expanders arrive only when the tile is expanded, the activation box has landed and the
+                // accumulator has been read out (this thread's loop is the critical path of the CTA)
+                if (!mbar_wait(afull0 + 8 * a, aph, abort_flag, error_flag, 12)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // descriptors differ from the first tile's only in the start-address field (16-byte units): + tile index, + 2 per K step of 32
                 const unsigned long long ad = adesc0 + (unsigned)(a * (TC_A_BYTES >> 4)), bd = bdesc0 + (unsigned)(s * (TC_X_BYTES >> 4));
@@ -187,12 +190,10 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                 tc_mma<true>(dt, ad + 2, bd + 2);
                 tc_mma<true>(dt, ad + 4, bd + 4);
                 tc_mma<true>(dt, ad + 6, bd + 6);
-                tc_commit(dfull0 + 8 * d);        // accumulator complete
-                tc_commit(aempty0 + 8 * a);       // expanded tile may be overwritten
-                tc_commit(xempty0 + 8 * s);       // activation box may be refilled
-                if (++s == TC_XS) { s = 0; sph ^= 1u; }
+                tc_commit(dfull0 + 8 * d);        // accumulator complete; tile and box of this block may be reused
+                if (++s == TC_XS) s = 0;
                 if (++a == TC_NA) { a = 0; aph ^= 1u; }
-                if (++d == TC_ND) { d = 0; dph ^= 1u; }
+                if (++d == TC_ND) d = 0;
             }
         }
     } else if (warp >= TC_EPI_WARPS) {
@@ -202,9 +203,10 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
         float* dws = reinterpret_cast<float*>(smem + L.dw);
         for (int b = eset; b < nb; b += TC_ESETS) {
             const int q = b / TC_KB, s = q % wstages, a = b % TC_NA;
-            const unsigned sph = (unsigned)(q / wstages) & 1u, aph = (unsigned)(b / TC_NA) & 1u;
+            const unsigned sph = (unsigned)(q / wstages) & 1u;
             if (!mbar_wait(wfull0 + 8 * s, sph, abort_flag, error_flag, 15)) break;
-            if (!mbar_wait(aempty0 + 8 * a, aph ^ 1u, abort_flag, error_flag, 16)) break;
+            // the tile buffer was last read by block b - TC_NA: wait for that block's commit
+            if (b >= TC_NA && !mbar_wait(dfull0 + 8 * ((b - TC_NA) % TC_ND), (unsigned)((b - TC_NA) / TC_ND) & 1u, abort_flag, error_flag, 16)) break;
             const unsigned char* tile = smem + L.w + s * TC_W_BYTES + (rgl * TC_KB + b % TC_KB) * IT_TILE_BYTES;
             const uint4 wa = *reinterpret_cast<const uint4*>(tile + 16 * lane);
             const uint4 wb = *reinterpret_cast<const uint4*>(tile + 512 + 16 * lane);
@@ -224,6 +226,9 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                 dw[0] = __low2float(h01); dw[8] = __high2float(h01); dw[16] = __low2float(h23); dw[24] = __high2float(h23);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores before the MMA's async-proxy reads
+            // the other two conditions of the block's MMA, checked here so that the issuing thread has a single wait
+            if (!mbar_wait(xfull0 + 8 * (b % TC_XS), (unsigned)(b / TC_XS) & 1u, abort_flag, error_flag, 13)) break;
+            if (!mbar_wait(dempty0 + 8 * (b % TC_ND), ((unsigned)(b / TC_ND) & 1u) ^ 1u, abort_flag, error_flag, 14)) break;
             mbar_arrive(afull0 + 8 * a);
             __syncwarp();
             if (lane == 0) mbar_arrive(wempty0 + 8 * s);                     // this warp has read its tile: one of the 4 * TC_KB arrivals that free the stage
