@@ -32,6 +32,8 @@ extern "C" {
 #define IT_ENOMEM (-3)   /* device allocation failed */
 #define IT_ESTATE (-4)   /* call not valid in the current state */
 #define IT_ETIMEOUT (-5) /* a bounded device-side wait ran out */
+#define IT_EFORMAT (-6)  /* a model file cannot be read or is not well formed */
+#define IT_EUNSUPPORTED (-7) /* a well-formed model that this library does not run (tensor type, layout) */
 
 typedef struct it_ctx it_ctx;
 typedef struct it_mat it_mat;   /* ternary (2-bit code) matrix, device resident      */
@@ -169,6 +171,7 @@ enum {
     IT_T_TOK_EMBD, IT_T_OUTPUT_NORM, IT_T_OUTPUT,
     IT_T_MTP_EH, IT_T_MTP_Q, IT_T_MTP_K, IT_T_MTP_V, IT_T_MTP_O, IT_T_MTP_GATE, IT_T_MTP_UP, IT_T_MTP_DOWN,
     IT_T_MTP_ENORM, IT_T_MTP_HNORM, IT_T_MTP_ATTN_NORM, IT_T_MTP_POST_NORM, IT_T_MTP_Q_NORM, IT_T_MTP_K_NORM, IT_T_MTP_HEAD_NORM,
+    IT_T_MTP_EMBD,   /* the NextN head's embedding table (its own, or the trunk's) */
     IT_T_COUNT
 };
 
@@ -183,6 +186,31 @@ int it_engine_create_synth(int device, const it_model_config* cfg, uint64_t seed
  * rows of `rank`); activations, recurrent state, KV cache and the NextN head stay replicated and every rank computes
  * the same tokens.  Attach the peers of it_engine_ctx() before the first pass. */
 int it_engine_create_synth_sharded(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, int rank, int world, it_engine** out);
+/* ---- model files ------------------------------------------------------------------------
+ * An engine with the weights of a qwen35 GGUF file (container v2/v3).  Stands where Gguf::open + Config::from_gguf +
+ * Model::load + VkEngine::new_with_mtp stand (src/gguf.rs:99-140, src/model.rs:16-62, src/cpu.rs:91-112,
+ * src/vk/mod.rs:494-631).  Accepted, as by the reference's device path: ternary trunk matrices and LM head (PQ2_0, or
+ * PTQ1_0 re-coded to the same 2-bit codes and scale), all of them Hadamard-folded with block 1024
+ * (prism.hadamard.weight_names; sign_mode "none" or "explicit"); F32 / F16 / BF16 vectors and beta / alpha matrices;
+ * an embedding table of any type below, brought back from latent space when prism.hadamard.inverse_weight_names lists
+ * it; a tied LM head (no output.weight).  head_path: NULL = no NextN head; "" or the same path = the NextN block
+ * appended to the trunk file; another path = a head-only sidecar whose architecture / qwen35.* / tokenizer.* /
+ * prism.hadamard.* metadata must equal the trunk's (validate_compatibility, src/mtp.rs:31-43).  The head's matrices
+ * must be Q8_0 (a Q6_K head is refused with IT_EUNSUPPORTED), its norms F32, and it may carry its own embedding table
+ * (nextn.embed_tokens).  rank / world as in it_engine_create_synth_sharded: a rank reads only its rows of every trunk
+ * matrix.  Everything is checked before the device is touched: IT_EFORMAT for a file that cannot be read or is
+ * malformed (short, bad magic, duplicate names, tensor outside the file, missing key or tensor, wrong shape),
+ * IT_EUNSUPPORTED for a well-formed model outside the set above. */
+int it_engine_create_gguf(int device, const char* path, const char* head_path, int ctx_len, int rank, int world, it_engine** out);
+/* The same checks without a device: fills the configuration, whether a NextN head was found, and the trunk file's
+ * tensor count and tensor bytes.  Outputs other than cfg may be NULL. */
+int it_gguf_inspect(const char* path, const char* head_path, int ctx_len, it_model_config* cfg, int* has_mtp, uint64_t* n_tensors, uint64_t* tensor_bytes);
+/* Host decoders of the ggml element types the loader reads (F32 0, F16 1, Q8_0 8, Q4_K 12, Q6_K 14, BF16 30, PQ2_0 142,
+ * PTQ1_0 143): n elements (a multiple of the type's block) to f32, in ggml's element order and float operation order
+ * (src/quant.rs:51-62, :189-228); and PTQ1_0 blocks (28 bytes) re-coded as PQ2_0 blocks (34 bytes). */
+int it_gguf_dequant(uint32_t ggml_type, const void* src, size_t n, float* out);
+int it_gguf_ptq1_to_pq2(const void* src, size_t nblocks, void* dst);
+
 void it_engine_destroy(it_engine* e);
 it_ctx* it_engine_ctx(it_engine* e);
 /* Read-back of weights and state for parity tests.  Ternary / Q8_0 tensors come back as raw ggml rows, f32 tensors as f32. */

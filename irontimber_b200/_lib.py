@@ -63,6 +63,10 @@ SIGNATURES = {
     "it_argmax_static": (C.c_int, [P, P, c_size, P]),
     "it_engine_create_synth": (C.c_int, [C.c_int, P, C.c_uint64, C.c_int, C.POINTER(P)]),
     "it_engine_create_synth_sharded": (C.c_int, [C.c_int, P, C.c_uint64, C.c_int, C.c_int, C.c_int, C.POINTER(P)]),
+    "it_engine_create_gguf": (C.c_int, [C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(P)]),
+    "it_gguf_inspect": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, P, C.POINTER(C.c_int), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "it_gguf_dequant": (C.c_int, [C.c_uint32, P, c_size, P]),
+    "it_gguf_ptq1_to_pq2": (C.c_int, [P, c_size, P]),
     "it_engine_destroy": (None, [P]),
     "it_engine_ctx": (P, [P]),
     "it_engine_tensor_bytes": (C.c_int, [P, C.c_int, C.c_int, C.POINTER(c_size)]),

@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libirontimber_cuda.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2", "-shared", "-cudart", "static"]
+         "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2,-ffp-contract=off", "-shared", "-cudart", "static"]
 
 
 def sources():

@@ -40,29 +40,45 @@ Range f32_range(int tensor) {
 }
 
 int dev_alloc(it_engine* e, void** p, size_t bytes, bool zero) {
-    IT_CUDA(cudaMalloc(p, bytes));
+    cudaError_t ce = cudaMalloc(p, bytes);
+    if (ce != cudaSuccess) return it_fail(IT_ENOMEM, "engine: cudaMalloc(%zu): %s", bytes, cudaGetErrorString(ce));
     e->owned.push_back(*p);
     if (zero) IT_CUDA(cudaMemsetAsync(*p, 0, bytes, e->ctx->stream));
     return IT_OK;
 }
-int synth_f32(it_engine* e, int layer, int tensor, size_t n, float** out) {
+// ---- weights come from an it_weight_source; the helpers below own allocation, sharding and the tile layout
+int load_f32(it_engine* e, it_weight_source* src, int layer, int tensor, size_t n, float** out) {
     IT_TRY(dev_alloc(e, (void**)out, n * sizeof(float), false));
-    const Range r = f32_range(tensor);
-    k_synth_f32<<<e->ctx->sm_count * 4, 256, 0, e->ctx->stream>>>(tensor_seed(e->seed, layer, tensor), n, r.lo, r.hi - r.lo, *out);
-    IT_LAUNCH_CHECK("synth_f32"); return IT_OK;
+    return src->f32(e, layer, tensor, n, *out);
+}
+// rows [row0, row0 + nrows) of a ternary tensor into tile storage that is already allocated
+int load_tiles(it_engine* e, it_weight_source* src, int layer, int tensor, size_t rows, size_t cols, size_t row0, size_t nrows, uint8_t* tiles) {
+    const size_t nbytes = nrows * (cols / 128) * 34; uint8_t* tmp = nullptr;
+    cudaError_t ce = cudaMalloc(&tmp, nbytes);
+    if (ce != cudaSuccess) return it_fail(IT_ENOMEM, "engine: staging allocation of %zu bytes failed: %s", nbytes, cudaGetErrorString(ce));
+    int r = src->ternary(e, layer, tensor, rows, cols, row0, nrows, tmp);
+    if (r == IT_OK) r = it_launch_repack_pq2(e->ctx, tmp, nrows, cols, tiles);
+    if (r == IT_OK) ce = cudaStreamSynchronize(e->ctx->stream);
+    cudaFree(tmp);
+    if (r) return r;
+    if (ce != cudaSuccess) return it_fail(IT_ECUDA, "engine: weight repack failed: %s", cudaGetErrorString(ce));
+    return IT_OK;
 }
 // Trunk matrices are split by output rows over the ranks (every row is an independent dot with the replicated
-// activations, src/cpu.rs:31-34): this engine generates and holds rows [rank*rows/world, (rank+1)*rows/world) only.
-int synth_mat(it_engine* e, int layer, int tensor, size_t rows, size_t cols, it_mat** out) {
-    if (e->world == 1) return it_matrix_synth(e->ctx, tensor_seed(e->seed, layer, tensor), rows, cols, 0, out);
+// activations, src/cpu.rs:31-34): this engine loads and holds rows [rank*rows/world, (rank+1)*rows/world) only.
+int load_mat(it_engine* e, it_weight_source* src, int layer, int tensor, size_t rows, size_t cols, it_mat** out) {
     size_t row0, n; IT_TRY(it_shard_range(rows, e->rank, e->world, &row0, &n));
-    return it_matrix_synth_rows(e->ctx, tensor_seed(e->seed, layer, tensor), rows, cols, 0, row0, n, out);
+    uint8_t* buf = nullptr;
+    IT_TRY(dev_alloc(e, (void**)&buf, (n + 31) / 32 * (cols / 128) * IT_TILE_BYTES, false));
+    IT_TRY(it_matrix_view(e->ctx, n, cols, buf, out));
+    IT_TRY(load_tiles(e, src, layer, tensor, rows, cols, row0, n, buf));
+    return e->world > 1 ? it_matrix_set_shard(*out, row0, rows) : IT_OK;
 }
 // Several ternary matrices with the same column count, stacked row-wise in one allocation: `stack` sees all rows,
 // parts[i] is a view of tensor i.  Row counts (per rank) must be multiples of 32 so that every part starts on a row
 // group.  On a sharded engine the stack holds this rank's rows of every part, and its row map sends each part's rows
 // to their place in the full stacked output.
-int synth_stack(it_engine* e, int layer, int n, const int* tensors, const size_t* rows, size_t cols, it_mat** parts, it_mat** stack) {
+int load_stack(it_engine* e, it_weight_source* src, int layer, int n, const int* tensors, const size_t* rows, size_t cols, it_mat** parts, it_mat** stack) {
     size_t total = 0, full = 0, local[4], row0[4];
     for (int i = 0; i < n; i++) {
         IT_TRY(it_shard_range(rows[i], e->rank, e->world, &row0[i], &local[i]));
@@ -73,7 +89,9 @@ int synth_stack(it_engine* e, int layer, int n, const int* tensors, const size_t
     IT_TRY(dev_alloc(e, (void**)&buf, total / 32 * (cols / 128) * IT_TILE_BYTES, false));
     size_t off = 0;
     for (int i = 0; i < n; i++) {
-        IT_TRY(it_matrix_synth_view(e->ctx, tensor_seed(e->seed, layer, tensors[i]), local[i], cols, buf + off / 32 * (cols / 128) * IT_TILE_BYTES, &parts[i], row0[i]));
+        uint8_t* tiles = buf + off / 32 * (cols / 128) * IT_TILE_BYTES;
+        IT_TRY(it_matrix_view(e->ctx, local[i], cols, tiles, &parts[i]));
+        IT_TRY(load_tiles(e, src, layer, tensors[i], rows[i], cols, row0[i], local[i], tiles));
         off += local[i];
     }
     IT_TRY(it_matrix_view(e->ctx, total, cols, buf, stack));
@@ -84,16 +102,28 @@ int synth_stack(it_engine* e, int layer, int n, const int* tensors, const size_t
     }
     return IT_OK;
 }
-int synth_qmat(it_engine* e, int tensor, size_t rows, size_t cols, it_qmat** out) {
-    return it_qmatrix_synth(e->ctx, tensor_seed(e->seed, -1, tensor), rows, cols, out);
-}
-int synth_signs(it_engine* e, size_t width) {
-    if (e->ctx->signs.count(width)) return IT_OK;
-    std::vector<float> s(width);
-    const uint64_t sd = it_hash(e->seed, 7000 + width / 1024);
-    for (size_t i = 0; i < width; i++) s[i] = (it_hash(sd, i) & 1) ? 1.0f : -1.0f;
-    return it_signs_set(e->ctx, width, s.data());
-}
+
+// Random-init weights generated on the device from a seed: each tensor's values are a pure function of
+// (seed, layer, tensor, element index), so a row shard generates exactly its rows of the full tensor.
+struct SynthSource : it_weight_source {
+    int signs(it_engine* e, size_t width, std::vector<float>* s) override {
+        s->resize(width);
+        const uint64_t sd = it_hash(e->seed, 7000 + width / 1024);
+        for (size_t i = 0; i < width; i++) (*s)[i] = (it_hash(sd, i) & 1) ? 1.0f : -1.0f;
+        return IT_OK;
+    }
+    int f32(it_engine* e, int layer, int tensor, size_t n, float* dev) override {
+        const Range r = f32_range(tensor);
+        k_synth_f32<<<e->ctx->sm_count * 4, 256, 0, e->ctx->stream>>>(tensor_seed(e->seed, layer, tensor), n, r.lo, r.hi - r.lo, dev);
+        IT_LAUNCH_CHECK("synth_f32"); return IT_OK;
+    }
+    int ternary(it_engine* e, int layer, int tensor, size_t, size_t cols, size_t row0, size_t nrows, uint8_t* raw_dev) override {
+        return it_launch_synth_pq2(e->ctx, tensor_seed(e->seed, layer, tensor), nrows, cols, 0, raw_dev, row0);
+    }
+    int q8(it_engine* e, int tensor, size_t rows, size_t cols, it_qmat** out) override {
+        return it_qmatrix_synth(e->ctx, tensor_seed(e->seed, -1, tensor), rows, cols, out);
+    }
+};
 
 size_t up64(size_t n) { return (n + 63) / 64 * 64; }
 
@@ -122,12 +152,19 @@ int validate(const it_model_config* c) {
 IT_API int it_engine_create_synth(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, it_engine** out) {
     return it_engine_create_synth_sharded(device, cfg, seed, with_mtp, 0, 1, out);
 }
-
 IT_API int it_engine_create_synth_sharded(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, int rank, int world, it_engine** out) {
-    IT_CHECK_ARG(out, "it_engine_create_synth: out is null");
+    SynthSource src;
+    return it_engine_build(device, cfg, seed, with_mtp, rank, world, &src, out);
+}
+
+int it_engine_validate_config(const it_model_config* cfg) { return validate(cfg); }
+int it_engine_dev_alloc(it_engine* e, void** p, size_t bytes, bool zero) { return dev_alloc(e, p, bytes, zero); }
+
+int it_engine_build(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, int rank, int world, it_weight_source* src, it_engine** out) {
+    IT_CHECK_ARG(out && src, "engine: null output or weight source");
     *out = nullptr;
     IT_TRY(validate(cfg));
-    IT_CHECK_ARG(world >= 1 && world <= IT_MAX_PEERS && rank >= 0 && rank < world, "it_engine_create_synth_sharded: bad rank %d of %d", rank, world);
+    IT_CHECK_ARG(world >= 1 && world <= IT_MAX_PEERS && rank >= 0 && rank < world, "engine: bad rank %d of %d", rank, world);
     {   // every trunk matrix must split evenly, stacked ones on row-group boundaries
         const int kvd_ = cfg->n_head_kv * cfg->head_dim, qf_ = 2 * cfg->n_head * cfg->head_dim, cd_ = it_cfg_conv_dim(*cfg);
         const int stacked[] = { cfg->n_ff, cd_, cfg->ssm_inner, qf_, kvd_ };
@@ -138,7 +175,7 @@ IT_API int it_engine_create_synth_sharded(int device, const it_model_config* cfg
     const int e_ = c.n_embd, ff = c.n_ff, hd = c.head_dim, nh = c.n_head, nkv = c.n_head_kv, kvd = nkv * hd, qf = 2 * nh * hd;
     const int cd = it_cfg_conv_dim(c), inner = c.ssm_inner, nv = c.ssm_vheads, sd = c.ssm_state;
     it_engine* e = new it_engine();
-    e->ctx = nullptr; e->cfg = c; e->seed = seed; e->has_mtp = with_mtp != 0; e->rank = rank; e->world = world; e->output = nullptr; e->q8 = nullptr; e->step_graph = nullptr; e->host_pin = nullptr;
+    e->ctx = nullptr; e->cfg = c; e->seed = seed; e->has_mtp = with_mtp != 0; e->rank = rank; e->world = world; e->output = nullptr; e->tok_embd = e->m_tok_embd = nullptr; e->q8 = nullptr; e->step_graph = nullptr; e->host_pin = nullptr;
     e->m_eh = e->m_q = e->m_k = e->m_v = e->m_o = e->m_gate = e->m_up = e->m_down = nullptr;
     e->pos = 0; e->mpos = 1; e->hp_off = 0; e->hp_n = 0; e->last_rows = 0;
     // arena layout
@@ -157,43 +194,49 @@ IT_API int it_engine_create_synth_sharded(int device, const it_model_config* cfg
 #define E_TRY(expr) do { int r__ = (expr); if (r__) return fail(r__); } while (0)
     e->theta_scale = powf(c.rope_base, -2.0f / (float)c.n_rot);      // the same host expression as src/cpu.rs:147
     const size_t widths[4] = { (size_t)e_, (size_t)inner, (size_t)(nh * hd), (size_t)ff };
-    for (size_t wdt : widths) E_TRY(synth_signs(e, wdt));
+    for (size_t wdt : widths) {
+        if (e->ctx->signs.count(wdt)) continue;
+        std::vector<float> sg; E_TRY(src->signs(e, wdt, &sg));
+        if (sg.size() != wdt) return fail(it_fail(IT_EINVAL, "engine: sign vector of width %zu has %zu entries", wdt, sg.size()));
+        E_TRY(it_signs_set(e->ctx, wdt, sg.data()));
+    }
     e->layers.resize(c.n_layer);
     for (int il = 0; il < c.n_layer; il++) {
         it_layer& l = e->layers[il]; memset(&l, 0, sizeof l);
         l.recurrent = it_cfg_recurrent(c, il);
-        E_TRY(synth_f32(e, il, IT_T_ATTN_NORM, e_, &l.attn_norm)); E_TRY(synth_f32(e, il, IT_T_POST_NORM, e_, &l.post_norm));
+        E_TRY(load_f32(e, src, il, IT_T_ATTN_NORM, e_, &l.attn_norm)); E_TRY(load_f32(e, src, il, IT_T_POST_NORM, e_, &l.post_norm));
         { const int ts[2] = { IT_T_FFN_GATE, IT_T_FFN_UP }; const size_t rs[2] = { (size_t)ff, (size_t)ff }; it_mat* parts[2];
-          E_TRY(synth_stack(e, il, 2, ts, rs, e_, parts, &l.gate_up)); l.ffn_gate = parts[0]; l.ffn_up = parts[1]; }
-        E_TRY(synth_mat(e, il, IT_T_FFN_DOWN, e_, ff, &l.ffn_down));
+          E_TRY(load_stack(e, src, il, 2, ts, rs, e_, parts, &l.gate_up)); l.ffn_gate = parts[0]; l.ffn_up = parts[1]; }
+        E_TRY(load_mat(e, src, il, IT_T_FFN_DOWN, e_, ff, &l.ffn_down));
         if (l.recurrent) {
             { const int ts[2] = { IT_T_QKV, IT_T_GATE }; const size_t rs[2] = { (size_t)cd, (size_t)inner }; it_mat* parts[2];
-              E_TRY(synth_stack(e, il, 2, ts, rs, e_, parts, &l.in_proj)); l.qkv = parts[0]; l.gate = parts[1]; }
-            E_TRY(synth_mat(e, il, IT_T_SSM_OUT, e_, inner, &l.ssm_out));
-            E_TRY(synth_f32(e, il, IT_T_CONV, (size_t)cd * c.conv_k, &l.conv_w)); E_TRY(synth_f32(e, il, IT_T_DT, nv, &l.dt)); E_TRY(synth_f32(e, il, IT_T_A, nv, &l.a));
-            E_TRY(synth_f32(e, il, IT_T_BETA, (size_t)nv * e_, &l.beta)); E_TRY(synth_f32(e, il, IT_T_ALPHA, (size_t)nv * e_, &l.alpha)); E_TRY(synth_f32(e, il, IT_T_SSM_NORM, sd, &l.ssm_norm));
+              E_TRY(load_stack(e, src, il, 2, ts, rs, e_, parts, &l.in_proj)); l.qkv = parts[0]; l.gate = parts[1]; }
+            E_TRY(load_mat(e, src, il, IT_T_SSM_OUT, e_, inner, &l.ssm_out));
+            E_TRY(load_f32(e, src, il, IT_T_CONV, (size_t)cd * c.conv_k, &l.conv_w)); E_TRY(load_f32(e, src, il, IT_T_DT, nv, &l.dt)); E_TRY(load_f32(e, src, il, IT_T_A, nv, &l.a));
+            E_TRY(load_f32(e, src, il, IT_T_BETA, (size_t)nv * e_, &l.beta)); E_TRY(load_f32(e, src, il, IT_T_ALPHA, (size_t)nv * e_, &l.alpha)); E_TRY(load_f32(e, src, il, IT_T_SSM_NORM, sd, &l.ssm_norm));
             const size_t csz = (size_t)(c.conv_k - 1) * cd, ssz = (size_t)nv * sd * sd;
             E_TRY(dev_alloc(e, (void**)&l.conv_st, csz * 4, true)); E_TRY(dev_alloc(e, (void**)&l.ssm_st, ssz * 4, true));
             E_TRY(dev_alloc(e, (void**)&l.ck_conv, IT_MAXCK * csz * 4, true)); E_TRY(dev_alloc(e, (void**)&l.ck_ssm, IT_MAXCK * ssz * 4, true));
         } else {
             { const int ts[3] = { IT_T_Q, IT_T_K, IT_T_V }; const size_t rs[3] = { (size_t)qf, (size_t)kvd, (size_t)kvd }; it_mat* parts[3];
-              E_TRY(synth_stack(e, il, 3, ts, rs, e_, parts, &l.in_proj)); l.q = parts[0]; l.k = parts[1]; l.v = parts[2]; }
-            E_TRY(synth_mat(e, il, IT_T_O, e_, nh * hd, &l.o));
-            E_TRY(synth_f32(e, il, IT_T_Q_NORM, hd, &l.q_norm)); E_TRY(synth_f32(e, il, IT_T_K_NORM, hd, &l.k_norm));
+              E_TRY(load_stack(e, src, il, 3, ts, rs, e_, parts, &l.in_proj)); l.q = parts[0]; l.k = parts[1]; l.v = parts[2]; }
+            E_TRY(load_mat(e, src, il, IT_T_O, e_, nh * hd, &l.o));
+            E_TRY(load_f32(e, src, il, IT_T_Q_NORM, hd, &l.q_norm)); E_TRY(load_f32(e, src, il, IT_T_K_NORM, hd, &l.k_norm));
             E_TRY(dev_alloc(e, (void**)&l.kc, (size_t)((c.ctx_len + 31) / 32 * 32) * kvd * 2, true));   // tiles of 32 positions
             E_TRY(dev_alloc(e, (void**)&l.vc, (size_t)c.ctx_len * kvd * 2, true));
         }
     }
-    E_TRY(synth_f32(e, -1, IT_T_TOK_EMBD, (size_t)c.n_vocab * e_, &e->tok_embd));
-    E_TRY(synth_f32(e, -1, IT_T_OUTPUT_NORM, e_, &e->output_norm));
-    E_TRY(synth_mat(e, -1, IT_T_OUTPUT, c.n_vocab, e_, &e->output));
+    E_TRY(load_f32(e, src, -1, IT_T_TOK_EMBD, (size_t)c.n_vocab * e_, &e->tok_embd));
+    E_TRY(load_f32(e, src, -1, IT_T_OUTPUT_NORM, e_, &e->output_norm));
+    E_TRY(load_mat(e, src, -1, IT_T_OUTPUT, c.n_vocab, e_, &e->output));
     if (e->has_mtp) {
-        E_TRY(synth_qmat(e, IT_T_MTP_EH, e_, 2 * e_, &e->m_eh)); E_TRY(synth_qmat(e, IT_T_MTP_Q, qf, e_, &e->m_q)); E_TRY(synth_qmat(e, IT_T_MTP_K, kvd, e_, &e->m_k));
-        E_TRY(synth_qmat(e, IT_T_MTP_V, kvd, e_, &e->m_v)); E_TRY(synth_qmat(e, IT_T_MTP_O, e_, nh * hd, &e->m_o)); E_TRY(synth_qmat(e, IT_T_MTP_GATE, ff, e_, &e->m_gate));
-        E_TRY(synth_qmat(e, IT_T_MTP_UP, ff, e_, &e->m_up)); E_TRY(synth_qmat(e, IT_T_MTP_DOWN, e_, ff, &e->m_down));
-        E_TRY(synth_f32(e, -1, IT_T_MTP_ENORM, e_, &e->m_enorm)); E_TRY(synth_f32(e, -1, IT_T_MTP_HNORM, e_, &e->m_hnorm)); E_TRY(synth_f32(e, -1, IT_T_MTP_ATTN_NORM, e_, &e->m_attn_norm));
-        E_TRY(synth_f32(e, -1, IT_T_MTP_POST_NORM, e_, &e->m_post_norm)); E_TRY(synth_f32(e, -1, IT_T_MTP_Q_NORM, hd, &e->m_q_norm)); E_TRY(synth_f32(e, -1, IT_T_MTP_K_NORM, hd, &e->m_k_norm));
-        E_TRY(synth_f32(e, -1, IT_T_MTP_HEAD_NORM, e_, &e->m_head_norm));
+        E_TRY(src->q8(e, IT_T_MTP_EH, e_, 2 * e_, &e->m_eh)); E_TRY(src->q8(e, IT_T_MTP_Q, qf, e_, &e->m_q)); E_TRY(src->q8(e, IT_T_MTP_K, kvd, e_, &e->m_k));
+        E_TRY(src->q8(e, IT_T_MTP_V, kvd, e_, &e->m_v)); E_TRY(src->q8(e, IT_T_MTP_O, e_, nh * hd, &e->m_o)); E_TRY(src->q8(e, IT_T_MTP_GATE, ff, e_, &e->m_gate));
+        E_TRY(src->q8(e, IT_T_MTP_UP, ff, e_, &e->m_up)); E_TRY(src->q8(e, IT_T_MTP_DOWN, e_, ff, &e->m_down));
+        E_TRY(load_f32(e, src, -1, IT_T_MTP_ENORM, e_, &e->m_enorm)); E_TRY(load_f32(e, src, -1, IT_T_MTP_HNORM, e_, &e->m_hnorm)); E_TRY(load_f32(e, src, -1, IT_T_MTP_ATTN_NORM, e_, &e->m_attn_norm));
+        E_TRY(load_f32(e, src, -1, IT_T_MTP_POST_NORM, e_, &e->m_post_norm)); E_TRY(load_f32(e, src, -1, IT_T_MTP_Q_NORM, hd, &e->m_q_norm)); E_TRY(load_f32(e, src, -1, IT_T_MTP_K_NORM, hd, &e->m_k_norm));
+        E_TRY(load_f32(e, src, -1, IT_T_MTP_HEAD_NORM, e_, &e->m_head_norm));
+        e->m_tok_embd = e->tok_embd; E_TRY(src->mtp_embd(e, &e->m_tok_embd));
         E_TRY(dev_alloc(e, (void**)&e->mkc, (size_t)c.ctx_len * kvd * 4, true)); E_TRY(dev_alloc(e, (void**)&e->mvc, (size_t)c.ctx_len * kvd * 4, true));
     }
     E_TRY(it_q8_create(e->ctx, (size_t)std::max(std::max(e_, ff), std::max(inner, nh * hd)), IT_MAXT, &e->q8));
@@ -255,7 +298,7 @@ TensorRef find_tensor(it_engine* e, int layer, int t) {
     if (e->has_mtp) switch (t) {
         case IT_T_MTP_ENORM: F(e->m_enorm, e_); break; case IT_T_MTP_HNORM: F(e->m_hnorm, e_); break; case IT_T_MTP_ATTN_NORM: F(e->m_attn_norm, e_); break;
         case IT_T_MTP_POST_NORM: F(e->m_post_norm, e_); break; case IT_T_MTP_Q_NORM: F(e->m_q_norm, hd); break; case IT_T_MTP_K_NORM: F(e->m_k_norm, hd); break;
-        case IT_T_MTP_HEAD_NORM: F(e->m_head_norm, e_); break;
+        case IT_T_MTP_HEAD_NORM: F(e->m_head_norm, e_); break; case IT_T_MTP_EMBD: F(e->m_tok_embd, (size_t)c.n_vocab * e_); break;
     }
     return r;
 }

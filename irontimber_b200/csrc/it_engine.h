@@ -38,6 +38,7 @@ struct it_engine {
     int rank, world;                                 // row shard of the trunk matrices held by this engine (0 of 1: everything)
     std::vector<it_layer> layers;
     float *tok_embd, *output_norm;
+    float* m_tok_embd;                               // embedding table of the NextN head: its own (src/mtp.rs:101) or tok_embd
     it_mat* output;
     // MTP head (src/mtp.rs:22-27)
     it_qmat *m_eh, *m_q, *m_k, *m_v, *m_o, *m_gate, *m_up, *m_down;
@@ -55,6 +56,26 @@ struct it_engine {
     it_graph* step_graph;                            // recorded single-token greedy step
     uint32_t* host_pin;                              // pinned staging, laid out like toks_dev, plus the position at [2*IT_MAXT]
 };
+
+// Where an engine under construction gets its weights.  The engine owns allocation, row sharding and the device
+// layouts; a source only fills what it is handed.  Every method returns an IT_* code.
+struct it_weight_source {
+    virtual ~it_weight_source() {}
+    // the +-1 vector of the Hadamard transform for activations of `width` elements (all +1 when the model has none)
+    virtual int signs(it_engine* e, size_t width, std::vector<float>* s) = 0;
+    // n floats of an f32 tensor into device memory
+    virtual int f32(it_engine* e, int layer, int tensor, size_t n, float* dev) = 0;
+    // rows [row0, row0 + nrows) of a rows x cols ternary tensor as 34-byte PQ2_0 blocks into device memory
+    virtual int ternary(it_engine* e, int layer, int tensor, size_t rows, size_t cols, size_t row0, size_t nrows, uint8_t* raw_dev) = 0;
+    // an int8-group matrix of the NextN head
+    virtual int q8(it_engine* e, int tensor, size_t rows, size_t cols, it_qmat** out) = 0;
+    // the NextN head's own embedding table ([n_vocab][n_embd] floats on the device, owned by the engine); leaves
+    // *dev alone when the head shares the trunk's table
+    virtual int mtp_embd(it_engine*, float**) { return IT_OK; }
+};
+int it_engine_build(int device, const it_model_config* cfg, uint64_t seed, int with_mtp, int rank, int world, it_weight_source* src, it_engine** out);
+int it_engine_validate_config(const it_model_config* cfg);
+int it_engine_dev_alloc(it_engine* e, void** p, size_t bytes, bool zero);   // freed with the engine
 
 // derived sizes (src/model.rs:40-43)
 static inline int it_cfg_qk(const it_model_config& c) { return c.ssm_state * c.ssm_groups; }

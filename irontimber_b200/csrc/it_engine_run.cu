@@ -131,7 +131,7 @@ int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, 
     IT_CHECK_ARG(nt >= 1 && nt <= IT_MAXT && pos0 >= 1 && pos0 + nt <= c.ctx_len, "engine: bad MTP pass geometry");
     for (int t = 0; t < nt; t++) e->host_pin[IT_MAXT + t] = toks[t];
     IT_CUDA(cudaMemcpyAsync(e->toks_dev + IT_MAXT, e->host_pin + IT_MAXT, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
-    IT_TRY(it_sup_embed(cx, e->toks_dev + IT_MAXT, e->tok_embd, e_, nt, A + L.me));
+    IT_TRY(it_sup_embed(cx, e->toks_dev + IT_MAXT, e->m_tok_embd, e_, nt, A + L.me));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + L.me, e_, e->m_enorm, e_, c.eps, A + L.mcat, 2 * e_, nt));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + hoff, e_, e->m_hnorm, e_, c.eps, A + L.mcat + e_, 2 * e_, nt));
     IT_TRY(it_matvec_q8(cx, e->m_eh, nt, L.mcat, 2 * e_, L.mx, e_, 0));

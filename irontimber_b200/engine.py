@@ -16,7 +16,7 @@ TENSORS = ("attn_norm", "post_norm", "ffn_gate", "ffn_up", "ffn_down",
            "q", "k", "v", "o", "q_norm", "k_norm",
            "tok_embd", "output_norm", "output",
            "mtp_eh", "mtp_q", "mtp_k", "mtp_v", "mtp_o", "mtp_gate", "mtp_up", "mtp_down",
-           "mtp_enorm", "mtp_hnorm", "mtp_attn_norm", "mtp_post_norm", "mtp_q_norm", "mtp_k_norm", "mtp_head_norm")
+           "mtp_enorm", "mtp_hnorm", "mtp_attn_norm", "mtp_post_norm", "mtp_q_norm", "mtp_k_norm", "mtp_head_norm", "mtp_embd")
 TENSOR_ID = {n: i for i, n in enumerate(TENSORS)}
 GDN_TENSORS = ("qkv", "gate", "conv", "dt", "a", "beta", "alpha", "ssm_norm", "ssm_out")
 ATTN_TENSORS = ("q", "k", "v", "o", "q_norm", "k_norm")
@@ -55,20 +55,42 @@ def _p(a):
     return a.ctypes.data_as(C.c_void_p)
 
 
+def inspect_gguf(path, head_path=None, ctx_len=4096):
+    """Reads and checks a qwen35 model file without a device: (ModelConfig, has_mtp, tensor count, tensor bytes).
+    head_path as in CudaEngine.from_gguf."""
+    L = _lib.load()
+    cfg, has, nt, nb = ModelConfig(), C.c_int(), C.c_uint64(), C.c_uint64()
+    hp = None if head_path is None else str(head_path).encode()
+    _lib.check(L.it_gguf_inspect(str(path).encode(), hp, ctx_len, C.byref(cfg), C.byref(has), C.byref(nt), C.byref(nb)))
+    return cfg, bool(has.value), nt.value, nb.value
+
+
 class CudaEngine:
-    def __init__(self, cfg, seed=1, with_mtp=False, device=0, rank=0, world=1, group=None):
+    def __init__(self, cfg, seed=1, with_mtp=False, device=0, rank=0, world=1, group=None, _gguf=None):
         """rank / world > 1: this engine holds the rows of `rank` of every trunk matrix; the arenas of all ranks (one
         process per GPU, torch.distributed initialised) are attached to each other before the constructor returns."""
         self.L = _lib.load()
         self.cfg = cfg
         h = C.c_void_p()
-        _lib.check(self.L.it_engine_create_synth_sharded(device, C.byref(cfg), seed, int(with_mtp), rank, world, C.byref(h)))
+        if _gguf is None:
+            _lib.check(self.L.it_engine_create_synth_sharded(device, C.byref(cfg), seed, int(with_mtp), rank, world, C.byref(h)))
+        else:
+            path, hp = _gguf
+            _lib.check(self.L.it_engine_create_gguf(device, path, hp, cfg.ctx_len, rank, world, C.byref(h)))
         self.h = h
         self.with_mtp = with_mtp
         self.rank, self.world = rank, world
         if world > 1:
             from .sharding import attach_peers
             attach_peers(self.L, self.L.it_engine_ctx(self.h), rank, world, group)
+
+    @classmethod
+    def from_gguf(cls, path, head_path=None, ctx_len=4096, device=0, rank=0, world=1, group=None):
+        """An engine with the weights of a qwen35 GGUF file (VkEngine::new_with_mtp over Model::load, src/vk/mod.rs:494,
+        src/cpu.rs:91).  head_path: None = no NextN head, "" = the block appended to the trunk file, else a sidecar."""
+        hp = None if head_path is None else str(head_path).encode()
+        cfg, has_mtp, _, _ = inspect_gguf(path, head_path, ctx_len)
+        return cls(cfg, 0, has_mtp, device, rank, world, group, _gguf=(str(path).encode(), hp))
 
     def sync(self):
         _lib.check(self.L.it_sync(self.L.it_engine_ctx(self.h)))

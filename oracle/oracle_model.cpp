@@ -49,6 +49,7 @@ enum Tensor {   // same numbering as IT_T_* in include/irontimber_cuda.h
     T_TOK_EMBD, T_OUTPUT_NORM, T_OUTPUT,
     T_MTP_EH, T_MTP_Q, T_MTP_K, T_MTP_V, T_MTP_O, T_MTP_GATE, T_MTP_UP, T_MTP_DOWN,
     T_MTP_ENORM, T_MTP_HNORM, T_MTP_ATTN_NORM, T_MTP_POST_NORM, T_MTP_Q_NORM, T_MTP_K_NORM, T_MTP_HEAD_NORM,
+    T_MTP_EMBD,   // the head's own embedding table; empty = the trunk's (MtpHead::embed, src/mtp.rs:101)
     T_COUNT
 };
 

@@ -240,7 +240,7 @@ TENSORS = ("attn_norm", "post_norm", "ffn_gate", "ffn_up", "ffn_down",
            "q", "k", "v", "o", "q_norm", "k_norm",
            "tok_embd", "output_norm", "output",
            "mtp_eh", "mtp_q", "mtp_k", "mtp_v", "mtp_o", "mtp_gate", "mtp_up", "mtp_down",
-           "mtp_enorm", "mtp_hnorm", "mtp_attn_norm", "mtp_post_norm", "mtp_q_norm", "mtp_k_norm", "mtp_head_norm")
+           "mtp_enorm", "mtp_hnorm", "mtp_attn_norm", "mtp_post_norm", "mtp_q_norm", "mtp_k_norm", "mtp_head_norm", "mtp_embd")
 TENSOR_ID = {n: i for i, n in enumerate(TENSORS)}
 
 
