@@ -110,6 +110,13 @@ void it_matrix_destroy(it_mat* m);
 int it_qmatrix_upload_q8_0(it_ctx* ctx, const uint8_t* raw, size_t rows, size_t cols, it_qmat** out);
 int it_qmatrix_synth(it_ctx* ctx, uint64_t seed, size_t rows, size_t cols, it_qmat** out);
 int it_qmatrix_download_q8_0(it_ctx* ctx, const it_qmat* m, uint8_t* raw);
+/* Q6_K rows (210-byte blocks of 256, cols a multiple of 256) as int8 values q - 32 with one f32 scale per 16 weights,
+ * scale = d * sub-block scale (exact in f32): Q8G16::from_ggml's Q6_K arm (src/quant.rs:245-257).  it_matvec_q8 runs both
+ * kinds with the same per-16 grouping (Q8G16::dot, src/quant.rs:266-270).  it_qmatrix_download_g16 reads any int8-group
+ * matrix back as rows*cols int8 values followed by rows*cols/16 f32 scales; it_qmatrix_group16 tells the kinds apart. */
+int it_qmatrix_upload_q6_k(it_ctx* ctx, const uint8_t* raw, size_t rows, size_t cols, it_qmat** out);
+int it_qmatrix_download_g16(it_ctx* ctx, const it_qmat* m, uint8_t* raw);
+int it_qmatrix_group16(const it_qmat* m);
 size_t it_qmatrix_rows(const it_qmat* m);
 size_t it_qmatrix_cols(const it_qmat* m);
 void it_qmatrix_destroy(it_qmat* m);
@@ -196,7 +203,7 @@ int it_engine_create_synth_sharded(int device, const it_model_config* cfg, uint6
  * it; a tied LM head (no output.weight).  head_path: NULL = no NextN head; "" or the same path = the NextN block
  * appended to the trunk file; another path = a head-only sidecar whose architecture / qwen35.* / tokenizer.* /
  * prism.hadamard.* metadata must equal the trunk's (validate_compatibility, src/mtp.rs:31-43).  The head's matrices
- * must be Q8_0 (a Q6_K head is refused with IT_EUNSUPPORTED), its norms F32, and it may carry its own embedding table
+ * must be Q8_0 or Q6_K (rows a multiple of 4, columns of 256, as src/mtp.rs:55), its norms F32, and it may carry its own embedding table
  * (nextn.embed_tokens).  rank / world as in it_engine_create_synth_sharded: a rank reads only its rows of every trunk
  * matrix.  Everything is checked before the device is touched: IT_EFORMAT for a file that cannot be read or is
  * malformed (short, bad magic, duplicate names, tensor outside the file, missing key or tensor, wrong shape),

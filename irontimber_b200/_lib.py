@@ -63,6 +63,9 @@ SIGNATURES = {
     "it_argmax_static": (C.c_int, [P, P, c_size, P]),
     "it_engine_create_synth": (C.c_int, [C.c_int, P, C.c_uint64, C.c_int, C.POINTER(P)]),
     "it_engine_create_synth_sharded": (C.c_int, [C.c_int, P, C.c_uint64, C.c_int, C.c_int, C.c_int, C.POINTER(P)]),
+    "it_qmatrix_upload_q6_k": (C.c_int, [P, P, c_size, c_size, C.POINTER(P)]),
+    "it_qmatrix_download_g16": (C.c_int, [P, P, P]),
+    "it_qmatrix_group16": (C.c_int, [P]),
     "it_engine_create_gguf": (C.c_int, [C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(P)]),
     "it_gguf_inspect": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, P, C.POINTER(C.c_int), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "it_gguf_dequant": (C.c_int, [C.c_uint32, P, c_size, P]),

@@ -63,11 +63,12 @@ k_argmax(const float* __restrict__ v, unsigned n, unsigned per_block, unsigned l
 // ---------------------------------------------------------------- int8-group matvec (f32 activations)
 // y[t, r] (+)= sum_g d[r, g/2] * (sum_{j<16} q[r,16g+j] * x[t,16g+j])   (src/quant.rs:266-270, shaders/matvec_q8.comp)
 // One warp per four rows: a lane takes 16 weights of each row per step (one 128-bit load per row) and
-// reuses its 16 activations for the four rows.  HBM-bound: rows*cols*(1 + 2/32) bytes of weights.
+// reuses its 16 activations for the four rows.  HBM-bound: rows*cols*(1 + 2/32) bytes of weights (Q8_0 source: one f16
+// scale per 32 weights) or rows*cols*(1 + 4/16) (G16, Q6_K source: one f32 scale per 16 weights).
 constexpr int QROWS = 4;
-template <int NT>
+template <int NT, bool G16>
 __global__ void __launch_bounds__(256)
-k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, int rows, int cols,
+k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, const float* __restrict__ ws, int rows, int cols,
             const float* x, size_t x_stride, float* arena, size_t y_off, size_t y_stride, int ntok, int accum,
             const it_peers* peers, int row_off, int* error_flag) {
     IT_PDL_TRIGGER(); IT_PDL_WAIT();
@@ -86,7 +87,7 @@ k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, int ro
             const int row = min(r0 + r, rows - 1);
             asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[r].x), "=r"(w[r].y), "=r"(w[r].z), "=r"(w[r].w)
                          : "l"(wq + (size_t)row * cols + 16 * g));
-            d[r] = __half2float(wd[(size_t)row * (cols / 32) + (g >> 1)]);
+            d[r] = G16 ? ws[(size_t)row * (cols / 16) + g] : __half2float(wd[(size_t)row * (cols / 32) + (g >> 1)]);
         }
 #pragma unroll
         for (int t = 0; t < NT; t++) {
@@ -161,9 +162,10 @@ IT_API int it_matvec_q8(it_ctx* c, const it_qmat* w, size_t ntok, size_t x_off, 
     for (size_t t0 = 0; t0 < ntok; t0 += 4) {
         const int nt = (int)((ntok - t0) < 4 ? (ntok - t0) : 4);
         const float* x = c->arena + x_off + t0 * x_stride; const size_t yo = y_off + t0 * y_stride;
-        if (nt == 1) it_pdl(k_matvec_q8<1>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, c->arena, yo, y_stride, nt, accum, peers, (int)w->row0, c->error_flag_dev);
-        else if (nt == 2) it_pdl(k_matvec_q8<2>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, c->arena, yo, y_stride, nt, accum, peers, (int)w->row0, c->error_flag_dev);
-        else it_pdl(k_matvec_q8<4>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, (int)w->rows, (int)w->cols, x, x_stride, c->arena, yo, y_stride, nt, accum, peers, (int)w->row0, c->error_flag_dev);
+#define IT_Q8_LAUNCH(NT, G) it_pdl(k_matvec_q8<NT, G>, dim3(grid), dim3(256), 0, c->stream, w->q, w->d, w->s16, (int)w->rows, (int)w->cols, x, x_stride, c->arena, yo, y_stride, nt, accum, peers, (int)w->row0, c->error_flag_dev)
+        if (w->s16) { if (nt == 1) IT_Q8_LAUNCH(1, true); else if (nt == 2) IT_Q8_LAUNCH(2, true); else IT_Q8_LAUNCH(4, true); }
+        else { if (nt == 1) IT_Q8_LAUNCH(1, false); else if (nt == 2) IT_Q8_LAUNCH(2, false); else IT_Q8_LAUNCH(4, false); }
+#undef IT_Q8_LAUNCH
         IT_LAUNCH_CHECK("matvec_q8");
     }
     return IT_OK;

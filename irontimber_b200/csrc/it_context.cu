@@ -417,7 +417,7 @@ static int qmat_alloc(it_ctx* c, size_t rows, size_t cols, it_qmat** out, const 
     *out = nullptr;
     IT_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "%s: bad shape %zux%zu (cols must be a multiple of 32)", who, rows, cols);
     IT_CUDA(cudaSetDevice(c->device));
-    it_qmat* m = new it_qmat(); m->ctx = c; m->rows = rows; m->cols = cols; m->q = nullptr; m->d = nullptr; m->sharded = false; m->row0 = 0; m->out_rows = rows;
+    it_qmat* m = new it_qmat(); m->ctx = c; m->rows = rows; m->cols = cols; m->q = nullptr; m->d = nullptr; m->s16 = nullptr; m->sharded = false; m->row0 = 0; m->out_rows = rows;
     m->bytes = rows * cols + rows * (cols / 32) * 2;
     cudaError_t e = cudaMalloc(&m->q, rows * cols);
     if (e == cudaSuccess) e = cudaMalloc(&m->d, rows * (cols / 32) * 2);
@@ -434,6 +434,55 @@ IT_API int it_qmatrix_upload_q8_0(it_ctx* c, const uint8_t* raw, size_t rows, si
     if (e == cudaSuccess) e = cudaMemcpyAsync((*out)->d, d.data(), d.size() * 2, cudaMemcpyHostToDevice, c->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     if (e != cudaSuccess) { it_qmatrix_destroy(*out); *out = nullptr; return it_fail(IT_ECUDA, "it_qmatrix_upload_q8_0: %s", cudaGetErrorString(e)); }
+    return IT_OK;
+}
+// Q6_K rows -> int8 values (q - 32) and one f32 scale per 16 weights, scale = d * sub-block scale, exact in f32
+// (Q8G16::from_ggml, src/quant.rs:245-257)
+IT_API int it_qmatrix_upload_q6_k(it_ctx* c, const uint8_t* raw, size_t rows, size_t cols, it_qmat** out) {
+    IT_CHECK_ARG(raw, "it_qmatrix_upload_q6_k: null data");
+    IT_CHECK_ARG(cols % 256 == 0, "it_qmatrix_upload_q6_k: cols %zu is not a multiple of the 256-element Q6_K block", cols);
+    int r = qmat_alloc(c, rows, cols, out, "it_qmatrix_upload_q6_k"); if (r) return r;
+    it_qmat* m = *out;
+    cudaFree(m->d); m->d = nullptr;
+    const size_t n = rows * cols, nblk = n / 256;
+    m->bytes = n + n / 16 * 4;
+    std::vector<int8_t> q(n); std::vector<float> sc(n / 16);
+    for (size_t i = 0; i < nblk; i++) {
+        const uint8_t* b = raw + i * 210;
+        unsigned short hb = (unsigned short)(b[208] | (b[209] << 8)); __half h; memcpy(&h, &hb, 2);
+        const float d = __half2float(h);
+        for (int g = 0; g < 16; g++) sc[i * 16 + g] = d * (float)(int8_t)b[192 + g];
+        for (int half = 0; half < 2; half++) {
+            const uint8_t* ql = b + half * 64; const uint8_t* qh = b + 128 + half * 32; int8_t* o = &q[i * 256 + half * 128];
+            for (int l = 0; l < 32; l++) {
+                o[l] = (int8_t)((int)((ql[l] & 0xF) | ((qh[l] & 3) << 4)) - 32);
+                o[l + 32] = (int8_t)((int)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32);
+                o[l + 64] = (int8_t)((int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32);
+                o[l + 96] = (int8_t)((int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32);
+            }
+        }
+    }
+    cudaError_t e = cudaMalloc(&m->s16, sc.size() * 4);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->q, q.data(), q.size(), cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->s16, sc.data(), sc.size() * 4, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { it_qmatrix_destroy(m); *out = nullptr; return it_fail(e == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_qmatrix_upload_q6_k: %s", cudaGetErrorString(e)); }
+    return IT_OK;
+}
+IT_API int it_qmatrix_group16(const it_qmat* m) { return m && m->s16 ? 1 : 0; }
+// int8 values [rows*cols], then the f32 scales [rows*cols/16] (for Q8_0 sources each block's scale twice)
+IT_API int it_qmatrix_download_g16(it_ctx* c, const it_qmat* m, uint8_t* raw) {
+    IT_CHECK_ARG(c && m && raw, "it_qmatrix_download_g16: null argument");
+    const size_t n = m->rows * m->cols;
+    IT_CUDA(cudaMemcpyAsync(raw, m->q, n, cudaMemcpyDeviceToHost, c->stream));
+    if (m->s16) IT_CUDA(cudaMemcpyAsync(raw + n, m->s16, n / 16 * 4, cudaMemcpyDeviceToHost, c->stream));
+    else {
+        std::vector<unsigned short> d(n / 32);
+        IT_CUDA(cudaMemcpyAsync(d.data(), m->d, d.size() * 2, cudaMemcpyDeviceToHost, c->stream));
+        IT_CUDA(cudaStreamSynchronize(c->stream));
+        for (size_t i = 0; i < n / 32; i++) { __half h; memcpy(&h, &d[i], 2); const float f = __half2float(h); memcpy(raw + n + 8 * i, &f, 4); memcpy(raw + n + 8 * i + 4, &f, 4); }
+    }
+    IT_CUDA(cudaStreamSynchronize(c->stream));
     return IT_OK;
 }
 IT_API int it_qmatrix_synth(it_ctx* c, uint64_t seed, size_t rows, size_t cols, it_qmat** out) {
@@ -461,6 +510,7 @@ IT_API int it_qmatrix_synth_rows(it_ctx* c, uint64_t seed, size_t total_rows, si
 }
 IT_API int it_qmatrix_download_q8_0(it_ctx* c, const it_qmat* m, uint8_t* raw) {
     IT_CHECK_ARG(c && m && raw, "it_qmatrix_download_q8_0: null argument");
+    IT_CHECK_ARG(m->d, "it_qmatrix_download_q8_0: the matrix holds 16-weight groups (use it_qmatrix_download_g16)");
     size_t nblk = m->rows * m->cols / 32;
     std::vector<int8_t> q(m->rows * m->cols); std::vector<unsigned short> d(nblk);
     IT_CUDA(cudaMemcpyAsync(q.data(), m->q, q.size(), cudaMemcpyDeviceToHost, c->stream));
@@ -471,7 +521,7 @@ IT_API int it_qmatrix_download_q8_0(it_ctx* c, const it_qmat* m, uint8_t* raw) {
 }
 IT_API size_t it_qmatrix_rows(const it_qmat* m) { return m ? m->rows : 0; }
 IT_API size_t it_qmatrix_cols(const it_qmat* m) { return m ? m->cols : 0; }
-IT_API void it_qmatrix_destroy(it_qmat* m) { if (!m) return; cudaSetDevice(m->ctx->device); if (m->q) cudaFree(m->q); if (m->d) cudaFree(m->d); delete m; }
+IT_API void it_qmatrix_destroy(it_qmat* m) { if (!m) return; cudaSetDevice(m->ctx->device); if (m->q) cudaFree(m->q); if (m->d) cudaFree(m->d); if (m->s16) cudaFree(m->s16); delete m; }
 
 // ---------------------------------------------------------------- q8 activation rows
 // Tensor map over the int8 rows for the tile kernel: boxes of 128 bytes (one 128-column block) x 64 rows, written to

@@ -308,7 +308,7 @@ IT_API int it_engine_tensor_bytes(it_engine* e, int layer, int tensor, size_t* n
     IT_CHECK_ARG(e && nbytes, "it_engine_tensor_bytes: null argument");
     const TensorRef r = find_tensor(e, layer, tensor);
     IT_CHECK_ARG(r.kind != 0, "it_engine_tensor_bytes: layer %d has no tensor %d", layer, tensor);
-    *nbytes = r.kind == 1 ? r.m->rows * (r.m->cols / 128) * 34 : r.kind == 2 ? r.q->rows * (r.q->cols / 32) * 34 : r.n * 4;
+    *nbytes = r.kind == 1 ? r.m->rows * (r.m->cols / 128) * 34 : r.kind == 2 ? (r.q->s16 ? r.q->rows * r.q->cols / 16 * 20 : r.q->rows * (r.q->cols / 32) * 34) : r.n * 4;
     return IT_OK;
 }
 IT_API int it_engine_tensor_read(it_engine* e, int layer, int tensor, void* host) {
@@ -316,7 +316,7 @@ IT_API int it_engine_tensor_read(it_engine* e, int layer, int tensor, void* host
     const TensorRef r = find_tensor(e, layer, tensor);
     IT_CHECK_ARG(r.kind != 0, "it_engine_tensor_read: layer %d has no tensor %d", layer, tensor);
     if (r.kind == 1) return it_matrix_download_pq2(e->ctx, r.m, (uint8_t*)host);
-    if (r.kind == 2) return it_qmatrix_download_q8_0(e->ctx, r.q, (uint8_t*)host);
+    if (r.kind == 2) return r.q->s16 ? it_qmatrix_download_g16(e->ctx, r.q, (uint8_t*)host) : it_qmatrix_download_q8_0(e->ctx, r.q, (uint8_t*)host);
     IT_CUDA(cudaMemcpyAsync(host, r.f, r.n * 4, cudaMemcpyDeviceToHost, e->ctx->stream));
     IT_CUDA(cudaStreamSynchronize(e->ctx->stream)); return IT_OK;
 }

@@ -169,8 +169,8 @@ int check_head(GgufModel& m) {
         { IT_T_MTP_O, q, e }, { IT_T_MTP_GATE, e, ff }, { IT_T_MTP_UP, e, ff }, { IT_T_MTP_DOWN, ff, e } };
     for (const auto& x : mats) {
         const it_gguf_tensor* t; IT_TRY(g.need(pre + head_tensor_name(x.t), &t)); IT_TRY(expect_dims(t, x.cols, x.rows));
-        if (t->type == GG_Q6_K) return it_fail(IT_EUNSUPPORTED, "gguf: NextN matrix %s is Q6_K; this library runs Q8_0 head matrices", t->name.c_str());
-        if (t->type != GG_Q8_0) return it_fail(IT_EUNSUPPORTED, "gguf: unsupported NextN matrix type %s for %s", it_gg_type_name(t->type), t->name.c_str());
+        if (t->type != GG_Q8_0 && t->type != GG_Q6_K) return it_fail(IT_EUNSUPPORTED, "gguf: unsupported NextN matrix type %s for %s (Q8_0 or Q6_K)", it_gg_type_name(t->type), t->name.c_str());
+        if (x.rows % 4 || x.cols % 256) return it_fail(IT_EUNSUPPORTED, "gguf: unsupported NextN matrix shape for %s", t->name.c_str());
     }
     const std::set<std::string> none;
     for (int t = IT_T_MTP_ENORM; t <= IT_T_MTP_K_NORM; t++) {
@@ -324,13 +324,15 @@ struct GgufSource : it_weight_source {
     int q8(it_engine* e, int tensor, size_t rows, size_t cols, it_qmat** out) override {
         const std::string name = name_of(-1, tensor);
         const it_gguf_tensor* t; IT_TRY(m->head->need(name, &t)); IT_TRY(expect_dims(t, cols, rows));
-        if (t->type != GG_Q8_0) return it_fail(IT_EUNSUPPORTED, "gguf: NextN matrix %s is not Q8_0", name.c_str());
         const uint8_t* raw = m->head->data(*t);
-        for (size_t i = 0; i < rows * cols / 32; i++) {   // the reference refuses non-finite scales (src/mtp.rs:93)
-            unsigned short b = (unsigned short)(raw[i * 34] | (raw[i * 34 + 1] << 8));
+        const bool k6 = t->type == GG_Q6_K;
+        if (!k6 && t->type != GG_Q8_0) return it_fail(IT_EUNSUPPORTED, "gguf: NextN matrix %s is neither Q8_0 nor Q6_K", name.c_str());
+        const size_t nblk = rows * cols / (k6 ? 256 : 32), stride = k6 ? 210 : 34, at = k6 ? 208 : 0;
+        for (size_t i = 0; i < nblk; i++) {               // the reference refuses non-finite scales (src/mtp.rs:93)
+            const unsigned short b = (unsigned short)(raw[i * stride + at] | (raw[i * stride + at + 1] << 8));
             if ((b & 0x7c00) == 0x7c00) return it_fail(IT_EFORMAT, "gguf: non-finite scale in NextN matrix %s", name.c_str());
         }
-        return it_qmatrix_upload_q8_0(e->ctx, raw, rows, cols, out);
+        return k6 ? it_qmatrix_upload_q6_k(e->ctx, raw, rows, cols, out) : it_qmatrix_upload_q8_0(e->ctx, raw, rows, cols, out);
     }
     int mtp_embd(it_engine* e, float** dev) override {
         const it_gguf_tensor* t = m->head->tensor("blk." + std::to_string(m->head_il) + ".nextn.embed_tokens.weight");

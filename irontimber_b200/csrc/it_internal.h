@@ -79,7 +79,8 @@ struct it_qmat {
     it_ctx* ctx;
     size_t rows, cols;
     int8_t* q;
-    __half* d;
+    __half* d;                             // one f16 scale per 32 weights (Q8_0 source), or null
+    float* s16;                            // one f32 scale per 16 weights (Q6_K source: d * sub-block scale), or null
     size_t bytes;
     bool sharded; size_t row0, out_rows;   // rows [row0, row0 + rows) of a logical matrix of out_rows rows (see it_mat)
 };

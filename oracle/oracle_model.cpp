@@ -139,13 +139,18 @@ void dense_matvec(const float* w, int rows, int cols, const float* x, float* y, 
 // acc = fma(t, scale, acc); the 32 lane sums are folded with a butterfly (offsets 16 .. 1).
 void mvq(const Blob& w, int rows, int cols, const float* x, float* y, int mode) {
     const uint8_t* raw = w.bytes.data(); int bpr = cols / 32;
+    // a blob of rows*cols int8 values followed by rows*cols/16 f32 scales is the 16-weight-group form (Q6_K source,
+    // Q8G16::from_ggml, src/quant.rs:245-257); anything else is raw Q8_0 blocks
+    const bool g16 = w.bytes.size() == (size_t)rows * cols / 16 * 20;
+    const float* s16 = reinterpret_cast<const float*>(raw + (size_t)rows * cols);
     for (int r = 0; r < rows; r++) {
         const uint8_t* rowb = raw + (size_t)r * bpr * 34;
-        auto scale = [&](int g) { const uint8_t* b = rowb + (g / 2) * 34; uint16_t hb = (uint16_t)(b[0] | (b[1] << 8)); uint32_t sign = (hb & 0x8000u) << 16, e = (hb >> 10) & 31, mm = hb & 0x3ff, bits;
+        auto scale8 = [&](int g) { const uint8_t* b = rowb + (g / 2) * 34; uint16_t hb = (uint16_t)(b[0] | (b[1] << 8)); uint32_t sign = (hb & 0x8000u) << 16, e = (hb >> 10) & 31, mm = hb & 0x3ff, bits;
             if (e == 0) { if (!mm) bits = sign; else { int k = -1; do { mm <<= 1; k++; } while (!(mm & 0x400)); bits = sign | ((uint32_t)(127 - 15 - k) << 23) | ((mm & 0x3ff) << 13); } }
             else if (e == 31) bits = sign | 0x7f800000u | (mm << 13); else bits = sign | ((e + 112) << 23) | (mm << 13);
             float f; std::memcpy(&f, &bits, 4); return f; };
-        auto q = [&](int j) { return (float)(int8_t)rowb[(j / 32) * 34 + 2 + (j % 32)]; };
+        auto scale = [&](int g) { return g16 ? s16[(size_t)r * (cols / 16) + g] : scale8(g); };
+        auto q = [&](int j) { return g16 ? (float)(int8_t)raw[(size_t)r * cols + j] : (float)(int8_t)rowb[(j / 32) * 34 + 2 + (j % 32)]; };
         if (!mode) { float s = 0.f; for (int g = 0; g < cols / 16; g++) { float t = 0.f; for (int j = 0; j < 16; j++) t += q(g * 16 + j) * x[g * 16 + j]; s += t * scale(g); } y[r] = s; continue; }
         float p[32];
         for (int l = 0; l < 32; l++) { float acc = 0.f; for (int g = l; g < cols / 16; g += 32) { float t = 0.f; for (int j = 0; j < 16; j++) t = it_fma(q(g * 16 + j), x[g * 16 + j], t); acc = it_fma(t, scale(g), acc); } p[l] = acc; }

@@ -103,6 +103,32 @@ def random_q8_0(rng, rows, cols, dlo=0.002, dhi=0.006):
     return raw.reshape(-1)
 
 
+def random_q6_k(rng, rows, cols):
+    """Random well-formed Q6_K blocks: 128 low nibbles, 64 bytes of high bit pairs, 16 int8 sub-block scales, f16 d."""
+    nb = rows * cols // 256
+    raw = rng.integers(0, 256, (nb, 210), dtype=np.uint8)
+    raw[:, 192:208] = rng.integers(-40, 41, (nb, 16)).astype(np.int8).view(np.uint8)
+    raw[:, 208:210] = rng.uniform(1e-4, 3e-4, nb).astype(np.float16).reshape(nb, 1).view(np.uint8)
+    return raw.reshape(-1)
+
+
+def q6_k_to_g16(raw):
+    """Q6_K blocks -> (int8 values q - 32, one f32 scale per 16 weights = d * sub-block scale), the int8-group form of
+    Q8G16::from_ggml (src/quant.rs:245-257), as one byte string: values, then scales."""
+    b = np.ascontiguousarray(raw, np.uint8).reshape(-1, 210)
+    nb = b.shape[0]
+    d = b[:, 208:210].copy().view(np.float16).astype(np.float32)                       # [nb, 1]
+    scales = d * b[:, 192:208].view(np.int8).astype(np.float32)                        # [nb, 16]
+    q = np.zeros((nb, 2, 4, 32), np.int32)
+    for h in range(2):
+        ql, qh = b[:, h * 64:h * 64 + 64].astype(np.int32), b[:, 128 + h * 32:160 + h * 32].astype(np.int32)
+        q[:, h, 0] = ((ql[:, :32] & 0xF) | ((qh & 3) << 4)) - 32
+        q[:, h, 1] = ((ql[:, 32:] & 0xF) | (((qh >> 2) & 3) << 4)) - 32
+        q[:, h, 2] = ((ql[:, :32] >> 4) | (((qh >> 4) & 3) << 4)) - 32
+        q[:, h, 3] = ((ql[:, 32:] >> 4) | (((qh >> 6) & 3) << 4)) - 32
+    return q.astype(np.int8).reshape(-1).view(np.uint8).tobytes() + scales.astype(np.float32).reshape(-1).tobytes()
+
+
 def to_bf16(x):
     """f32 -> bf16 bytes, round to nearest even; returns (bytes, the f32 values they decode to)."""
     u = np.ascontiguousarray(x, np.float32).view(np.uint32)
@@ -138,11 +164,12 @@ def config_kvs(cfg, n_blocks, nextn):
             ("tokenizer.ggml.token_type", ARR, [1] * 7, I32)]
 
 
-def build_model(rng, cfg, shapes, dequant, hadamard_inverse, head="same", head_embd=True, explicit_signs=True, tied=False):
+def build_model(rng, cfg, shapes, dequant, hadamard_inverse, head="same", head_embd=True, explicit_signs=True, tied=False, head_type="q8_0"):
     """Random weights for `cfg` in a mix of the accepted storage types.
 
     shapes: tests.util.tensor_shapes(cfg); dequant(ggml_type, bytes, n) -> f32 and hadamard_inverse(row, signs) supply
-    the arithmetic for the tensors whose expected values are decoded ones.  head: "same", "sidecar" or None.
+    the arithmetic for the tensors whose expected values are decoded ones.  head: "same", "sidecar" or None;
+    head_type: "q8_0", "q6_k" or "mixed" (alternating) storage of the head's matrices.
     Returns (trunk_kvs, trunk_tensors, head_kvs, head_tensors, expect) where expect maps (name, layer) -> what the oracle
     is given (raw PQ2_0 / Q8_0 bytes or f32 arrays) and expect["signs"] maps width -> sign vector.
     """
@@ -210,8 +237,14 @@ def build_model(rng, cfg, shapes, dequant, hadamard_inverse, head="same", head_e
             kind, r, c = shapes[n]
             g = "blk.%d.%s" % (il, gname)
             if kind == "q8":
-                expect[(n, -1)] = random_q8_0(rng, r, c)
-                head_tensors.append((g, [c, r], Q8_0, expect[(n, -1)]))
+                flip[0] ^= 1
+                if head_type == "q6_k" or (head_type == "mixed" and flip[0]):
+                    raw = random_q6_k(rng, r, c)
+                    expect[(n, -1)] = np.frombuffer(q6_k_to_g16(raw), np.uint8)
+                    head_tensors.append((g, [c, r], Q6_K, raw))
+                else:
+                    expect[(n, -1)] = random_q8_0(rng, r, c)
+                    head_tensors.append((g, [c, r], Q8_0, expect[(n, -1)]))
             else:
                 vector(g, (n, -1), r * c, n, into=head_tensors)
         if head_embd:

@@ -49,6 +49,17 @@ def test_decoders_match_ggml_vectors_bit_exact(name, ty):
     assert np.array_equal(bits(dequant(ty, raw, want.size)), bits(want))
 
 
+def test_q6_k_int8_group_form_decodes_to_ggml_values():
+    """The writer's restatement of Q8G16::from_ggml's Q6_K arm: scale * q equals ggml's decode bit for bit
+    (tests/dequant_vs_ggml.rs:29-32)."""
+    raw = np.fromfile(os.path.join(DATA, "mtp_q6k3.raw"), np.uint8)
+    want = np.fromfile(os.path.join(DATA, "mtp_q6k3.f32"), np.float32)
+    g = np.frombuffer(W.q6_k_to_g16(raw), np.uint8)
+    q = g[:want.size].view(np.int8).astype(np.float32)
+    sc = g[want.size:].view(np.float32)
+    assert np.array_equal(bits(np.repeat(sc, 16) * q), bits(want))
+
+
 @pytest.mark.parametrize("name", ["attn_k3", "ssm_out4"])
 def test_ptq1_recoded_as_pq2_decodes_to_the_same_values(name):
     raw = np.fromfile(os.path.join(DATA, name + ".ptq1.raw"), np.uint8)
@@ -196,10 +207,14 @@ def test_models_outside_the_supported_set_are_refused(tmp_path, model_parts):
     bad = [(n, [d[0], d[1] - 32] if n == "blk.0.ffn_gate.weight" else d, ty, (raw[:-32 * (d[0] // 128) * (34 if ty == W.PQ2_0 else 28)] if n == "blk.0.ffn_gate.weight" else raw))
            for n, d, ty, raw in tensors]
     assert code(ts=bad)[0] == EFORMAT                                                                                    # wrong shape
-    q6 = [(n, d, W.Q6_K if n == "blk.%d.ffn_up.weight" % il else ty, (np.zeros(d[0] * d[1] // 256 * 210, np.uint8) if n == "blk.%d.ffn_up.weight" % il else raw))
-          for n, d, ty, raw in tensors]
-    c, msg = code(ts=q6)
-    assert c == EUNSUPPORTED and "Q6_K" in msg
+    f16 = [(n, d, W.F16 if n == "blk.%d.ffn_up.weight" % il else ty, (np.zeros(d[0] * d[1], np.float16).view(np.uint8) if n == "blk.%d.ffn_up.weight" % il else raw))
+           for n, d, ty, raw in tensors]
+    c, msg = code(ts=f16)
+    assert c == EUNSUPPORTED and "F16" in msg                                                                            # a dense head matrix
+    inf = np.zeros(cfg.n_embd * cfg.n_ff // 256 * 210, np.uint8).reshape(-1, 210)
+    inf[3, 208:210] = np.array([np.inf], np.float16).view(np.uint8)
+    q6 = [(n, d, W.Q6_K if n == "blk.%d.ffn_up.weight" % il else ty, (inf.reshape(-1) if n == "blk.%d.ffn_up.weight" % il else raw)) for n, d, ty, raw in tensors]
+    _inspect(_write(tmp_path, "q6.gguf", kvs, q6), "")                   # a Q6_K head matrix is accepted; its scales are checked at load
     own = tensors + [("blk.%d.nextn.shared_head_head.weight" % il, [32], W.F32, np.zeros(32, np.float32).view(np.uint8))]
     assert code(ts=own)[0] == EUNSUPPORTED
     dense = [(n, d, W.F16 if n == "blk.3.attn_k.weight" else ty, (np.zeros(d[0] * d[1], np.float16).view(np.uint8) if n == "blk.3.attn_k.weight" else raw))
@@ -271,12 +286,13 @@ def _check_engine(orc, eng, cfg, expect, with_mtp):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("head,head_embd,explicit,tied", [("same", True, True, False), ("sidecar", False, False, False), (None, False, True, True)])
-def test_engine_from_file_matches_oracle_bit_exact(tmp_path, orc, head, head_embd, explicit, tied):
+@pytest.mark.parametrize("head,head_embd,explicit,tied,head_type", [("same", True, True, False, "q8_0"), ("sidecar", False, False, False, "mixed"),
+                                                                    ("same", True, True, False, "q6_k"), (None, False, True, True, "q8_0")])
+def test_engine_from_file_matches_oracle_bit_exact(tmp_path, orc, head, head_embd, explicit, tied, head_type):
     from irontimber_b200.engine import CudaEngine, ModelConfig
     cfg = tiny_config(ModelConfig)
     tk, tt, hk, ht, expect = W.build_model(np.random.default_rng(17), cfg, tensor_shapes(cfg), dequant, lambda z, s: orc.hadamard_inverse(z, 1024, s),
-                                           head=head, head_embd=head_embd, explicit_signs=explicit, tied=tied)
+                                           head=head, head_embd=head_embd, explicit_signs=explicit, tied=tied, head_type=head_type)
     trunk = _write(tmp_path, "trunk.gguf", tk, tt)
     hp = None if head is None else "" if head == "same" else str(_write(tmp_path, "head.gguf", hk, ht))
     eng = CudaEngine.from_gguf(trunk, hp, ctx_len=64)
