@@ -2,6 +2,7 @@
 // it_engine_run.cu (forward passes, MTP hooks, generation loops).
 #pragma once
 #include "it_internal.h"
+#include <map>
 #include <vector>
 
 #define IT_MAXT 64    // activation rows per pass: the prompt chunk of prefill_chunks (src/vk/mod.rs:130-134)
@@ -55,7 +56,16 @@ struct it_engine {
     int last_rows;                                   // rows of the last verification pass (it_engine_mtp_rollback)
     it_graph* step_graph;                            // recorded single-token greedy step
     uint32_t* host_pin;                              // pinned staging, laid out like toks_dev, plus the position at [2*IT_MAXT]
+    // Recorded passes of up to IT_SMALL_ROWS rows (single tokens, verification rows, draft steps of the head), one graph
+    // per shape; their token ids and positions are staged through a ring of pinned slots so that a slot is never
+    // rewritten while an earlier copy out of it may still be pending.
+    std::map<uint64_t, it_graph*> pass_graphs;
+    uint32_t* small_pin;                             // IT_SMALL_SLOTS slots of 16 words: [0, 8) token ids, [8] position
+    int small_next;
+    bool record_passes;                              // environment IT_PASS_GRAPHS (default on)
 };
+#define IT_SMALL_ROWS 8
+#define IT_SMALL_SLOTS 64
 
 // Where an engine under construction gets its weights.  The engine owns allocation, row sharding and the device
 // layouts; a source only fills what it is handed.  Every method returns an IT_* code.

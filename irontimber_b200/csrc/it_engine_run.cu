@@ -111,13 +111,15 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
 
 namespace {
 
+int trunk_pass(it_engine* e, const uint32_t* toks, int nt, int logit_rows, int nck);
+
 // prefill_chunks (src/vk/mod.rs:130-134) with a chunk of IT_MAXT rows; the greedy pick of the last token lands in amx[0]
 int eval_tokens(it_engine* e, const uint32_t* toks, size_t n, bool want_last) {
     IT_CHECK_ARG(e && (toks || n == 0), "engine: null argument");
     if (e->pos + (long long)n > e->cfg.ctx_len) return it_fail(IT_ESTATE, "engine: context full (%d + %zu > %d)", e->pos, n, e->cfg.ctx_len);
     for (size_t s = 0; s < n; s += IT_MAXT) {
         const int nt = (int)std::min<size_t>(IT_MAXT, n - s); const bool last = s + nt == n;
-        IT_TRY(it_engine_run_chunk(e, toks + s, nt, (want_last && last) ? 1 : 0, 0, false));
+        IT_TRY(trunk_pass(e, toks + s, nt, (want_last && last) ? 1 : 0, 0));
     }
     return IT_OK;
 }
@@ -125,12 +127,17 @@ int read_pick(it_engine* e, size_t slot, uint32_t* out) { return it_arena_read(e
 
 // One MTP head pass over nt rows at positions pos0.. paired with the h rows at arena offset hoff (mtp_pass_mode,
 // src/vk/mod.rs:912-959; arithmetic of cpu_step, src/mtp.rs:100-137).  predict = false only extends the head's KV cache.
-int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, bool predict) {
+// from_dev: the token ids are already in toks_dev[IT_MAXT..] and the first position is read from pos_dev[1] (recorded pass).
+int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, bool predict, bool from_dev = false) {
     it_ctx* cx = e->ctx; const it_model_config& c = e->cfg; const it_arena_layout& L = e->lay; float* A = cx->arena;
     const int e_ = c.n_embd, ff = c.n_ff, hd = c.head_dim, nh = c.n_head, nkv = c.n_head_kv, kvd = nkv * hd, qf = 2 * nh * hd;
     IT_CHECK_ARG(nt >= 1 && nt <= IT_MAXT && pos0 >= 1 && pos0 + nt <= c.ctx_len, "engine: bad MTP pass geometry");
-    for (int t = 0; t < nt; t++) e->host_pin[IT_MAXT + t] = toks[t];
-    IT_CUDA(cudaMemcpyAsync(e->toks_dev + IT_MAXT, e->host_pin + IT_MAXT, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+    const int* pos_ptr = from_dev ? e->pos_dev + 1 : nullptr;
+    if (from_dev) pos0 = 0;                                   // the kernels add the device-resident position
+    else {
+        for (int t = 0; t < nt; t++) e->host_pin[IT_MAXT + t] = toks[t];
+        IT_CUDA(cudaMemcpyAsync(e->toks_dev + IT_MAXT, e->host_pin + IT_MAXT, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+    }
     IT_TRY(it_sup_embed(cx, e->toks_dev + IT_MAXT, e->m_tok_embd, e_, nt, A + L.me));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + L.me, e_, e->m_enorm, e_, c.eps, A + L.mcat, 2 * e_, nt));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + hoff, e_, e->m_hnorm, e_, c.eps, A + L.mcat + e_, 2 * e_, nt));
@@ -142,11 +149,11 @@ int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, 
     IT_TRY(it_matvec_q8(cx, e->m_v, nt, L.xn, e_, L.vcur, kvd, 0));
     if (predict) IT_TRY(it_sup_norm_head(cx, A + L.big1, 2 * hd, qf, A + L.big1, 2 * hd, qf, hd, nh, e->m_q_norm, 0, c.eps, nullptr, 0, 0, nt));
     IT_TRY(it_sup_norm_head(cx, A + L.kcur, hd, kvd, A + L.kcur, hd, kvd, hd, nkv, e->m_k_norm, 0, c.eps, nullptr, 0, 0, nt));
-    if (predict) IT_TRY(it_sup_rope(cx, A + L.big1, 2 * hd, qf, nh, nt, pos0, nullptr, c.n_rot, e->theta_scale, c.rope_sections));
-    IT_TRY(it_sup_rope(cx, A + L.kcur, hd, kvd, nkv, nt, pos0, nullptr, c.n_rot, e->theta_scale, c.rope_sections));
-    IT_TRY(it_sup_kv_store(cx, A + L.kcur, A + L.vcur, kvd, e->mkc, e->mvc, kvd, hd, slot0, nullptr, nt, 0));
+    if (predict) IT_TRY(it_sup_rope(cx, A + L.big1, 2 * hd, qf, nh, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
+    IT_TRY(it_sup_rope(cx, A + L.kcur, hd, kvd, nkv, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
+    IT_TRY(it_sup_kv_store(cx, A + L.kcur, A + L.vcur, kvd, e->mkc, e->mvc, kvd, hd, slot0, pos_ptr, nt, 0));
     if (!predict) return IT_OK;
-    IT_TRY(it_sup_attention(cx, A + L.big1, 2 * hd, qf, A + L.big1 + hd, e->mkc, e->mvc, kvd, hd, nh, nkv, slot0, nullptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 0));
+    IT_TRY(it_sup_attention(cx, A + L.big1, 2 * hd, qf, A + L.big1 + hd, e->mkc, e->mvc, kvd, hd, nh, nkv, slot0, pos_ptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 0));
     IT_TRY(it_matvec_q8(cx, e->m_o, nt, L.o, (size_t)nh * hd, L.mx, e_, 1));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + L.mx, e_, e->m_post_norm, e_, c.eps, A + L.xn, e_, nt));
     IT_TRY(it_matvec_q8(cx, e->m_gate, nt, L.xn, e_, L.big1, ff, 0));
@@ -155,6 +162,72 @@ int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, 
     IT_TRY(it_matvec_q8(cx, e->m_down, nt, L.big1, ff, L.mx, e_, 1));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + L.mx + (size_t)(nt - 1) * e_, e_, e->m_head_norm, e_, c.eps, A + L.xn, e_, 1));
     return logits_and_argmax(e, L.xn, 1);
+}
+
+// ---- recorded passes ------------------------------------------------------------------------------------------
+// A pass of a few rows is several hundred short launches, more host time than device time when they are issued one by
+// one.  Each shape (rows, logit rows, checkpoints; for the head: rows, hidden-row offset, predict) is recorded once with
+// the token ids and the position read from device memory, and replayed after one small copy of ids and position.
+uint32_t* stage_slot(it_engine* e) {
+    if (e->small_next == IT_SMALL_SLOTS) { cudaStreamSynchronize(e->ctx->stream); e->small_next = 0; }   // every copy out of the ring has run
+    return e->small_pin + 16 * (size_t)(e->small_next++);
+}
+template <typename F> int replay_pass(it_engine* e, uint64_t key, F&& record) {
+    it_ctx* cx = e->ctx;
+    auto it = e->pass_graphs.find(key);
+    if (it == e->pass_graphs.end()) {
+        IT_TRY(it_capture_begin(cx));
+        const int r = record();
+        it_graph* g = nullptr; const int r2 = it_capture_end(cx, &g);
+        if (r || r2) { if (g) it_graph_destroy(g); return r ? r : r2; }
+        it = e->pass_graphs.emplace(key, g).first;
+    }
+    return it_graph_launch(cx, it->second);
+}
+bool can_record(const it_engine* e, int nt) { return e->record_passes && nt <= IT_SMALL_ROWS && !e->ctx->capturing; }
+
+int trunk_pass(it_engine* e, const uint32_t* toks, int nt, int logit_rows, int nck) {
+    if (!can_record(e, nt)) return it_engine_run_chunk(e, toks, nt, logit_rows, nck, false);
+    const it_model_config& c = e->cfg; it_ctx* cx = e->ctx;
+    if (e->pos + nt > c.ctx_len) return it_fail(IT_ESTATE, "engine: context full (%d + %d > %d)", e->pos, nt, c.ctx_len);
+    for (int t = 0; t < nt; t++) if (toks[t] >= (uint32_t)c.n_vocab) return it_fail(IT_EINVAL, "engine: token id %u outside the vocabulary", toks[t]);
+    uint32_t* slot = stage_slot(e);
+    for (int t = 0; t < nt; t++) slot[t] = toks[t];
+    slot[8] = (uint32_t)e->pos;
+    IT_CUDA(cudaMemcpyAsync(e->toks_dev, slot, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+    IT_CUDA(cudaMemcpyAsync(e->pos_dev, slot + 8, sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+    IT_TRY(replay_pass(e, 1ull << 60 | (uint64_t)nt | (uint64_t)logit_rows << 8 | (uint64_t)nck << 16,
+                       [&]() { return it_engine_run_chunk(e, nullptr, nt, logit_rows, nck, true); }));
+    e->pos += nt;
+    return IT_OK;
+}
+int head_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, bool predict) {
+    if (!can_record(e, nt)) return mtp_pass(e, toks, nt, pos0, hoff, predict);
+    const it_model_config& c = e->cfg; it_ctx* cx = e->ctx;
+    IT_CHECK_ARG(pos0 >= 1 && pos0 + nt <= c.ctx_len, "engine: bad MTP pass geometry");
+    uint32_t* slot = stage_slot(e);
+    for (int t = 0; t < nt; t++) slot[t] = toks[t];
+    slot[8] = (uint32_t)pos0;
+    IT_CUDA(cudaMemcpyAsync(e->toks_dev + IT_MAXT, slot, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+    IT_CUDA(cudaMemcpyAsync(e->pos_dev + 1, slot + 8, sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+    return replay_pass(e, 2ull << 60 | (uint64_t)nt | (uint64_t)(predict ? 1 : 0) << 8 | (uint64_t)hoff << 16,
+                       [&]() { return mtp_pass(e, nullptr, nt, 1, hoff, predict, true); });
+}
+
+// Recurrent state of every delta-net layer back to checkpoint `ck` (the state after row ck of the last pass): two
+// device-to-device copies per layer, recorded once per checkpoint index and replayed as one graph.
+int restore_checkpoint(it_engine* e, int ck) {
+    const it_model_config& c = e->cfg; it_ctx* cx = e->ctx; it_note_op(cx);
+    const size_t csz = (size_t)(c.conv_k - 1) * it_cfg_conv_dim(c), ssz = (size_t)c.ssm_vheads * c.ssm_state * c.ssm_state;
+    auto copies = [&]() {
+        for (it_layer& l : e->layers) if (l.recurrent) {
+            IT_CUDA(cudaMemcpyAsync(l.conv_st, l.ck_conv + (size_t)ck * csz, csz * 4, cudaMemcpyDeviceToDevice, cx->stream));
+            IT_CUDA(cudaMemcpyAsync(l.ssm_st, l.ck_ssm + (size_t)ck * ssz, ssz * 4, cudaMemcpyDeviceToDevice, cx->stream));
+        }
+        return (int)IT_OK;
+    };
+    if (!e->record_passes || cx->capturing) return copies();
+    return replay_pass(e, 3ull << 60 | (uint64_t)ck, copies);
 }
 
 int copy_rows(it_engine* e, size_t src, size_t dst, size_t n) {
@@ -254,13 +327,13 @@ IT_API int it_engine_mtp_prefill(it_engine* e, const uint32_t* prompt, size_t n,
     const it_arena_layout& L = e->lay; const size_t e_ = e->cfg.n_embd;
     for (size_t s = 0; s < n; s += IT_MAXT) {
         const int nt = (int)std::min<size_t>(IT_MAXT, n - s); const bool last = s + nt == n;
-        IT_TRY(it_engine_run_chunk(e, prompt + s, nt, last ? 1 : 0, 0, false));
+        IT_TRY(trunk_pass(e, prompt + s, nt, last ? 1 : 0, 0));
         // MTP catch-up over the pairs (h_{q-1}, x_q), q in [s, s+nt), q >= 1 (src/vk/mod.rs:989-1003)
         if (s > 0) IT_TRY(copy_rows(e, L.hprev, L.mh, e_));
         if (nt > 1) IT_TRY(copy_rows(e, L.hrow, L.mh + e_, (size_t)(nt - 1) * e_));
         IT_TRY(copy_rows(e, L.hrow + (size_t)(nt - 1) * e_, L.hprev, e_));
-        if (s == 0) { if (nt > 1) IT_TRY(mtp_pass(e, prompt + 1, nt - 1, 1, L.mh + e_, false)); }
-        else IT_TRY(mtp_pass(e, prompt + s, nt, (int)s, L.mh, false));
+        if (s == 0) { if (nt > 1) IT_TRY(head_pass(e, prompt + 1, nt - 1, 1, L.mh + e_, false)); }
+        else IT_TRY(head_pass(e, prompt + s, nt, (int)s, L.mh, false));
     }
     e->mpos = (int)n; e->hp_off = L.hprev; e->hp_n = 1;
     return read_pick(e, 0, next);
@@ -269,7 +342,7 @@ IT_API int it_engine_mtp_single(it_engine* e, uint32_t x, uint32_t* next) { IT_N
 IT_API int it_engine_mtp_draft(it_engine* e, const uint32_t* toks, size_t n, uint32_t* draft) {
     IT_NEED_MTP(e, "it_engine_mtp_draft");
     IT_CHECK_ARG(toks && draft && (int)n == e->hp_n && n >= 1, "it_engine_mtp_draft: token count must equal the pending hidden rows");   // src/vk/mod.rs:1008
-    IT_TRY(mtp_pass(e, toks, (int)n, e->mpos, e->hp_off, true));
+    IT_TRY(head_pass(e, toks, (int)n, e->mpos, e->hp_off, true));
     e->mpos += (int)n;
     return read_pick(e, 0, draft);
 }
@@ -277,7 +350,7 @@ IT_API int it_engine_mtp_verify(it_engine* e, uint32_t x, uint32_t d, uint32_t* 
     IT_NEED_MTP(e, "it_engine_mtp_verify");
     IT_CHECK_ARG(a0 && a1, "it_engine_mtp_verify: null output");
     const uint32_t toks[2] = { x, d };
-    IT_TRY(it_engine_run_chunk(e, toks, 2, 2, 1, false));      // both rows' picks, state checkpointed after x
+    IT_TRY(trunk_pass(e, toks, 2, 2, 1));                       // both rows' picks, state checkpointed after x
     e->hp_off = e->lay.hrow; e->hp_n = 2;
     uint32_t picks[2]; IT_TRY(it_arena_read(e->ctx, e->lay.amx, picks, 2));
     *a0 = picks[0]; *a1 = picks[1]; return IT_OK;
@@ -285,12 +358,7 @@ IT_API int it_engine_mtp_verify(it_engine* e, uint32_t x, uint32_t d, uint32_t* 
 IT_API int it_engine_mtp_reject(it_engine* e) {   // src/vk/mod.rs:1018-1025
     IT_NEED_MTP(e, "it_engine_mtp_reject");
     if (e->pos < 1) return it_fail(IT_ESTATE, "it_engine_mtp_reject: nothing to roll back");
-    const it_model_config& c = e->cfg; cudaStream_t st = e->ctx->stream; it_note_op(e->ctx);
-    const size_t csz = (size_t)(c.conv_k - 1) * it_cfg_conv_dim(c) * 4, ssz = (size_t)c.ssm_vheads * c.ssm_state * c.ssm_state * 4;
-    for (it_layer& l : e->layers) if (l.recurrent) {
-        IT_CUDA(cudaMemcpyAsync(l.conv_st, l.ck_conv, csz, cudaMemcpyDeviceToDevice, st));
-        IT_CUDA(cudaMemcpyAsync(l.ssm_st, l.ck_ssm, ssz, cudaMemcpyDeviceToDevice, st));
-    }
+    IT_TRY(restore_checkpoint(e, 0));
     e->pos -= 1; e->hp_off = e->lay.hrow; e->hp_n = 1;
     return IT_OK;
 }
@@ -301,12 +369,12 @@ IT_API int it_engine_mtp_draft_k(it_engine* e, const uint32_t* toks, size_t n, s
     IT_CHECK_ARG(toks && drafts && (int)n == e->hp_n && n >= 1 && k >= 1 && k <= IT_MAXCK, "it_engine_mtp_draft_k: bad token count or draft length");
     if (e->mpos + (int)n + (int)k - 1 > e->cfg.ctx_len) return it_fail(IT_ESTATE, "it_engine_mtp_draft_k: context full");
     const size_t e_ = e->cfg.n_embd;
-    IT_TRY(mtp_pass(e, toks, (int)n, e->mpos, e->hp_off, true));
+    IT_TRY(head_pass(e, toks, (int)n, e->mpos, e->hp_off, true));
     e->mpos += (int)n;
     IT_TRY(read_pick(e, 0, &drafts[0]));
     size_t hid = e->lay.mx + (n - 1) * e_;                  // the head's hidden state before head_norm, last row of the pass
     for (size_t i = 1; i < k; i++) {                        // chained steps: provisional KV entries at positions mpos, mpos + 1, ..
-        IT_TRY(mtp_pass(e, &drafts[i - 1], 1, e->mpos + (int)i - 1, hid, true));
+        IT_TRY(head_pass(e, &drafts[i - 1], 1, e->mpos + (int)i - 1, hid, true));
         IT_TRY(read_pick(e, 0, &drafts[i]));
         hid = e->lay.mx;
     }
@@ -317,7 +385,7 @@ IT_API int it_engine_mtp_verify_k(it_engine* e, uint32_t x, const uint32_t* draf
     IT_CHECK_ARG(drafts && picks && k >= 1 && k <= IT_MAXCK, "it_engine_mtp_verify_k: bad argument");
     uint32_t toks[IT_MAXCK + 1]; toks[0] = x;
     for (size_t i = 0; i < k; i++) toks[i + 1] = drafts[i];
-    IT_TRY(it_engine_run_chunk(e, toks, (int)k + 1, 2, (int)k, false));      // a pick per row, state checkpointed after rows 0 .. k - 1
+    IT_TRY(trunk_pass(e, toks, (int)k + 1, 2, (int)k));                      // a pick per row, state checkpointed after rows 0 .. k - 1
     e->hp_off = e->lay.hrow; e->hp_n = (int)k + 1; e->last_rows = (int)k + 1;
     return it_arena_read(e->ctx, e->lay.amx, picks, k + 1);
 }
@@ -326,12 +394,7 @@ IT_API int it_engine_mtp_rollback(it_engine* e, size_t keep_rows) {
     IT_CHECK_ARG(e->last_rows >= 2 && keep_rows >= 1 && (int)keep_rows <= e->last_rows, "it_engine_mtp_rollback: no verification pass to roll back, or bad row count");
     const int drop = e->last_rows - (int)keep_rows;
     if (drop > 0) {
-        const it_model_config& c = e->cfg; cudaStream_t st = e->ctx->stream; it_note_op(e->ctx);
-        const size_t csz = (size_t)(c.conv_k - 1) * it_cfg_conv_dim(c), ssz = (size_t)c.ssm_vheads * c.ssm_state * c.ssm_state;
-        for (it_layer& l : e->layers) if (l.recurrent) {      // checkpoint t holds the state after row t
-            IT_CUDA(cudaMemcpyAsync(l.conv_st, l.ck_conv + (keep_rows - 1) * csz, csz * 4, cudaMemcpyDeviceToDevice, st));
-            IT_CUDA(cudaMemcpyAsync(l.ssm_st, l.ck_ssm + (keep_rows - 1) * ssz, ssz * 4, cudaMemcpyDeviceToDevice, st));
-        }
+        IT_TRY(restore_checkpoint(e, (int)keep_rows - 1));      // checkpoint t holds the state after row t
         e->pos -= drop;
     }
     e->hp_off = e->lay.hrow; e->hp_n = (int)keep_rows; e->last_rows = 0;
