@@ -108,10 +108,6 @@ struct it_ctx {
     unsigned int* argmax_counter;
     int sm_count;
     bool capturing;
-    // matvec split-K scratch: one slot of per-block terms per CTA of the persistent grid, plus arrival
-    // counters; fixed at creation so that recorded graphs keep valid pointers
-    float* splitk_terms;
-    unsigned int* splitk_counters;
     // raised by a kernel whose bounded wait ran out; lives in mapped host memory so that reading it
     // costs nothing on the normal path
     int* error_flag_host;
@@ -133,7 +129,6 @@ struct it_ctx {
 static inline void it_note_op(it_ctx* c) { c->pdl_safe_q8 = nullptr; }
 
 // bytes of split-K terms per slot: enough for 8 activation rows of width 17408 (8 * 136 blocks * 32 rows * 4)
-#define IT_SPLITK_SLOT_BYTES (8 * 136 * 32 * 4)
 int it_check_device_error(it_ctx* ctx, const char* who);
 
 #define IT_ARGMAX_MAX_BLOCKS 1024

@@ -41,10 +41,10 @@ constexpr int SM_SMEM = 227 * 1024;               // shared memory one SM can gi
 struct Smem {   // byte offsets into dynamic shared memory
     int ring, x, dx, s128, terms, bars, flag, total, plane, xrow;
 };
-__host__ __device__ inline Smem smem_layout(int MT, int nb, int slots, int nbuf) {
+__host__ __device__ inline Smem smem_layout(int MT, int nb, int slots, int nbuf, int cw = CWARPS) {
     Smem L; int o = 0;
     L.plane = nb * 32 + TERM_PAD; L.xrow = nb * 128 + XROW_PAD;
-    L.ring = o; o += slots * CHUNK_BYTES;
+    L.ring = o; o += slots * cw * IT_TILE_BYTES;
     L.x = o; o += MT * L.xrow;
     L.dx = o; o += MT * (nb / 2) * 4;
     L.s128 = o; o += MT * nb * 4;
@@ -62,32 +62,32 @@ __host__ __device__ inline Smem smem_layout(int MT, int nb, int slots, int nbuf)
 // has a single row group, else 2).
 // ONESHOT: the grid has one CTA per row group and the ring holds a whole row group: thread 0 issues every
 // copy at once, there is no producer warp and no slot is ever refilled.
-template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI>
-__global__ void __launch_bounds__((NG * CWARPS + (ONESHOT ? 0 : 1)) * 32, MINB)
+template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI, int CW = CWARPS>
+__global__ void __launch_bounds__((NG * CW + (ONESHOT ? 0 : 1)) * 32, MINB)
 k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int slots, int nbuf,
             const int8_t* __restrict__ xq, const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
             float* arena, size_t y_off, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag, int wait_early,
             const it_peers* peers, const it_rowmap map, int ll_mode, int out_rows) {
-    constexpr int NCONS = NG * CWARPS;
+    constexpr int NCONS = NG * CW, CHUNK = CW * IT_TILE_BYTES;   // consumer warps; bytes of one ring slot (CW tiles)
     extern __shared__ __align__(128) unsigned char smem[];
-    const Smem L = smem_layout(MT, nb, slots, nbuf);
+    const Smem L = smem_layout(MT, nb, slots, nbuf, CW);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.flag);
     const unsigned bars = smem_u32(smem + L.bars);             // full[s] at bars + 8*s, empty[s] at bars + 8*(slots + s)
-    const int cpr = (nb + CWARPS - 1) / CWARPS;                 // chunks per row group
+    const int cpr = (nb + CW - 1) / CW;                 // chunks per row group
     const int my_rgs = row_groups > (int)blockIdx.x ? (row_groups - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < slots; s++) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (slots + s), CWARPS); }
+        for (int s = 0; s < slots; s++) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (slots + s), CW); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (ONESHOT) {
             // the weights do not depend on the kernel before this one: request them all right away
             const uint8_t* src = tiles + ((size_t)blockIdx.x * nb) * IT_TILE_BYTES;
             for (int cq = 0; cq < cpr; cq++) {
-                const unsigned bytes = (unsigned)min(CWARPS, nb - cq * CWARPS) * IT_TILE_BYTES;
+                const unsigned bytes = (unsigned)min(CW, nb - cq * CW) * IT_TILE_BYTES;
                 mbar_expect_tx(bars + 8 * cq, bytes);
-                bulk_load(smem_u32(smem + L.ring + cq * CHUNK_BYTES), src + (size_t)cq * CHUNK_BYTES, bytes, bars + 8 * cq);
+                bulk_load(smem_u32(smem + L.ring + cq * CHUNK), src + (size_t)cq * CHUNK, bytes, bars + 8 * cq);
             }
         }
     }
@@ -100,10 +100,10 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 const uint8_t* src = tiles + ((size_t)((int)blockIdx.x + i * (int)gridDim.x) * nb) * IT_TILE_BYTES;
                 for (int cq = 0; cq < cpr; cq++) {
                     if (!mbar_wait(bars + 8 * (slots + s), ph ^ 1u, abort_flag, error_flag)) break;
-                    const int ntile = min(CWARPS, nb - cq * CWARPS);
+                    const int ntile = min(CW, nb - cq * CW);
                     const unsigned bytes = (unsigned)ntile * IT_TILE_BYTES;
                     mbar_expect_tx(bars + 8 * s, bytes);
-                    bulk_load(smem_u32(smem + L.ring + s * CHUNK_BYTES), src + (size_t)cq * CHUNK_BYTES, bytes, bars + 8 * s);
+                    bulk_load(smem_u32(smem + L.ring + s * CHUNK), src + (size_t)cq * CHUNK, bytes, bars + 8 * s);
                     issued++;
                     if (++s == slots) { s = 0; ph ^= 1u; }
                 }
@@ -150,7 +150,7 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
     const bool x_lane = g < ntok && g < MT;          // this lane feeds column g of the B operand
     const int c0 = 2 * t, c1 = 2 * t + 1;            // token columns this lane receives from the mma
     const bool v0 = c0 < MT && c0 < ntok, v1 = c1 < MT && c1 < ntok;
-    const int group = warp / CWARPS, wi = warp % CWARPS;   // consumer group and tile index inside a chunk
+    const int group = warp / CW, wi = warp % CW;   // consumer group and tile index inside a chunk
 
     int s = 0; unsigned ph = 0; int kg = 0;           // ring slot, its phase, and (chunk index) % NG
     for (int i = 0; i < my_rgs; i++) {
@@ -162,10 +162,10 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
             if (++s == slots) { s = 0; ph ^= 1u; }
             if (NG > 1 && ++kg == NG) kg = 0;
             if (!mine) continue;
+            const int b = cq * CW + wi;
             const bool ready = mbar_wait(bars + 8 * cs, cph, abort_flag, error_flag);
-            const int b = cq * CWARPS + wi;
             if (ready && b < nb) {
-                const unsigned char* tile = smem + L.ring + cs * CHUNK_BYTES + wi * IT_TILE_BYTES;
+                const unsigned char* tile = smem + L.ring + cs * CHUNK + wi * IT_TILE_BYTES;
                 const uint4 wa = *reinterpret_cast<const uint4*>(tile + 16 * lane);
                 const uint4 wb = *reinterpret_cast<const uint4*>(tile + 512 + 16 * lane);
                 const uint2 sc = *reinterpret_cast<const uint2*>(tile + 1024 + 8 * g);
@@ -245,16 +245,16 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
     }
 }
 
-template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI>
+template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI, int CW = CWARPS>
 int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi,
                int slots, int nbuf, int grid) {
     const int nb = (int)(w->cols / 128);
-    const Smem L = smem_layout(MT, nb, slots, nbuf);
-    auto kern = k_matvec_t2<MT, NG, MINB, ONESHOT, SUMI>;
+    const Smem L = smem_layout(MT, nb, slots, nbuf, CW);
+    auto kern = k_matvec_t2<MT, NG, MINB, ONESHOT, SUMI, CW>;
     static bool attr_set[16] = {};
     if (!attr_set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM - 1024)); attr_set[c->device & 15] = true; }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((NG * CWARPS + (ONESHOT ? 0 : 1)) * 32); cfg.dynamicSmemBytes = (size_t)L.total; cfg.stream = c->stream;
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((NG * CW + (ONESHOT ? 0 : 1)) * 32); cfg.dynamicSmemBytes = (size_t)L.total; cfg.stream = c->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
@@ -271,9 +271,9 @@ int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow
 }
 
 // Largest ring (up to `want` chunks) that fits `per_cta` bytes of shared memory; 0 if not even `need` fit.
-int ring_slots(int MT, int nb, int nbuf, int per_cta, int want, int need) {
+int ring_slots(int MT, int nb, int nbuf, int per_cta, int want, int need, int cw = CWARPS) {
     int slots = want;
-    while (slots >= need && smem_layout(MT, nb, slots, nbuf).total > per_cta) slots--;
+    while (slots >= need && smem_layout(MT, nb, slots, nbuf, cw).total > per_cta) slots--;
     return slots >= need ? slots : 0;
 }
 
@@ -287,6 +287,19 @@ template <int MT, bool SUMI>
 int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi) {
     const int nb = (int)(w->cols / 128), cpr = (nb + CWARPS - 1) / CWARPS, rgs = (int)w->row_groups;
     const bool long_rows = nb > 64;
+    // Short rows, one to four activation rows, enough row groups for two CTAs per SM: CTAs of four consumer warps and a
+    // small ring, up to eight per SM.  Two consecutive launches then fit an SM side by side, so the CTAs of the next
+    // matvec are resident and filling their rings while this one drains, and its first chunks are in shared memory
+    // when its turn comes (17408 x 5120 in a back-to-back sweep: 5.98 us with the eight-warp CTAs below).
+    static const bool small_ctas = !getenv("IT_MV_CW4") || atoi(getenv("IT_MV_CW4")) != 0;
+    if (small_ctas && !SUMI && MT <= 4 && !long_rows && rgs >= 2 * c->sm_count) {
+        constexpr int CW = 4, PER_SM = 8;
+        const int grid = rgs < PER_SM * c->sm_count ? rgs : PER_SM * c->sm_count;
+        const int nbuf = grid == rgs ? 1 : 2;
+        const int cpr4 = (nb + CW - 1) / CW;
+        const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / PER_SM - 1024, 4, cpr4 < 2 ? cpr4 : 2, CW);
+        if (slots) return launch_cfg<MT, 1, PER_SM, false, false, CW>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+    }
     for (int per_sm = long_rows ? 3 : 4; per_sm >= 1; per_sm--) {
         const int grid = rgs < per_sm * c->sm_count ? rgs : per_sm * c->sm_count;
         const int nbuf = SUMI ? 0 : (grid == rgs ? 1 : 2);

@@ -1,6 +1,7 @@
 """Host-side mirror of the reference's backend traits over the C ABI.
 
-`CudaEngine` offers the methods of `Engine` (src/engine.rs:8-15: eval, eval_argmax, reset) and of `MtpBackend`
+`CudaEngine` offers the methods of `Engine` (src/engine.rs:8-15: eval, eval_argmax, reset), of `ServeEngine`
+(src/engine.rs:69-78: as_engine, mtp_backend) and of `MtpBackend`
 (src/mtp.rs:150-163: mtp_prefill, mtp_single, mtp_draft, mtp_verify, mtp_reject, reset_all) with the reference's
 names and argument meaning, plus the two generation loops (`generate`, `generate_mtp`; src/engine.rs:151-191).
 Everything runs in libirontimber_cuda.so; this file only marshals arguments.
@@ -115,6 +116,14 @@ class CudaEngine:
 
     def reset(self):
         _lib.check(self.L.it_engine_reset(self.h))
+
+    # ---- ServeEngine (src/engine.rs:69-78): what a long-lived server holds -------------------------
+    def as_engine(self):
+        return self
+
+    def mtp_backend(self):
+        """The speculative path when a NextN head was loaded at start-up, else None (VkEngine's impl, src/engine.rs:75-78)."""
+        return self if self.with_mtp else None
 
     @property
     def pos(self):

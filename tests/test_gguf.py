@@ -298,6 +298,7 @@ def test_engine_from_file_matches_oracle_bit_exact(tmp_path, orc, head, head_emb
     eng = CudaEngine.from_gguf(trunk, hp, ctx_len=64)
     try:
         assert eng.with_mtp == (head is not None)
+        assert eng.as_engine() is eng and (eng.mtp_backend() is eng) == (head is not None)      # ServeEngine, src/engine.rs:69-78
         _check_engine(orc, eng, eng.cfg, expect, head is not None)
     finally:
         eng.close()

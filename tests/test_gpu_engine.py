@@ -169,3 +169,29 @@ def test_bad_geometry_fails_before_device_work():
     cfg = tiny_config(ModelConfig); cfg.n_embd = 1000
     h = C.c_void_p()
     assert _lib.load().it_engine_create_synth(0, C.byref(cfg), 1, 0, C.byref(h)) == -1
+
+
+def test_recorded_and_direct_small_passes_agree(orc, monkeypatch):
+    """Passes of up to eight rows replay a recorded graph by default; IT_PASS_GRAPHS=0 issues the same launches one by
+    one.  Logits, picks, speculative histories and counters must not depend on the choice."""
+    from irontimber_b200.engine import CudaEngine, ModelConfig
+    results = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("IT_PASS_GRAPHS", flag)
+        eng = CudaEngine(tiny_config(ModelConfig), seed=31, with_mtp=True)
+        try:
+            lg = eng.eval(PROMPT[:3])                       # one recorded 3-row pass / three direct rows
+            lg2 = eng.eval([PROMPT[3]])
+            eng.reset()
+            out1, st1 = eng.generate_mtp(PROMPT, 14)
+            out3, st3 = eng.generate_mtp_k(PROMPT, 14, 3)
+            eng.reset()
+            with pytest.raises(Exception):
+                eng.eval([eng.cfg.n_vocab])                 # out-of-vocabulary id: refused before any device work
+            assert eng.pos == 0
+            results.append((bits(lg).copy(), bits(lg2).copy(), out1, st1, out3, st3))
+        finally:
+            eng.close()
+    a, b = results
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    assert a[2:] == b[2:]
