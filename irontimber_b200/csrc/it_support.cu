@@ -338,20 +338,48 @@ __global__ void __launch_bounds__(256) k_conv_l2_dense(const float* mixed, size_
 }
 
 // Gated delta rule (src/cpu.rs:215-232) and the gated per-head norm that follows it (:233-237) in one launch: one CTA
-// per head, one thread per state row; after each token the head's outputs are normed (squares added by one thread in
-// index order), weighted and multiplied by silu(z).  State layout [head][j][i] as on the CPU.  nt <= 8.
+// per head.  Warps 0..SD/32-1 own one state row per thread and walk the tokens; an extra warp norms the outputs of row t
+// (squares added by one lane in index order), weights them and multiplies by silu(z) while the row owners are already
+// on row t + 1 (the outputs are double-buffered).  State layout [head][j][i] as on the CPU.
 // The head's SD x SD state sits in shared memory for the whole launch, rows unpadded, the 16-byte pieces of row j
 // stored at piece index ^ (j & 7): both the coalesced 16-byte moves of the tile and the 16-byte accesses of the row
 // owners are then free of bank conflicts.
 template <int SD>
-__global__ void __launch_bounds__(SD) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
-                                                 float* state, float* o, size_t o_ts, int nk, int qk, int nt, float* ck, size_t ck_stride, int nck,
-                                                 const float* __restrict__ nw, float eps, const float* z, size_t z_ts) {
+__global__ void __launch_bounds__(SD + 32) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
+                                                      float* state, float* o, size_t o_ts, int nk, int qk, int nt, float* ck, size_t ck_stride, int nck,
+                                                      const float* __restrict__ nw, float eps, const float* z, size_t z_ts) {
     IT_PDL_TRIGGER(); IT_PDL_WAIT();
-    extern __shared__ __align__(16) float tile[];      // [SD][SD] swizzled rows, then q[SD], k[SD], o[SD], 1 scale
+    extern __shared__ __align__(16) float tile[];      // [SD][SD] swizzled rows, then q[SD], k[SD], o[2][SD]
     constexpr int PPR = SD / 4;                         // 16-byte pieces per row
     const int h = blockIdx.x, tid = threadIdx.x, kh = h % nk;
-    float* qs = tile + SD * SD; float* ks = qs + SD; float* os = ks + SD; float* scp = os + SD;
+    float* qs = tile + SD * SD; float* ks = qs + SD; float* os = ks + SD;
+    // named barriers: 1 = the row owners among themselves, 2 + (t & 1) = "outputs of row t are in os[t & 1]" (owners + norm warp)
+    auto owners_sync = [] { asm volatile("bar.sync 1, %0;" :: "n"(SD) : "memory"); };
+    auto row_done = [](int t) { asm volatile("bar.sync %0, %1;" :: "r"(2 + (t & 1)), "n"(SD + 32) : "memory"); };
+    if (tid >= SD) {
+        // ---- norm warp: row t's outputs -> o, one row behind the owners
+        const int lane = tid - SD;
+        float zr[SD / 32], wr[SD / 32];
+#pragma unroll
+        for (int i = 0; i < SD / 32; i++) wr[i] = nw[lane + 32 * i];
+        for (int t = 0; t < nt; t++) {
+#pragma unroll
+            for (int i = 0; i < SD / 32; i++) zr[i] = z[t * z_ts + h * SD + lane + 32 * i];      // in flight while the owners compute
+            row_done(t);
+            const float* ob = os + (t & 1) * SD;
+            float sc = 0.f;
+            if (lane == 0) {
+                float s = 0.f;
+#pragma unroll 8
+                for (int i = 0; i < SD; i++) s = it_add(s, it_mul(ob[i], ob[i]));
+                sc = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)SD), eps)));
+            }
+            sc = __shfl_sync(0xffffffffu, sc, 0);
+#pragma unroll
+            for (int i = 0; i < SD / 32; i++) o[t * o_ts + h * SD + lane + 32 * i] = it_mul(it_mul(it_mul(ob[lane + 32 * i], sc), wr[i]), it_silu(zr[i]));
+        }
+        return;
+    }
     float* m = state + (size_t)h * SD * SD;
     auto piece = [&](int j, int c) { return reinterpret_cast<float4*>(tile + j * SD + ((c ^ (j & 7)) << 2)); };
     auto tile_in = [&](const float* src) {   // asynchronous 16-byte copies: the whole 64 KB is in flight at once
@@ -364,49 +392,48 @@ __global__ void __launch_bounds__(SD) k_gdn_norm(const float* co, size_t co_ts, 
 #pragma unroll 8
         for (int f = tid; f < SD * PPR; f += SD) reinterpret_cast<float4*>(dst)[f] = *piece(f / PPR, f % PPR);
     };
+    // The inputs of row t + 1 are requested while row t is computed, so that a row never waits for L2.
+    float qn, kn, vn, bn, an;
+    auto fetch = [&](int t) {
+        const float* c = co + t * co_ts;
+        qn = c[kh * SD + tid]; kn = c[qk + kh * SD + tid]; vn = c[2 * qk + h * SD + tid];
+        bn = beta[t * ba_ts + h]; an = alpha[t * ba_ts + h];
+    };
+    fetch(0);
     tile_in(m);
     const float scale = it_div(1.0f, it_sqrt((float)SD));
     for (int t = 0; t < nt; t++) {
-        const float* c = co + t * co_ts;
-        __syncthreads();
-        qs[tid] = c[kh * SD + tid]; ks[tid] = c[qk + kh * SD + tid];
-        __syncthreads();
-        {
-            const float v = c[2 * qk + h * SD + tid];
-            const float bt = it_sigmoid(beta[t * ba_ts + h]);
-            const float g = it_mul(it_softplus(it_add(alpha[t * ba_ts + h], dt[h])), a[h]);
-            const float eg = it_expf(g);
-            float s = 0.f;
+        owners_sync();                                  // the reads of q and k of row t - 1 are over (and, at t = 0, the tile is in)
+        qs[tid] = qn; ks[tid] = kn;
+        const float v = vn;
+        const float bt = it_sigmoid(bn);
+        const float g = it_mul(it_softplus(it_add(an, dt[h])), a[h]);
+        if (t + 1 < nt) fetch(t + 1);
+        owners_sync();
+        const float eg = it_expf(g);
+        float s = 0.f;
 #pragma unroll 4
-            for (int cc = 0; cc < PPR; cc++) {
-                float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc);
-                r.x = it_mul(r.x, eg); r.y = it_mul(r.y, eg); r.z = it_mul(r.z, eg); r.w = it_mul(r.w, eg);
-                *rp = r;
-                s = it_add(s, it_mul(r.x, k4.x)); s = it_add(s, it_mul(r.y, k4.y)); s = it_add(s, it_mul(r.z, k4.z)); s = it_add(s, it_mul(r.w, k4.w));
-            }
-            const float delta = it_mul(it_sub(v, s), bt);
-            float acc = 0.f;
+        for (int cc = 0; cc < PPR; cc++) {
+            float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc);
+            r.x = it_mul(r.x, eg); r.y = it_mul(r.y, eg); r.z = it_mul(r.z, eg); r.w = it_mul(r.w, eg);
+            *rp = r;
+            s = it_add(s, it_mul(r.x, k4.x)); s = it_add(s, it_mul(r.y, k4.y)); s = it_add(s, it_mul(r.z, k4.z)); s = it_add(s, it_mul(r.w, k4.w));
+        }
+        const float delta = it_mul(it_sub(v, s), bt);
+        float acc = 0.f;
 #pragma unroll 4
-            for (int cc = 0; cc < PPR; cc++) {
-                float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc), q4 = *reinterpret_cast<const float4*>(qs + 4 * cc);
-                r.x = it_add(r.x, it_mul(k4.x, delta)); r.y = it_add(r.y, it_mul(k4.y, delta)); r.z = it_add(r.z, it_mul(k4.z, delta)); r.w = it_add(r.w, it_mul(k4.w, delta));
-                *rp = r;
-                acc = it_add(acc, it_mul(r.x, q4.x)); acc = it_add(acc, it_mul(r.y, q4.y)); acc = it_add(acc, it_mul(r.z, q4.z)); acc = it_add(acc, it_mul(r.w, q4.w));
-            }
-            os[tid] = it_mul(acc, scale);
+        for (int cc = 0; cc < PPR; cc++) {
+            float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc), q4 = *reinterpret_cast<const float4*>(qs + 4 * cc);
+            r.x = it_add(r.x, it_mul(k4.x, delta)); r.y = it_add(r.y, it_mul(k4.y, delta)); r.z = it_add(r.z, it_mul(k4.z, delta)); r.w = it_add(r.w, it_mul(k4.w, delta));
+            *rp = r;
+            acc = it_add(acc, it_mul(r.x, q4.x)); acc = it_add(acc, it_mul(r.y, q4.y)); acc = it_add(acc, it_mul(r.z, q4.z)); acc = it_add(acc, it_mul(r.w, q4.w));
         }
-        __syncthreads();
-        if (tid == 0) {
-            float s = 0.f;
-#pragma unroll 8
-            for (int i = 0; i < SD; i++) s = it_add(s, it_mul(os[i], os[i]));
-            *scp = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)SD), eps)));
-        }
-        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * SD * SD);
-        __syncthreads();
-        o[t * o_ts + h * SD + tid] = it_mul(it_mul(it_mul(os[tid], *scp), nw[tid]), it_silu(z[t * z_ts + h * SD + tid]));
+        // os[t & 1] was last read by the norm warp for row t - 2, which it finished before it joined row_done(t - 1)
+        os[(t & 1) * SD + tid] = it_mul(acc, scale);
+        row_done(t);
+        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * SD * SD);     // every owner's row is final after the barrier
     }
-    __syncthreads();
+    owners_sync();
     tile_out(m);
 }
 
@@ -606,8 +633,8 @@ int it_sup_gdn_norm(it_ctx* c, const float* co, size_t co_ts, const float* beta,
                     int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck, const float* nw, float eps, const float* z, size_t z_ts) {
     if (sd != 128) return it_fail(IT_EINVAL, "gdn_norm: the fused kernel is built for a state size of 128");
     it_note_op(c);
-    const size_t smem = ((size_t)sd * sd + 3 * sd + 4) * sizeof(float);
+    const size_t smem = ((size_t)sd * sd + 4 * sd) * sizeof(float);
     static bool set = false; if (!set) { cudaFuncSetAttribute(k_gdn_norm<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
-    it_pdl(k_gdn_norm<128>, dim3(dim3(nv)), dim3(128), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
+    it_pdl(k_gdn_norm<128>, dim3(dim3(nv)), dim3(128 + 32), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
     KCHK("gdn_norm"); return IT_OK;
 }
