@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(256) k_conv_l2_dense(const float* mixed, size_
 // stored at piece index ^ (j & 7): both the coalesced 16-byte moves of the tile and the 16-byte accesses of the row
 // owners are then free of bank conflicts.
 template <int SD>
-__global__ void __launch_bounds__(SD + 32) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
+__global__ void __launch_bounds__(SD + 32, 1) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
                                                       float* state, float* o, size_t o_ts, int nk, int qk, int nt, float* ck, size_t ck_stride, int nck,
                                                       const float* __restrict__ nw, float eps, const float* z, size_t z_ts) {
     IT_PDL_TRIGGER(); IT_PDL_WAIT();
@@ -355,7 +355,9 @@ __global__ void __launch_bounds__(SD + 32) k_gdn_norm(const float* co, size_t co
     float* qs = tile + SD * SD; float* ks = qs + SD; float* os = ks + SD;
     // named barriers: 1 = the row owners among themselves, 2 + (t & 1) = "outputs of row t are in os[t & 1]" (owners + norm warp)
     auto owners_sync = [] { asm volatile("bar.sync 1, %0;" :: "n"(SD) : "memory"); };
-    auto row_done = [](int t) { asm volatile("bar.sync %0, %1;" :: "r"(2 + (t & 1)), "n"(SD + 32) : "memory"); };
+    auto row_done = [](int t) {
+        if (t & 1) asm volatile("bar.sync 3, %0;" :: "n"(SD + 32) : "memory"); else asm volatile("bar.sync 2, %0;" :: "n"(SD + 32) : "memory");
+    };
     if (tid >= SD) {
         // ---- norm warp: row t's outputs -> o, one row behind the owners
         const int lane = tid - SD;
@@ -401,9 +403,15 @@ __global__ void __launch_bounds__(SD + 32) k_gdn_norm(const float* co, size_t co
     };
     fetch(0);
     tile_in(m);
+    owners_sync();
+    // Each owner keeps its state row in registers for the whole launch (the loops below are fully unrolled); the shared
+    // tile only stages the coalesced moves from and to global memory.
+    float st[SD];
+#pragma unroll
+    for (int cc = 0; cc < PPR; cc++) { const float4 r = *piece(tid, cc); st[4 * cc] = r.x; st[4 * cc + 1] = r.y; st[4 * cc + 2] = r.z; st[4 * cc + 3] = r.w; }
     const float scale = it_div(1.0f, it_sqrt((float)SD));
     for (int t = 0; t < nt; t++) {
-        owners_sync();                                  // the reads of q and k of row t - 1 are over (and, at t = 0, the tile is in)
+        owners_sync();                                  // the reads of q and k of row t - 1 (and of a checkpoint tile) are over
         qs[tid] = qn; ks[tid] = kn;
         const float v = vn;
         const float bt = it_sigmoid(bn);
@@ -412,27 +420,32 @@ __global__ void __launch_bounds__(SD + 32) k_gdn_norm(const float* co, size_t co
         owners_sync();
         const float eg = it_expf(g);
         float s = 0.f;
-#pragma unroll 4
+#pragma unroll
         for (int cc = 0; cc < PPR; cc++) {
-            float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc);
-            r.x = it_mul(r.x, eg); r.y = it_mul(r.y, eg); r.z = it_mul(r.z, eg); r.w = it_mul(r.w, eg);
-            *rp = r;
-            s = it_add(s, it_mul(r.x, k4.x)); s = it_add(s, it_mul(r.y, k4.y)); s = it_add(s, it_mul(r.z, k4.z)); s = it_add(s, it_mul(r.w, k4.w));
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc);
+            st[4 * cc] = it_mul(st[4 * cc], eg); st[4 * cc + 1] = it_mul(st[4 * cc + 1], eg); st[4 * cc + 2] = it_mul(st[4 * cc + 2], eg); st[4 * cc + 3] = it_mul(st[4 * cc + 3], eg);
+            s = it_add(s, it_mul(st[4 * cc], k4.x)); s = it_add(s, it_mul(st[4 * cc + 1], k4.y)); s = it_add(s, it_mul(st[4 * cc + 2], k4.z)); s = it_add(s, it_mul(st[4 * cc + 3], k4.w));
         }
         const float delta = it_mul(it_sub(v, s), bt);
         float acc = 0.f;
-#pragma unroll 4
+#pragma unroll
         for (int cc = 0; cc < PPR; cc++) {
-            float4* rp = piece(tid, cc); float4 r = *rp; const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc), q4 = *reinterpret_cast<const float4*>(qs + 4 * cc);
-            r.x = it_add(r.x, it_mul(k4.x, delta)); r.y = it_add(r.y, it_mul(k4.y, delta)); r.z = it_add(r.z, it_mul(k4.z, delta)); r.w = it_add(r.w, it_mul(k4.w, delta));
-            *rp = r;
-            acc = it_add(acc, it_mul(r.x, q4.x)); acc = it_add(acc, it_mul(r.y, q4.y)); acc = it_add(acc, it_mul(r.z, q4.z)); acc = it_add(acc, it_mul(r.w, q4.w));
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc), q4 = *reinterpret_cast<const float4*>(qs + 4 * cc);
+            st[4 * cc] = it_add(st[4 * cc], it_mul(k4.x, delta)); st[4 * cc + 1] = it_add(st[4 * cc + 1], it_mul(k4.y, delta));
+            st[4 * cc + 2] = it_add(st[4 * cc + 2], it_mul(k4.z, delta)); st[4 * cc + 3] = it_add(st[4 * cc + 3], it_mul(k4.w, delta));
+            acc = it_add(acc, it_mul(st[4 * cc], q4.x)); acc = it_add(acc, it_mul(st[4 * cc + 1], q4.y)); acc = it_add(acc, it_mul(st[4 * cc + 2], q4.z)); acc = it_add(acc, it_mul(st[4 * cc + 3], q4.w));
         }
         // os[t & 1] was last read by the norm warp for row t - 2, which it finished before it joined row_done(t - 1)
         os[(t & 1) * SD + tid] = it_mul(acc, scale);
+        if (t < nck) {                                  // checkpoint: the state after row t, through the tile
+#pragma unroll
+            for (int cc = 0; cc < PPR; cc++) *piece(tid, cc) = make_float4(st[4 * cc], st[4 * cc + 1], st[4 * cc + 2], st[4 * cc + 3]);
+        }
         row_done(t);
-        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * SD * SD);     // every owner's row is final after the barrier
+        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * SD * SD);
     }
+#pragma unroll
+    for (int cc = 0; cc < PPR; cc++) *piece(tid, cc) = make_float4(st[4 * cc], st[4 * cc + 1], st[4 * cc + 2], st[4 * cc + 3]);
     owners_sync();
     tile_out(m);
 }
