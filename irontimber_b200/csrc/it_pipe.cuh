@@ -18,18 +18,28 @@ __device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: the warp may sleep up to `ns` nanoseconds inside the instruction and wakes when the
+// phase completes, so a long wait costs a few instructions instead of a spin loop's thousands of issue slots.
+__device__ __forceinline__ bool mbar_test_hint(unsigned bar, unsigned parity, unsigned ns) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 // Non-blocking probe of a phase.
 __device__ __forceinline__ bool mbar_poll(unsigned bar, unsigned parity) {
     unsigned ok;
     asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+#ifndef IT_MBAR_SLEEP_NS
+#define IT_MBAR_SLEEP_NS 20000u
+#endif
 // Bounded wait: gives up after WAIT_CLOCKS, or as soon as another thread of the CTA has given up.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag, int site = 1) {
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        for (int i = 0; i < 64; i++) if (mbar_test(bar, parity)) return true;
+        for (int i = 0; i < 8; i++) if (mbar_test_hint(bar, parity, IT_MBAR_SLEEP_NS)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_CLOCKS) { if (!*abort_flag) atomicExch(error_flag, site); *abort_flag = 1; return false; }
     }
