@@ -50,7 +50,7 @@ __host__ __device__ inline Smem smem_layout(int MT, int nb, int slots, int nbuf,
     L.s128 = o; o += MT * nb * 4;
     L.terms = o; o += nbuf * MT * L.plane * 4;
     o = (o + 15) & ~15;
-    L.wsc = o; o += (cw != CWARPS && MT == 1) ? nbuf * nb * 64 : 0;   // copies of the tiles' f16 scales (small-CTA variant, see LATE)
+    L.wsc = o; o += nbuf * nb * 64;                 // copies of the tiles' f16 scales (see LATE)
     L.bars = o; o += 2 * slots * 8;
     L.flag = o; o += 16;
     L.total = o;
@@ -135,10 +135,10 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
     float* dxs = reinterpret_cast<float*>(smem + L.dx);
     int* sss = reinterpret_cast<int*>(smem + L.s128);
     float* terms = reinterpret_cast<float*>(smem + L.terms);
-    // LATE (four-warp CTAs, one activation row): a tile only leaves its integer block sums and its 32 scales in shared
-    // memory; the warp that adds the terms in block order also forms them, one row per lane, instead of every tile's
-    // warp doing it with a quarter of its lanes.  Same operations on the same values, 15 % fewer instructions.
-    constexpr bool LATE = CW != CWARPS && MT == 1 && !SUMI;
+    // LATE: a tile only leaves its integer block sums and its 32 scales in shared memory; the warp that adds the terms
+    // of an activation row in block order also forms them, one matrix row per lane, instead of every tile's warp doing
+    // it with a quarter of its lanes.  Same operations on the same values, 15 % fewer instructions at one row.
+    constexpr bool LATE = !SUMI;
     {   // stage the activation rows, their q8k scales and block sums once per CTA
         const int pieces = nb * 8;
         for (int m = 0; m < MT; m++) {
@@ -196,9 +196,13 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 const float dw[4] = { __low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23) };
                 if (LATE) {
                     if (v0) {
-                        int* ib = reinterpret_cast<int*>(tbuf) + b * 32 + g;
+                        int* ib = reinterpret_cast<int*>(tbuf) + c0 * L.plane + b * 32 + g;
                         ib[0] = S0[0]; ib[8] = S0[1]; ib[16] = S0[2]; ib[24] = S0[3];
-                        wsc[b * 8 + g] = sc;
+                        if (t == 0) wsc[b * 8 + g] = sc;
+                    }
+                    if (MT > 1 && v1) {
+                        int* ib = reinterpret_cast<int*>(tbuf) + c1 * L.plane + b * 32 + g;
+                        ib[0] = S1[0]; ib[8] = S1[1]; ib[16] = S1[2]; ib[24] = S1[3];
                     }
                 } else if (v0) {
                     const float dx = dxs[c0 * (nb / 2) + (b >> 1)]; const int s128 = sss[c0 * nb + b];
@@ -209,7 +213,7 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                         else tbuf[c0 * L.plane + b * 32 + g + 8 * r] = __fmul_rn(__fmul_rn(dw[r], dx), (float)sumi);
                     }
                 }
-                if (MT > 1 && v1) {
+                if (!LATE && MT > 1 && v1) {
                     const float dx = dxs[c1 * (nb / 2) + (b >> 1)]; const int s128 = sss[c1 * nb + b];
 #pragma unroll
                     for (int r = 0; r < 4; r++) {
@@ -244,8 +248,9 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                     const int* icol = reinterpret_cast<const int*>(tcol);
                     const __half* hs = reinterpret_cast<const __half*>(wsc) + 4 * (lane & 7) + (lane >> 3);   // row g + 8 j: half j of group g
 #pragma unroll 8
+                    const float* dxr = dxs + warp * (nb / 2); const int* ssr = sss + warp * nb;
                     for (int b = 0; b < nb; b++)
-                        sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__half2float(hs[b * 32]), dxs[b >> 1]), (float)(icol[b * 32] - sss[b])));
+                        sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__half2float(hs[b * 32]), dxr[b >> 1]), (float)(icol[b * 32] - ssr[b])));
                 } else {
 #pragma unroll 8
                     for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
