@@ -176,13 +176,18 @@ def matvec_roofline(torch, local_rank, steps):
     for _ in range(5):
         be.graph_launch(graph)
     be.sync()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for _ in range(steps):
-        be.graph_launch(graph)
-    ev1.record(stream)
+    # five timed segments of `steps / 5` replays each; the median segment is reported (and all five listed), so that one
+    # disturbed segment (another process waking up, a clock step) does not move the figure
+    seg = max(steps // 5, 1)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+    evs[0].record(stream)
+    for k in range(5):
+        for _ in range(seg):
+            be.graph_launch(graph)
+        evs[k + 1].record(stream)
     be.sync(); torch.cuda.synchronize()
-    per_launch = ev0.elapsed_time(ev1) / 1e3 / (steps * N_WEIGHTS)
+    segs = sorted(evs[k].elapsed_time(evs[k + 1]) / 1e3 / (seg * N_WEIGHTS) for k in range(5))
+    per_launch = segs[2]
     be.graph_destroy(graph)
     for m in mats:
         m.close()
@@ -192,7 +197,8 @@ def matvec_roofline(torch, local_rank, steps):
     ach = abytes / per_launch / 1e9
     return {"bound": "hbm", "kernel": "k_matvec_t2<1> alone on config 1 (K=5120, N=17408, batch 1), sweep of 12 matrices (285 MB > L2)",
             "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind,
-            "algorithmic_bytes_per_launch": abytes, "us_per_launch": per_launch * 1e6, "traffic": NCU_DRAM_BYTES_PER_LAUNCH}
+            "algorithmic_bytes_per_launch": abytes, "us_per_launch": per_launch * 1e6, "segments_us_per_launch": [round(x * 1e6, 3) for x in segs],
+            "traffic": NCU_DRAM_BYTES_PER_LAUNCH}
 
 
 def sweep(args, torch, np, rank, world, local_rank, base):
