@@ -89,6 +89,30 @@ def gpu_sharded_engine(rank, world, port, q, n_layer, prompt, n_predict, with_mt
         q.put((rank, False, traceback.format_exc()))
 
 
+def gpu_sharded_gguf_engine(rank, world, port, q, path, head_path, prompt, n_predict):
+    """GPU ranks: each loads its rows of every trunk matrix from the same model file; logits, greedy and speculative
+    continuations as in gpu_sharded_engine."""
+    try:
+        import torch
+        from irontimber_b200.engine import CudaEngine
+        dist = _init(rank, world, port)
+        torch.cuda.set_device(rank)
+        eng = CudaEngine.from_gguf(path, head_path, ctx_len=128, device=rank, rank=rank, world=world)
+        try:
+            lg = eng.eval(prompt)
+            eng.reset()
+            hist = eng.generate(prompt, n_predict)
+            spec = eng.generate_mtp(prompt, n_predict) if eng.with_mtp else None
+            eng.sync()
+            dist.barrier()
+        finally:
+            eng.close()
+        dist.destroy_process_group()
+        q.put((rank, True, (lg, hist, spec)))
+    except Exception:
+        q.put((rank, False, traceback.format_exc()))
+
+
 def gpu_sharded_matvec(rank, world, port, q, seed, rows, cols, ntok, acc):
     """GPU ranks: one sharded ternary matvec (rows split by the library's rule), results pushed to every rank's arena."""
     try:

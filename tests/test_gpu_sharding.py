@@ -133,3 +133,31 @@ def test_two_gpus_sharded_engine_equals_single_gpu():
     for lg_r, hist_r, spec_r in run_ranks(gpu_sharded_engine, 2, 4, prompt, 12, True):
         assert np.array_equal(bits(lg_r), bits(lg))
         assert hist_r == hist and spec_r == spec
+
+
+def test_model_file_loaded_as_row_shards_matches_single_gpu(tmp_path, orc):
+    """Two ranks load their rows of the same GGUF file (PQ2_0 and PTQ1_0 matrices, Q6_K / Q8_0 head in a sidecar): logits and
+    token histories equal the single-GPU engine built from the file."""
+    if _gpus() < 2:
+        pytest.skip("needs two GPUs")
+    from irontimber_b200.engine import CudaEngine, ModelConfig
+    from tests import gguf_writer as W
+    from tests.mp_workers import gpu_sharded_gguf_engine, run_ranks
+    from tests.test_gguf import dequant
+    from tests.util import tensor_shapes
+    cfg = tiny_config(ModelConfig, n_layer=4, ctx_len=128)
+    tk, tt, hk, ht, _ = W.build_model(np.random.default_rng(21), cfg, tensor_shapes(cfg), dequant, lambda z, s: orc.hadamard_inverse(z, 1024, s),
+                                      head="sidecar", head_embd=True, head_type="mixed")
+    trunk, head = str(tmp_path / "trunk.gguf"), str(tmp_path / "head.gguf")
+    W.write_gguf(trunk, tk, tt); W.write_gguf(head, hk, ht)
+    prompt = [int(t) for t in np.random.default_rng(4).integers(0, 1000, 70)]
+    eng = CudaEngine.from_gguf(trunk, head, ctx_len=128)
+    try:
+        lg = eng.eval(prompt); eng.reset()
+        hist = eng.generate(prompt, 12)
+        spec = eng.generate_mtp(prompt, 12)
+    finally:
+        eng.close()
+    for lg_r, hist_r, spec_r in run_ranks(gpu_sharded_gguf_engine, 2, trunk, head, prompt, 12):
+        assert np.array_equal(bits(lg_r), bits(lg))
+        assert hist_r == hist and spec_r == spec
