@@ -29,11 +29,11 @@
 // + 4*ntok*rows (x2 when accumulating).  The kernel is HBM-bound.
 #include "it_internal.h"
 #include "it_pipe.cuh"
+#include <algorithm>
 
 namespace {
 
 constexpr int CWARPS = 8;                         // warps per consumer group = tiles per chunk
-constexpr int CHUNK_BYTES = CWARPS * IT_TILE_BYTES;
 constexpr int TERM_PAD = 4;                       // floats of padding between token planes
 constexpr int XROW_PAD = 16;                      // bytes of padding between staged activation rows
 constexpr int SM_SMEM = 227 * 1024;               // shared memory one SM can give to CTAs
@@ -57,14 +57,12 @@ __host__ __device__ inline Smem smem_layout(int MT, int nb, int slots, int nbuf,
     return L;
 }
 
-// MT: activation rows per launch (columns of the mma B operand in use).  NG: consumer groups of eight
-// warps; group j takes the chunks k of the CTA's stream with k % NG == j.  MINB: CTAs per SM the
+// MT: activation rows per launch (columns of the mma B operand in use).  CW: consumer warps per group = tiles per
+// chunk.  NG: consumer groups of CW warps; group j takes the chunks k of the CTA's stream with k % NG == j.  MINB: CTAs per SM the
 // register budget allows.  nbuf: terms buffers (0 for the integer-accumulator variant, 1 when every CTA
 // has a single row group, else 2).
-// ONESHOT: the grid has one CTA per row group and the ring holds a whole row group: thread 0 issues every
-// copy at once, there is no producer warp and no slot is ever refilled.
-template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI, int CW = CWARPS>
-__global__ void __launch_bounds__((NG * CW + (ONESHOT ? 0 : 1)) * 32, MINB)
+template <int MT, int NG, int MINB, bool SUMI, int CW = CWARPS>
+__global__ void __launch_bounds__((NG * CW + 1) * 32, MINB)
 k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int slots, int nbuf,
             const int8_t* __restrict__ xq, const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
             float* arena, size_t y_off, size_t y_stride, int accum, int32_t* __restrict__ sumi_out, int* error_flag, int wait_early,
@@ -82,18 +80,9 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
         *abort_flag = 0;
         for (int s = 0; s < slots; s++) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (slots + s), CW); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (ONESHOT) {
-            // the weights do not depend on the kernel before this one: request them all right away
-            const uint8_t* src = tiles + ((size_t)blockIdx.x * nb) * IT_TILE_BYTES;
-            for (int cq = 0; cq < cpr; cq++) {
-                const unsigned bytes = (unsigned)min(CW, nb - cq * CW) * IT_TILE_BYTES;
-                mbar_expect_tx(bars + 8 * cq, bytes);
-                bulk_load(smem_u32(smem + L.ring + cq * CHUNK), src + (size_t)cq * CHUNK, bytes, bars + 8 * cq);
-            }
-        }
     }
     __syncthreads();
-    if (!ONESHOT && warp == NCONS) {
+    if (warp == NCONS) {
         // ---------------- producer: one thread keeps the ring full
         if (lane == 0) {
             int issued = 0, s = 0; unsigned ph = 0;
@@ -223,10 +212,8 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                     }
                 }
             }
-            if (!ONESHOT) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bars + 8 * (slots + cs)); // the slot may be refilled
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + 8 * (slots + cs));     // the slot may be refilled
         }
         if (SUMI) continue;
         consumer_barrier<NCONS * 32>();                              // every term of this row group is in shared memory
@@ -270,16 +257,16 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
     }
 }
 
-template <int MT, int NG, int MINB, bool ONESHOT, bool SUMI, int CW = CWARPS>
+template <int MT, int NG, int MINB, bool SUMI, int CW = CWARPS>
 int launch_cfg(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, float* y, size_t y_stride, int accum, int32_t* sumi,
                int slots, int nbuf, int grid) {
     const int nb = (int)(w->cols / 128);
     const Smem L = smem_layout(MT, nb, slots, nbuf, CW);
-    auto kern = k_matvec_t2<MT, NG, MINB, ONESHOT, SUMI, CW>;
+    auto kern = k_matvec_t2<MT, NG, MINB, SUMI, CW>;
     static bool attr_set[16] = {};
     if (!attr_set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM - 1024)); attr_set[c->device & 15] = true; }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((NG * CW + (ONESHOT ? 0 : 1)) * 32); cfg.dynamicSmemBytes = (size_t)L.total; cfg.stream = c->stream;
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((NG * CW + 1) * 32); cfg.dynamicSmemBytes = (size_t)L.total; cfg.stream = c->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
@@ -318,12 +305,15 @@ int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, f
     // when its turn comes (17408 x 5120 in a back-to-back sweep: 5.98 us with the eight-warp CTAs below).
     static const bool small_ctas = !getenv("IT_MV_CW4") || atoi(getenv("IT_MV_CW4")) != 0;
     if (small_ctas && !SUMI && MT <= 4 && !long_rows && rgs >= 2 * c->sm_count) {
-        constexpr int CW = 4, PER_SM = 8;
-        const int grid = rgs < PER_SM * c->sm_count ? rgs : PER_SM * c->sm_count;
-        const int nbuf = grid == rgs ? 1 : 2;
-        const int cpr4 = (nb + CW - 1) / CW;
-        const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / PER_SM - 1024, 3, cpr4 < 2 ? cpr4 : 2, CW);
-        if (slots) return launch_cfg<MT, 1, PER_SM, false, false, CW>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        // as many of these CTAs per SM as their footprint allows (eight at one activation row, six at two: every row
+        // adds its staged bytes and its block sums), and only when every row group gets a CTA of its own in one wave:
+        // with fewer than four per SM, or with CTAs that loop over row groups, the eight-warp CTAs below do better
+        // (34816 x 5120 at two rows: 13.8 us against 12.1 us)
+        constexpr int CW = 4, MAX_PER_SM = 8;
+        const int cpr4 = (nb + CW - 1) / CW, slots = cpr4 < 3 ? cpr4 : 3;
+        const int per_sm = std::min(MAX_PER_SM, SM_SMEM / (smem_layout(MT, nb, slots, 1, CW).total + 1024));
+        if (per_sm >= 4 && rgs <= per_sm * c->sm_count)
+            return launch_cfg<MT, 1, MAX_PER_SM, false, CW>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, 1, rgs);
     }
     for (int per_sm = long_rows ? 3 : 4; per_sm >= 1; per_sm--) {
         const int grid = rgs < per_sm * c->sm_count ? rgs : per_sm * c->sm_count;
@@ -331,13 +321,13 @@ int launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, size_t xrow0, f
         const int want = long_rows ? 16 : (per_sm == 4 ? 6 : (cpr + 2 > 4 ? cpr + 2 : 4));
         const int slots = ring_slots(MT, nb, nbuf, SM_SMEM / per_sm - 1024, want, cpr < 4 ? cpr : 4);
         if (!slots) continue;
-        if (SUMI) return launch_cfg<MT, 1, 1, false, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
-        if (per_sm == 4) return launch_cfg<MT, 1, 4, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
-        if (per_sm == 3) return launch_cfg<MT, 1, 3, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
-        if (per_sm == 2) return launch_cfg<MT, 1, 2, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (SUMI) return launch_cfg<MT, 1, 1, SUMI>(c, w, ntok, x, xrow0, y, y_stride, accum, sumi, slots, nbuf, grid);
+        if (per_sm == 4) return launch_cfg<MT, 1, 4, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (per_sm == 3) return launch_cfg<MT, 1, 3, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (per_sm == 2) return launch_cfg<MT, 1, 2, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
         // a single CTA per SM: long rows get three consumer groups so that the per-warp chain stays short
-        if (long_rows) return launch_cfg<MT, 3, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
-        return launch_cfg<MT, 1, 1, false, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        if (long_rows) return launch_cfg<MT, 3, 1, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
+        return launch_cfg<MT, 1, 1, false>(c, w, ntok, x, xrow0, y, y_stride, accum, nullptr, slots, nbuf, grid);
     }
     return it_fail(IT_EINVAL, "it_matvec_t2: %d rows of width %zu exceed the shared-memory budget", MT, w->cols);
 }
