@@ -234,8 +234,8 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 if (LATE) {
                     const int* icol = reinterpret_cast<const int*>(tcol);
                     const __half* hs = reinterpret_cast<const __half*>(wsc) + 4 * (lane & 7) + (lane >> 3);   // row g + 8 j: half j of group g
-#pragma unroll 8
                     const float* dxr = dxs + warp * (nb / 2); const int* ssr = sss + warp * nb;
+#pragma unroll 8
                     for (int b = 0; b < nb; b++)
                         sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__half2float(hs[b * 32]), dxr[b >> 1]), (float)(icol[b * 32] - ssr[b])));
                 } else {
