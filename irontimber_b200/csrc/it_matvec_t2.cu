@@ -185,13 +185,12 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 const float dw[4] = { __low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23) };
                 if (LATE) {
                     if (v0) {
-                        int* ib = reinterpret_cast<int*>(tbuf) + c0 * L.plane + b * 32 + g;
-                        ib[0] = S0[0]; ib[8] = S0[1]; ib[16] = S0[2]; ib[24] = S0[3];
+                        // rows g, g + 8, g + 16, g + 24 side by side: one 16-byte store; row L of the tile sits at 4 * (L & 7) + (L >> 3)
+                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(tbuf) + c0 * L.plane + b * 32 + 4 * g) = make_int4(S0[0], S0[1], S0[2], S0[3]);
                         if (t == 0) wsc[b * 8 + g] = sc;
                     }
                     if (MT > 1 && v1) {
-                        int* ib = reinterpret_cast<int*>(tbuf) + c1 * L.plane + b * 32 + g;
-                        ib[0] = S1[0]; ib[8] = S1[1]; ib[16] = S1[2]; ib[24] = S1[3];
+                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(tbuf) + c1 * L.plane + b * 32 + 4 * g) = make_int4(S1[0], S1[1], S1[2], S1[3]);
                     }
                 } else if (v0) {
                     const float dx = dxs[c0 * (nb / 2) + (b >> 1)]; const int s128 = sss[c0 * nb + b];
@@ -232,7 +231,7 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 }
                 float sum = 0.f;
                 if (LATE) {
-                    const int* icol = reinterpret_cast<const int*>(tcol);
+                    const int* icol = reinterpret_cast<const int*>(tbuf + warp * L.plane) + 4 * (lane & 7) + (lane >> 3);
                     const __half* hs = reinterpret_cast<const __half*>(wsc) + 4 * (lane & 7) + (lane >> 3);   // row g + 8 j: half j of group g
                     const float* dxr = dxs + warp * (nb / 2); const int* ssr = sss + warp * nb;
 #pragma unroll 8

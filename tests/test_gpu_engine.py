@@ -195,3 +195,25 @@ def test_recorded_and_direct_small_passes_agree(orc, monkeypatch):
     a, b = results
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
     assert a[2:] == b[2:]
+
+
+def test_context_capacity_is_enforced_on_every_path(orc):
+    """A full context refuses further tokens before any device work, on the recorded small-pass path, on the direct
+    path and in the generation loops (the reference asserts pos + n <= ctx_len, src/vk/mod.rs:765)."""
+    from irontimber_b200 import _lib
+    from irontimber_b200.engine import CudaEngine, ModelConfig
+    eng = CudaEngine(tiny_config(ModelConfig, ctx_len=16), seed=5, with_mtp=True)
+    try:
+        eng.eval(list(range(16)), want_logits=False)          # fills the context in one 16-row pass
+        assert eng.pos == 16
+        for toks in ([1], [1, 2, 3], list(range(12))):         # recorded one- and three-row passes, a direct 12-row pass
+            with pytest.raises(_lib.IronTimberError):
+                eng.eval(toks)
+            assert eng.pos == 16
+        eng.reset()
+        with pytest.raises(_lib.IronTimberError):
+            eng.generate(list(range(10)), 8)                   # 10 + 8 - 1 > 16
+        eng.reset()
+        assert len(eng.generate(list(range(10)), 7)) == 7      # exactly fills it
+    finally:
+        eng.close()
