@@ -186,11 +186,11 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 if (LATE) {
                     if (v0) {
                         // rows g, g + 8, g + 16, g + 24 side by side: one 16-byte store; row L of the tile sits at 4 * (L & 7) + (L >> 3)
-                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(tbuf) + c0 * L.plane + b * 32 + 4 * g) = make_int4(S0[0], S0[1], S0[2], S0[3]);
+                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(tbuf) + c0 * L.plane + b * 32 + 4 * g) = make_int4(cx[0], cx[2], cy[0], cy[2]);   // still carrying 1, 4, 16, 64
                         if (t == 0) wsc[b * 8 + g] = sc;
                     }
                     if (MT > 1 && v1) {
-                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(tbuf) + c1 * L.plane + b * 32 + 4 * g) = make_int4(S1[0], S1[1], S1[2], S1[3]);
+                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(tbuf) + c1 * L.plane + b * 32 + 4 * g) = make_int4(cx[1], cx[3], cy[1], cy[3]);
                     }
                 } else if (v0) {
                     const float dx = dxs[c0 * (nb / 2) + (b >> 1)]; const int s128 = sss[c0 * nb + b];
@@ -234,9 +234,10 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                     const int* icol = reinterpret_cast<const int*>(tbuf + warp * L.plane) + 4 * (lane & 7) + (lane >> 3);
                     const __half* hs = reinterpret_cast<const __half*>(wsc) + 4 * (lane & 7) + (lane >> 3);   // row g + 8 j: half j of group g
                     const float* dxr = dxs + warp * (nb / 2); const int* ssr = sss + warp * nb;
+                    const int sh = 2 * (lane >> 3);            // the factor 4^j the tile's warp left on the sums of rows g + 8 j
 #pragma unroll 8
                     for (int b = 0; b < nb; b++)
-                        sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__half2float(hs[b * 32]), dxr[b >> 1]), (float)(icol[b * 32] - ssr[b])));
+                        sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__half2float(hs[b * 32]), dxr[b >> 1]), (float)((icol[b * 32] >> sh) - ssr[b])));
                 } else {
 #pragma unroll 8
                     for (int b = 0; b < nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
