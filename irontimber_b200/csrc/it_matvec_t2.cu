@@ -164,11 +164,10 @@ k_matvec_t2(const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups,
                 const uint4 wa = *reinterpret_cast<const uint4*>(tile + 16 * lane);
                 const uint4 wb = *reinterpret_cast<const uint4*>(tile + 512 + 16 * lane);
                 const uint2 sc = *reinterpret_cast<const uint2*>(tile + 1024 + 8 * g);
-                uint4 xa = make_uint4(0, 0, 0, 0), xb4 = make_uint4(0, 0, 0, 0);
-                if (x_lane) {
-                    const uint4* xp = reinterpret_cast<const uint4*>(xs + g * L.xrow + 128 * b + 32 * t);
-                    xa = xp[0]; xb4 = xp[1];
-                }
+                // B column g is activation row g; a lane whose column holds no row reads row 0 instead of zeros: the
+                // mma results of such a column are never looked at (v0 / v1), and the load needs no predicate
+                const uint4* xp = reinterpret_cast<const uint4*>(xs + (x_lane ? g : 0) * L.xrow + 128 * b + 32 * t);
+                const uint4 xa = xp[0], xb4 = xp[1];
                 int cx[4] = {0, 0, 0, 0}, cy[4] = {0, 0, 0, 0};
                 const uint32_t w[8] = { wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w };
                 const uint32_t xb[8] = { xa.x, xa.y, xa.z, xa.w, xb4.x, xb4.y, xb4.z, xb4.w };
