@@ -5,8 +5,8 @@
 Workload (config 2 of the baseline): the 64-layer random-init ternary decoder with the reference architecture
 (48 gated-delta-net + 16 attention layers, n_embd 5120, n_ff 17408, vocab 248320, f16 KV), batch 1, greedy decode
 after a prompt of P = 512 uniform-random token ids.  One step = one decoded token = one replay of the engine's
-recorded step (about 1,300 kernel launches, 401 of them ternary matvecs streaming 6.8 GB of weights - far more
-than the 126 MB L2, so every step reads its weights from HBM).
+recorded step (`launches_per_step` kernels, counted from the recorded graph; 401 ternary matvecs stream 6.8 GB of
+weights - far more than the 126 MB L2, so every step reads its weights from HBM).
 
 `value`: decode tokens/s with everything resident and no read-back between steps, timed with CUDA events on the
 library's stream.  `e2e`: the same through the public call `it_engine_generate`, which takes the token ids from
@@ -14,13 +14,15 @@ host memory and reads every pick back to the host (4 bytes per token), timed on 
 `roofline`: the dominant kernel, `k_matvec_t2`, timed alone on the baseline's config 1 (K=5120 -> N=17408, batch 1)
 as a sweep over 12 distinct weight matrices (285 MB), against the measured HBM copy bandwidth.
 `cpu_baseline` / `--impl reference`: the reference's CPU path (C++ port of src/cpu.rs forward_token, reference
-order, all host threads) on a truncated stack, extrapolated to the full depth; the sample is stated.
-With N > 1 (one process per GPU, torchrun) `value` is the aggregate of N independent sequences, one full engine per
-GPU and no collective (the model is 6.8 GB, sequences are independent units: weak scaling).  The same run also decodes
-ONE sequence with the row-sharded engine (`sharded`): every trunk matrix and the LM head split by output rows over the
-ranks, each rank's matvec kernels push their result slices into every peer's arena over NVLink (8-byte value+epoch
-slots) and collect the peers' slices at the end of the kernel, everything else replicated, every rank producing the
-same tokens (strong scaling; tokens of the one sequence per second, max over ranks of the device time).
+order, every host thread the process may use) on a truncated stack, extrapolated to the full depth; the sample is stated.
+`prefill_lengths` (config 4): prompts of 64 / 2048 / 4096 / 7168 tokens in 64-row passes.  `mtp` (config 3): 256 tokens
+after prompts of 128 and 2048 tokens with draft lengths 1..3, random head and scripted right drafts.
+With N > 1 (one process per GPU, torchrun) `value` is ONE sequence on the row-sharded engine (strong scaling): every
+trunk matrix and the LM head split by output rows over the ranks, each rank's matvec kernels push their result slices
+into every peer's arena over NVLink (8-byte value+epoch slots) and collect the peers' slices at the end of the kernel,
+everything else replicated, every rank producing the same tokens; tokens per second from the max over ranks of the
+device time.  `sharded.parity` says whether every rank produced the tokens of rank 0's unsharded engine.  `replicas` is
+the aggregate of N independent sequences, one full engine per GPU and no collective, for comparison.
 """
 import argparse
 import json
@@ -36,8 +38,8 @@ if ROOT not in sys.path:
 ROWS, COLS = 17408, 5120
 N_WEIGHTS = 12
 METRIC = "decode_tok_s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_t2 launch on config 1, from the ncu capture
-# summarised in profiles/matvec_t2_config1_K5120_N17408.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_t2 launch on config 1, taken from an ncu capture of
+# `bench.py --roofline-only` (a constant of the kernel and shape, not measured by this script)
 NCU_DRAM_BYTES_PER_LAUNCH = 23717632
 CPU_LAYERS = 4      # layers of the truncated stack the CPU arm runs
 
@@ -121,7 +123,8 @@ def cpu_decode_tok_s(n_layer_full, steps):
     from irontimber_b200.engine import config_27b
     cfg = orc.ModelConfig.from_buffer_copy(bytes(config_27b(n_layer=CPU_LAYERS, ctx_len=64)))
     rng = np.random.default_rng(0)
-    m = orc.Model(cfg, nthreads=orc.max_threads())
+    nthreads = host_threads()
+    m = orc.Model(cfg, nthreads=nthreads)
     shapes = tensor_shapes(cfg)
     cache = {}
 
@@ -152,7 +155,7 @@ def cpu_decode_tok_s(n_layer_full, steps):
     t_head = max(t_with_head - t_layers, 0.0)
     t_full = t_layers * n_layer_full / CPU_LAYERS + t_head
     m.close()
-    return {"value": 1.0 / t_full, "unit": "tok/s", "cores": orc.max_threads(), "kind": "port",
+    return {"value": 1.0 / t_full, "unit": "tok/s", "cores": nthreads, "kind": "port",
             "sample": f"{n} tokens through a {CPU_LAYERS}-layer stack of the 27B shapes ({t_layers * 1e3:.0f} ms per token) + one LM head ({t_head * 1e3:.0f} ms); "
                       f"extrapolated to {n_layer_full} layers: {t_full:.2f} s per token"}, t_full
 
@@ -279,6 +282,66 @@ def sweep(args, torch, np, rank, world, local_rank, base):
         dist.destroy_process_group()
 
 
+def host_threads():
+    """Host threads this process may run on (torchrun exports OMP_NUM_THREADS=1, which says nothing about the machine)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def prefill_leg(eng, cfg, rng, lengths):
+    """Config 4: end-to-end prompt passes (64-row chunks into the f16 KV cache at ctx 8192), host clock, pick read back."""
+    out = []
+    for n in lengths:
+        if n + 1 > cfg.ctx_len:
+            continue
+        toks = rng.integers(0, cfg.n_vocab, n).tolist()
+        eng.reset(); eng.sync()
+        t0 = time.perf_counter()
+        eng.eval_argmax(toks)
+        dt = time.perf_counter() - t0
+        out.append({"tokens": n, "seconds": dt, "tok_s": n / dt})
+    return out
+
+
+def mtp_leg(eng, cfg, rng, prompt_len, n_tokens):
+    """Config 3 on one prompt length: the library's speculative loop with the random-init NextN head (its drafts are almost
+    never right: the reject path) and with the head's draft replaced by the token plain greedy decoding produced (every
+    draft accepted: the accept path, as the reference's scripted-draft tests do, tests/mtp_review.rs:23-26), draft length 1..3."""
+    from irontimber_b200 import engine as E
+    prompt = rng.integers(0, cfg.n_vocab, prompt_len).tolist()
+    keep = ("drafted", "accepted", "rejected", "steps", "verify_calls", "single_forwards")
+
+    def timed(fn):
+        t0 = time.perf_counter()
+        r = fn()
+        return time.perf_counter() - t0, r
+    eng.generate_mtp_k(prompt[:8], 6, 3); eng.generate_mtp(prompt[:8], 6)       # records the pass graphs of every shape met below
+    eng.mtp_prefill(prompt)
+    pre_s, _ = timed(lambda: eng.mtp_prefill(prompt))                             # prompt pass with the head's catch-up, common to all runs
+    eng.reset()
+    plain_s, plain = timed(lambda: eng.generate(prompt, n_tokens))
+    res = {"prompt_tokens": prompt_len, "tokens": n_tokens, "prefill_with_head_catch_up_s": pre_s,
+           "plain_greedy_tok_s": (n_tokens - 1) / max(plain_s - pre_s, 1e-9)}
+    for kd in (1, 2, 3):
+        class Scripted:
+            def __init__(self, e): self.e, self.i = e, 1
+            def __getattr__(self, name): return getattr(self.e, name)
+            def mtp_draft_k(self, toks, kk):
+                self.e.mtp_draft_k(toks, kk)                 # the head still runs; only its picks are overridden
+                return [plain[min(self.i + j, len(plain) - 1)] for j in range(kk)]
+            def mtp_rollback(self, keep_rows):
+                self.i += keep_rows; return self.e.mtp_rollback(keep_rows)
+        k_s, (out_k, st_k) = timed(lambda: E.greedy_mtp_k(Scripted(eng), prompt, n_tokens, kd))
+        assert out_k == plain, "speculative decoding must reproduce plain greedy decoding"
+        n_s, (out_n, st_n) = timed(lambda: eng.generate_mtp_k(prompt, n_tokens, kd) if kd > 1 else eng.generate_mtp(prompt, n_tokens))
+        assert out_n == plain, "speculative decoding must reproduce plain greedy decoding"
+        res[f"k{kd}"] = {"scripted_right_drafts": {"tok_s": (n_tokens - 1) / max(k_s - pre_s, 1e-9), **{q: st_k[q] for q in keep if q in st_k}},
+                         "random_head": {"tok_s": (n_tokens - 1) / max(n_s - pre_s, 1e-9), **{q: st_n[q] for q in keep if q in st_n}}}
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -290,6 +353,7 @@ def main():
     ap.add_argument("--roofline-only", action="store_true", help="only the k_matvec_t2 sweep on config 1 (the run to put under a profiler for that kernel)")
     ap.add_argument("--sweep", action="store_true", help="config 5: op-level sweep of the ternary product (N x M grid) and the q8 LM head, row-sharded over the ranks when N > 1")
     ap.add_argument("--decode-only", action="store_true", help="prompt + timed decode steps only (no end-to-end, speculative, roofline or CPU legs): the run to put under a profiler")
+    ap.add_argument("--no-extras", action="store_true", help="skip the config 3 / 4 / 5 legs (speculative decoding, prompt lengths, op sweep)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -301,13 +365,15 @@ def main():
                           f"after a {args.prompt}-token random prompt, f16 KV, ctx 8192",
               "prompt_tokens": args.prompt, "weights_bytes_per_token": step_weight_bytes(cfg),
               "l2": "inputs larger than L2: every step streams its weights (6.8 GB at 64 layers) from HBM; L2 is 126 MB",
-              "sharding": "single GPU" if world == 1 else f"value: {world} independent sequences, one engine per GPU, no collective; sharded: one sequence, trunk matrices and LM head split by output rows over {world} GPUs"}
+              "sharding": "single GPU" if world == 1 else f"one sequence, trunk matrices and LM head split by output rows over {world} GPUs, result slices exchanged over NVLink inside the kernels; "
+                                                            f"everything else replicated (side object `replicas`: {world} independent sequences, one engine per GPU, no collective)"}
     base = {"metric": METRIC, "unit": "tok/s", "n_gpus": world if args.impl != "reference" else args.gpus, "steps": args.steps, "warmup": warmup,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x 2-bit codes -> int32, f32 epilogue", "data": "synthetic", "config": config}
+            "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "int8 x 2-bit codes -> int32, f32 epilogue", "data": "synthetic", "config": config}
 
     if args.impl == "reference":
         if rank != 0:
             return
+        base["scaling"] = "weak" if args.gpus == 1 else "strong"      # one CPU whatever N is: the same single sequence
         cb, t_full = cpu_decode_tok_s(args.layers, max(args.steps, 2))
         print(json.dumps(dict(base, impl="reference", value=cb["value"], ms_per_step=t_full * 1e3, cpu_baseline=cb,
                               e2e={"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})))
@@ -331,6 +397,9 @@ def main():
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = _lib.load()
+    dev = f"cuda:{local_rank}"
+
     def barrier(ctx=None):
         if ctx is not None:
             _lib.check(L.it_sync(ctx))
@@ -339,151 +408,108 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    L = _lib.load()
-    sharded = None
-    if world > 1:
-        # one sequence on the row-sharded engine: same seed and prompt on every rank
-        seng = CudaEngine(cfg, seed=7, with_mtp=False, device=local_rank, rank=rank, world=world)
-        sctx = L.it_engine_ctx(seng.h)
-        sstream = torch.cuda.ExternalStream(L.it_ctx_stream(sctx), device=f"cuda:{local_rank}")
-        sprompt = np.random.default_rng(100).integers(0, cfg.n_vocab, args.prompt).tolist()
-        barrier(sctx)
+    def max_over_ranks(x):
+        if not dist:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_decode(eng, prompt, steps, sampler=None):
+        """Prompt pass, warm-up steps, then `steps` chained greedy steps between CUDA events on the library's stream."""
+        ctx = L.it_engine_ctx(eng.h)
+        stream = torch.cuda.ExternalStream(L.it_ctx_stream(ctx), device=dev)
+        barrier(ctx)
         t0 = time.perf_counter()
-        seng.eval_argmax(sprompt)
-        sprefill = time.perf_counter() - t0
-        seng.decode_steps(warmup)
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier(sctx)
-        s0.record(sstream)
-        seng.decode_steps(args.steps, read_last=False)
-        s1.record(sstream)
-        barrier(sctx)
-        t = torch.tensor([s0.elapsed_time(s1)], device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sms = float(t.item())
+        eng.eval_argmax(prompt)
+        prefill_s = time.perf_counter() - t0
+        eng.decode_steps(warmup)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def region():
+            barrier(ctx)
+            ev0.record(stream)
+            eng.decode_steps(steps, read_last=False)
+            ev1.record(stream)
+            barrier(ctx)
+        if sampler is not None:
+            with sampler:
+                region()
+        else:
+            region()
+        return max_over_ranks(ev0.elapsed_time(ev1)), prefill_s
+
+    def timed_e2e(eng, prompt, steps):
+        """The public generate call: token ids from host memory, every pick read back (4 bytes each way per token), host clock."""
+        eng.reset()
+        first = eng.eval_argmax(prompt)
+        barrier(L.it_engine_ctx(eng.h))
+        t0 = time.perf_counter()
+        hist = eng.generate([first], steps)
+        dt = time.perf_counter() - t0
+        assert len(hist) == steps
+        return max_over_ranks(dt), [first] + hist
+
+    # the same model and prompt on every rank (seed 7, rng 100): the row-sharded engine must reproduce rank 0's unsharded engine
+    prompt = np.random.default_rng(100).integers(0, cfg.n_vocab, args.prompt).tolist()
+    clocks = ClockSampler(local_rank)
+    sharded = replicas = None
+    if world > 1:
+        seng = CudaEngine(cfg, seed=7, with_mtp=False, device=local_rank, rank=rank, world=world)
+        ms, prefill_s = timed_decode(seng, prompt, args.steps, clocks)
+        launches = seng.step_kernels()
+        e2e_s, hist = timed_e2e(seng, prompt, args.steps)
+        n_par = min(args.steps + 1, 33)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, hist[:n_par])
         seng.close()
-        sharded = {"value": args.steps / (sms / 1e3), "unit": "tok/s", "ms_per_step": sms / args.steps, "scaling": "strong",
-                   "prefill_tok_s": args.prompt / sprefill,
-                   "exchange": "257 exchanges per token (4 per layer + LM head), each inside the matvec kernel: peer stores of 8-byte value+epoch slots over NVLink, no NCCL call"}
-    eng = CudaEngine(cfg, seed=7 + rank, with_mtp=True, device=local_rank)
-    ctx = L.it_engine_ctx(eng.h)
-    stream = torch.cuda.ExternalStream(L.it_ctx_stream(ctx), device=f"cuda:{local_rank}")
-    rng = np.random.default_rng(100 + rank)
-    prompt = rng.integers(0, cfg.n_vocab, args.prompt).tolist()
-    _barrier = barrier
-
-    def barrier():
-        _barrier(ctx)
-
-    t0 = time.perf_counter()
-    eng.eval_argmax(prompt)
-    prefill_s = time.perf_counter() - t0
-    eng.decode_steps(warmup)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        ev0.record(stream)
-        eng.decode_steps(args.steps, read_last=False)
-        ev1.record(stream)
-        barrier()
-    ms = ev0.elapsed_time(ev1)
-    if dist:
-        t = torch.tensor([ms], device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    if args.decode_only:
-        eng.close()
+        eng = CudaEngine(cfg, seed=7 + rank, with_mtp=False, device=local_rank)      # rank 0: the same model, unsharded
+        rprompt = prompt if rank == 0 else np.random.default_rng(100 + rank).integers(0, cfg.n_vocab, args.prompt).tolist()
+        rsteps = min(args.steps, 32)
+        rms, _ = timed_decode(eng, rprompt, rsteps)
+        parity = None
         if rank == 0:
-            print(json.dumps(dict(base, value=world * args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(),
+            eng.reset()
+            first = eng.eval_argmax(prompt)
+            want = [first] + eng.generate([first], n_par - 1)
+            parity = {"tokens_compared": n_par, "ranks_agree": all(g == gathered[0] for g in gathered), "equals_unsharded_engine": gathered[0] == want}
+        eng.close()
+        replicas = {"value": world * rsteps / (rms / 1e3), "unit": "tok/s", "steps": rsteps, "scaling": "weak",
+                    "note": f"{world} independent sequences, one full engine per GPU, no collective"}
+        sharded = {"parity": bool(parity and parity["ranks_agree"] and parity["equals_unsharded_engine"]) if rank == 0 else None, "parity_detail": parity,
+                   "prefill_tok_s": args.prompt / prefill_s,
+                   "exchange": "257 exchanges per token (4 per layer + LM head), each inside the matvec kernel: peer stores of 8-byte value+epoch slots over NVLink, no NCCL call on the data path"}
+    else:
+        eng = CudaEngine(cfg, seed=7, with_mtp=True, device=local_rank)
+        ms, prefill_s = timed_decode(eng, prompt, args.steps, clocks)
+        launches = eng.step_kernels()
+        if args.decode_only:
+            eng.close()
+            print(json.dumps(dict(base, value=args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * launches,
                                   prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64}, decode_only=True)))
-        if dist:
-            dist.destroy_process_group()
-        return
-    # end to end through the public generate call: token ids from host memory, every pick read back (4 bytes)
-    eng.reset()
-    first = eng.eval_argmax(prompt)
-    barrier()
-    t0 = time.perf_counter()
-    hist = eng.generate([first], args.steps)
-    e2e_s = time.perf_counter() - t0
-    assert len(hist) == args.steps
-    if dist:
-        t = torch.tensor([e2e_s], device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    # speculative decode (config 3): the library's greedy_mtp loop with the random-init NextN head (its drafts are almost
-    # never right, so this is the cost of the reject path), and the same loop with the head's draft replaced by the
-    # token plain greedy decoding produced (every draft accepted: the accept path, as the reference's scripted-draft tests do)
-    mtp = None
-    if world == 1:
-        from irontimber_b200 import engine as E
-        n_mtp = min(args.steps, 64)
-
-        def timed(fn):
-            """Second of two runs: the first one records the pass graphs of the shapes it meets."""
-            fn()
-            t0 = time.perf_counter()
-            r = fn()
-            return time.perf_counter() - t0, r
-        pre_s, _ = timed(lambda: eng.mtp_prefill(prompt))   # prompt pass with the head's catch-up, common to all runs
-        nat_s, (out_mtp, st_nat) = timed(lambda: eng.generate_mtp(prompt, n_mtp))
-        eng.reset()
-        plain = eng.generate(prompt, n_mtp)
-        assert out_mtp == plain, "speculative decoding must reproduce plain greedy decoding"
-
-        class Scripted:
-            def __init__(self, e): self.e, self.i = e, 1
-            def __getattr__(self, name): return getattr(self.e, name)
-            def mtp_draft(self, toks):
-                self.e.mtp_draft(toks)                      # the head still runs; only its pick is overridden
-                return plain[min(self.i, len(plain) - 1)]
-            def mtp_verify(self, x, d):
-                r = self.e.mtp_verify(x, d); self.i += 2 if r[0] == d else 1; return r
-        eng.reset()
-        acc_s, (out_acc, st_acc) = timed(lambda: E.greedy_mtp(Scripted(eng), prompt, n_mtp))
-        assert out_acc == plain
-        keep = ("drafted", "accepted", "rejected", "steps", "verify_calls", "single_forwards")
-        # draft length 2 and 3 (extension: chained head steps, k + 1 verification rows), scripted right drafts and the random head
-        longer = {}
-        for kd in (2, 3):
-            class ScriptedK:
-                def __init__(self, e): self.e, self.i = e, 1
-                def __getattr__(self, name): return getattr(self.e, name)
-                def mtp_draft_k(self, toks, kk):
-                    self.e.mtp_draft_k(toks, kk)
-                    return [plain[min(self.i + j, len(plain) - 1)] for j in range(kk)]
-                def mtp_rollback(self, keep_rows):
-                    self.i += keep_rows; return self.e.mtp_rollback(keep_rows)
-            k_s, (out_k, st_k) = timed(lambda: E.greedy_mtp_k(ScriptedK(eng), prompt, n_mtp, kd))
-            assert out_k == plain
-            n_s, (out_n, st_n) = timed(lambda: eng.generate_mtp_k(prompt, n_mtp, kd))
-            assert out_n == plain
-            longer[f"k{kd}"] = {"scripted_right_drafts": {"tok_s": (n_mtp - 1) / max(k_s - pre_s, 1e-9), **{q: st_k[q] for q in keep if q in st_k}},
-                                "random_head": {"tok_s": (n_mtp - 1) / max(n_s - pre_s, 1e-9), **{q: st_n[q] for q in keep if q in st_n}}}
-        mtp = {"tokens": n_mtp, "prefill_with_head_catch_up_s": pre_s, "note": "decode tok/s = (tokens - 1) / (run time - prefill time); every run is the second of two (the first records the pass graphs)",
-               "random_head": {"tok_s": (n_mtp - 1) / max(nat_s - pre_s, 1e-9), "run_s": nat_s, **{k: st_nat[k] for k in keep if k in st_nat}},
-               "scripted_right_drafts": {"tok_s": (n_mtp - 1) / max(acc_s - pre_s, 1e-9), "run_s": acc_s, **{k: st_acc[k] for k in keep if k in st_acc}},
-               **longer}
-    # launches of one recorded step: 13 per delta-net layer, 15 per attention layer, embedding, output norm, LM head
-    # (Hadamard + matvec), argmax and the two token/position updates
-    n_kernels = sum(13 if cfg.is_recurrent(il) else 15 for il in range(cfg.n_layer)) + 7
-    barrier()
-    eng.close()
-    out = dict(base, value=world * args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * n_kernels,
-               e2e={"value": world * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "ms_per_token": e2e_s / args.steps * 1e3},
+            return
+        e2e_s, _ = timed_e2e(eng, prompt, args.steps)
+    out = dict(base, value=args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * launches, launches_per_step=launches,
+               e2e={"value": args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "ms_per_token": e2e_s / args.steps * 1e3},
                prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64},
                step_weight_gbs=step_weight_bytes(cfg) * args.steps / (ms / 1e3) / 1e9)
-    if mtp:
-        out["mtp"] = mtp
+    if world == 1 and not args.no_extras:
+        rng = np.random.default_rng(300)
+        out["prefill_lengths"] = prefill_leg(eng, cfg, rng, (64, 2048, 4096, 7168))                  # config 4
+        out["mtp"] = {"note": "decode tok/s = (tokens - 1) / (run time - prefill time); pass graphs recorded beforehand",
+                      "prompts": [mtp_leg(eng, cfg, rng, p, 256) for p in (128, 2048)]}               # config 3
+    if world == 1:
+        eng.close()
     if sharded:
         out["sharded"] = sharded
+        out["replicas"] = replicas
     if rank == 0:
-        if world > 1:
-            os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())     # torchrun pins it to 1; the CPU arm uses every host thread
         out["roofline"] = matvec_roofline(torch, local_rank, 200)
+        out["roofline"]["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed profile summary (not measured in this run)"
         out["cpu_baseline"] = cpu_decode_tok_s(args.layers, 8)[0]
         print(json.dumps(out))
     if dist:
+        barrier()
         dist.destroy_process_group()
 
 

@@ -72,6 +72,7 @@ int it_capture_begin(it_ctx* ctx);
 int it_capture_end(it_ctx* ctx, it_graph** out);
 int it_graph_launch(it_ctx* ctx, it_graph* g);
 void it_graph_destroy(it_graph* g);
+int it_graph_kernel_nodes(const it_graph* g);              /* kernel launches one replay makes (>= 0), or a negative code */
 
 /* Hadamard sign vector for activations of width n (prism.hadamard.sign_values; src/model.rs:48-60,
  * uploaded into the params buffer by the reference, src/vk/mod.rs:536).  Values must be +1 or -1. */
@@ -241,6 +242,8 @@ int it_engine_generate(it_engine* e, const uint32_t* prompt, size_t n_prompt, si
 /* n more greedy steps chained on the device (the pick of a step is the next step's token) without reading anything back
  * in between; continues from the last pick.  Used to time decoding with everything resident; last_pick may be NULL. */
 int it_engine_decode_steps(it_engine* e, size_t n, uint32_t* last_pick);
+/* Kernel launches of one recorded greedy step (>= 0; counted from the recorded graph), or a negative code. */
+int it_engine_step_kernels(it_engine* e);
 
 /* MtpBackend trait (src/mtp.rs:150-163), one to one. */
 int it_engine_mtp_prefill(it_engine* e, const uint32_t* prompt, size_t n, uint32_t* next);

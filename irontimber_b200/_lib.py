@@ -28,6 +28,7 @@ SIGNATURES = {
     "it_capture_end": (C.c_int, [P, C.POINTER(P)]),
     "it_graph_launch": (C.c_int, [P, P]),
     "it_graph_destroy": (None, [P]),
+    "it_graph_kernel_nodes": (C.c_int, [P]),
     "it_signs_set": (C.c_int, [P, c_size, P]),
     "it_matrix_upload_pq2": (C.c_int, [P, P, c_size, c_size, C.POINTER(P)]),
     "it_matrix_upload_packed2": (C.c_int, [P, P, P, c_size, c_size, C.POINTER(P)]),
@@ -83,6 +84,7 @@ SIGNATURES = {
     "it_engine_reset": (C.c_int, [P]),
     "it_engine_generate": (C.c_int, [P, P, c_size, c_size, C.c_uint32, P, C.POINTER(c_size)]),
     "it_engine_decode_steps": (C.c_int, [P, c_size, C.POINTER(C.c_uint32)]),
+    "it_engine_step_kernels": (C.c_int, [P]),
     "it_engine_mtp_prefill": (C.c_int, [P, P, c_size, C.POINTER(C.c_uint32)]),
     "it_engine_mtp_single": (C.c_int, [P, C.c_uint32, C.POINTER(C.c_uint32)]),
     "it_engine_mtp_draft": (C.c_int, [P, P, c_size, C.POINTER(C.c_uint32)]),

@@ -202,6 +202,11 @@ IT_API int it_argmax_static(void* stream, const float* logits_dev, size_t n, uin
     unsigned long long* partials = g_argmax_static_ptr[dev];
     unsigned* counter = reinterpret_cast<unsigned*>(partials + IT_ARGMAX_MAX_BLOCKS);
     cudaStream_t st = (cudaStream_t)stream;
+    {   // the scratch resolved above belongs to the current device: a stream of another GPU is refused here, not at the launch
+        int sdev = dev;
+        if (st && st != cudaStreamLegacy && st != cudaStreamPerThread && cudaStreamGetDevice(st, &sdev) != cudaSuccess) { cudaGetLastError(); sdev = dev; }
+        IT_CHECK_ARG(sdev == dev, "it_argmax_static: the stream belongs to device %d but device %d is current", sdev, dev);
+    }
     // the counter must start at zero; the kernel leaves it at zero, but a launch that failed earlier may not have
     IT_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned), st));
     unsigned blocks = (unsigned)((n + 4095) / 4096);

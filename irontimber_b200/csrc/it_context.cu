@@ -245,6 +245,16 @@ IT_API int it_graph_launch(it_ctx* c, it_graph* g) {
     it_note_op(c);
     IT_CUDA(cudaGraphLaunch(g->exec, c->stream)); return IT_OK;
 }
+IT_API int it_graph_kernel_nodes(const it_graph* g) {
+    if (!g) return it_fail(IT_EINVAL, "it_graph_kernel_nodes: null graph");
+    size_t n = 0;
+    IT_CUDA(cudaGraphGetNodes(g->graph, nullptr, &n));
+    std::vector<cudaGraphNode_t> nodes(n);
+    if (n) IT_CUDA(cudaGraphGetNodes(g->graph, nodes.data(), &n));
+    int kernels = 0;
+    for (size_t i = 0; i < n; i++) { cudaGraphNodeType t; IT_CUDA(cudaGraphNodeGetType(nodes[i], &t)); if (t == cudaGraphNodeTypeKernel) kernels++; }
+    return kernels;
+}
 IT_API void it_graph_destroy(it_graph* g) { if (!g) return; cudaSetDevice(g->ctx->device); cudaGraphExecDestroy(g->exec); cudaGraphDestroy(g->graph); delete g; }
 IT_API void* it_ctx_stream(it_ctx* c) { return c ? (void*)c->stream : nullptr; }
 IT_API float* it_arena_ptr(it_ctx* c) { return c ? c->arena : nullptr; }

@@ -1,6 +1,7 @@
 // Engine construction (random-init weights generated on the device), teardown and read-back for parity tests.
 #include "it_engine.h"
 #include "it_support.h"
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 
@@ -142,7 +143,10 @@ int validate(const it_model_config* c) {
     IT_CHECK_ARG(c->ssm_groups > 0 && c->ssm_vheads > 0 && c->ssm_vheads % c->ssm_groups == 0, "engine: ssm_vheads must be a multiple of ssm_groups");
     IT_CHECK_ARG(c->ssm_inner == c->ssm_vheads * c->ssm_state && c->ssm_inner % 1024 == 0, "engine: ssm_inner must equal vheads * state and be a multiple of 1024");
     IT_CHECK_ARG(c->full_attn_interval >= 1, "engine: bad full_attention_interval");
-    IT_CHECK_ARG(c->ctx_len >= 16 && c->ctx_len <= 32768, "engine: context capacity must be 16..32768");
+    {   // the attention kernel keeps one row of scores in shared memory: the context capacity is bounded by what fits there
+        const int cap = std::min(32768, it_sup_attention_max_positions(c->head_dim));
+        IT_CHECK_ARG(c->ctx_len >= 16 && c->ctx_len <= cap, "engine: context capacity %d outside 16..%d (limit of the attention kernel at head dimension %d)", c->ctx_len, cap, c->head_dim);
+    }
     IT_CHECK_ARG(c->eps > 0.f && c->rope_base > 1.f, "engine: bad eps or rope base");
     return IT_OK;
 }

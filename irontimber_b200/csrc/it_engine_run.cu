@@ -314,6 +314,14 @@ IT_API int it_engine_decode_steps(it_engine* e, size_t n, uint32_t* last_pick) {
     return IT_OK;
 }
 
+// Kernel launches of one recorded greedy decode step (records the step when it has not been recorded yet).
+IT_API int it_engine_step_kernels(it_engine* e) {
+    IT_CHECK_ARG(e, "it_engine_step_kernels: null engine");
+    if (e->pos < 1) return it_fail(IT_ESTATE, "it_engine_step_kernels: nothing has been evaluated yet");
+    IT_TRY(begin_device_decode(e));
+    return it_graph_kernel_nodes(e->step_graph);
+}
+
 // ---------------------------------------------------------------- MtpBackend trait (impl for VkEngine, src/vk/mod.rs:979-1027)
 #define IT_NEED_MTP(e, who) do { IT_CHECK_ARG(e, who ": null engine"); if (!(e)->has_mtp) return it_fail(IT_ESTATE, who ": the engine has no MTP head"); } while (0)
 

@@ -612,18 +612,29 @@ int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* 
     else it_pdl(k_kv_store<float>, dim3(dim3((kvd + 255) / 256, nt)), dim3(256), 0, c->stream, k, v, ts, (float*)kc, (float*)vc, kvd, hd, slot0, pos_ptr);
     KCHK("kv_store"); return IT_OK;
 }
+// Positions one attention launch can score: the row of scores, the q row and the ring of V chunks share the CTA's
+// dynamic shared memory (IT_ATT_SMEM bytes at most).
+#define IT_ATT_SMEM (220 * 1024)
+#define IT_ATT_RING (4 * 32768)
+int it_sup_attention_max_positions(int hd) {
+    const long long room = (long long)IT_ATT_SMEM - IT_ATT_RING - 16 - (long long)hd * 4;
+    return room < 4 ? 0 : (int)(room / 4 / 4 * 4);
+}
 int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0, const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16) {
     it_note_op(c);
     // shared memory is sized for the longest row of scores this launch can meet (max_pos when the position is read on the device)
-    const size_t smem = (((size_t)(pos_ptr ? max_pos : slot0 + nt) + 3) / 4 * 4 + hd) * sizeof(float) + 16 + 4 * 32768;   // scores, q, ring of V chunks
-    if (smem > 220 * 1024 || hd > 1024 || (hd * (f16 ? 2 : 4)) % 16) return it_fail(IT_EINVAL, "attention over %d positions exceeds the shared-memory budget", slot0 + nt);
-    if (f16) {
-        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); set = true; }
-        it_pdl(k_attention<__half>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const __half*)kc, (const __half*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
-    } else {
-        static bool set = false; if (!set) { cudaFuncSetAttribute(k_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); set = true; }
-        it_pdl(k_attention<float>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const float*)kc, (const float*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
+    const int positions = pos_ptr ? max_pos : slot0 + nt;
+    const size_t smem = (((size_t)positions + 3) / 4 * 4 + hd) * sizeof(float) + 16 + IT_ATT_RING;   // scores, q, ring of V chunks
+    if (hd > 1024 || (hd * (f16 ? 2 : 4)) % 16) return it_fail(IT_EINVAL, "attention: head dimension %d is not supported", hd);
+    if (smem > IT_ATT_SMEM) return it_fail(IT_EINVAL, "attention over %d positions exceeds the shared-memory budget (%d positions at head dimension %d)", positions, it_sup_attention_max_positions(hd), hd);
+    static bool set[2][16] = {};    // the attribute is per device
+    if (!set[f16 ? 1 : 0][c->device & 15]) {
+        if (f16) IT_CUDA(cudaFuncSetAttribute(k_attention<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, IT_ATT_SMEM));
+        else IT_CUDA(cudaFuncSetAttribute(k_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, IT_ATT_SMEM));
+        set[f16 ? 1 : 0][c->device & 15] = true;
     }
+    if (f16) it_pdl(k_attention<__half>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const __half*)kc, (const __half*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
+    else it_pdl(k_attention<float>, dim3(dim3(nh, nt)), dim3(1024), smem, c->stream, q, q_hs, q_ts, gate, (const float*)kc, (const float*)vc, kvd, hd, nh, nkv, slot0, pos_ptr, out, o_ts);
     KCHK("attention"); return IT_OK;
 }
 
@@ -647,7 +658,8 @@ int it_sup_gdn_norm(it_ctx* c, const float* co, size_t co_ts, const float* beta,
     if (sd != 128) return it_fail(IT_EINVAL, "gdn_norm: the fused kernel is built for a state size of 128");
     it_note_op(c);
     const size_t smem = ((size_t)sd * sd + 4 * sd) * sizeof(float);
-    static bool set = false; if (!set) { cudaFuncSetAttribute(k_gdn_norm<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set = true; }
+    static bool set[16] = {};       // the attribute is per device
+    if (!set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(k_gdn_norm<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set[c->device & 15] = true; }
     it_pdl(k_gdn_norm<128>, dim3(dim3(nv)), dim3(128 + 32), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
     KCHK("gdn_norm"); return IT_OK;
 }

@@ -33,6 +33,9 @@ int it_sup_kv_store(it_ctx* c, const float* k, const float* v, size_t ts, void* 
 int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int kvd, int hd, int nh, int nkv, int slot0,
                      const int* pos_ptr, int max_pos, float* out, size_t o_ts, int nt, int f16);
 
+// Longest context one attention launch can serve at this head dimension (its row of scores lives in shared memory).
+int it_sup_attention_max_positions(int hd);
+
 // Fused forms for passes of up to 8 rows (same arithmetic and order as the separate kernels; see it_support.cu).
 int it_sup_attn_prep(it_ctx* c, float* qkv, size_t ts, int nh, int nkv, int hd, const float* q_norm, const float* k_norm, float eps, int pos0, const int* pos_ptr,
                      int n_rot, float theta_scale, const int* sections, void* kc, void* vc, int nt);

@@ -141,6 +141,13 @@ class CudaEngine:
         _lib.check(self.L.it_engine_decode_steps(self.h, n, C.byref(out) if read_last else None))
         return out.value if read_last else None
 
+    def step_kernels(self):
+        """Kernel launches of one recorded greedy decode step (counted from the recorded graph)."""
+        n = self.L.it_engine_step_kernels(self.h)
+        if n < 0:
+            _lib.check(n)
+        return n
+
     # ---- MtpBackend --------------------------------------------------------------------------------
     def mtp_prefill(self, prompt):
         p = _u32(prompt); out = C.c_uint32()

@@ -41,3 +41,14 @@ def test_calls_fail_cleanly_without_a_device_or_with_bad_arguments(lib):
     assert lib.it_matvec_t2(None, None, 1, None, 0, 0, 0) == -1
     assert lib.it_arena_write(None, 0, None, 0) == -1
     lib.it_ctx_destroy(None); lib.it_matrix_destroy(None); lib.it_qmatrix_destroy(None); lib.it_q8_destroy(None)
+
+
+def test_context_capacity_beyond_the_attention_kernel_is_refused_before_device_work(lib):
+    """The attention kernel keeps a row of scores in shared memory, so the engine refuses a context capacity it could
+    not serve (about 23 k positions at head dimension 256) when it is built, with the limit in the message."""
+    from irontimber_b200.engine import config_27b
+    h = C.c_void_p()
+    cfg = config_27b(n_layer=4, ctx_len=24000, n_vocab=2048)
+    assert lib.it_engine_create_synth(0, C.byref(cfg), 1, 0, C.byref(h)) == -1
+    msg = lib.it_last_error().decode()
+    assert "context capacity 24000" in msg and "23292" in msg

@@ -8,7 +8,7 @@ plain greedy decoding with the oracle's acceptance counts.
 import numpy as np
 import pytest
 
-from tests.util import bits, oracle_model_from_engine, tiny_config
+from tests.util import assert_reference_order_history, bits, oracle_model_from_engine, reference_order_walk, tiny_config
 
 pytestmark = pytest.mark.gpu
 
@@ -66,6 +66,13 @@ def test_greedy_history_identical_and_graph_replay(orc, pair):
     for _ in range(7):
         t = eng.eval_argmax([t]); hist.append(t)
     assert hist == want[:8]
+
+
+def test_history_against_the_reference_summation_order(orc, pair):
+    """The oracle's REFERENCE_ORDER mode is the reference CPU arithmetic as written (src/cpu.rs:168-192); the engine's
+    greedy pick equals its pick at every step that the top-1 margin decides (tests/util.py states the rule)."""
+    eng, m = pair
+    assert_reference_order_history(reference_order_walk(orc, eng, m, PROMPT, 24))
 
 
 def test_speculative_decode_equals_plain_greedy_with_oracle_counts(orc, pair):

@@ -1,0 +1,89 @@
+"""GPU parity of the decoder engine at the 27B model's real widths (n_embd 5120, n_ff 17408, ssm_inner 6144, 48 value
+heads in 16 groups, 24 attention heads over 4 KV heads, Hadamard blocks with the (128, 16, 3) permutation), on a
+4-layer stack (3 delta-net layers + 1 attention layer) with a reduced vocabulary, as the reference's own model tests
+truncate the stack (tests/mtp_tests.rs:25).
+
+Bit-identical to the oracle's device order: logits, recurrent / KV state, hidden rows, greedy and speculative
+histories with their counters.  Against the reference's own summation order (src/cpu.rs:168-192) the engine's pick
+must equal the reference pick wherever the reference's top-1 margin exceeds twice the largest logit deviation.
+"""
+import numpy as np
+import pytest
+
+from tests.util import assert_reference_order_history, bits, oracle_model_from_engine, reference_order_walk
+
+pytestmark = pytest.mark.gpu
+
+N_VOCAB = 2048
+
+
+@pytest.fixture(scope="module")
+def pair(orc):
+    from irontimber_b200.engine import CudaEngine, config_27b
+    eng = CudaEngine(config_27b(n_layer=4, ctx_len=128, n_vocab=N_VOCAB), seed=17, with_mtp=True)
+    model = oracle_model_from_engine(orc, eng, with_mtp=True)
+    yield eng, model
+    model.close(); eng.close()
+
+
+PROMPT = [int(t) for t in np.random.default_rng(27).integers(0, N_VOCAB, 70)]     # one pass of 64 rows + a ragged one of 6
+
+
+def test_prompt_passes_logits_state_and_hidden_bit_exact(orc, pair):
+    eng, m = pair
+    eng.reset()
+    lg = eng.eval(PROMPT)
+    st = m.new_state()
+    for i, t in enumerate(PROMPT):
+        want = m.forward_token(st, t, i + 1 == len(PROMPT), orc.DEVICE_ORDER)
+    assert np.array_equal(bits(lg), bits(want))
+    assert eng.pos == m.state_pos(st) == len(PROMPT)
+    assert np.array_equal(bits(eng.hidden(len(PROMPT) - 64 - 1)), bits(m.state_h(st)))     # last row of the ragged pass
+    for il in range(eng.cfg.n_layer):
+        kinds = (0, 1) if eng.cfg.is_recurrent(il) else (2, 3)
+        for kind in kinds:
+            assert np.array_equal(bits(eng.state(il, kind)), bits(m.state_read(st, il, kind))), f"state {kind} of layer {il}"
+    # single-token passes continue from that state with the same bits
+    for t in (3, 1999):
+        lg = eng.eval([t]); want = m.forward_token(st, t, True, orc.DEVICE_ORDER)
+        assert np.array_equal(bits(lg), bits(want))
+    m.free_state(st)
+
+
+def test_greedy_history_bit_exact(orc, pair):
+    eng, m = pair
+    want = orc.generate_greedy(m, PROMPT, 14, orc.DEVICE_ORDER)
+    eng.reset()
+    assert eng.generate(PROMPT, 14) == want
+
+
+@pytest.mark.parametrize("k", [1, 2, 3])
+def test_speculative_histories_and_counters(orc, pair, k):
+    eng, m = pair
+    n = 13
+    plain = orc.generate_greedy(m, PROMPT, n, orc.DEVICE_ORDER)
+    want_out, want_stats = orc.greedy_mtp_k(orc.CpuMtp(m, orc.DEVICE_ORDER), PROMPT, n, k)
+    assert want_out == plain
+    out, stats = eng.generate_mtp_k(PROMPT, n, k)
+    assert out == plain and stats == want_stats
+    if k == 1:
+        ref_out, ref_stats = orc.greedy_mtp(orc.CpuMtp(m, orc.DEVICE_ORDER), PROMPT, n)
+        assert eng.generate_mtp(PROMPT, n) == (ref_out, ref_stats)
+
+    class Right:                                   # the head runs, its drafts are replaced by the true continuation
+        def __init__(self, e): self.e, self.i = e, 1
+        def __getattr__(self, name): return getattr(self.e, name)
+        def mtp_draft_k(self, toks, kk):
+            self.e.mtp_draft_k(toks, kk)
+            return [plain[min(self.i + j, n - 1)] for j in range(kk)]
+        def mtp_rollback(self, keep):
+            self.i += keep; return self.e.mtp_rollback(keep)
+    out, st = orc.greedy_mtp_k(Right(eng), PROMPT, n, k)
+    assert out == plain and st["rejected"] == 0 and st["accepted"] == st["drafted"] > 0
+
+
+def test_history_against_the_reference_summation_order(orc, pair):
+    eng, m = pair
+    steps = reference_order_walk(orc, eng, m, PROMPT, 14)
+    dev, rel, margin = assert_reference_order_history(steps)
+    assert rel <= 1e-3 or dev <= 0.02

@@ -144,3 +144,43 @@ def oracle_model_from_engine(orc, eng, with_mtp):
     for w in {cfg.n_embd, cfg.ssm_inner, cfg.n_head * cfg.head_dim, cfg.n_ff}:
         m.set_signs(eng.signs(w))
     return m
+
+
+def reference_order_walk(orc, eng, model, prompt, n_steps):
+    """Walks the REFERENCE_ORDER greedy history of the oracle (the reference CPU arithmetic as written, src/cpu.rs:168-192)
+    and feeds the same tokens to the engine.  At every step returns the reference's top-1 margin, the largest logit
+    deviation of the engine, and whether the picks agree.  The engine is teacher-forced along the reference history,
+    so one low-margin step cannot hide what follows it."""
+    st = model.new_state()
+    ref = None
+    for i, t in enumerate(prompt):
+        ref = model.forward_token(st, t, i + 1 == len(prompt), orc.REFERENCE_ORDER)
+    eng.reset()
+    got = eng.eval(prompt)
+    steps = []
+    for _ in range(n_steps):
+        top2 = np.partition(ref, -2)[-2:]
+        margin = float(top2[1] - top2[0])
+        dev = float(np.max(np.abs(ref - got)))
+        scale = float(np.max(np.abs(ref)))
+        pick_ref, pick_got = orc.argmax(ref), int(np.argmax(got))
+        steps.append({"margin": margin, "dev": dev, "rel": dev / scale, "same": pick_ref == pick_got, "pick": pick_ref})
+        ref = model.forward_token(st, pick_ref, True, orc.REFERENCE_ORDER)
+        got = eng.eval([pick_ref])
+    model.free_state(st)
+    return steps
+
+
+def assert_reference_order_history(steps, bound=0.1):
+    """The engine's pick equals the reference-order pick at every step whose reference top-1 margin exceeds twice the
+    largest logit deviation seen on the walk (the rule the reference applies between its own GPU and CPU paths,
+    src/bin/bonsai-tools.rs:247, :278); prints the smallest margin and the largest deviation."""
+    dev = max(s["dev"] for s in steps)
+    rel = max(s["rel"] for s in steps)
+    margin = min(s["margin"] for s in steps)
+    decided = [s for s in steps if s["margin"] > 2 * dev]
+    print(f"reference-order walk: {len(steps)} steps, min top-1 margin {margin:.4g}, max |dlogit| {dev:.4g} "
+          f"({rel:.2e} of the largest logit), {len(decided)} steps decided by margin, {sum(s['same'] for s in steps)} picks equal")
+    assert dev <= bound
+    assert all(s["same"] for s in decided)
+    return dev, rel, margin
