@@ -133,13 +133,15 @@ IT_API int it_ctx_create(int device, size_t arena_floats, it_ctx** out) {
     it_ctx* c = new it_ctx(); c->device = device; c->arena = nullptr; c->arena_floats = arena_floats; c->sm_count = prop.multiProcessorCount;
     c->argmax_partials = nullptr; c->argmax_counter = nullptr; c->stream = nullptr; c->capturing = false;
     c->peers_dev = nullptr; c->rank = 0; c->world = 1; for (int i = 0; i < IT_MAX_PEERS; i++) c->peer_base[i] = nullptr;
-    c->pdl_safe_q8 = nullptr; c->error_flag_host = nullptr; c->error_flag_dev = nullptr;
+    c->pdl_safe_q8 = nullptr; c->error_flag_host = nullptr; c->error_flag_dev = nullptr; c->grid_sync = nullptr;
     cudaError_t e1 = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     c->ll_slots = arena_floats < IT_LL_MAX_SLOTS ? arena_floats : IT_LL_MAX_SLOTS;
     const size_t arena_bytes = arena_floats * sizeof(float) + IT_ARENA_TAIL + 2 * c->ll_slots * 8;
     cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc(&c->arena, arena_bytes) : e1;
     cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc(&c->argmax_partials, IT_ARGMAX_MAX_BLOCKS * sizeof(unsigned long long)) : e2;
     cudaError_t e4 = e3 == cudaSuccess ? cudaMalloc(&c->argmax_counter, 256) : e3;
+    if (e4 == cudaSuccess) e4 = cudaMalloc(&c->grid_sync, 256);
+    if (e4 == cudaSuccess) e4 = cudaMemsetAsync(c->grid_sync, 0, 256, c->stream);
     if (e4 == cudaSuccess) e4 = cudaHostAlloc(&c->error_flag_host, sizeof(int), cudaHostAllocMapped);
     if (e4 == cudaSuccess) { *c->error_flag_host = 0; e4 = cudaHostGetDevicePointer(&c->error_flag_dev, c->error_flag_host, 0); }
     if (e4 != cudaSuccess) { it_ctx_destroy(c); return it_fail(e4 == cudaErrorMemoryAllocation ? IT_ENOMEM : IT_ECUDA, "it_ctx_create: %s", cudaGetErrorString(e4)); }
@@ -156,6 +158,7 @@ IT_API void it_ctx_destroy(it_ctx* c) {
     if (c->peers_dev) cudaFree(c->peers_dev);
     for (auto& kv : c->signs) cudaFree(kv.second);
     if (c->error_flag_host) cudaFreeHost(c->error_flag_host);
+    if (c->grid_sync) cudaFree(c->grid_sync);
     if (c->argmax_counter) cudaFree(c->argmax_counter);
     if (c->argmax_partials) cudaFree(c->argmax_partials);
     if (c->arena) cudaFree(c->arena);
@@ -216,6 +219,8 @@ int it_check_device_error(it_ctx* c, const char* who) {
     if (c->error_flag_host && *(volatile int*)c->error_flag_host) {
         const int code = *(volatile int*)c->error_flag_host;
         *(volatile int*)c->error_flag_host = 0;
+        // a persistent kernel that gave up leaves its barrier words inconsistent and the abort word set
+        if (c->grid_sync && !c->capturing) { cudaMemsetAsync(c->grid_sync, 0, 256, c->stream); cudaStreamSynchronize(c->stream); }
         return it_fail(IT_ETIMEOUT, "%s: a kernel gave up on a bounded wait (site %d); its results are not valid", who, code);
     }
     return IT_OK;

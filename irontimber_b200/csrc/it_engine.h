@@ -31,8 +31,11 @@ struct it_arena_layout {   // element offsets into the context's f32 arena; ever
     size_t big1_stride, big2_stride, o_stride, logits_stride;
 };
 
+struct it_step_state;   // geometry and device tables of the persistent decode-step kernel (it_step.cu)
+
 struct it_engine {
     it_ctx* ctx;
+    it_step_state* step;                             // null when the step runs op by op (row shards, unsupported geometry, IT_STEP_KERNEL=0)
     it_model_config cfg;
     uint64_t seed;
     bool has_mtp;
@@ -98,3 +101,10 @@ static inline bool it_cfg_recurrent(const it_model_config& c, int il) { return (
 // row; nck: recurrent-state checkpoints to take (after rows 0..nck-1); from_dev: token ids are already in toks_dev and the
 // position is read from pos_dev (recorded decode step).
 int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_rows, int nck, bool from_dev);
+
+// The whole single-row pass as one persistent kernel (it_step.cu).  it_step_prepare decides whether the engine can use it
+// (e->step stays null otherwise); it_step_launch enqueues one step: flags 1 = the token is the previous pick (amx) instead
+// of toks_dev[0], 2 = hand the pick over to the next step (toks_dev[0] = pick, position + 1), 4 = logits and pick wanted.
+int it_step_prepare(it_engine* e);
+void it_step_release(it_engine* e);
+int it_step_launch(it_engine* e, int flags);

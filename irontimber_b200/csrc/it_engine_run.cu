@@ -41,6 +41,8 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
     const int cd = it_cfg_conv_dim(c), inner = c.ssm_inner, nv = c.ssm_vheads, sd = c.ssm_state, nk = c.ssm_groups, qk = it_cfg_qk(c);
     IT_CHECK_ARG(nt >= 1 && nt <= IT_MAXT && nck >= 0 && nck <= IT_MAXCK && nck < nt + 1 && (logit_rows != 2 || nt <= IT_MAXLOGIT), "engine: bad pass geometry");
     if (e->pos + nt > c.ctx_len) return it_fail(IT_ESTATE, "engine: context full (%d + %d > %d)", e->pos, nt, c.ctx_len);   // src/vk/mod.rs:765
+    // a single row whose token and position are already on the device: the whole pass is one persistent kernel
+    if (e->step && nt == 1 && nck == 0 && from_dev) return it_step_launch(e, logit_rows ? 4 : 0);
     const int* pos_ptr = from_dev ? e->pos_dev : nullptr; const int pos0 = from_dev ? 0 : e->pos;
     if (!from_dev) {
         for (int t = 0; t < nt; t++) { if (toks[t] >= (uint32_t)c.n_vocab) return it_fail(IT_EINVAL, "engine: token id %u outside the vocabulary", toks[t]); e->host_pin[t] = toks[t]; }
@@ -269,9 +271,13 @@ int begin_device_decode(it_engine* e) {
     IT_CUDA(cudaMemcpyAsync(e->pos_dev, e->host_pin + 2 * IT_MAXT, 4, cudaMemcpyHostToDevice, cx->stream));
     if (e->step_graph) return IT_OK;
     IT_TRY(it_capture_begin(cx));
-    k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 0);
-    int r = it_engine_run_chunk(e, nullptr, 1, 1, 0, true);
-    k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 1);
+    int r;
+    if (e->step) r = it_step_launch(e, 1 | 2 | 4);       // takes the previous pick as its token and hands its own pick over
+    else {
+        k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 0);
+        r = it_engine_run_chunk(e, nullptr, 1, 1, 0, true);
+        k_set_tokens<<<1, 1, 0, cx->stream>>>(cx->arena + e->lay.amx, e->toks_dev, e->pos_dev, 1);
+    }
     it_graph* g = nullptr; int r2 = it_capture_end(cx, &g);
     if (r || r2) { if (g) it_graph_destroy(g); return r ? r : r2; }
     e->step_graph = g;

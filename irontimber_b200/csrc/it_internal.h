@@ -112,6 +112,9 @@ struct it_ctx {
     // costs nothing on the normal path
     int* error_flag_host;
     int* error_flag_dev;
+    // words of the grid-wide barrier of persistent kernels: [0] arrivals so far, [1] arrivals at the end of the last
+    // launch, [2] abort word (set by a CTA whose wait ran out; cleared by the host together with the error flag)
+    unsigned* grid_sync;
     // Programmatic-dependent-launch bookkeeping: the q8 buffer whose contents are known to be complete by the
     // time the most recently enqueued kernel lets its dependents start (null after any op that is not a matvec).
     const it_q8* pdl_safe_q8;

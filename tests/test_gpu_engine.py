@@ -224,3 +224,28 @@ def test_context_capacity_is_enforced_on_every_path(orc):
         assert len(eng.generate(list(range(10)), 7)) == 7      # exactly fills it
     finally:
         eng.close()
+
+
+def test_step_kernel_and_per_op_schedule_agree(orc, monkeypatch):
+    """A single-row pass runs as one persistent kernel by default; IT_STEP_KERNEL=0 runs the same pass op by op.  Logits,
+    picks, histories and state must not depend on the choice."""
+    from irontimber_b200.engine import CudaEngine, ModelConfig
+    results = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("IT_STEP_KERNEL", flag)
+        eng = CudaEngine(tiny_config(ModelConfig), seed=41, with_mtp=True)
+        try:
+            eng.eval(PROMPT[:7], want_logits=False)
+            lgs = [bits(eng.eval([t])).copy() for t in PROMPT[7:]]
+            hist = eng.generate(PROMPT[:3], 20)
+            n_kernels = eng.step_kernels()
+            states = [bits(eng.state(il, k)).copy() for il in range(eng.cfg.n_layer) for k in ((0, 1) if eng.cfg.is_recurrent(il) else (2, 3))]
+            out3, st3 = eng.generate_mtp_k(PROMPT, 14, 3)
+            results.append((lgs, hist, states, out3, st3, n_kernels))
+        finally:
+            eng.close()
+    a, b = results
+    assert a[5] == 1 and b[5] > 10
+    assert all(np.array_equal(x, y) for x, y in zip(a[0], b[0]))
+    assert a[1] == b[1] and a[3:5] == b[3:5]
+    assert all(np.array_equal(x, y) for x, y in zip(a[2], b[2]))
