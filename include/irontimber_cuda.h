@@ -244,6 +244,10 @@ int it_engine_generate(it_engine* e, const uint32_t* prompt, size_t n_prompt, si
 int it_engine_decode_steps(it_engine* e, size_t n, uint32_t* last_pick);
 /* Kernel launches of one recorded greedy step (>= 0; counted from the recorded graph), or a negative code. */
 int it_engine_step_kernels(it_engine* e);
+/* Diagnostics of the persistent decode-step kernel (engine built with the environment value IT_STEP_TRACE=1): the
+ * nanosecond clock at which CTA 0 and the last CTA arrived at and left each grid barrier of the most recent step,
+ * out[(cta * 1024 + barrier) * 2 + {0 arrive, 1 leave}] with cta in {0, 1}; max_barriers must be 1024. */
+int it_engine_step_trace(it_engine* e, uint64_t* out, size_t max_barriers);
 
 /* MtpBackend trait (src/mtp.rs:150-163), one to one. */
 int it_engine_mtp_prefill(it_engine* e, const uint32_t* prompt, size_t n, uint32_t* next);

@@ -85,6 +85,7 @@ SIGNATURES = {
     "it_engine_generate": (C.c_int, [P, P, c_size, c_size, C.c_uint32, P, C.POINTER(c_size)]),
     "it_engine_decode_steps": (C.c_int, [P, c_size, C.POINTER(C.c_uint32)]),
     "it_engine_step_kernels": (C.c_int, [P]),
+    "it_engine_step_trace": (C.c_int, [P, P, c_size]),
     "it_engine_mtp_prefill": (C.c_int, [P, P, c_size, C.POINTER(C.c_uint32)]),
     "it_engine_mtp_single": (C.c_int, [P, C.c_uint32, C.POINTER(C.c_uint32)]),
     "it_engine_mtp_draft": (C.c_int, [P, P, c_size, C.POINTER(C.c_uint32)]),

@@ -39,12 +39,16 @@
 
 namespace {
 
-constexpr int ST_CW = 8;                               // tiles per ring slot = warps per consumer group
-constexpr int ST_NG = 2;                               // consumer groups; group j takes the chunks k of the CTA's stream with k % ST_NG == j
+constexpr int ST_CW = 4;                               // warps per consumer group
+constexpr int ST_NG = 3;                               // consumer groups; group j takes the chunks k of the CTA's stream with k % ST_NG == j
+constexpr int ST_TPW = 2;                              // tiles a warp takes from a chunk (computed side by side)
+constexpr int ST_TPC = ST_CW * ST_TPW;                 // tiles per chunk = per ring slot
 constexpr int ST_NCONS = ST_CW * ST_NG;                // consumer warps
 constexpr int ST_CT = ST_NCONS * 32;                   // consumer threads
-constexpr int ST_THREADS = ST_CT + 32;                 // + the producer warp
-constexpr int ST_CHUNK = ST_CW * IT_TILE_BYTES;        // bytes of one ring slot
+constexpr int ST_NSUM = 2;                             // warps that only add the per-block terms of finished row groups in block order
+constexpr int ST_TB = 3;                               // terms buffers (row groups in flight between the consumer warps and the sum warps)
+constexpr int ST_THREADS = ST_CT + (ST_NSUM + 1) * 32; // + the sum warps + the producer warp
+constexpr int ST_CHUNK = ST_TPC * IT_TILE_BYTES;       // bytes of one ring slot
 constexpr int ST_SMEM = 227 * 1024;                    // dynamic shared memory of the CTA
 constexpr int ST_BARS = 1024;                          // bytes reserved for mbarriers and flags
 constexpr int ST_SD = 128;                             // delta-rule state size this kernel is built for
@@ -72,7 +76,9 @@ struct StepParams {
     unsigned* sync;                    // [0] arrivals, [1] arrivals at the end of the last launch, [2] abort word
     unsigned long long* partials;      // one greedy-pick partial per CTA
     int* error_flag;
+    unsigned long long* trace;         // optional: clock readings of CTA 0 and of the last CTA at every grid barrier (arrive, leave)
     int slots, scratch;                // ring slots; bytes of the phase scratch that follows the ring
+    int gdn_off;                       // where the delta-net block keeps its state tile inside the scratch (clear of the input projection's buffers)
     int flags;                         // bit 0: the token is the previous pick (amx) instead of toks[0]; bit 1: hand the pick over (toks[0], pos + 1); bit 2: logits wanted
 };
 
@@ -83,11 +89,22 @@ __device__ __forceinline__ Pick pick_better(Pick a, Pick b) { return (b.v > a.v 
 struct Cta {
     unsigned char* smem; unsigned char* scratch; unsigned bars; volatile int* abort_flag;
     int tid, warp, lane;
-    int slot; unsigned ph; int kg;     // ring position of the consumers: next slot, its phase, (chunk index) % ST_NG
+    unsigned q;                        // chunks of the CTA's stream the consumers have passed (slot = q % slots, phase = (q / slots) & 1; slots is a power of two)
+    unsigned nseq;                     // row groups this CTA has started in all matvec phases so far (terms buffer = nseq % ST_TB)
+    unsigned mph;                      // matvec phases finished so far
+    unsigned tf, te, pd, ps;           // mbarriers: terms full [ST_TB], terms empty [ST_TB], phase done, phase started
+    const StepLayer* lay;              // the two shared-memory copies of layer descriptions (layer il at lay[il & 1])
     unsigned target;                   // arrivals the next grid barrier waits for
+    int nsync;                         // grid barriers passed so far (index into the trace)
+    int evt_on, evt_warp, evt_cta;     // diagnostics: fine-grained events of one warp of one CTA
 };
+constexpr int ST_TRACE_MAX = 1024;     // barriers recorded per traced CTA
+constexpr int ST_EVT_MAX = 2048;       // fine-grained events (diagnostics)
+#define ST_EVT(P, c, id) do { if ((P).trace && (c).evt_on && blockIdx.x == (unsigned)(c).evt_cta && (c).lane == 0 && (c).warp == (c).evt_warp) { unsigned long long* ev = (P).trace + 4 * ST_TRACE_MAX; unsigned n = (unsigned)ev[0]; if (n < ST_EVT_MAX - 1) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); ev[1 + n] = ((unsigned long long)(id) << 48) | (t & 0xffffffffffffull); ev[0] = n + 1; } } } while (0)
 
 __device__ __forceinline__ void cons_sync() { consumer_barrier<ST_CT>(); }
+// four u8 x s8 products added to c
+__device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) { int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
 
 // Barrier over the grid (consumer threads only; the producer warp never takes part).  Writes made by any CTA before the
 // barrier are visible to every CTA after it: thread 0 fences, announces the CTA with a release add, waits with acquire
@@ -97,33 +114,55 @@ __device__ __forceinline__ bool grid_sync(const StepParams& P, Cta& c, int site)
     cons_sync();
     if (c.tid == 0 && *c.abort_flag) atomicExch(P.sync + 2, 1u);      // a wait of this CTA ran out: tell the others
     if (c.tid == 0 && !*c.abort_flag) {
+        const bool traced = P.trace && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && c.nsync < ST_TRACE_MAX;
+        unsigned long long* rec = traced ? P.trace + ((size_t)(blockIdx.x ? 1 : 0) * ST_TRACE_MAX + c.nsync) * 2 : nullptr;
+        if (rec) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); rec[0] = t; }
         c.target += gridDim.x;
-        __threadfence();
+        // release: the CTA's writes (ordered before this thread by the barrier above) become visible before the arrival
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(P.sync) : "memory");
         const long long t0 = clock64();
         for (unsigned it = 0;; it++) {
-            unsigned v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.sync) : "memory");
+            unsigned v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.sync) : "memory");
             if ((int)(v - c.target) >= 0) break;
             if ((it & 63u) == 63u) {
                 if (*reinterpret_cast<volatile unsigned*>(P.sync + 2)) { *c.abort_flag = 1; break; }
                 if (clock64() - t0 > WAIT_CLOCKS) { atomicExch(P.error_flag, 100 + site); atomicExch(P.sync + 2, 1u); *c.abort_flag = 1; break; }
             }
         }
-        __threadfence();
+        asm volatile("fence.acq_rel.gpu;" ::: "memory");             // acquire: what the other CTAs wrote before they arrived
+        if (rec) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); rec[1] = t; }
+        c.nsync++;
     }
     cons_sync();
     return !*c.abort_flag;
 }
 
+// The ternary matvecs of a step in order: four per layer (input projection, output projection, gate/up, down), then the
+// LM head.  Every role of the CTA (producer, consumers, sum warps) walks this list with ONE copy of its loop in the code:
+// the kernel is executed once per step, front to back, so its size is what the instruction cache sees.
+struct MatDesc { const uint8_t* tiles; int nb, rows, accum, pick; size_t y_off; };
+__device__ __forceinline__ MatDesc mat_desc(const StepParams& P, int mp) {
+    MatDesc d; d.pick = 0;
+    const int il = mp >> 2, sub = mp & 3;
+    if (il >= P.n_layer) { d.tiles = P.output; d.nb = P.e / 128; d.rows = P.n_vocab; d.accum = 0; d.y_off = P.logits; d.pick = 1; return d; }
+    const StepLayer& L = P.layers[il];
+    if (sub == 0) { d.tiles = L.in_proj; d.nb = P.e / 128; d.rows = L.in_rows; d.accum = 0; d.y_off = P.big1; }
+    else if (sub == 1) { d.tiles = L.out_proj; d.nb = (L.recurrent ? P.inner : P.nh * P.hd) / 128; d.rows = P.e; d.accum = 1; d.y_off = P.x; }
+    else if (sub == 2) { d.tiles = L.gate_up; d.nb = P.e / 128; d.rows = 2 * P.ff; d.accum = 0; d.y_off = P.big1; }
+    else { d.tiles = L.down; d.nb = P.ff / 128; d.rows = P.e; d.accum = 1; d.y_off = P.x; }
+    return d;
+}
+__device__ __forceinline__ int mat_count(const StepParams& P) { return 4 * P.n_layer + ((P.flags & 4) ? 1 : 0); }
+
 // ---------------------------------------------------------------- producer
 struct Ring { int s; unsigned ph; int issued; };
 __device__ __forceinline__ bool produce_matrix(const StepParams& P, const Cta& c, Ring& r, const uint8_t* tiles, int nb, int rows, int* error_flag) {
-    const int rgs = (rows + 31) / 32, cpr = (nb + ST_CW - 1) / ST_CW;
+    const int rgs = (rows + 31) / 32, cpr = (nb + ST_TPC - 1) / ST_TPC;
     for (int rg = blockIdx.x; rg < rgs; rg += gridDim.x) {
         const uint8_t* src = tiles + (size_t)rg * nb * IT_TILE_BYTES;
         for (int cq = 0; cq < cpr; cq++) {
             if (!mbar_wait(c.bars + 8 * (P.slots + r.s), r.ph ^ 1u, c.abort_flag, error_flag, 2)) return false;
-            const int ntile = min(ST_CW, nb - cq * ST_CW);
+            const int ntile = min(ST_TPC, nb - cq * ST_TPC);
             const unsigned bytes = (unsigned)ntile * IT_TILE_BYTES;
             mbar_expect_tx(c.bars + 8 * r.s, bytes);
             bulk_load(smem_u32(c.smem + r.s * ST_CHUNK), src + (size_t)cq * ST_CHUNK, bytes, c.bars + 8 * r.s);
@@ -133,18 +172,11 @@ __device__ __forceinline__ bool produce_matrix(const StepParams& P, const Cta& c
     }
     return true;
 }
-__device__ void producer(const StepParams& P, const Cta& c) {
+__device__ __forceinline__ void producer(const StepParams& P, const Cta& c) {
     Ring r{0, 0u, 0};
-    const int nb_e = P.e / 128;
     bool ok = true;
-    for (int il = 0; il < P.n_layer && ok; il++) {
-        const StepLayer& L = P.layers[il];
-        ok = produce_matrix(P, c, r, L.in_proj, nb_e, L.in_rows, P.error_flag)
-          && produce_matrix(P, c, r, L.out_proj, (L.recurrent ? P.inner : P.nh * P.hd) / 128, P.e, P.error_flag)
-          && produce_matrix(P, c, r, L.gate_up, nb_e, 2 * P.ff, P.error_flag)
-          && produce_matrix(P, c, r, L.down, P.ff / 128, P.e, P.error_flag);
-    }
-    if (ok && (P.flags & 4)) ok = produce_matrix(P, c, r, P.output, nb_e, P.n_vocab, P.error_flag);
+    const int nmat = mat_count(P);
+    for (int mp = 0; mp < nmat && ok; mp++) { const MatDesc d = mat_desc(P, mp); ok = produce_matrix(P, c, r, d.tiles, d.nb, d.rows, P.error_flag); }
     if (!ok || *c.abort_flag) {
         // leave only after every copy this thread started has landed (each wait bounded by the clock limit)
         const int first = r.issued > P.slots ? r.issued - P.slots : 0;
@@ -156,105 +188,153 @@ __device__ void producer(const StepParams& P, const Cta& c) {
 }
 
 // ---------------------------------------------------------------- ternary matvec phase (one activation row)
-// Same arithmetic as k_matvec_t2<1> (it_matvec_t2.cu): per 32 x 128 tile eight mma.m16n8k32 (u8 x s8) give the exact
-// integer block sums; one warp per row group then adds (d_w * d_x) * float(S - sum128) in ascending block order.
-struct MvSmem { int x, dx, s128, terms, wsc, plane, total; };
+// Same arithmetic as k_matvec_t2<1> (it_matvec_t2.cu): per 32 x 128 tile the exact integer block sums, the per-block terms
+// (d_w * d_x) * float(S - sum128), and per row group one warp that adds the terms in ascending block order.  The sixteen
+// consumer warps only form terms; two sum warps add them, a row group at a time, out of ST_TB buffers handed over through
+// mbarriers, so that the consumers never stop at a row-group boundary.
+struct MvSmem { int x, dx, s128, terms, plane, total; };
 __host__ __device__ inline MvSmem mv_layout(int nb) {
     MvSmem L; int o = 0;
-    L.plane = nb * 32 + 4;
+    L.plane = nb * 32;
     L.x = o; o += nb * 128 + 16;
     L.dx = o; o += (nb / 2) * 4;
     L.s128 = o; o += nb * 4;
-    o = (o + 15) & ~15;
-    L.terms = o; o += 2 * L.plane * 4;
-    o = (o + 15) & ~15;
-    L.wsc = o; o += 2 * nb * 64;
+    o = (o + 127) & ~127;
+    L.terms = o; o += ST_TB * L.plane * 4;
     L.total = o;
     return L;
 }
 
-template <bool PICK>
-__device__ void matvec_phase(const StepParams& P, Cta& c, int nb, int rows, size_t y_off, int accum, Pick& best) {
+// prefetch_layer: when set, the delta-net block's state tile of that layer is requested right after the activation row has
+// been staged (asynchronous copies for the phase after this one)
+__device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c);
+__device__ __forceinline__ void matvec_phase(const StepParams& P, Cta& c, int nb, int rows, const StepLayer* prefetch_layer) {
     const MvSmem L = mv_layout(nb);
     int8_t* xs = reinterpret_cast<int8_t*>(c.scratch + L.x);
     float* dxs = reinterpret_cast<float*>(c.scratch + L.dx);
     int* sss = reinterpret_cast<int*>(c.scratch + L.s128);
     const int tid = c.tid, warp = c.warp, lane = c.lane;
+    if (lane == 0) mbar_arrive(c.ps);                                // the sum warps may enter this phase (they never run ahead of the consumers)
     {   // the q8k row, its scales and block sums, once per CTA (written by other CTAs before the last barrier: read through L2)
         for (int ch = tid; ch < nb * 8; ch += ST_CT) cp_async16(xs + 16 * ch, P.qs + 16 * ch);
         for (int i = tid; i < nb / 2; i += ST_CT) dxs[i] = __ldcg(P.qd + i);
         for (int i = tid; i < nb; i += ST_CT) sss[i] = __ldcg(P.qsum + i);
         cp_async_wait_all();
+        if (prefetch_layer) gdn_prefetch(P, *prefetch_layer, c);
         cons_sync();
     }
-    const int g = lane >> 2, t = lane & 3;
+    const int t = lane & 3;
     const int group = warp / ST_CW, wi = warp % ST_CW;
-    const int rgs = (rows + 31) / 32, cpr = (nb + ST_CW - 1) / ST_CW;
-    float* arena = P.arena;
-    int i = 0;
-    for (int rg = blockIdx.x; rg < rgs; rg += gridDim.x, i++) {
-        int* tbuf = reinterpret_cast<int*>(c.scratch + L.terms) + (i & 1) * L.plane;
-        uint2* wsc = reinterpret_cast<uint2*>(c.scratch + L.wsc + (i & 1) * nb * 64);
-        for (int cq = 0; cq < cpr; cq++) {
-            const bool mine = c.kg == group;
-            const int cs = c.slot; const unsigned cph = c.ph;
-            if (++c.slot == P.slots) { c.slot = 0; c.ph ^= 1u; }
-            if (++c.kg == ST_NG) c.kg = 0;
-            if (!mine) continue;
-            const int b = cq * ST_CW + wi;
-            const bool ready = mbar_wait(c.bars + 8 * cs, cph, c.abort_flag, P.error_flag, 3);
-            if (ready && b < nb) {
-                const unsigned char* tile = c.smem + cs * ST_CHUNK + wi * IT_TILE_BYTES;
-                const uint4 wa = *reinterpret_cast<const uint4*>(tile + 16 * lane);
-                const uint4 wb = *reinterpret_cast<const uint4*>(tile + 512 + 16 * lane);
-                const uint4* xp = reinterpret_cast<const uint4*>(xs + 128 * b + 32 * t);
-                const uint4 xa = xp[0], xb4 = xp[1];
-                int cx[4] = {0, 0, 0, 0}, cy[4] = {0, 0, 0, 0};
-                const uint32_t w[8] = { wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w };
-                const uint32_t xb[8] = { xa.x, xa.y, xa.z, xa.w, xb4.x, xb4.y, xb4.z, xb4.w };
+    const int rgs = (rows + 31) / 32, cpr = (nb + ST_TPC - 1) / ST_TPC;
+    const int trow = (lane >> 2) + 8 * t;                            // the matrix row of a tile whose term this lane forms: g + 8 t
+    const unsigned smask = (unsigned)P.slots - 1u; const int sshift = 31 - __clz(P.slots);
+    // One activation row: integer dot products on the SIMT pipe (dp4a, u8 x s8).  Lane 4 g + t owns the 32 columns
+    // 32 t .. 32 t + 31 of a tile and, per 32-bit word, the four matrix rows g, g + 8, g + 16, g + 24 (bit pairs 0..3 of
+    // every byte): masking a word with 0x03030303 << 2 i leaves row g + 8 i's four codes scaled by 4^i.  The four lanes of a
+    // row group g then add their sums (exact integers) in a reduce-scatter that leaves row g + 8 t with lane t, which forms
+    // that row's term.  (At eight activation columns the tensor-core path of it_matvec_t2.cu does this work; at one column
+    // its dependent mma chain costs more latency than these short instructions, and this kernel has 16 warps per SM.)
+    auto dots = [&](const unsigned char* tile, int b, int (&a)[4]) {
+        const uint4 wa = *reinterpret_cast<const uint4*>(tile + 16 * lane);
+        const uint4 wb = *reinterpret_cast<const uint4*>(tile + 512 + 16 * lane);
+        const uint4* xp = reinterpret_cast<const uint4*>(xs + 128 * b + 32 * t);
+        const uint4 xa = xp[0], xb4 = xp[1];
+        const uint32_t w[8] = { wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w };
+        const int xb[8] = { (int)xa.x, (int)xa.y, (int)xa.z, (int)xa.w, (int)xb4.x, (int)xb4.y, (int)xb4.z, (int)xb4.w };
+        a[0] = a[1] = a[2] = a[3] = 0;
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint32_t lo = w[2 * j], hi = w[2 * j + 1];
-                    mma_u8s8(cx, lo & 0x03030303u, lo & 0x0c0c0c0cu, hi & 0x03030303u, hi & 0x0c0c0c0cu, xb[2 * j], xb[2 * j + 1]);
-                    mma_u8s8(cy, lo & 0x30303030u, lo & 0xc0c0c0c0u, hi & 0x30303030u, hi & 0xc0c0c0c0u, xb[2 * j], xb[2 * j + 1]);
-                }
-                if (t == 0) {
-                    // rows g, g + 8, g + 16, g + 24 side by side, still carrying the factors 1, 4, 16, 64: row r of the tile sits at 4 * (r & 7) + (r >> 3)
-                    *reinterpret_cast<int4*>(tbuf + b * 32 + 4 * g) = make_int4(cx[0], cx[2], cy[0], cy[2]);
-                    wsc[b * 8 + g] = *reinterpret_cast<const uint2*>(tile + 1024 + 8 * g);
+        for (int k = 0; k < 8; k++) {
+            a[0] = dp4a_us(w[k] & 0x03030303u, xb[k], a[0]);
+            a[1] = dp4a_us(w[k] & 0x0c0c0c0cu, xb[k], a[1]);
+            a[2] = dp4a_us(w[k] & 0x30303030u, xb[k], a[2]);
+            a[3] = dp4a_us(w[k] & 0xc0c0c0c0u, xb[k], a[3]);
+        }
+    };
+    auto term = [&](const unsigned char* tile, int b, const int (&a)[4], float* tbuf) {
+        const bool hi2 = t & 2, hi1 = t & 1;
+        int k0 = hi2 ? a[2] : a[0], k1 = hi2 ? a[3] : a[1];
+        const int s0 = hi2 ? a[0] : a[2], s1 = hi2 ? a[1] : a[3];
+        k0 += __shfl_xor_sync(0xffffffffu, s0, 2); k1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        int S = hi1 ? k1 : k0;
+        S += __shfl_xor_sync(0xffffffffu, hi1 ? k0 : k1, 1);
+        const __half dwh = *reinterpret_cast<const __half*>(tile + 1024 + 2 * lane);   // scale of row g + 8 t: half 4 g + t
+        tbuf[b * 32 + trow] = __fmul_rn(__fmul_rn(__half2float(dwh), dxs[b >> 1]), (float)((S >> (2 * t)) - sss[b]));
+    };
+    unsigned n = c.nseq;
+    for (int rg = blockIdx.x; rg < rgs; rg += gridDim.x, n++) {
+        const unsigned k = n % ST_TB, u = n / ST_TB;
+        float* tbuf = reinterpret_cast<float*>(c.scratch + L.terms) + k * L.plane;
+        // the buffer's previous row group has been added up (the sum warp's arrival number u - 1)
+        if (u && !mbar_wait(c.te + 8 * k, (u - 1) & 1u, c.abort_flag, P.error_flag, 4)) break;
+        for (int cq = (int)((unsigned)(group + ST_NG) - c.q % ST_NG) % ST_NG; cq < cpr; cq += ST_NG) {      // the chunks of this row group that fall to this group
+            const unsigned q = c.q + (unsigned)cq;
+            const int cs = (int)(q & smask); const unsigned cph = (q >> sshift) & 1u;
+            const int b0 = cq * ST_TPC + wi, b1 = b0 + ST_CW;
+            const bool ready = mbar_wait(c.bars + 8 * cs, cph, c.abort_flag, P.error_flag, 3);
+            if (ready && b0 < nb) {
+                const unsigned char* tile0 = c.smem + cs * ST_CHUNK + wi * IT_TILE_BYTES;
+                const unsigned char* tile1 = tile0 + ST_CW * IT_TILE_BYTES;
+                int a0[4], a1[4];
+                if (b1 < nb) {          // warp-uniform
+                    dots(tile0, b0, a0); dots(tile1, b1, a1);
+                    term(tile0, b0, a0, tbuf); term(tile1, b1, a1, tbuf);
+                } else {
+                    dots(tile0, b0, a0); term(tile0, b0, a0, tbuf);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(c.bars + 8 * (P.slots + cs));     // the slot may be refilled
         }
-        cons_sync();                                                     // every block sum of this row group is in shared memory
-        if (warp == (i % ST_NCONS)) {
-            // ordered f32 accumulation, one matrix row per lane, while the other warps go on with the next row group
-            const int row = rg * 32 + lane;
-            if (row < rows) {
-                const int* icol = tbuf + 4 * (lane & 7) + (lane >> 3);
-                const __half* hs = reinterpret_cast<const __half*>(wsc) + 4 * (lane & 7) + (lane >> 3);
-                const int sh = 2 * (lane >> 3);
-                float sum = 0.f;
-#pragma unroll 8
-                for (int b = 0; b < nb; b++)
-                    sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__half2float(hs[b * 32]), dxs[b >> 1]), (float)((icol[b * 32] >> sh) - sss[b])));
-                if (accum) sum = __fadd_rn(__ldcg(arena + y_off + row), sum);
-                __stcg(arena + y_off + row, sum);
-                if (PICK) best = pick_better(best, Pick{ sum, (unsigned)row });
-            }
-        }
+        c.q += (unsigned)cpr;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.tf + 8 * k);                        // this warp's terms of the row group are in place
     }
-    // the warp that added the last row group may still be reading the terms: the barrier that follows (grid_sync) orders that
+    c.nseq = n;
+    // the phase is over when the sum warps have stored its last results
+    mbar_wait(c.pd, c.mph & 1u, c.abort_flag, P.error_flag, 5);
+    c.mph++;
 }
 
-// ---------------------------------------------------------------- Hadamard + q8k phases
-__device__ __forceinline__ void had_phase(const StepParams& P, const Cta& c, int nblocks, const float* in, const float* signs,
-                                          unsigned perm_hd, unsigned perm_nk, unsigned perm_rep, const it_had_prologue& pro) {
-    if ((int)blockIdx.x < nblocks && c.tid < 256) {
-        it_had_smem& sm = *reinterpret_cast<it_had_smem*>(c.scratch);
-        it_hadamard_block<true>(sm, (unsigned)c.tid, blockIdx.x, 0, in, 0, 0, nullptr, 0, 0, signs, 1, 0, perm_hd, perm_nk, perm_rep,
-                                P.qs, P.qd, P.qsum, P.q_stride, pro);
+// The sum warps' side of a matvec phase: warp j adds the row groups whose sequence number is j modulo ST_NSUM.
+__device__ __forceinline__ void sum_warps(const StepParams& P, Cta& c) {
+    const int j = c.warp - ST_NCONS, lane = c.lane;
+    float* arena = P.arena;
+    Pick best{ -INFINITY, 0xffffffffu };
+    const int nmat = mat_count(P);
+    unsigned n = 0;
+    bool ok = true;
+    for (int mp = 0; mp < nmat && ok; mp++) {
+        const MatDesc d = mat_desc(P, mp);
+        const MvSmem L = mv_layout(d.nb);
+        const int rgs = (d.rows + 31) / 32;
+        // not before the consumers have entered the phase: a CTA without row groups in a phase would otherwise run through
+        // its phase-done arrivals and leave the consumers waiting on a parity that has come round again
+        if (!mbar_wait(c.ps, (unsigned)mp & 1u, c.abort_flag, P.error_flag, 7)) break;
+        for (int rg = blockIdx.x; rg < rgs; rg += gridDim.x, n++) {
+            if ((int)(n % ST_NSUM) != j) continue;
+            const unsigned k = n % ST_TB, u = n / ST_TB;
+            const int row = rg * 32 + lane;
+            const float old = (d.accum && row < d.rows) ? __ldcg(arena + d.y_off + row) : 0.f;   // on its way while the terms are still being formed
+            if (!mbar_wait(c.tf + 8 * k, u & 1u, c.abort_flag, P.error_flag, 6)) { ok = false; break; }
+            if (row < d.rows) {
+                const float* tcol = reinterpret_cast<const float*>(c.scratch + L.terms) + k * L.plane + lane;
+                float sum = 0.f;
+#pragma unroll 8
+                for (int b = 0; b < d.nb; b++) sum = __fadd_rn(sum, tcol[b * 32]);
+                if (d.accum) sum = __fadd_rn(old, sum);
+                __stcg(arena + d.y_off + row, sum);
+                if (d.pick) best = pick_better(best, Pick{ sum, (unsigned)row });
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(c.te + 8 * k);
+        }
+        if (d.pick) {       // greedy pick (first index of the maximum) over this warp's rows, left behind the layer descriptions
+#pragma unroll
+            for (unsigned mm = 16; mm > 0; mm >>= 1) { Pick o{ __shfl_xor_sync(0xffffffffu, best.v, mm), __shfl_xor_sync(0xffffffffu, best.i, mm) }; best = pick_better(best, o); }
+            if (lane == 0) reinterpret_cast<Pick*>(const_cast<StepLayer*>(c.lay) + 2)[j] = best;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.pd);
     }
 }
 
@@ -264,11 +344,26 @@ __device__ __forceinline__ void had_phase(const StepParams& P, const Cta& c, int
 // runs of a key group are recomputed by each of the value heads that share it.  The new conv state of the runs this CTA
 // is responsible for (its own v run; the q and k runs when it is the first head of the group) is returned in `keep`
 // and stored after the next grid barrier, when no CTA reads the old state any more.
-struct ConvKeep { int ch; float st[8]; };
-__device__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c, ConvKeep& keep) {
+struct ConvKeep { int ch; float mx; };    // a conv channel whose state this thread shifts after the next barrier, and this step's input of that channel
+// Issued by the CTA of value head blockIdx.x while the input projection runs: the head's state tile (64 KB, it does not
+// depend on this step's activations) into its place in shared memory, and the head's beta / alpha rows into L2.
+__device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c) {
+    constexpr int SD = ST_SD, PPR = SD / 4;
+    const int h = blockIdx.x, tid = c.tid;
+    float* tile = reinterpret_cast<float*>(c.scratch + P.gdn_off);
+    const float4* m = reinterpret_cast<const float4*>(L.ssm_st + (size_t)h * SD * SD);
+    for (int f = tid; f < SD * PPR; f += ST_CT) { const int j = f / PPR, cc = f % PPR; cp_async16(tile + j * SD + ((cc ^ (j & 7)) << 2), m + f); }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int lines = P.e * 4 / 128;
+    for (int i = tid; i < 2 * lines; i += ST_CT) {
+        const float* row = (i < lines ? L.beta : L.alpha) + (size_t)h * P.e + (size_t)(i % lines) * 32;
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(row));
+    }
+}
+__device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c, ConvKeep& keep) {
     constexpr int SD = ST_SD, PPR = SD / 4;
     const int h = blockIdx.x, tid = c.tid, warp = c.warp, lane = c.lane, kh = h % P.nk, kk = P.conv_k, cd = P.cd;
-    float* tile = reinterpret_cast<float*>(c.scratch);               // [SD][SD], 16-byte pieces of row j stored at piece index ^ (j & 7)
+    float* tile = reinterpret_cast<float*>(c.scratch + P.gdn_off);   // [SD][SD], 16-byte pieces of row j stored at piece index ^ (j & 7); requested by gdn_prefetch
     float* vals = tile + SD * SD;                                    // [3][SD]: q, k, v runs after conv + SiLU
     float* os = vals + 3 * SD;                                       // [SD] delta-rule outputs
     float* scs = os + SD;                                            // [2] l2norm scales, [2] beta, alpha
@@ -276,33 +371,55 @@ __device__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c,
     const float* A = P.arena;
     auto piece = [&](int j, int cc) { return reinterpret_cast<float4*>(tile + j * SD + ((cc ^ (j & 7)) << 2)); };
     float* m = L.ssm_st + (size_t)h * SD * SD;
-    for (int f = tid; f < SD * PPR; f += ST_CT) cp_async16(piece(f / PPR, f % PPR), reinterpret_cast<const float4*>(m) + f);
-    asm volatile("cp.async.commit_group;" ::: "memory");
     keep.ch = -1;
+    // dense rows: warps 0-7 beta row h, warps 8-15 alpha row h, in the order of k_dense_rows (thread i of 256 adds the products
+    // i, i + 256, ... in f64).  The first sixteen products' operands are requested before anything else so that their
+    // latency overlaps the conv; the gate values the norm needs at the very end are requested here too.
+    // sixteen virtual warps (0-7: beta row h, 8-15: alpha row h) on the CTA's consumer warps; virtual thread i of a row's
+    // 256 adds the products i, i + 256, ... in f64 (the order of k_dense_rows)
+    const float* xr = A + P.xn;
+    float wv[16], xv[16];
+    {
+        const int t8 = (warp & 7) * 32 + lane; const float* wr = (warp >= 8 ? L.alpha : L.beta) + (size_t)h * P.e;
+#pragma unroll
+        for (int k = 0; k < 16; k++) { const int i = t8 + 256 * k; wv[k] = i < P.e ? wr[i] : 0.f; xv[k] = i < P.e ? __ldcg(xr + i) : 0.f; }
+    }
+    float zr[SD / 32], nwr[SD / 32];
+    if (warp == 0) {
+#pragma unroll
+        for (int i = 0; i < SD / 32; i++) { zr[i] = __ldcg(A + P.big1 + cd + h * SD + lane + 32 * i); nwr[i] = L.ssm_norm[lane + 32 * i]; }
+    }
     if (tid < 3 * SD) {
         const int r = tid / SD, cc = tid % SD;
         const int ch = (r == 0 ? kh * SD : r == 1 ? P.qk + kh * SD : 2 * P.qk + h * SD) + cc;
-        float st[8];
-        for (int i = 0; i < kk - 1; i++) st[i] = L.conv_st[(size_t)i * cd + ch];
+        float st[8], cw[8];                                          // kk <= 8 taps: fixed-size loops keep these in registers
+#pragma unroll
+        for (int i = 0; i < 8; i++) { st[i] = i < kk - 1 ? L.conv_st[(size_t)i * cd + ch] : 0.f; cw[i] = i < kk ? L.conv_w[ch * kk + i] : 0.f; }
         const float mx = __ldcg(A + P.big1 + ch);
         float s = 0.f;
-        for (int i = 0; i < kk; i++) s = it_add(s, it_mul(i < kk - 1 ? st[i] : mx, L.conv_w[ch * kk + i]));
+#pragma unroll
+        for (int i = 0; i < 8; i++) if (i < kk) s = it_add(s, it_mul(i < kk - 1 ? st[i] : mx, cw[i]));
         vals[r * SD + cc] = it_silu(s);
-        if (r == 2 || h < P.nk) {
-            keep.ch = ch;
-            for (int i = 0; i < kk - 2; i++) keep.st[i] = st[i + 1];
-            keep.st[kk - 2] = mx;
-        }
+        if (r == 2 || h < P.nk) { keep.ch = ch; keep.mx = mx; }
     }
-    {   // dense rows: warps 0-7 beta row h, warps 8-15 alpha row h (order of k_dense_rows)
-        const int half = tid >> 8, t8 = tid & 255;
-        const float* wr = (half ? L.alpha : L.beta) + (size_t)h * P.e; const float* xr = A + P.xn;
+    for (int vw = warp; vw < 16; vw += ST_NCONS) {
+        const int t8 = (vw & 7) * 32 + lane; const float* wr = (vw >= 8 ? L.alpha : L.beta) + (size_t)h * P.e;
+        if (vw != warp) {
+#pragma unroll
+            for (int k = 0; k < 16; k++) { const int i = t8 + 256 * k; wv[k] = i < P.e ? wr[i] : 0.f; xv[k] = i < P.e ? __ldcg(xr + i) : 0.f; }
+        }
         double s = 0.0;
-#pragma unroll 4
-        for (int i = t8; i < P.e; i += 256) s += (double)it_mul(wr[i], __ldcg(xr + i));
+#pragma unroll
+        for (int k = 0; k < 16; k++) if (t8 + 256 * k < P.e) s += (double)it_mul(wv[k], xv[k]);
+        for (int base = 16 * 256; base < P.e; base += 16 * 256) {
+#pragma unroll
+            for (int k = 0; k < 16; k++) { const int i = base + t8 + 256 * k; wv[k] = i < P.e ? wr[i] : 0.f; xv[k] = i < P.e ? __ldcg(xr + i) : 0.f; }
+#pragma unroll
+            for (int k = 0; k < 16; k++) if (base + t8 + 256 * k < P.e) s += (double)it_mul(wv[k], xv[k]);
+        }
 #pragma unroll
         for (int mm = 16; mm >= 1; mm >>= 1) s += __shfl_xor_sync(0xffffffffu, s, mm);
-        if (lane == 0) wsum[warp] = s;
+        if (lane == 0) wsum[vw] = s;
     }
     cons_sync();
     if (lane == 0 && warp < 2) {                                     // l2norm of the q run (warp 0) and the k run (warp 1): squares in index order
@@ -330,28 +447,44 @@ __device__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c,
         const float gg = it_mul(it_softplus(it_add(scs[3], L.dt[h])), L.a[h]);
         const float eg = it_expf(gg);
         const float scale = it_div(1.0f, it_sqrt((float)SD));
+        // Two passes over the thread's state row, eight 16-byte pieces at a time (requested together, then used in order).
+        // The first pass only reads: s = sum_i (row[i] * eg) * k[i] in index order.  The second forms row[i] * eg again (the
+        // same rounded product), adds k[i] * delta, stores the new state and accumulates the output in index order.
         float s = 0.f;
-#pragma unroll 4
-        for (int cc = 0; cc < PPR; cc++) {
-            float4 r = *piece(tid, cc); const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc);
-            r.x = it_mul(r.x, eg); r.y = it_mul(r.y, eg); r.z = it_mul(r.z, eg); r.w = it_mul(r.w, eg);
-            *piece(tid, cc) = r;
-            s = it_add(s, it_mul(r.x, k4.x)); s = it_add(s, it_mul(r.y, k4.y)); s = it_add(s, it_mul(r.z, k4.z)); s = it_add(s, it_mul(r.w, k4.w));
+#pragma unroll 1
+        for (int c0 = 0; c0 < PPR; c0 += 8) {
+            float4 rr[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) rr[u] = *piece(tid, c0 + u);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * (c0 + u));
+                s = it_add(s, it_mul(it_mul(rr[u].x, eg), k4.x)); s = it_add(s, it_mul(it_mul(rr[u].y, eg), k4.y));
+                s = it_add(s, it_mul(it_mul(rr[u].z, eg), k4.z)); s = it_add(s, it_mul(it_mul(rr[u].w, eg), k4.w));
+            }
         }
         const float delta = it_mul(it_sub(v, s), bt);
         float acc = 0.f;
-#pragma unroll 4
-        for (int cc = 0; cc < PPR; cc++) {
-            float4 r = *piece(tid, cc); const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc), q4 = *reinterpret_cast<const float4*>(qs + 4 * cc);
-            r.x = it_add(r.x, it_mul(k4.x, delta)); r.y = it_add(r.y, it_mul(k4.y, delta)); r.z = it_add(r.z, it_mul(k4.z, delta)); r.w = it_add(r.w, it_mul(k4.w, delta));
-            *piece(tid, cc) = r;
-            acc = it_add(acc, it_mul(r.x, q4.x)); acc = it_add(acc, it_mul(r.y, q4.y)); acc = it_add(acc, it_mul(r.z, q4.z)); acc = it_add(acc, it_mul(r.w, q4.w));
+#pragma unroll 1
+        for (int c0 = 0; c0 < PPR; c0 += 8) {
+            float4 rr[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) rr[u] = *piece(tid, c0 + u);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * (c0 + u)), q4 = *reinterpret_cast<const float4*>(qs + 4 * (c0 + u));
+                float4 r;
+                r.x = it_add(it_mul(rr[u].x, eg), it_mul(k4.x, delta)); r.y = it_add(it_mul(rr[u].y, eg), it_mul(k4.y, delta));
+                r.z = it_add(it_mul(rr[u].z, eg), it_mul(k4.z, delta)); r.w = it_add(it_mul(rr[u].w, eg), it_mul(k4.w, delta));
+                *piece(tid, c0 + u) = r;
+                acc = it_add(acc, it_mul(r.x, q4.x)); acc = it_add(acc, it_mul(r.y, q4.y)); acc = it_add(acc, it_mul(r.z, q4.z)); acc = it_add(acc, it_mul(r.w, q4.w));
+            }
         }
         os[tid] = it_mul(acc, scale);
     }
     cons_sync();
-    // the new state back to global memory (coalesced 16-byte stores by every thread) while warp 0 norms the outputs
-    for (int f = tid; f < SD * PPR; f += ST_CT) reinterpret_cast<float4*>(m)[f] = *piece(f / PPR, f % PPR);
+    // the new state back to global memory (coalesced 16-byte stores by warps 1..15) while warp 0 norms the outputs
+    if (warp > 0) for (int f = tid - 32; f < SD * PPR; f += ST_CT - 32) reinterpret_cast<float4*>(m)[f] = *piece(f / PPR, f % PPR);
     if (warp == 0) {
         float sc = 0.f;
         if (lane == 0) {
@@ -361,12 +494,11 @@ __device__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c,
             sc = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)SD), P.eps)));
         }
         sc = __shfl_sync(0xffffffffu, sc, 0);
-        const float* z = A + P.big1 + cd + h * SD;                   // the gate rows follow the qkv rows in the stacked output
-        float* o = P.arena + P.o + h * SD;
+        float* o = P.arena + P.o + h * SD;                           // zr: the gate rows, which follow the qkv rows in the stacked output
 #pragma unroll
         for (int i = 0; i < SD / 32; i++) {
             const int j = lane + 32 * i;
-            __stcg(o + j, it_mul(it_mul(it_mul(os[j], sc), L.ssm_norm[j]), it_silu(__ldcg(z + j))));
+            __stcg(o + j, it_mul(it_mul(it_mul(os[j], sc), nwr[i]), it_silu(zr[i])));
         }
     }
 }
@@ -376,7 +508,7 @@ __device__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c,
 // k_attn_prep and k_attention (it_support.cu; src/cpu.rs:252-272).  The k and v rows of the new position are recomputed by
 // each of the heads that share the KV head and used from shared memory (after the same f16 rounding the cache applies);
 // the first head of the group stores them into the cache.
-__device__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c) {
+__device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c) {
     const int h = blockIdx.x, tid = c.tid, warp = c.warp, lane = c.lane, hd = P.hd, nkv = P.nkv, kvd = nkv * hd;
     const int rep = P.nh / nkv, kh = h / rep;
     const bool writer = h % rep == 0;
@@ -392,10 +524,21 @@ __device__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c
     const __half* kc = L.kc; const __half* vc = L.vc;
     const int cp = ST_VCHUNK / (hd * 2), ppr = hd * 2 / 16;          // positions per chunk of V rows; 16-byte pieces per row
     const int nold = n - 1, nchunks = (nold + cp - 1) / cp;
+    // chunks of V rows in flight: as many as the scratch holds behind the scores (two to four)
+    const int room = (int)((c.scratch + P.scratch) - reinterpret_cast<unsigned char*>(ring)) / ST_VCHUNK;
+    const int depth = room >= 4 ? 4 : room >= 3 ? 3 : 2;
+    {   // the head's K tiles and V rows on their way into L2 before anything waits for them
+        const int ktiles = (nold + 31) / 32, klines = hd * 32 * 2 / 128;
+        for (int i = tid; i < ktiles * klines; i += ST_CT)
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(kc + it_kc_index((size_t)(i / klines) * 32, kh, 0, nkv, hd) + (size_t)(i % klines) * 64));
+        const int vlines = hd * 2 / 128;
+        for (int i = tid; i < nold * vlines; i += ST_CT)
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(vc + (size_t)(i / vlines) * kvd + kh * hd + (size_t)(i % vlines) * 64));
+    }
     auto issue = [&](int ck) {
         if (ck < nchunks) {
             const int p0 = ck * cp, rows = min(cp, nold - p0);
-            __half* dst = ring + (size_t)(ck & 1) * cp * hd;
+            __half* dst = ring + (size_t)(ck % depth) * cp * hd;
             for (int i = tid; i < rows * ppr; i += ST_CT) {
                 const int r = i / ppr, k = i % ppr;
                 cp_async16(dst + r * hd + k * 8, vc + (size_t)(p0 + r) * kvd + kh * hd + k * 8);
@@ -403,7 +546,7 @@ __device__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    issue(0);
+    for (int ck = 0; ck < depth - 1; ck++) issue(ck);
     if (warp < 2) {
         // warp 0: q head; warp 1: k head.  rmsnorm with the squares added by one lane in index order, weight, rope.
         float* buf = warp == 0 ? qs : kl;
@@ -453,17 +596,22 @@ __device__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c
         float s = 0.f;
         if (p < nold) {
             const uint4* kp = reinterpret_cast<const uint4*>(kc + it_kc_index(p, kh, 0, nkv, hd));    // piece v of 32 consecutive positions is contiguous
-            for (int v0 = 0; v0 < nvec; v0 += 8) {
-                uint4 buf[8];
+            // four 16-byte pieces per batch; the next batch is requested before the current one is added up
+            uint4 cur[4], nxt[4];
 #pragma unroll
-                for (int u = 0; u < 8; u++) if (v0 + u < nvec) buf[u] = __ldcg(kp + (v0 + u) * 32);
+            for (int u = 0; u < 4; u++) if (u < nvec) cur[u] = __ldcg(kp + u * 32);
+            for (int v0 = 0; v0 < nvec; v0 += 4) {
 #pragma unroll
-                for (int u = 0; u < 8; u++) if (v0 + u < nvec) {
-                    const __half2* hh = reinterpret_cast<const __half2*>(&buf[u]);
+                for (int u = 0; u < 4; u++) if (v0 + 4 + u < nvec) nxt[u] = __ldcg(kp + (v0 + 4 + u) * 32);
+#pragma unroll
+                for (int u = 0; u < 4; u++) if (v0 + u < nvec) {
+                    const __half2* hh = reinterpret_cast<const __half2*>(&cur[u]);
                     const float* qv = qs + (v0 + u) * 8;
 #pragma unroll
                     for (int i2 = 0; i2 < 4; i2++) { const float2 f = __half22float2(hh[i2]); s = it_add(s, it_mul(qv[2 * i2], f.x)); s = it_add(s, it_mul(qv[2 * i2 + 1], f.y)); }
                 }
+#pragma unroll
+                for (int u = 0; u < 4; u++) cur[u] = nxt[u];
             }
         } else {
 #pragma unroll 8
@@ -493,12 +641,14 @@ __device__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c
     // output element j adds w[p] * v[p][j] in ascending p; the V rows stream through two chunks in shared memory
     float acc0 = 0.f, acc1 = 0.f;
     for (int ck = 0; ck < nchunks; ck++) {
-        issue(ck + 1);
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        issue(ck + depth - 1);
+        if (depth == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
+        else if (depth == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+        else asm volatile("cp.async.wait_group 1;" ::: "memory");
         cons_sync();
         if (2 * tid < hd) {
             const int p0 = ck * cp, rows = min(cp, nold - p0);
-            const __half* src = ring + (size_t)(ck & 1) * cp * hd + 2 * tid;
+            const __half* src = ring + (size_t)(ck % depth) * cp * hd + 2 * tid;
             int r = 0;
             for (; r + 4 <= rows; r += 4) {
                 const float w[4] = { sc[p0 + r], sc[p0 + r + 1], sc[p0 + r + 2], sc[p0 + r + 3] };
@@ -531,118 +681,119 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
     c.bars = smem_u32(tail);                                         // full[s] at bars + 8 s, empty[s] at bars + 8 (slots + s)
     c.abort_flag = reinterpret_cast<volatile int*>(tail + ST_BARS - 16);
     c.tid = threadIdx.x; c.warp = c.tid >> 5; c.lane = c.tid & 31;
-    c.slot = 0; c.ph = 0u; c.kg = 0;
+    c.q = 0u; c.nseq = 0u; c.mph = 0u; c.nsync = 0; c.evt_on = 0; c.evt_warp = 0; c.evt_cta = 0;
+    c.tf = c.bars + 8 * (2 * P.slots); c.te = c.tf + 8 * ST_TB; c.pd = c.te + 8 * ST_TB; c.ps = c.pd + 8;
+    c.lay = reinterpret_cast<const StepLayer*>(tail + 384);         // two layer descriptions, then the sum warps' greedy picks
     if (c.tid == 0) {
         *c.abort_flag = *reinterpret_cast<volatile unsigned*>(P.sync + 2) ? 1 : 0;      // a step that was given up earlier: nothing runs until the host has cleared the words
         for (int s = 0; s < P.slots; s++) { mbar_init(c.bars + 8 * s, 1); mbar_init(c.bars + 8 * (P.slots + s), ST_CW); }
+        for (int k = 0; k < ST_TB; k++) { mbar_init(c.tf + 8 * k, ST_NCONS); mbar_init(c.te + 8 * k, 1); }
+        mbar_init(c.pd, ST_NSUM); mbar_init(c.ps, ST_NCONS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    {   // the first layer's description into shared memory (later ones are copied a layer ahead)
+        constexpr int words = (int)(sizeof(StepLayer) / 4);
+        if (c.tid < words) reinterpret_cast<uint32_t*>(tail + 384)[c.tid] = reinterpret_cast<const uint32_t*>(P.layers)[c.tid];
     }
     __syncthreads();
     if (*c.abort_flag) return;
-    if (c.warp == ST_NCONS) { if (c.lane == 0) producer(P, c); return; }
+    if (c.warp == ST_NCONS + ST_NSUM) { if (c.lane == 0) producer(P, c); return; }
+    if (c.warp >= ST_NCONS) { sum_warps(P, c); return; }
 
     c.target = *reinterpret_cast<volatile unsigned*>(P.sync + 1);
+    if (P.trace && blockIdx.x == 0 && c.tid == 32) P.trace[4 * ST_TRACE_MAX] = 0;
     const int e = P.e, nb_e = e / 128;
     float* A = P.arena;
     const uint32_t tok = (P.flags & 1) ? __float_as_uint(*reinterpret_cast<volatile float*>(A + P.amx)) : *reinterpret_cast<volatile uint32_t*>(P.toks);
     const float* xsrc = P.tok_embd + (size_t)tok * e;               // the residual row of layer 0 is the embedding row (Model::embed, src/cpu.rs:118-122)
-    ConvKeep keep; keep.ch = -1;
-    Pick best{ -INFINITY, 0xffffffffu };
-#define STEP_SYNC(site) do { if (!grid_sync(P, c, site)) goto done; } while (0)
-    for (int il = 0; il < P.n_layer; il++) {
-        const StepLayer& L = P.layers[il];
-        {   // A: rmsnorm -> Hadamard -> q8k; the normed row is kept for the dense rows of a delta-net layer
-            if (il == 0 && (int)blockIdx.x < nb_e / 8 && c.tid < 256)
-                *reinterpret_cast<float4*>(A + P.x + blockIdx.x * 1024 + 4 * c.tid) = *reinterpret_cast<const float4*>(xsrc + blockIdx.x * 1024 + 4 * c.tid);
-            it_had_prologue p; p.mode = 2; p.w = L.attn_norm; p.eps = P.eps; p.n = (unsigned)e; p.xn_out = L.recurrent ? A + P.xn : nullptr; p.xn_stride = e;
-            had_phase(P, c, nb_e / 8, il == 0 ? xsrc : A + P.x, P.sg_e, 0, 0, 0, p);
+    ConvKeep keep; keep.ch = -1; keep.mx = 0.f;
+    // Phases: nine per layer (0 norm+Hadamard, 1 input projection, 2 delta-net / attention block, 3 Hadamard of its output,
+    // 4 output projection, 5 norm+Hadamard, 6 gate/up, 7 silu*mul+Hadamard, 8 down), then the output norm (+ Hadamard), the LM
+    // head and the pick.  One loop, one copy of each kind of phase: the kernel runs front to back once per step, so its code
+    // size, not its loop structure, is what the instruction cache sees.
+    const bool logits = (P.flags & 4) != 0;
+    const int nphase = 9 * P.n_layer + (logits ? 3 : 1);
+    for (int ph = 0; ph < nphase; ph++) {
+        const int il = ph / 9, sub = ph - 9 * il;
+        const bool tail = il >= P.n_layer;
+        const StepLayer& L = c.lay[il & 1];
+        if (!tail && sub == 0 && il + 1 < P.n_layer && c.warp == ST_NCONS - 1) {          // the next layer's description, long before it is needed
+            constexpr int words = (int)(sizeof(StepLayer) / 4);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(const_cast<StepLayer*>(c.lay + ((il + 1) & 1)));
+            for (int i = c.lane; i < words; i += 32) dst[i] = reinterpret_cast<const uint32_t*>(P.layers + il + 1)[i];
         }
-        STEP_SYNC(1);
-        matvec_phase<false>(P, c, nb_e, L.in_rows, P.big1, 0, best);
-        STEP_SYNC(2);
-        if (L.recurrent) { if ((int)blockIdx.x < P.nv) gdn_phase(P, L, c, keep); }
-        else if ((int)blockIdx.x < P.nh) attn_phase(P, L, c);
-        STEP_SYNC(3);
-        if (keep.ch >= 0) { for (int i = 0; i < P.conv_k - 1; i++) L.conv_st[(size_t)i * P.cd + keep.ch] = keep.st[i]; keep.ch = -1; }
-        {   // D: Hadamard -> q8k of the block output (delta-net: with the value-head permutation)
-            const int w = L.recurrent ? P.inner : P.nh * P.hd;
-            const bool perm = L.recurrent && P.v_grouped;
-            had_phase(P, c, w / 1024, A + P.o, L.recurrent ? P.sg_inner : P.sg_att, perm ? ST_SD : 0, perm ? P.nk : 0, perm ? P.nv / P.nk : 0, it_had_prologue{});
-        }
-        STEP_SYNC(4);
-        matvec_phase<false>(P, c, (L.recurrent ? P.inner : P.nh * P.hd) / 128, e, P.x, 1, best);
-        STEP_SYNC(5);
-        { it_had_prologue p; p.mode = 2; p.w = L.post_norm; p.eps = P.eps; p.n = (unsigned)e; p.xn_out = nullptr; p.xn_stride = e;
-          had_phase(P, c, nb_e / 8, A + P.x, P.sg_e, 0, 0, 0, p); }
-        STEP_SYNC(6);
-        matvec_phase<false>(P, c, nb_e, 2 * P.ff, P.big1, 0, best);
-        STEP_SYNC(7);
-        { it_had_prologue p; p.mode = 1; p.b = A + P.big1 + P.ff; p.b_stride = 2 * (size_t)P.ff;
-          had_phase(P, c, P.ff / 1024, A + P.big1, P.sg_ff, 0, 0, 0, p); }
-        STEP_SYNC(8);
-        matvec_phase<false>(P, c, P.ff / 128, e, P.x, 1, best);
-        STEP_SYNC(9);
-    }
-    {   // output norm (kept as the h_nextn row) -> Hadamard -> q8k
-        it_had_prologue p; p.mode = 2; p.w = P.output_norm; p.eps = P.eps; p.n = (unsigned)e; p.xn_out = A + P.hrow; p.xn_stride = e;
-        had_phase(P, c, (P.flags & 4) ? nb_e / 8 : 0, A + P.x, P.sg_e, 0, 0, 0, p);
-        if (!(P.flags & 4) && blockIdx.x == 0 && c.tid < 256) {
-            // no logits wanted: only the normed row, in the order of k_rmsnorm_wide
-            it_had_smem& sm = *reinterpret_cast<it_had_smem*>(c.scratch);
-            const float* x = A + P.x;
-            float v[32];
+        const int kind = tail ? (sub == 0 ? 0 : sub == 1 ? 1 : 3) : (sub == 2 ? 2 : sub < 2 ? sub : ((sub & 1) ? 0 : 1));   // 0 Hadamard, 1 matvec, 2 block, 3 pick
+        if (kind == 0) {
+            it_had_prologue p; const float* in = A + P.x; const float* signs = P.sg_e; int nblocks = nb_e / 8; unsigned ph_hd = 0, ph_nk = 0, ph_rep = 0;
+            float shift[6]; const bool shifting = !tail && sub == 3 && keep.ch >= 0;
+            if (tail || sub == 0 || sub == 5) {
+                // rmsnorm -> Hadamard -> q8k of the residual row; the normed row is kept where a later op reads it in f32
+                p.mode = 2; p.w = tail ? P.output_norm : sub == 0 ? L.attn_norm : L.post_norm; p.eps = P.eps; p.n = (unsigned)e; p.xn_stride = e;
+                p.xn_out = tail ? A + P.hrow : (sub == 0 && L.recurrent) ? A + P.xn : nullptr;
+                if (!tail && sub == 0 && il == 0) {
+                    in = xsrc;
+                    if ((int)blockIdx.x < nblocks && c.tid < 256)
+                        *reinterpret_cast<float4*>(A + P.x + blockIdx.x * 1024 + 4 * c.tid) = *reinterpret_cast<const float4*>(xsrc + blockIdx.x * 1024 + 4 * c.tid);
+                }
+            } else if (sub == 3) {
+                // the block's output row (delta-net: with the value-head permutation).  The conv state of the channels this
+                // thread owns moves on by one input now that no CTA reads the old one: loads here, stores after the transform
+                if (shifting) {
 #pragma unroll
-            for (int k = 0; k < 32; k++) { const int j = c.tid + 256 * k; v[k] = j < e ? x[j] : 0.f; }
-            float s = 0.f;
-#pragma unroll
-            for (int k = 0; k < 32; k++) if (c.tid + 256 * k < e) s = it_add(s, it_mul(v[k], v[k]));
-#pragma unroll
-            for (int mm = 16; mm >= 1; mm >>= 1) s = it_add(s, __shfl_xor_sync(0xffffffffu, s, mm));
-            if (c.lane == 0) sm.wsum[c.warp] = s;
-            it_had_sync();
-            float t = sm.wsum[0];
-#pragma unroll
-            for (int k = 1; k < 8; k++) t = it_add(t, sm.wsum[k]);
-            const float scl = it_div(1.0f, it_sqrt(it_add(it_div(t, (float)e), P.eps)));
-#pragma unroll
-            for (int k = 0; k < 32; k++) { const int j = c.tid + 256 * k; if (j < e) A[P.hrow + j] = it_mul(it_mul(v[k], scl), P.output_norm[j]); }
-        }
-    }
-    if (P.flags & 4) {
-        STEP_SYNC(10);
-        matvec_phase<true>(P, c, nb_e, P.n_vocab, P.logits, 0, best);
-        // greedy pick (first index of the maximum): lanes -> warp -> CTA -> one partial per CTA
-#pragma unroll
-        for (unsigned mm = 16; mm > 0; mm >>= 1) { Pick o{ __shfl_xor_sync(0xffffffffu, best.v, mm), __shfl_xor_sync(0xffffffffu, best.i, mm) }; best = pick_better(best, o); }
-        cons_sync();                                                 // the ordered sums of the last row group are over: the terms can be overwritten
-        Pick* sh = reinterpret_cast<Pick*>(c.scratch);
-        if (c.lane == 0) sh[c.warp] = best;
-        cons_sync();
-        if (c.warp == 0) {
-            Pick p = c.lane < ST_NCONS ? sh[c.lane] : Pick{ -INFINITY, 0xffffffffu };
-#pragma unroll
-            for (unsigned mm = 16; mm > 0; mm >>= 1) { Pick o{ __shfl_xor_sync(0xffffffffu, p.v, mm), __shfl_xor_sync(0xffffffffu, p.i, mm) }; p = pick_better(p, o); }
-            if (c.lane == 0) P.partials[blockIdx.x] = ((unsigned long long)__float_as_uint(p.v) << 32) | p.i;
-        }
-        STEP_SYNC(11);
-        if (blockIdx.x == 0 && c.warp == 0) {
-            Pick q{ -INFINITY, 0xffffffffu };
-            for (unsigned b = c.lane; b < gridDim.x; b += 32) { const unsigned long long u = __ldcg(P.partials + b); q = pick_better(q, Pick{ __uint_as_float((unsigned)(u >> 32)), (unsigned)u }); }
-#pragma unroll
-            for (unsigned mm = 16; mm > 0; mm >>= 1) { Pick o{ __shfl_xor_sync(0xffffffffu, q.v, mm), __shfl_xor_sync(0xffffffffu, q.i, mm) }; q = pick_better(q, o); }
-            if (c.lane == 0) {
-                const unsigned pick = q.i == 0xffffffffu ? 0u : q.i;
-                A[P.amx] = __uint_as_float(pick);
-                if (P.flags & 2) { P.toks[0] = pick; *P.pos += 1; }
+                    for (int i = 0; i < 6; i++) shift[i] = i < P.conv_k - 2 ? L.conv_st[(size_t)(i + 1) * P.cd + keep.ch] : 0.f;
+                }
+                const bool perm = L.recurrent && P.v_grouped;
+                in = A + P.o; signs = L.recurrent ? P.sg_inner : P.sg_att; nblocks = (L.recurrent ? P.inner : P.nh * P.hd) / 1024;
+                if (perm) { ph_hd = ST_SD; ph_nk = (unsigned)P.nk; ph_rep = (unsigned)(P.nv / P.nk); }
+            } else {
+                p.mode = 1; p.b = A + P.big1 + P.ff; p.b_stride = 2 * (size_t)P.ff;        // silu(gate) * up on the way in
+                in = A + P.big1; signs = P.sg_ff; nblocks = P.ff / 1024;
             }
+            if ((int)blockIdx.x < nblocks && c.tid < 256) {
+                it_had_smem& sm = *reinterpret_cast<it_had_smem*>(c.scratch);
+                it_hadamard_block<true>(sm, (unsigned)c.tid, blockIdx.x, 0, in, 0, 0, nullptr, 0, 0, signs, 1, 0, ph_hd, ph_nk, ph_rep, P.qs, P.qd, P.qsum, P.q_stride, p);
+            }
+            if (shifting) {
+#pragma unroll
+                for (int i = 0; i < 6; i++) if (i < P.conv_k - 2) L.conv_st[(size_t)i * P.cd + keep.ch] = shift[i];
+                L.conv_st[(size_t)(P.conv_k - 2) * P.cd + keep.ch] = keep.mx;
+                keep.ch = -1;
+            }
+        } else if (kind == 1) {
+            int nb, rows;
+            if (tail) { nb = nb_e; rows = P.n_vocab; }
+            else if (sub == 1) { nb = nb_e; rows = L.in_rows; }
+            else if (sub == 4) { nb = (L.recurrent ? P.inner : P.nh * P.hd) / 128; rows = e; }
+            else if (sub == 6) { nb = nb_e; rows = 2 * P.ff; }
+            else { nb = P.ff / 128; rows = e; }
+            matvec_phase(P, c, nb, rows, (!tail && sub == 1 && L.recurrent && (int)blockIdx.x < P.nv) ? &L : nullptr);
+            if (tail && c.warp == 0 && c.lane == 0) {
+                // greedy pick (first index of the maximum): each sum warp has left the best of its rows behind the layer descriptions
+                const Pick* pk = reinterpret_cast<const Pick*>(c.lay + 2);
+                Pick pbest = pk[0];
+                for (int j = 1; j < ST_NSUM; j++) pbest = pick_better(pbest, pk[j]);
+                P.partials[blockIdx.x] = ((unsigned long long)__float_as_uint(pbest.v) << 32) | pbest.i;
+            }
+        } else if (kind == 2) {
+            if (L.recurrent) { if ((int)blockIdx.x < P.nv) gdn_phase(P, L, c, keep); }
+            else if ((int)blockIdx.x < P.nh) attn_phase(P, L, c);
+        } else {
+            if (blockIdx.x == 0 && c.warp == 0) {
+                Pick q{ -INFINITY, 0xffffffffu };
+                for (unsigned b = c.lane; b < gridDim.x; b += 32) { const unsigned long long u = __ldcg(P.partials + b); q = pick_better(q, Pick{ __uint_as_float((unsigned)(u >> 32)), (unsigned)u }); }
+#pragma unroll
+                for (unsigned mm = 16; mm > 0; mm >>= 1) { Pick o{ __shfl_xor_sync(0xffffffffu, q.v, mm), __shfl_xor_sync(0xffffffffu, q.i, mm) }; q = pick_better(q, o); }
+                if (c.lane == 0) {
+                    const unsigned pick = q.i == 0xffffffffu ? 0u : q.i;
+                    A[P.amx] = __uint_as_float(pick);
+                    if (P.flags & 2) { P.toks[0] = pick; *P.pos += 1; }
+                }
+            }
+            break;                                                   // nothing follows the pick
         }
-    } else {
-        STEP_SYNC(11);
+        if (!grid_sync(P, c, 1 + sub + (tail ? 9 : 0))) return;
     }
     if (blockIdx.x == 0 && c.tid == 0) P.sync[1] = c.target;        // every CTA has read the old value before its first arrival
-done:
-#undef STEP_SYNC
-    return;
 }
 
 }  // namespace
@@ -650,16 +801,18 @@ done:
 // ---------------------------------------------------------------- host side
 struct it_step_state {
     StepLayer* layers_dev;
+    unsigned long long* trace;
     unsigned long long* partials;
-    int grid, slots, scratch;
+    int grid, slots, scratch, gdn_off;
     bool cooperative;
 };
 
+static size_t step_gdn_off(const it_model_config& c) { return ((size_t)mv_layout(c.n_embd / 128).total + 127) / 128 * 128; }
 static size_t step_scratch_bytes(const it_model_config& c) {
     const int widest = std::max(std::max(c.n_embd, c.n_ff), std::max(c.ssm_inner, c.n_head * c.head_dim));
     size_t s = (size_t)mv_layout(widest / 128).total;
     s = std::max(s, sizeof(it_had_smem));
-    s = std::max(s, (size_t)(ST_SD * ST_SD + 4 * ST_SD + 8) * 4 + 16 * 8 + 64);
+    s = std::max(s, step_gdn_off(c) + (size_t)(ST_SD * ST_SD + 4 * ST_SD + 8) * 4 + 16 * 8 + 64);
     s = std::max(s, ((size_t)c.ctx_len + 4 + 3 * c.head_dim + 48) * 4 + 16 + 2 * (size_t)ST_VCHUNK);
     return (s + 127) / 128 * 128;
 }
@@ -670,13 +823,13 @@ int it_step_prepare(it_engine* e) {
     e->step = nullptr;
     { const char* v = getenv("IT_STEP_KERNEL"); if (v && atoi(v) == 0) return IT_OK; }
     if (e->world != 1) return IT_OK;                                  // row shards exchange results inside the per-op kernels
-    if (c.ssm_state != ST_SD || c.conv_k > 9 || c.head_dim > 256 || c.head_dim % 8 || c.n_embd > 8192 || c.n_ff % 1024 || c.ssm_inner % 1024 || (c.n_head * c.head_dim) % 1024) return IT_OK;
+    if (c.ssm_state != ST_SD || c.conv_k > 8 || c.head_dim > 256 || c.head_dim % 8 || c.n_embd > 8192 || c.n_ff % 1024 || c.ssm_inner % 1024 || (c.n_head * c.head_dim) % 1024) return IT_OK;
     if (c.ssm_vheads > cx->sm_count || c.n_head > cx->sm_count || c.n_ff / 1024 > cx->sm_count || c.ssm_vheads % c.ssm_groups) return IT_OK;
     if (ST_VCHUNK / (c.head_dim * 2) < 1) return IT_OK;
     const size_t scratch = step_scratch_bytes(c);
     const long long ring = (long long)ST_SMEM - (long long)scratch - ST_BARS;
-    int slots = (int)(ring / ST_CHUNK);
-    if (slots > 48) slots = 48;                                       // 2 * slots mbarriers must fit the reserved bytes
+    int slots = 1;
+    while (2 * slots <= 16 && (long long)(2 * slots) * ST_CHUNK <= ring) slots *= 2;   // a power of two: slot = chunk index & (slots - 1); at most 16 (the mbarriers share 384 reserved bytes)
     if (slots < 4) return IT_OK;
     IT_CUDA(cudaSetDevice(cx->device));
     static bool attr_set[16] = {};
@@ -685,7 +838,7 @@ int it_step_prepare(it_engine* e) {
     IT_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step, ST_THREADS, (size_t)slots * ST_CHUNK + scratch + ST_BARS));
     if (per_sm < 1) return IT_OK;
     it_step_state* st = new it_step_state();
-    st->grid = cx->sm_count; st->slots = slots; st->scratch = (int)scratch; st->layers_dev = nullptr; st->partials = nullptr;
+    st->grid = cx->sm_count; st->slots = slots; st->scratch = (int)scratch; st->gdn_off = (int)step_gdn_off(c); st->layers_dev = nullptr; st->partials = nullptr; st->trace = nullptr;
     { const char* v = getenv("IT_STEP_COOP"); st->cooperative = !v || atoi(v) != 0; }
     std::vector<StepLayer> hl(c.n_layer);
     for (int il = 0; il < c.n_layer; il++) {
@@ -698,6 +851,7 @@ int it_step_prepare(it_engine* e) {
     }
     int r = it_engine_dev_alloc(e, (void**)&st->layers_dev, hl.size() * sizeof(StepLayer), false);
     if (r == IT_OK) r = it_engine_dev_alloc(e, (void**)&st->partials, (size_t)st->grid * sizeof(unsigned long long), true);
+    { const char* v = getenv("IT_STEP_TRACE"); if (r == IT_OK && v && atoi(v) != 0) r = it_engine_dev_alloc(e, (void**)&st->trace, (2 * ST_TRACE_MAX * 2 + ST_EVT_MAX) * sizeof(unsigned long long), true); }
     if (r) { delete st; return r; }
     IT_CUDA(cudaMemcpyAsync(st->layers_dev, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice, cx->stream));
     IT_CUDA(cudaStreamSynchronize(cx->stream));
@@ -720,7 +874,7 @@ int it_step_launch(it_engine* e, int flags) {
     P.tok_embd = e->tok_embd; P.output_norm = e->output_norm; P.output = e->output->tiles;
     P.toks = e->toks_dev; P.pos = e->pos_dev;
     P.sync = cx->grid_sync; P.partials = st->partials; P.error_flag = cx->error_flag_dev;
-    P.slots = st->slots; P.scratch = st->scratch; P.flags = flags;
+    P.slots = st->slots; P.scratch = st->scratch; P.flags = flags; P.trace = st->trace; P.gdn_off = st->gdn_off;
     it_note_op(cx);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)st->grid); cfg.blockDim = dim3(ST_THREADS); cfg.dynamicSmemBytes = (size_t)st->slots * ST_CHUNK + st->scratch + ST_BARS; cfg.stream = cx->stream;
@@ -729,5 +883,16 @@ int it_step_launch(it_engine* e, int flags) {
     cfg.attrs = attr; cfg.numAttrs = st->cooperative ? 1 : 0;
     IT_CUDA(cudaLaunchKernelEx(&cfg, k_decode_step, P));
     e->q8->n = (size_t)c.n_embd;
+    return IT_OK;
+}
+
+// Diagnostics (IT_STEP_TRACE=1 when the engine is built): the nanosecond clock of CTA 0 and of the last CTA when they arrive
+// at and leave each grid barrier of the most recent step: out[(cta * max + barrier) * 2 + {0, 1}], cta in {0, 1}.
+IT_API int it_engine_step_trace(it_engine* e, uint64_t* out, size_t max_barriers) {
+    IT_CHECK_ARG(e && out, "it_engine_step_trace: null argument");
+    if (!e->step || !e->step->trace) return it_fail(IT_ESTATE, "it_engine_step_trace: the engine was not built with IT_STEP_TRACE=1, or does not run the step kernel");
+    IT_CHECK_ARG(max_barriers == ST_TRACE_MAX || max_barriers == ST_TRACE_MAX + ST_EVT_MAX / 4, "it_engine_step_trace: pass room for %d barriers per CTA", ST_TRACE_MAX);
+    IT_CUDA(cudaMemcpyAsync(out, e->step->trace, (2 * ST_TRACE_MAX * 2 + (max_barriers > ST_TRACE_MAX ? ST_EVT_MAX : 0)) * sizeof(unsigned long long), cudaMemcpyDeviceToHost, e->ctx->stream));
+    IT_CUDA(cudaStreamSynchronize(e->ctx->stream));
     return IT_OK;
 }

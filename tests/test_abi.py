@@ -52,3 +52,16 @@ def test_context_capacity_beyond_the_attention_kernel_is_refused_before_device_w
     assert lib.it_engine_create_synth(0, C.byref(cfg), 1, 0, C.byref(h)) == -1
     msg = lib.it_last_error().decode()
     assert "context capacity 24000" in msg and "23292" in msg
+
+
+def test_rust_sys_crate_declares_exactly_the_headers_entry_points():
+    """ffi/irontimber-cuda-sys/src/lib.rs (not compiled here: no Rust toolchain) must bind every entry point of the
+    header and nothing else, so that it cannot drift from the library."""
+    src = open(os.path.join(ROOT, "ffi", "irontimber-cuda-sys", "src", "lib.rs")).read()
+    block = src[src.index('extern "C" {'):]
+    block = block[:block.index("\n}\n")]
+    names = sorted(set(re.findall(r"pub fn (it_[a-z0-9_]+)\s*\(", block)))
+    assert names == header_symbols()
+    # and the engine wrapper only calls what the crate declares
+    eng = open(os.path.join(ROOT, "ffi", "cuda_engine.rs")).read()
+    assert set(re.findall(r"sys::(it_[a-z0-9_]+)\s*\(", eng)) <= set(names)
