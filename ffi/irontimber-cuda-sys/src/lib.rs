@@ -80,6 +80,8 @@ extern "C" {
     pub fn it_ctx_ipc_handle(ctx: *mut it_ctx, handle64: *mut c_void) -> c_int;
     pub fn it_ctx_attach_peers(ctx: *mut it_ctx, rank: c_int, world: c_int, handles: *const c_void) -> c_int;
     pub fn it_ctx_world(ctx: *const it_ctx) -> c_int;
+    pub fn it_ctx_attach_peers_local(ctx: *mut it_ctx, rank: c_int, world: c_int, all: *const *mut it_ctx) -> c_int;
+    pub fn it_ctx_set_peer_wait_us(ctx: *mut it_ctx, microseconds: f64) -> c_int;
     pub fn it_arena_zero(ctx: *mut it_ctx, off: usize, n_floats: usize) -> c_int;
     pub fn it_capture_begin(ctx: *mut it_ctx) -> c_int;
     pub fn it_capture_end(ctx: *mut it_ctx, out: *mut *mut it_graph) -> c_int;

@@ -62,6 +62,12 @@ int it_arena_read(it_ctx* ctx, size_t off, void* host, size_t n_floats);        
 int it_ctx_ipc_handle(it_ctx* ctx, void* handle64);
 int it_ctx_attach_peers(it_ctx* ctx, int rank, int world, const void* handles);
 int it_ctx_world(const it_ctx* ctx);
+/* The same attachment for contexts that live in one process (a single-process host driving several GPUs, as the reference's
+ * single-threaded server would, or two contexts on one GPU): all[p] is rank p's context (the own entry is ignored). */
+int it_ctx_attach_peers_local(it_ctx* ctx, int rank, int world, it_ctx* const* all);
+/* How long a kernel of this context waits for a peer's results before it gives up and the next it_sync / read-back
+ * returns IT_ETIMEOUT (default about four seconds).  Peers must be attached. */
+int it_ctx_set_peer_wait_us(it_ctx* ctx, double microseconds);
 int it_arena_zero(it_ctx* ctx, size_t off, size_t n_floats);                    /* zero_state,    src/vk/mod.rs:645 */
 
 /* Record the ops issued between begin and end into a CUDA graph and replay them with one launch.

@@ -41,6 +41,8 @@ SIGNATURES = {
     "it_ctx_ipc_handle": (C.c_int, [P, P]),
     "it_ctx_attach_peers": (C.c_int, [P, C.c_int, C.c_int, P]),
     "it_ctx_world": (C.c_int, [P]),
+    "it_ctx_attach_peers_local": (C.c_int, [P, C.c_int, C.c_int, P]),
+    "it_ctx_set_peer_wait_us": (C.c_int, [P, C.c_double]),
     "it_matrix_download_pq2": (C.c_int, [P, P, P]),
     "it_matrix_rows": (c_size, [P]),
     "it_matrix_cols": (c_size, [P]),

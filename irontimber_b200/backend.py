@@ -173,6 +173,14 @@ class CudaBackend:
         from .sharding import attach_peers
         attach_peers(self.L, self.ctx, rank, world, group)
 
+    def attach_peers_local(self, rank, backends):
+        """Peers that live in this process (one CudaBackend per rank, in rank order): it_ctx_attach_peers_local."""
+        arr = (C.c_void_p * len(backends))(*[b.ctx for b in backends])
+        _lib.check(self.L.it_ctx_attach_peers_local(self.ctx, rank, len(backends), arr))
+
+    def set_peer_wait_us(self, microseconds):
+        _lib.check(self.L.it_ctx_set_peer_wait_us(self.ctx, float(microseconds)))
+
     def qmat(self, raw_q8_0, rows, cols):
         raw = np.ascontiguousarray(raw_q8_0, np.uint8)
         if raw.size != rows * (cols // 32) * 34:

@@ -1,5 +1,6 @@
 // Context, arena, weight upload / repack and q8 activation buffers of libirontimber_cuda.so.
 #include "it_internal.h"
+#include <cstddef>
 #include <cstring>
 #include <vector>
 
@@ -173,17 +174,34 @@ IT_API int it_ctx_ipc_handle(it_ctx* c, void* handle64) {
     IT_CUDA(cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle64), c->arena));
     return IT_OK;
 }
+// Common part of the two attach calls: bases[p] is rank p's arena allocation as this process sees it (own arena at [rank]).
+static int attach_common(it_ctx* c, int rank, int world, char* const* bases) {
+    it_peers P; memset(&P, 0, sizeof P);
+    P.rank = rank; P.world = world;
+    const size_t tail = c->arena_floats * sizeof(float);
+    for (int p = 0; p < world; p++) {
+        P.arena[p] = reinterpret_cast<float*>(bases[p]);
+        P.flags[p] = reinterpret_cast<unsigned*>(bases[p] + tail);
+        P.ll[p] = reinterpret_cast<unsigned long long*>(bases[p] + tail + IT_ARENA_TAIL);
+    }
+    P.ll_slots = c->ll_slots;
+    P.wait_clocks = 1ll << 33;             // about four seconds: another process may be a little behind
+    P.done = P.flags[rank] + IT_MAX_PEERS; P.epoch = P.flags[rank] + IT_MAX_PEERS + 1;
+    IT_CUDA(cudaMalloc(&c->peers_dev, sizeof P));
+    IT_CUDA(cudaMemcpyAsync(c->peers_dev, &P, sizeof P, cudaMemcpyHostToDevice, c->stream));
+    IT_CUDA(cudaStreamSynchronize(c->stream));
+    c->rank = rank; c->world = world;
+    return IT_OK;
+}
 IT_API int it_ctx_attach_peers(it_ctx* c, int rank, int world, const void* handles) {
     IT_CHECK_ARG(c && handles, "it_ctx_attach_peers: null argument");
     IT_CHECK_ARG(world >= 1 && world <= IT_MAX_PEERS && rank >= 0 && rank < world, "it_ctx_attach_peers: bad rank %d of %d", rank, world);
     if (c->peers_dev) return it_fail(IT_ESTATE, "it_ctx_attach_peers: peers are already attached");
     if (c->capturing) return it_fail(IT_ESTATE, "it_ctx_attach_peers: not allowed while recording a graph");
     IT_CUDA(cudaSetDevice(c->device));
-    it_peers P; memset(&P, 0, sizeof P);
-    P.rank = rank; P.world = world;
-    const size_t tail = c->arena_floats * sizeof(float);
+    char* bases[IT_MAX_PEERS] = {};
     for (int p = 0; p < world; p++) {
-        char* base = reinterpret_cast<char*>(c->arena);
+        bases[p] = reinterpret_cast<char*>(c->arena);
         if (p != rank) {
             cudaIpcMemHandle_t h; memcpy(&h, static_cast<const char*>(handles) + 64 * p, 64);
             void* mapped = nullptr;
@@ -192,18 +210,45 @@ IT_API int it_ctx_attach_peers(it_ctx* c, int rank, int world, const void* handl
                 for (int q = 0; q < p; q++) if (c->peer_base[q]) { cudaIpcCloseMemHandle(c->peer_base[q]); c->peer_base[q] = nullptr; }
                 return it_fail(IT_ECUDA, "it_ctx_attach_peers: cannot map the arena of rank %d: %s", p, cudaGetErrorString(e));
             }
-            c->peer_base[p] = mapped; base = static_cast<char*>(mapped);
+            c->peer_base[p] = mapped; bases[p] = static_cast<char*>(mapped);
         }
-        P.arena[p] = reinterpret_cast<float*>(base);
-        P.flags[p] = reinterpret_cast<unsigned*>(base + tail);
-        P.ll[p] = reinterpret_cast<unsigned long long*>(base + tail + IT_ARENA_TAIL);
     }
-    P.ll_slots = c->ll_slots;
-    P.done = P.flags[rank] + IT_MAX_PEERS; P.epoch = P.flags[rank] + IT_MAX_PEERS + 1;
-    IT_CUDA(cudaMalloc(&c->peers_dev, sizeof P));
-    IT_CUDA(cudaMemcpyAsync(c->peers_dev, &P, sizeof P, cudaMemcpyHostToDevice, c->stream));
+    return attach_common(c, rank, world, bases);
+}
+// The same for contexts that live in ONE process (a single-process host that drives several GPUs, or two contexts on one
+// GPU): the arenas are addressed directly, with peer access enabled between different devices.
+IT_API int it_ctx_attach_peers_local(it_ctx* c, int rank, int world, it_ctx* const* all) {
+    IT_CHECK_ARG(c && all, "it_ctx_attach_peers_local: null argument");
+    IT_CHECK_ARG(world >= 1 && world <= IT_MAX_PEERS && rank >= 0 && rank < world, "it_ctx_attach_peers_local: bad rank %d of %d", rank, world);
+    if (c->peers_dev) return it_fail(IT_ESTATE, "it_ctx_attach_peers_local: peers are already attached");
+    if (c->capturing) return it_fail(IT_ESTATE, "it_ctx_attach_peers_local: not allowed while recording a graph");
+    IT_CUDA(cudaSetDevice(c->device));
+    char* bases[IT_MAX_PEERS] = {};
+    for (int p = 0; p < world; p++) {
+        it_ctx* o = p == rank ? c : all[p];
+        IT_CHECK_ARG(o && o->arena_floats == c->arena_floats, "it_ctx_attach_peers_local: rank %d has no context or an arena of another size", p);
+        if (o->device != c->device) {
+            int can = 0; IT_CUDA(cudaDeviceCanAccessPeer(&can, c->device, o->device));
+            if (!can) return it_fail(IT_ECUDA, "it_ctx_attach_peers_local: device %d cannot address the memory of device %d", c->device, o->device);
+            const cudaError_t e = cudaDeviceEnablePeerAccess(o->device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return it_fail(IT_ECUDA, "it_ctx_attach_peers_local: %s", cudaGetErrorString(e));
+            cudaGetLastError();
+        }
+        bases[p] = reinterpret_cast<char*>(o->arena);
+    }
+    return attach_common(c, rank, world, bases);
+}
+// How long a kernel of this context waits for a peer's results before it gives up and raises IT_ETIMEOUT (default about
+// four seconds).  For tests and for hosts that want to notice a lost peer sooner.
+IT_API int it_ctx_set_peer_wait_us(it_ctx* c, double microseconds) {
+    IT_CHECK_ARG(c && microseconds > 0.0 && microseconds <= 60e6, "it_ctx_set_peer_wait_us: bad argument");
+    if (!c->peers_dev) return it_fail(IT_ESTATE, "it_ctx_set_peer_wait_us: no peers are attached");
+    if (c->capturing) return it_fail(IT_ESTATE, "it_ctx_set_peer_wait_us: not allowed while recording a graph");
+    IT_CUDA(cudaSetDevice(c->device));
+    int khz = 0; IT_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device));
+    const long long clocks = (long long)(microseconds * 1e-3 * (double)khz) + 1;
     IT_CUDA(cudaStreamSynchronize(c->stream));
-    c->rank = rank; c->world = world;
+    IT_CUDA(cudaMemcpy(reinterpret_cast<char*>(c->peers_dev) + offsetof(it_peers, wait_clocks), &clocks, sizeof clocks, cudaMemcpyHostToDevice));
     return IT_OK;
 }
 IT_API int it_ctx_world(const it_ctx* c) { return c ? c->world : 0; }

@@ -51,6 +51,7 @@ struct it_peers {                       // lives in device memory, one per attac
     // even and odd epochs; a slot is complete as soon as its epoch tag matches, no fence or flag needed
     unsigned long long* ll[IT_MAX_PEERS];
     size_t ll_slots;
+    long long wait_clocks;              // how long a kernel waits for a peer's results before it gives up (SM clock cycles)
 };
 // Local row r belongs to the last segment with start[s] <= r and lands at output row r + delta[s].
 struct it_rowmap { int nseg; int start[4]; int delta[4]; int shift[4]; };   // shift[s]: how far segment s moves from one rank to the next

@@ -16,6 +16,14 @@
 #else
 #define IT_HD static inline
 #endif
+// The longer functions (IEEE division and square root expand to dozens of instructions on the device, the elementary
+// functions to more) can be compiled as calls instead of inline copies: a translation unit that defines IT_MATH_OUTLINE
+// before including this header gets one copy of each.  The operations, and so the results, are the same either way.
+#if defined(__CUDACC__) && defined(IT_MATH_OUTLINE)
+#define IT_HD_BIG static __host__ __device__ __noinline__
+#else
+#define IT_HD_BIG IT_HD
+#endif
 
 IT_HD float it_fma(float a, float b, float c) {
 #if defined(__CUDA_ARCH__)
@@ -39,14 +47,14 @@ IT_HD float it_add(float a, float b) {
 #endif
 }
 IT_HD float it_sub(float a, float b) { return it_add(a, -b); }
-IT_HD float it_div(float a, float b) {
+IT_HD_BIG float it_div(float a, float b) {
 #if defined(__CUDA_ARCH__)
     return __fdiv_rn(a, b);
 #else
     volatile float r = a / b; return r;
 #endif
 }
-IT_HD float it_sqrt(float a) {
+IT_HD_BIG float it_sqrt(float a) {
 #if defined(__CUDA_ARCH__)
     return __fsqrt_rn(a);
 #else
@@ -69,7 +77,7 @@ IT_HD uint32_t it_float_to_bits(float f) {
 }
 
 // exp(x).  n = round(x / ln 2), r = x - n ln 2 in two pieces, degree-6 polynomial, exact scaling by 2^n.
-IT_HD float it_expf(float x) {
+IT_HD_BIG float it_expf(float x) {
     if (!(x == x)) return x;
     if (x > 88.72283935546875f) return it_bits_to_float(0x7f800000u);
     if (x < -103.97208404541015625f) return 0.0f;
@@ -90,7 +98,7 @@ IT_HD float it_expf(float x) {
 }
 
 // log(x) for finite x > 0 (normal numbers): x = m 2^e with m in [sqrt(1/2), sqrt(2)), polynomial in m - 1.
-IT_HD float it_logf(float x) {
+IT_HD_BIG float it_logf(float x) {
     uint32_t u = it_float_to_bits(x);
     int e = (int)(u >> 23) - 126;
     float m = it_bits_to_float((u & 0x007fffffu) | 0x3f000000u);   // m in [0.5, 1)
@@ -115,7 +123,7 @@ IT_HD float it_logf(float x) {
 }
 
 // sin and cos of x for |x| up to about 1e5 (rope angles are position * scale <= context length).
-IT_HD void it_sincosf(float x, float* s, float* c) {
+IT_HD_BIG void it_sincosf(float x, float* s, float* c) {
     const float k = rintf(it_mul(x, 0.636619772367581343f));          // nearest multiple of pi/2
     float r = it_fma(k, -1.5703125f, x);                              // pi/2 in three pieces
     r = it_fma(k, -4.837512969970703125e-4f, r);

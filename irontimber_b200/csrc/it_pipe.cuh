@@ -7,7 +7,7 @@
 namespace {
 
 constexpr long long WAIT_CLOCKS = 1ll << 31;      // about one second
-constexpr long long PEER_WAIT_CLOCKS = 1ll << 33; // about four seconds: another process may be a little behind
+constexpr long long PEER_WAIT_CLOCKS = 1ll << 33; // default limit of a wait for a peer, about four seconds: another process may be a little behind
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count)); }
@@ -94,7 +94,7 @@ __device__ __forceinline__ void it_shard_finish(const it_peers* P, unsigned tota
         for (;;) {
             unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if ((int)(v - e) >= 0) break;
-            if (clock64() - t0 > PEER_WAIT_CLOCKS) { atomicExch(error_flag, 1); q = world; break; }
+            if (clock64() - t0 > P->wait_clocks) { atomicExch(error_flag, 21); q = world; break; }
         }
     }
     *P->epoch = e;
@@ -123,7 +123,7 @@ __device__ __forceinline__ void it_result_exchange_ll(const it_peers* P, float* 
         for (;;) {
             asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(x) : "l"(slot) : "memory");
             if ((unsigned)(x >> 32) == e) break;
-            if (clock64() - t0 > PEER_WAIT_CLOCKS) { atomicExch(error_flag, 1); return; }
+            if (clock64() - t0 > P->wait_clocks) { atomicExch(error_flag, 22); return; }
         }
         arena[row_off + gp] = __uint_as_float((unsigned)x);
     }

@@ -29,9 +29,10 @@
 //
 // Every wait (mbarrier, grid barrier) is bounded; when one runs out the CTA raises the context's error flag and an abort
 // word that makes every other CTA leave at its next barrier, drains its copies and returns (IT_ETIMEOUT on the host).
+#define IT_MATH_OUTLINE      // one copy of division, square root and the elementary functions: this kernel's code size is its speed
+#include "it_math.h"
 #include "it_engine.h"
 #include "it_support.h"
-#include "it_math.h"
 #include "it_pipe.cuh"
 #include "it_hadamard.cuh"
 #include <algorithm>
@@ -78,6 +79,8 @@ struct StepParams {
     int* error_flag;
     unsigned long long* trace;         // optional: clock readings of CTA 0 and of the last CTA at every grid barrier (arrive, leave)
     int slots, scratch;                // ring slots; bytes of the phase scratch that follows the ring
+    int had_base, attn_base;           // first CTA of the Hadamard blocks / of the attention heads (value heads start at CTA 0): roles on
+                                       // different CTAs keep each CTA's instruction footprint small
     int gdn_off;                       // where the delta-net block keeps its state tile inside the scratch (clear of the input projection's buffers)
     int flags;                         // bit 0: the token is the previous pick (amx) instead of toks[0]; bit 1: hand the pick over (toks[0], pos + 1); bit 2: logits wanted
 };
@@ -96,11 +99,12 @@ struct Cta {
     const StepLayer* lay;              // the two shared-memory copies of layer descriptions (layer il at lay[il & 1])
     unsigned target;                   // arrivals the next grid barrier waits for
     int nsync;                         // grid barriers passed so far (index into the trace)
-    int evt_on, evt_warp, evt_cta;     // diagnostics: fine-grained events of one warp of one CTA
+    int evt_on, evt_base;              // diagnostics: this thread records fine-grained events into slots evt_base ..
 };
 constexpr int ST_TRACE_MAX = 1024;     // barriers recorded per traced CTA
 constexpr int ST_EVT_MAX = 2048;       // fine-grained events (diagnostics)
-#define ST_EVT(P, c, id) do { if ((P).trace && (c).evt_on && blockIdx.x == (unsigned)(c).evt_cta && (c).lane == 0 && (c).warp == (c).evt_warp) { unsigned long long* ev = (P).trace + 4 * ST_TRACE_MAX; unsigned n = (unsigned)ev[0]; if (n < ST_EVT_MAX - 1) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); ev[1 + n] = ((unsigned long long)(id) << 48) | (t & 0xffffffffffffull); ev[0] = n + 1; } } } while (0)
+// Diagnostics: slot `id` of the event area receives the nanosecond clock when the chosen thread passes (one store, no read).
+#define ST_EV(P, c, id) do { if ((P).trace && (c).evt_on && (c).lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); (P).trace[4 * ST_TRACE_MAX + (id)] = t_; } } while (0)
 
 __device__ __forceinline__ void cons_sync() { consumer_barrier<ST_CT>(); }
 // four u8 x s8 products added to c
@@ -207,22 +211,24 @@ __host__ __device__ inline MvSmem mv_layout(int nb) {
 
 // prefetch_layer: when set, the delta-net block's state tile of that layer is requested right after the activation row has
 // been staged (asynchronous copies for the phase after this one)
-__device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c);
+__device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c, int h);
 __device__ __forceinline__ void matvec_phase(const StepParams& P, Cta& c, int nb, int rows, const StepLayer* prefetch_layer) {
     const MvSmem L = mv_layout(nb);
     int8_t* xs = reinterpret_cast<int8_t*>(c.scratch + L.x);
     float* dxs = reinterpret_cast<float*>(c.scratch + L.dx);
     int* sss = reinterpret_cast<int*>(c.scratch + L.s128);
     const int tid = c.tid, warp = c.warp, lane = c.lane;
+    ST_EV(P, c, c.evt_base + 0);
     if (lane == 0) mbar_arrive(c.ps);                                // the sum warps may enter this phase (they never run ahead of the consumers)
     {   // the q8k row, its scales and block sums, once per CTA (written by other CTAs before the last barrier: read through L2)
         for (int ch = tid; ch < nb * 8; ch += ST_CT) cp_async16(xs + 16 * ch, P.qs + 16 * ch);
         for (int i = tid; i < nb / 2; i += ST_CT) dxs[i] = __ldcg(P.qd + i);
         for (int i = tid; i < nb; i += ST_CT) sss[i] = __ldcg(P.qsum + i);
         cp_async_wait_all();
-        if (prefetch_layer) gdn_prefetch(P, *prefetch_layer, c);
+        if (prefetch_layer) gdn_prefetch(P, *prefetch_layer, c, (int)blockIdx.x);
         cons_sync();
     }
+    ST_EV(P, c, c.evt_base + 1);
     const int t = lane & 3;
     const int group = warp / ST_CW, wi = warp % ST_CW;
     const int rgs = (rows + 31) / 32, cpr = (nb + ST_TPC - 1) / ST_TPC;
@@ -290,9 +296,11 @@ __device__ __forceinline__ void matvec_phase(const StepParams& P, Cta& c, int nb
         if (lane == 0) mbar_arrive(c.tf + 8 * k);                        // this warp's terms of the row group are in place
     }
     c.nseq = n;
+    ST_EV(P, c, c.evt_base + 2);
     // the phase is over when the sum warps have stored its last results
     mbar_wait(c.pd, c.mph & 1u, c.abort_flag, P.error_flag, 5);
     c.mph++;
+    ST_EV(P, c, c.evt_base + 3);
 }
 
 // The sum warps' side of a matvec phase: warp j adds the row groups whose sequence number is j modulo ST_NSUM.
@@ -347,9 +355,9 @@ __device__ __forceinline__ void sum_warps(const StepParams& P, Cta& c) {
 struct ConvKeep { int ch; float mx; };    // a conv channel whose state this thread shifts after the next barrier, and this step's input of that channel
 // Issued by the CTA of value head blockIdx.x while the input projection runs: the head's state tile (64 KB, it does not
 // depend on this step's activations) into its place in shared memory, and the head's beta / alpha rows into L2.
-__device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c) {
+__device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c, int h) {
     constexpr int SD = ST_SD, PPR = SD / 4;
-    const int h = blockIdx.x, tid = c.tid;
+    const int tid = c.tid;
     float* tile = reinterpret_cast<float*>(c.scratch + P.gdn_off);
     const float4* m = reinterpret_cast<const float4*>(L.ssm_st + (size_t)h * SD * SD);
     for (int f = tid; f < SD * PPR; f += ST_CT) { const int j = f / PPR, cc = f % PPR; cp_async16(tile + j * SD + ((cc ^ (j & 7)) << 2), m + f); }
@@ -360,9 +368,9 @@ __device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLaye
         asm volatile("prefetch.global.L2 [%0];" :: "l"(row));
     }
 }
-__device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c, ConvKeep& keep) {
+__device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& L, const Cta& c, ConvKeep& keep, int h) {
     constexpr int SD = ST_SD, PPR = SD / 4;
-    const int h = blockIdx.x, tid = c.tid, warp = c.warp, lane = c.lane, kh = h % P.nk, kk = P.conv_k, cd = P.cd;
+    const int tid = c.tid, warp = c.warp, lane = c.lane, kh = h % P.nk, kk = P.conv_k, cd = P.cd;
     float* tile = reinterpret_cast<float*>(c.scratch + P.gdn_off);   // [SD][SD], 16-byte pieces of row j stored at piece index ^ (j & 7); requested by gdn_prefetch
     float* vals = tile + SD * SD;                                    // [3][SD]: q, k, v runs after conv + SiLU
     float* os = vals + 3 * SD;                                       // [SD] delta-rule outputs
@@ -402,6 +410,7 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
         vals[r * SD + cc] = it_silu(s);
         if (r == 2 || h < P.nk) { keep.ch = ch; keep.mx = mx; }
     }
+    ST_EV(P, c, c.evt_base + 5);
     for (int vw = warp; vw < 16; vw += ST_NCONS) {
         const int t8 = (vw & 7) * 32 + lane; const float* wr = (vw >= 8 ? L.alpha : L.beta) + (size_t)h * P.e;
         if (vw != warp) {
@@ -421,6 +430,7 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
         for (int mm = 16; mm >= 1; mm >>= 1) s += __shfl_xor_sync(0xffffffffu, s, mm);
         if (lane == 0) wsum[vw] = s;
     }
+    ST_EV(P, c, c.evt_base + 6);
     cons_sync();
     if (lane == 0 && warp < 2) {                                     // l2norm of the q run (warp 0) and the k run (warp 1): squares in index order
         const float* v = vals + warp * SD;
@@ -434,8 +444,10 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
         for (int k = 1; k < 8; k++) tt += ws[k];
         scs[warp] = (float)tt;                                       // scs[2] = beta, scs[3] = alpha
     }
+    ST_EV(P, c, c.evt_base + 7);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     cons_sync();
+    ST_EV(P, c, c.evt_base + 8);
     if (tid < SD) {
         const float q = it_mul(vals[tid], scs[0]), k = it_mul(vals[SD + tid], scs[1]);
         asm volatile("bar.sync 3, %0;" :: "n"(SD) : "memory");       // every owner has read the raw q / k values
@@ -482,7 +494,9 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
         }
         os[tid] = it_mul(acc, scale);
     }
+    ST_EV(P, c, c.evt_base + 9);
     cons_sync();
+    ST_EV(P, c, c.evt_base + 10);
     // the new state back to global memory (coalesced 16-byte stores by warps 1..15) while warp 0 norms the outputs
     if (warp > 0) for (int f = tid - 32; f < SD * PPR; f += ST_CT - 32) reinterpret_cast<float4*>(m)[f] = *piece(f / PPR, f % PPR);
     if (warp == 0) {
@@ -501,6 +515,7 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
             __stcg(o + j, it_mul(it_mul(it_mul(os[j], sc), nwr[i]), it_silu(zr[i])));
         }
     }
+    ST_EV(P, c, c.evt_base + 11);
 }
 
 // ---------------------------------------------------------------- attention block of one head
@@ -508,8 +523,8 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
 // k_attn_prep and k_attention (it_support.cu; src/cpu.rs:252-272).  The k and v rows of the new position are recomputed by
 // each of the heads that share the KV head and used from shared memory (after the same f16 rounding the cache applies);
 // the first head of the group stores them into the cache.
-__device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c) {
-    const int h = blockIdx.x, tid = c.tid, warp = c.warp, lane = c.lane, hd = P.hd, nkv = P.nkv, kvd = nkv * hd;
+__device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c, int h) {
+    const int tid = c.tid, warp = c.warp, lane = c.lane, hd = P.hd, nkv = P.nkv, kvd = nkv * hd;
     const int rep = P.nh / nkv, kh = h / rep;
     const bool writer = h % rep == 0;
     const int pos = *P.pos, n = pos + 1;
@@ -546,6 +561,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    ST_EV(P, c, c.evt_base + 4);
     for (int ck = 0; ck < depth - 1; ck++) issue(ck);
     if (warp < 2) {
         // warp 0: q head; warp 1: k head.  rmsnorm with the squares added by one lane in index order, weight, rope.
@@ -588,6 +604,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
             vl[i] = __half2float(hv);
         }
     }
+    ST_EV(P, c, c.evt_base + 5);
     cons_sync();
     const float scale = it_div(1.0f, it_sqrt((float)hd));
     const int nvec = hd / 8;
@@ -619,6 +636,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         }
         s = it_mul(s, scale); sc[p] = s; mx = fmaxf(mx, s);
     }
+    ST_EV(P, c, c.evt_base + 6);
 #pragma unroll
     for (int mm = 16; mm >= 1; mm >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, mm));
     if (lane == 0) red[warp] = mx;
@@ -639,6 +657,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
     for (int p = tid; p < n; p += ST_CT) sc[p] = it_div(sc[p], sum);
     cons_sync();
     // output element j adds w[p] * v[p][j] in ascending p; the V rows stream through two chunks in shared memory
+    ST_EV(P, c, c.evt_base + 7);
     float acc0 = 0.f, acc1 = 0.f;
     for (int ck = 0; ck < nchunks; ck++) {
         issue(ck + depth - 1);
@@ -662,6 +681,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         }
         cons_sync();
     }
+    ST_EV(P, c, c.evt_base + 8);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (2 * tid < hd) {
         const float w = sc[nold];
@@ -681,7 +701,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
     c.bars = smem_u32(tail);                                         // full[s] at bars + 8 s, empty[s] at bars + 8 (slots + s)
     c.abort_flag = reinterpret_cast<volatile int*>(tail + ST_BARS - 16);
     c.tid = threadIdx.x; c.warp = c.tid >> 5; c.lane = c.tid & 31;
-    c.q = 0u; c.nseq = 0u; c.mph = 0u; c.nsync = 0; c.evt_on = 0; c.evt_warp = 0; c.evt_cta = 0;
+    c.q = 0u; c.nseq = 0u; c.mph = 0u; c.nsync = 0; c.evt_on = 0;
     c.tf = c.bars + 8 * (2 * P.slots); c.te = c.tf + 8 * ST_TB; c.pd = c.te + 8 * ST_TB; c.ps = c.pd + 8;
     c.lay = reinterpret_cast<const StepLayer*>(tail + 384);         // two layer descriptions, then the sum warps' greedy picks
     if (c.tid == 0) {
@@ -722,6 +742,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
             uint32_t* dst = reinterpret_cast<uint32_t*>(const_cast<StepLayer*>(c.lay + ((il + 1) & 1)));
             for (int i = c.lane; i < words; i += 32) dst[i] = reinterpret_cast<const uint32_t*>(P.layers + il + 1)[i];
         }
+        c.evt_on = (il == 1 || il == 3) && c.warp == 0 && ((sub == 2) ? ((int)blockIdx.x == (il == 1 ? 0 : P.attn_base)) : (blockIdx.x == gridDim.x - 1)); c.evt_base = (il == 1 ? 0 : 256) + 16 * sub;
         const int kind = tail ? (sub == 0 ? 0 : sub == 1 ? 1 : 3) : (sub == 2 ? 2 : sub < 2 ? sub : ((sub & 1) ? 0 : 1));   // 0 Hadamard, 1 matvec, 2 block, 3 pick
         if (kind == 0) {
             it_had_prologue p; const float* in = A + P.x; const float* signs = P.sg_e; int nblocks = nb_e / 8; unsigned ph_hd = 0, ph_nk = 0, ph_rep = 0;
@@ -732,8 +753,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
                 p.xn_out = tail ? A + P.hrow : (sub == 0 && L.recurrent) ? A + P.xn : nullptr;
                 if (!tail && sub == 0 && il == 0) {
                     in = xsrc;
-                    if ((int)blockIdx.x < nblocks && c.tid < 256)
-                        *reinterpret_cast<float4*>(A + P.x + blockIdx.x * 1024 + 4 * c.tid) = *reinterpret_cast<const float4*>(xsrc + blockIdx.x * 1024 + 4 * c.tid);
+                    const int vb0 = (int)blockIdx.x - P.had_base;
+                    if (vb0 >= 0 && vb0 < nblocks && c.tid < 256)
+                        *reinterpret_cast<float4*>(A + P.x + vb0 * 1024 + 4 * c.tid) = *reinterpret_cast<const float4*>(xsrc + vb0 * 1024 + 4 * c.tid);
                 }
             } else if (sub == 3) {
                 // the block's output row (delta-net: with the value-head permutation).  The conv state of the channels this
@@ -749,9 +771,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
                 p.mode = 1; p.b = A + P.big1 + P.ff; p.b_stride = 2 * (size_t)P.ff;        // silu(gate) * up on the way in
                 in = A + P.big1; signs = P.sg_ff; nblocks = P.ff / 1024;
             }
-            if ((int)blockIdx.x < nblocks && c.tid < 256) {
+            const int vb = (int)blockIdx.x - P.had_base;
+            if (vb >= 0 && vb < nblocks && c.tid < 256) {
                 it_had_smem& sm = *reinterpret_cast<it_had_smem*>(c.scratch);
-                it_hadamard_block<true>(sm, (unsigned)c.tid, blockIdx.x, 0, in, 0, 0, nullptr, 0, 0, signs, 1, 0, ph_hd, ph_nk, ph_rep, P.qs, P.qd, P.qsum, P.q_stride, p);
+                it_hadamard_block<true>(sm, (unsigned)c.tid, (unsigned)vb, 0, in, 0, 0, nullptr, 0, 0, signs, 1, 0, ph_hd, ph_nk, ph_rep, P.qs, P.qd, P.qsum, P.q_stride, p);
             }
             if (shifting) {
 #pragma unroll
@@ -775,8 +798,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
                 P.partials[blockIdx.x] = ((unsigned long long)__float_as_uint(pbest.v) << 32) | pbest.i;
             }
         } else if (kind == 2) {
-            if (L.recurrent) { if ((int)blockIdx.x < P.nv) gdn_phase(P, L, c, keep); }
-            else if ((int)blockIdx.x < P.nh) attn_phase(P, L, c);
+            const int ah = (int)blockIdx.x - P.attn_base;
+            if (L.recurrent) { if ((int)blockIdx.x < P.nv) gdn_phase(P, L, c, keep, (int)blockIdx.x); }
+            else if (ah >= 0 && ah < P.nh) attn_phase(P, L, c, ah);
         } else {
             if (blockIdx.x == 0 && c.warp == 0) {
                 Pick q{ -INFINITY, 0xffffffffu };
@@ -803,7 +827,7 @@ struct it_step_state {
     StepLayer* layers_dev;
     unsigned long long* trace;
     unsigned long long* partials;
-    int grid, slots, scratch, gdn_off;
+    int grid, slots, scratch, gdn_off, had_base, attn_base;
     bool cooperative;
 };
 
@@ -838,7 +862,13 @@ int it_step_prepare(it_engine* e) {
     IT_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_step, ST_THREADS, (size_t)slots * ST_CHUNK + scratch + ST_BARS));
     if (per_sm < 1) return IT_OK;
     it_step_state* st = new it_step_state();
-    st->grid = cx->sm_count; st->slots = slots; st->scratch = (int)scratch; st->gdn_off = (int)step_gdn_off(c); st->layers_dev = nullptr; st->partials = nullptr; st->trace = nullptr;
+    st->grid = cx->sm_count; st->slots = slots; st->scratch = (int)scratch; st->gdn_off = (int)step_gdn_off(c);
+    {   // Hadamard blocks on the last CTAs, attention heads behind the value heads when they all fit side by side
+        const int widest = std::max(std::max(c.n_embd, c.n_ff), std::max(c.ssm_inner, c.n_head * c.head_dim)) / 1024;
+        st->had_base = st->grid - widest;
+        st->attn_base = (c.ssm_vheads + c.n_head <= st->had_base) ? c.ssm_vheads : 0;
+    }
+    st->layers_dev = nullptr; st->partials = nullptr; st->trace = nullptr;
     { const char* v = getenv("IT_STEP_COOP"); st->cooperative = !v || atoi(v) != 0; }
     std::vector<StepLayer> hl(c.n_layer);
     for (int il = 0; il < c.n_layer; il++) {
@@ -874,7 +904,7 @@ int it_step_launch(it_engine* e, int flags) {
     P.tok_embd = e->tok_embd; P.output_norm = e->output_norm; P.output = e->output->tiles;
     P.toks = e->toks_dev; P.pos = e->pos_dev;
     P.sync = cx->grid_sync; P.partials = st->partials; P.error_flag = cx->error_flag_dev;
-    P.slots = st->slots; P.scratch = st->scratch; P.flags = flags; P.trace = st->trace; P.gdn_off = st->gdn_off;
+    P.slots = st->slots; P.scratch = st->scratch; P.flags = flags; P.trace = st->trace; P.gdn_off = st->gdn_off; P.had_base = st->had_base; P.attn_base = st->attn_base;
     it_note_op(cx);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)st->grid); cfg.blockDim = dim3(ST_THREADS); cfg.dynamicSmemBytes = (size_t)st->slots * ST_CHUNK + st->scratch + ST_BARS; cfg.stream = cx->stream;
