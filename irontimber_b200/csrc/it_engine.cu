@@ -15,15 +15,12 @@ __global__ void k_synth_f32(uint64_t seed, size_t n, float lo, float span, float
         out[i] = __fadd_rn(lo, __fmul_rn(span, u));
     }
 }
-template <typename T> __global__ void k_kv_decode(const T* src, float* dst, size_t n) {
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = (float)src[i];
-}
-// the tiled f16 K cache (it_kc_index) back to rows [pos][kvd]
-__global__ void k_kc_decode(const __half* src, float* dst, size_t n, int nkv, int hd) {
+// the tiled f16 K / V caches (it_kc_index, it_vc_index) back to rows [pos][kvd]
+__global__ void k_kc_decode(const __half* src, float* dst, size_t n, int nkv, int hd, int is_v) {
     const size_t kvd = (size_t)nkv * hd;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t pos = i / kvd, r = i % kvd;
-        dst[i] = __half2float(src[it_kc_index(pos, (int)(r / hd), (int)(r % hd), nkv, hd)]);
+        dst[i] = __half2float(src[is_v ? it_vc_index(pos, (int)(r / hd), (int)(r % hd), nkv, hd) : it_kc_index(pos, (int)(r / hd), (int)(r % hd), nkv, hd)]);
     }
 }
 
@@ -228,7 +225,7 @@ int it_engine_build(int device, const it_model_config* cfg, uint64_t seed, int w
             E_TRY(load_mat(e, src, il, IT_T_O, e_, nh * hd, &l.o));
             E_TRY(load_f32(e, src, il, IT_T_Q_NORM, hd, &l.q_norm)); E_TRY(load_f32(e, src, il, IT_T_K_NORM, hd, &l.k_norm));
             E_TRY(dev_alloc(e, (void**)&l.kc, (size_t)((c.ctx_len + 31) / 32 * 32) * kvd * 2, true));   // tiles of 32 positions
-            E_TRY(dev_alloc(e, (void**)&l.vc, (size_t)c.ctx_len * kvd * 2, true));
+            E_TRY(dev_alloc(e, (void**)&l.vc, (size_t)((c.ctx_len + 31) / 32 * 32) * kvd * 2, true));   // tiled like K (it_vc_index)
         }
     }
     E_TRY(load_f32(e, src, -1, IT_T_TOK_EMBD, (size_t)c.n_vocab * e_, &e->tok_embd));
@@ -354,8 +351,7 @@ IT_API int it_engine_state_read(it_engine* e, int layer, int which, float* host,
     IT_CHECK_ARG(n <= max_floats, "it_engine_state_read: buffer too small (%zu > %zu)", n, max_floats);
     if (hsrc) {   // decode f16 -> f32 on the device (decode_kv_readback, src/vk/mod.rs:965)
         float* tmp = nullptr; IT_CUDA(cudaMalloc(&tmp, n * 4));
-        if (which == 2) k_kc_decode<<<e->ctx->sm_count, 256, 0, e->ctx->stream>>>(hsrc, tmp, n, c.n_head_kv, c.head_dim);
-        else k_kv_decode<__half><<<e->ctx->sm_count, 256, 0, e->ctx->stream>>>(hsrc, tmp, n);
+        k_kc_decode<<<e->ctx->sm_count, 256, 0, e->ctx->stream>>>(hsrc, tmp, n, c.n_head_kv, c.head_dim, which == 3 ? 1 : 0);
         cudaError_t er = cudaMemcpyAsync(host, tmp, n * 4, cudaMemcpyDeviceToHost, e->ctx->stream);
         if (er == cudaSuccess) er = cudaStreamSynchronize(e->ctx->stream);
         cudaFree(tmp);

@@ -53,7 +53,6 @@ constexpr int ST_CHUNK = ST_TPC * IT_TILE_BYTES;       // bytes of one ring slot
 constexpr int ST_SMEM = 227 * 1024;                    // dynamic shared memory of the CTA
 constexpr int ST_BARS = 1024;                          // bytes reserved for mbarriers and flags
 constexpr int ST_SD = 128;                             // delta-rule state size this kernel is built for
-constexpr int ST_VCHUNK = 16384;                       // bytes of one chunk of V rows in the attention phase (two chunks in flight)
 
 struct StepLayer {
     const uint8_t *in_proj, *out_proj, *gate_up, *down;
@@ -96,6 +95,7 @@ struct Cta {
     unsigned nseq;                     // row groups this CTA has started in all matvec phases so far (terms buffer = nseq % ST_TB)
     unsigned mph;                      // matvec phases finished so far
     unsigned tf, te, pd, ps;           // mbarriers: terms full [ST_TB], terms empty [ST_TB], phase done, phase started
+    unsigned at;                       // mbarriers of the attention block: K full / free, V full / free, eight of each
     const StepLayer* lay;              // the two shared-memory copies of layer descriptions (layer il at lay[il & 1])
     unsigned target;                   // arrivals the next grid barrier waits for
     int nsync;                         // grid barriers passed so far (index into the trace)
@@ -212,6 +212,7 @@ __host__ __device__ inline MvSmem mv_layout(int nb) {
 // prefetch_layer: when set, the delta-net block's state tile of that layer is requested right after the activation row has
 // been staged (asynchronous copies for the phase after this one)
 __device__ __forceinline__ void gdn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c, int h);
+__device__ __forceinline__ void attn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c, int h);
 __device__ __forceinline__ void matvec_phase(const StepParams& P, Cta& c, int nb, int rows, const StepLayer* prefetch_layer) {
     const MvSmem L = mv_layout(nb);
     int8_t* xs = reinterpret_cast<int8_t*>(c.scratch + L.x);
@@ -225,7 +226,7 @@ __device__ __forceinline__ void matvec_phase(const StepParams& P, Cta& c, int nb
         for (int i = tid; i < nb / 2; i += ST_CT) dxs[i] = __ldcg(P.qd + i);
         for (int i = tid; i < nb; i += ST_CT) sss[i] = __ldcg(P.qsum + i);
         cp_async_wait_all();
-        if (prefetch_layer) gdn_prefetch(P, *prefetch_layer, c, (int)blockIdx.x);
+        if (prefetch_layer) { if (prefetch_layer->recurrent) gdn_prefetch(P, *prefetch_layer, c, (int)blockIdx.x); else attn_prefetch(P, *prefetch_layer, c, (int)blockIdx.x - P.attn_base); }
         cons_sync();
     }
     ST_EV(P, c, c.evt_base + 1);
@@ -519,65 +520,98 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
 }
 
 // ---------------------------------------------------------------- attention block of one head
-// q / k head norms, rope, the new K / V entries and the causal gated attention of head blockIdx.x in the operation order of
-// k_attn_prep and k_attention (it_support.cu; src/cpu.rs:252-272).  The k and v rows of the new position are recomputed by
-// each of the heads that share the KV head and used from shared memory (after the same f16 rounding the cache applies);
-// the first head of the group stores them into the cache.
-__device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer& L, const Cta& c, int h) {
+// q / k head norms, rope, the new K / V entries and the causal gated attention of head h in the operation order of
+// k_attn_prep and k_attention (it_support.cu; src/cpu.rs:252-272): every score a sequential dot over the head dimension,
+// the exponentials added in ascending position order by one thread, every output element accumulating w[p] * v[p][j] in
+// ascending position order.  The k and v rows of the new position are recomputed by each of the heads that share the KV
+// head and used from shared memory (after the same f16 rounding the cache applies); the first head of the group stores
+// them into the cache.
+// Data movement: both caches are tiled (32 positions x head_dim halves = one contiguous 16 KB block per KV head), so a
+// loader warp brings whole tiles into a ring of 16 KB slots with one bulk copy each.  One warp per slot scores its K
+// tiles, a position per lane, from shared memory; the V tiles follow through the same ring and four warps (two output
+// elements per thread) walk them in order.  Full / free mbarriers pace both; they are set up afresh by every attention
+// block.  The tiles were sent on their way into L2 while the input projection ran (attn_prefetch).
+__device__ __forceinline__ void attn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c, int h) {
+    if (c.warp != 0) return;
+    const int kh = h / (P.nh / P.nkv), ntiles = (*P.pos + 31) / 32; const unsigned bytes = (unsigned)(P.hd * 64);
+    for (int i = c.lane; i < ntiles; i += 32) {
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(L.kc + it_kc_index((size_t)i * 32, kh, 0, P.nkv, P.hd)), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(L.vc + it_vc_index((size_t)i * 32, kh, 0, P.nkv, P.hd)), "r"(bytes) : "memory");
+    }
+}
+constexpr int ST_AT_MAXS = 8, ST_AT_VWARPS = 4, ST_AT_LOADER = ST_NCONS - 1, ST_AT_T = (ST_NCONS - 1) * 32;
+// the block's own barrier: every consumer warp but the loader, which runs ahead and only joins the grid barrier
+__device__ __forceinline__ void at_sync() { asm volatile("bar.sync 4, %0;" :: "n"(ST_AT_T) : "memory"); }
+__device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer& L, Cta& c, int h) {
     const int tid = c.tid, warp = c.warp, lane = c.lane, hd = P.hd, nkv = P.nkv, kvd = nkv * hd;
     const int rep = P.nh / nkv, kh = h / rep;
     const bool writer = h % rep == 0;
-    const int pos = *P.pos, n = pos + 1;
+    const int pos = *P.pos, n = pos + 1, nold = pos;
+    const int ntiles = (nold + 31) / 32;                             // K tiles = V tiles of 32 positions
+    const int tile_bytes = hd * 64;                                  // 32 positions x hd halves
     float* sc = reinterpret_cast<float*>(c.scratch);                 // [n] scores
     float* qs = sc + ((n + 3) & ~3);                                 // [hd] q head after norm + rope
     float* kl = qs + hd;                                             // [hd] k row of the new position as the cache holds it
     float* vl = kl + hd;                                             // [hd] v row of the new position as the cache holds it
     float* red = vl + hd;                                            // [32] + the sum
-    __half* ring = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(red + 48) + ((16u - (smem_u32(red + 48) & 15u)) & 15u));
+    unsigned char* ring = reinterpret_cast<unsigned char*>(red + 48) + ((128u - (smem_u32(red + 48) & 127u)) & 127u);
+    // slots of the ring = warps that score: as many tiles as the scratch holds behind the scores, up to eight; tile i goes
+    // to slot i % S and is scored by warp i % S, so every slot is filled and emptied by the same two warps in order
+    const int S = max(1, min(ST_AT_MAXS, (int)((c.scratch + P.scratch) - ring) / tile_bytes));
+    const unsigned kf = c.at, ke = c.at + 8 * ST_AT_MAXS, vf = c.at + 16 * ST_AT_MAXS, ve = c.at + 24 * ST_AT_MAXS;
+    if (tid == 0) {
+        for (int k = 0; k < 4 * ST_AT_MAXS; k++) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" :: "r"(c.at + 8 * k) : "memory");
+        for (int k = 0; k < ST_AT_MAXS; k++) { mbar_init(kf + 8 * k, 1); mbar_init(ke + 8 * k, 1); mbar_init(vf + 8 * k, 1); mbar_init(ve + 8 * k, ST_AT_VWARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    cons_sync();                                                     // all twelve warps, the loader included
     const float* row = P.arena + P.big1;
     const float* qh = row + (size_t)h * 2 * hd; const float* gate = qh + hd;
     const __half* kc = L.kc; const __half* vc = L.vc;
-    const int cp = ST_VCHUNK / (hd * 2), ppr = hd * 2 / 16;          // positions per chunk of V rows; 16-byte pieces per row
-    const int nold = n - 1, nchunks = (nold + cp - 1) / cp;
-    // chunks of V rows in flight: as many as the scratch holds behind the scores (two to four)
-    const int room = (int)((c.scratch + P.scratch) - reinterpret_cast<unsigned char*>(ring)) / ST_VCHUNK;
-    const int depth = room >= 4 ? 4 : room >= 3 ? 3 : 2;
-    {   // the head's K tiles and V rows on their way into L2 before anything waits for them
-        const int ktiles = (nold + 31) / 32, klines = hd * 32 * 2 / 128;
-        for (int i = tid; i < ktiles * klines; i += ST_CT)
-            asm volatile("prefetch.global.L2 [%0];" :: "l"(kc + it_kc_index((size_t)(i / klines) * 32, kh, 0, nkv, hd) + (size_t)(i % klines) * 64));
-        const int vlines = hd * 2 / 128;
-        for (int i = tid; i < nold * vlines; i += ST_CT)
-            asm volatile("prefetch.global.L2 [%0];" :: "l"(vc + (size_t)(i / vlines) * kvd + kh * hd + (size_t)(i % vlines) * 64));
-    }
-    auto issue = [&](int ck) {
-        if (ck < nchunks) {
-            const int p0 = ck * cp, rows = min(cp, nold - p0);
-            __half* dst = ring + (size_t)(ck % depth) * cp * hd;
-            for (int i = tid; i < rows * ppr; i += ST_CT) {
-                const int r = i / ppr, k = i % ppr;
-                cp_async16(dst + r * hd + k * 8, vc + (size_t)(p0 + r) * kvd + kh * hd + k * 8);
+
+    if (warp == ST_AT_LOADER) {
+        // ---- loader: K tiles, then V tiles, as far ahead as the ring allows
+        for (int i = 0; i < ntiles; i++) {
+            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+            if (!mbar_wait(ke + 8 * sl, (u & 1u) ^ 1u, c.abort_flag, P.error_flag, 8)) break;
+            if (lane == 0) {
+                mbar_expect_tx(kf + 8 * sl, (unsigned)tile_bytes);
+                bulk_load(smem_u32(ring + sl * tile_bytes), kc + it_kc_index((size_t)i * 32, kh, 0, nkv, hd), (unsigned)tile_bytes, kf + 8 * sl);
             }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    ST_EV(P, c, c.evt_base + 4);
-    for (int ck = 0; ck < depth - 1; ck++) issue(ck);
+        // the V tiles go through the same slots: not before the last K tile of every slot has been scored
+        for (int i = ntiles > S ? ntiles - S : 0; i < ntiles; i++) {
+            if (!mbar_wait(ke + 8 * (i % S), (unsigned)(i / S) & 1u, c.abort_flag, P.error_flag, 8)) break;
+        }
+        for (int i = 0; i < ntiles; i++) {
+            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+            if (!mbar_wait(ve + 8 * sl, (u & 1u) ^ 1u, c.abort_flag, P.error_flag, 9)) break;
+            if (lane == 0) {
+                mbar_expect_tx(vf + 8 * sl, (unsigned)tile_bytes);
+                bulk_load(smem_u32(ring + sl * tile_bytes), vc + it_vc_index((size_t)i * 32, kh, 0, nkv, hd), (unsigned)tile_bytes, vf + 8 * sl);
+            }
+        }
+        return;                                                      // the loader meets the others at the grid barrier
+    }
     if (warp < 2) {
         // warp 0: q head; warp 1: k head.  rmsnorm with the squares added by one lane in index order, weight, rope.
         float* buf = warp == 0 ? qs : kl;
         const float* x = warp == 0 ? qh : row + (size_t)P.nh * 2 * hd + kh * hd;
         const float* w = warp == 0 ? L.q_norm : L.k_norm;
+        float wr[8];                                                  // hd <= 256: the norm weights are requested before the sum needs time
+#pragma unroll
+        for (int k = 0; k < 8; k++) wr[k] = lane + 32 * k < hd ? w[lane + 32 * k] : 0.f;
         for (int i = lane; i < hd; i += 32) buf[i] = __ldcg(x + i);
         __syncwarp();
         float s = 0.f;
         if (lane == 0) {
-#pragma unroll 8
+#pragma unroll 16
             for (int i = 0; i < hd; i++) s = it_add(s, it_mul(buf[i], buf[i]));
         }
         s = __shfl_sync(0xffffffffu, s, 0);
         const float scl = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)hd), P.eps)));
-        for (int i = lane; i < hd; i += 32) buf[i] = it_mul(it_mul(buf[i], scl), w[i]);
+#pragma unroll
+        for (int k = 0; k < 8; k++) if (lane + 32 * k < hd) buf[lane + 32 * k] = it_mul(it_mul(buf[lane + 32 * k], scl), wr[k]);
         __syncwarp();
         const int half = P.n_rot / 2, sect = P.sec[0] + P.sec[1] + P.sec[2] + P.sec[3];
         for (int i = lane; i < half; i += 32) {
@@ -600,95 +634,91 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         const float* v = row + (size_t)P.nh * 2 * hd + kvd + kh * hd;
         for (int i = lane; i < hd; i += 32) {
             const __half hv = __float2half_rn(__ldcg(v + i));
-            if (writer) const_cast<__half*>(vc)[(size_t)pos * kvd + kh * hd + i] = hv;
+            if (writer) const_cast<__half*>(vc)[it_vc_index(pos, kh, i, nkv, hd)] = hv;
             vl[i] = __half2float(hv);
         }
     }
-    ST_EV(P, c, c.evt_base + 5);
-    cons_sync();
+    at_sync();                                                       // q, and the new position's k and v, are in shared memory
     const float scale = it_div(1.0f, it_sqrt((float)hd));
     const int nvec = hd / 8;
     float mx = -INFINITY;
-    for (int p = tid; p < n; p += ST_CT) {
-        float s = 0.f;
-        if (p < nold) {
-            const uint4* kp = reinterpret_cast<const uint4*>(kc + it_kc_index(p, kh, 0, nkv, hd));    // piece v of 32 consecutive positions is contiguous
-            // four 16-byte pieces per batch; the next batch is requested before the current one is added up
-            uint4 cur[4], nxt[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) if (u < nvec) cur[u] = __ldcg(kp + u * 32);
-            for (int v0 = 0; v0 < nvec; v0 += 4) {
-#pragma unroll
-                for (int u = 0; u < 4; u++) if (v0 + 4 + u < nvec) nxt[u] = __ldcg(kp + (v0 + 4 + u) * 32);
-#pragma unroll
-                for (int u = 0; u < 4; u++) if (v0 + u < nvec) {
-                    const __half2* hh = reinterpret_cast<const __half2*>(&cur[u]);
-                    const float* qv = qs + (v0 + u) * 8;
-#pragma unroll
-                    for (int i2 = 0; i2 < 4; i2++) { const float2 f = __half22float2(hh[i2]); s = it_add(s, it_mul(qv[2 * i2], f.x)); s = it_add(s, it_mul(qv[2 * i2 + 1], f.y)); }
+    if (warp < S) {
+        // ---- scores: tile i by warp i % S, position 32 i + lane; piece v of the tile's 32 positions is contiguous
+        for (int i = warp; i < ntiles; i += S) {
+            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+            if (!mbar_wait(kf + 8 * sl, u & 1u, c.abort_flag, P.error_flag, 10)) break;
+            const int p = i * 32 + lane;
+            if (p < nold) {
+                const uint4* kp = reinterpret_cast<const uint4*>(ring + sl * tile_bytes) + lane;
+                float s = 0.f;
+#pragma unroll 4
+                for (int v = 0; v < nvec; v++) {
+                    const uint4 kk = kp[v * 32];
+                    const __half2* hh = reinterpret_cast<const __half2*>(&kk);
+                    const float4 qa = *reinterpret_cast<const float4*>(qs + v * 8), qb = *reinterpret_cast<const float4*>(qs + v * 8 + 4);
+                    float2 f = __half22float2(hh[0]); s = it_add(s, it_mul(qa.x, f.x)); s = it_add(s, it_mul(qa.y, f.y));
+                    f = __half22float2(hh[1]); s = it_add(s, it_mul(qa.z, f.x)); s = it_add(s, it_mul(qa.w, f.y));
+                    f = __half22float2(hh[2]); s = it_add(s, it_mul(qb.x, f.x)); s = it_add(s, it_mul(qb.y, f.y));
+                    f = __half22float2(hh[3]); s = it_add(s, it_mul(qb.z, f.x)); s = it_add(s, it_mul(qb.w, f.y));
                 }
-#pragma unroll
-                for (int u = 0; u < 4; u++) cur[u] = nxt[u];
+                s = it_mul(s, scale); sc[p] = s; mx = fmaxf(mx, s);
             }
-        } else {
-#pragma unroll 8
-            for (int j = 0; j < hd; j++) s = it_add(s, it_mul(qs[j], kl[j]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ke + 8 * sl);
         }
-        s = it_mul(s, scale); sc[p] = s; mx = fmaxf(mx, s);
+    } else if (warp == ST_AT_MAXS && lane == 0) {
+        float s = 0.f;                                               // the new position, from its row in shared memory
+#pragma unroll 16
+        for (int j = 0; j < hd; j++) s = it_add(s, it_mul(qs[j], kl[j]));
+        s = it_mul(s, scale); sc[nold] = s; mx = s;
     }
-    ST_EV(P, c, c.evt_base + 6);
 #pragma unroll
     for (int mm = 16; mm >= 1; mm >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, mm));
     if (lane == 0) red[warp] = mx;
-    cons_sync();
+    at_sync();
     mx = red[0];
 #pragma unroll
-    for (int k = 1; k < ST_NCONS; k++) mx = fmaxf(mx, red[k]);
-    for (int p = tid; p < n; p += ST_CT) sc[p] = it_expf(it_sub(sc[p], mx));
-    cons_sync();
+    for (int k = 1; k < ST_NCONS - 1; k++) mx = fmaxf(mx, red[k]);
+    for (int p = tid; p < n; p += ST_AT_T) sc[p] = it_expf(it_sub(sc[p], mx));
+    at_sync();
     if (tid == 0) {
         float s = 0.f;
-#pragma unroll 8
+#pragma unroll 32
         for (int p = 0; p < n; p++) s = it_add(s, sc[p]);
         red[32] = s;
     }
-    cons_sync();
+    at_sync();
     const float sum = red[32];
-    for (int p = tid; p < n; p += ST_CT) sc[p] = it_div(sc[p], sum);
-    cons_sync();
-    // output element j adds w[p] * v[p][j] in ascending p; the V rows stream through two chunks in shared memory
-    ST_EV(P, c, c.evt_base + 7);
-    float acc0 = 0.f, acc1 = 0.f;
-    for (int ck = 0; ck < nchunks; ck++) {
-        issue(ck + depth - 1);
-        if (depth == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
-        else if (depth == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
-        else asm volatile("cp.async.wait_group 1;" ::: "memory");
-        cons_sync();
-        if (2 * tid < hd) {
-            const int p0 = ck * cp, rows = min(cp, nold - p0);
-            const __half* src = ring + (size_t)(ck % depth) * cp * hd + 2 * tid;
-            int r = 0;
-            for (; r + 4 <= rows; r += 4) {
-                const float w[4] = { sc[p0 + r], sc[p0 + r + 1], sc[p0 + r + 2], sc[p0 + r + 3] };
-                float2 v[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) v[u] = __half22float2(*reinterpret_cast<const __half2*>(src + (r + u) * hd));
-#pragma unroll
-                for (int u = 0; u < 4; u++) { acc0 = it_add(acc0, it_mul(w[u], v[u].x)); acc1 = it_add(acc1, it_mul(w[u], v[u].y)); }
+    for (int p = tid; p < n; p += ST_AT_T) sc[p] = it_div(sc[p], sum);
+    at_sync();
+    if (warp < ST_AT_VWARPS) {
+        // ---- output: element j adds w[p] * v[p][j] in ascending p; thread tid owns elements 2 tid, 2 tid + 1 (hd <= 256)
+        const bool live = 2 * tid < hd;
+        float acc0 = 0.f, acc1 = 0.f;
+        for (int i = 0; i < ntiles; i++) {
+            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+            if (!mbar_wait(vf + 8 * sl, u & 1u, c.abort_flag, P.error_flag, 11)) break;
+            const int rows = min(32, nold - i * 32);
+            if (live) {
+                const __half* src = reinterpret_cast<const __half*>(ring + sl * tile_bytes) + 2 * tid;
+                const float* wp = sc + i * 32;
+#pragma unroll 8
+                for (int r = 0; r < rows; r++) {
+                    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(src + r * hd));
+                    const float w = wp[r];
+                    acc0 = it_add(acc0, it_mul(w, v.x)); acc1 = it_add(acc1, it_mul(w, v.y));
+                }
             }
-            for (; r < rows; r++) { const float w = sc[p0 + r]; const float2 v = __half22float2(*reinterpret_cast<const __half2*>(src + r * hd)); acc0 = it_add(acc0, it_mul(w, v.x)); acc1 = it_add(acc1, it_mul(w, v.y)); }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ve + 8 * sl);
         }
-        cons_sync();
-    }
-    ST_EV(P, c, c.evt_base + 8);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (2 * tid < hd) {
-        const float w = sc[nold];
-        acc0 = it_add(acc0, it_mul(w, vl[2 * tid])); acc1 = it_add(acc1, it_mul(w, vl[2 * tid + 1]));
-        float* op = P.arena + P.o + (size_t)h * hd + 2 * tid;
-        __stcg(op, it_mul(acc0, it_sigmoid(__ldcg(gate + 2 * tid))));
-        __stcg(op + 1, it_mul(acc1, it_sigmoid(__ldcg(gate + 2 * tid + 1))));
+        if (live) {
+            const float w = sc[nold];
+            acc0 = it_add(acc0, it_mul(w, vl[2 * tid])); acc1 = it_add(acc1, it_mul(w, vl[2 * tid + 1]));
+            float* op = P.arena + P.o + (size_t)h * hd + 2 * tid;
+            __stcg(op, it_mul(acc0, it_sigmoid(__ldcg(gate + 2 * tid))));
+            __stcg(op + 1, it_mul(acc1, it_sigmoid(__ldcg(gate + 2 * tid + 1))));
+        }
     }
 }
 
@@ -702,13 +732,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
     c.abort_flag = reinterpret_cast<volatile int*>(tail + ST_BARS - 16);
     c.tid = threadIdx.x; c.warp = c.tid >> 5; c.lane = c.tid & 31;
     c.q = 0u; c.nseq = 0u; c.mph = 0u; c.nsync = 0; c.evt_on = 0;
-    c.tf = c.bars + 8 * (2 * P.slots); c.te = c.tf + 8 * ST_TB; c.pd = c.te + 8 * ST_TB; c.ps = c.pd + 8;
+    c.tf = c.bars + 8 * (2 * P.slots); c.te = c.tf + 8 * ST_TB; c.pd = c.te + 8 * ST_TB; c.ps = c.pd + 8; c.at = c.bars + 704;
     c.lay = reinterpret_cast<const StepLayer*>(tail + 384);         // two layer descriptions, then the sum warps' greedy picks
     if (c.tid == 0) {
         *c.abort_flag = *reinterpret_cast<volatile unsigned*>(P.sync + 2) ? 1 : 0;      // a step that was given up earlier: nothing runs until the host has cleared the words
         for (int s = 0; s < P.slots; s++) { mbar_init(c.bars + 8 * s, 1); mbar_init(c.bars + 8 * (P.slots + s), ST_CW); }
         for (int k = 0; k < ST_TB; k++) { mbar_init(c.tf + 8 * k, ST_NCONS); mbar_init(c.te + 8 * k, 1); }
         mbar_init(c.pd, ST_NSUM); mbar_init(c.ps, ST_NCONS);
+        for (int k = 0; k < 4 * ST_AT_MAXS; k++) mbar_init(c.at + 8 * k, 1);     // set up again, with their counts, by every attention block
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     {   // the first layer's description into shared memory (later ones are copied a layer ahead)
@@ -789,7 +820,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
             else if (sub == 4) { nb = (L.recurrent ? P.inner : P.nh * P.hd) / 128; rows = e; }
             else if (sub == 6) { nb = nb_e; rows = 2 * P.ff; }
             else { nb = P.ff / 128; rows = e; }
-            matvec_phase(P, c, nb, rows, (!tail && sub == 1 && L.recurrent && (int)blockIdx.x < P.nv) ? &L : nullptr);
+            const bool block_cta = L.recurrent ? (int)blockIdx.x < P.nv : ((int)blockIdx.x >= P.attn_base && (int)blockIdx.x < P.attn_base + P.nh);
+            matvec_phase(P, c, nb, rows, (!tail && sub == 1 && block_cta) ? &L : nullptr);
             if (tail && c.warp == 0 && c.lane == 0) {
                 // greedy pick (first index of the maximum): each sum warp has left the best of its rows behind the layer descriptions
                 const Pick* pk = reinterpret_cast<const Pick*>(c.lay + 2);
@@ -837,7 +869,7 @@ static size_t step_scratch_bytes(const it_model_config& c) {
     size_t s = (size_t)mv_layout(widest / 128).total;
     s = std::max(s, sizeof(it_had_smem));
     s = std::max(s, step_gdn_off(c) + (size_t)(ST_SD * ST_SD + 4 * ST_SD + 8) * 4 + 16 * 8 + 64);
-    s = std::max(s, ((size_t)c.ctx_len + 4 + 3 * c.head_dim + 48) * 4 + 16 + 2 * (size_t)ST_VCHUNK);
+    s = std::max(s, ((size_t)c.ctx_len + 4 + 3 * c.head_dim + 48) * 4 + 128 + 3 * (size_t)c.head_dim * 64);
     return (s + 127) / 128 * 128;
 }
 
@@ -849,7 +881,6 @@ int it_step_prepare(it_engine* e) {
     if (e->world != 1) return IT_OK;                                  // row shards exchange results inside the per-op kernels
     if (c.ssm_state != ST_SD || c.conv_k > 8 || c.head_dim > 256 || c.head_dim % 8 || c.n_embd > 8192 || c.n_ff % 1024 || c.ssm_inner % 1024 || (c.n_head * c.head_dim) % 1024) return IT_OK;
     if (c.ssm_vheads > cx->sm_count || c.n_head > cx->sm_count || c.n_ff / 1024 > cx->sm_count || c.ssm_vheads % c.ssm_groups) return IT_OK;
-    if (ST_VCHUNK / (c.head_dim * 2) < 1) return IT_OK;
     const size_t scratch = step_scratch_bytes(c);
     const long long ring = (long long)ST_SMEM - (long long)scratch - ST_BARS;
     int slots = 1;

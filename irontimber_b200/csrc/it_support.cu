@@ -226,7 +226,8 @@ __global__ void k_kv_store(const float* k, const float* v, size_t ts, T* kc, T* 
     if (i >= kvd) return;
     const size_t ki = sizeof(T) == 2 ? it_kc_index(slot0 + t, i / hd, i % hd, kvd / hd, hd) : (size_t)(slot0 + t) * kvd + i;   // the f16 K cache is tiled
     kc[ki] = kv_pack<T>(k[t * ts + i]);
-    vc[(size_t)(slot0 + t) * kvd + i] = kv_pack<T>(v[t * ts + i]);
+    const size_t vi = sizeof(T) == 2 ? it_vc_index(slot0 + t, i / hd, i % hd, kvd / hd, hd) : (size_t)(slot0 + t) * kvd + i;       // the f16 V cache is tiled too
+    vc[vi] = kv_pack<T>(v[t * ts + i]);
 }
 
 // ---------------------------------------------------------------- fused kernels of the decode path (up to 8 rows)
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(128) k_attn_prep(float* qkv, size_t ts, int nh
     float* row = qkv + t * ts;
     if (job >= nh + nkv) {                                   // v head: into the cache as it is
         const int kh = job - nh - nkv; const float* v = row + (size_t)nh * 2 * hd + kvd + kh * hd;
-        for (int i = lane; i < hd; i += 32) vc[(size_t)(slot0 + t) * kvd + kh * hd + i] = __float2half_rn(v[i]);
+        for (int i = lane; i < hd; i += 32) vc[it_vc_index(slot0 + t, kh, i, nkv, hd)] = __float2half_rn(v[i]);
         return;
     }
     const bool is_q = job < nh;
@@ -487,7 +488,8 @@ __global__ void __launch_bounds__(1024) k_attention(const float* q, size_t q_hs,
             for (int i = tid; i < rows * ppr; i += 1024) {
                 const int r = i / ppr, k = i % ppr;
                 const unsigned d = (unsigned)__cvta_generic_to_shared(dst + r * hd + k * epp);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(d), "l"(vc + (size_t)(p0 + r) * kvd + kh * hd + k * epp));
+                const T* vsrc = sizeof(T) == 2 ? vc + it_vc_index(p0 + r, kh, k * epp, nkv, hd) : vc + (size_t)(p0 + r) * kvd + kh * hd + k * epp;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(d), "l"(vsrc));
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");

@@ -9,6 +9,12 @@ __host__ __device__ static inline size_t it_kc_index(size_t pos, int kh, int j, 
     return (((pos >> 5) * (size_t)nkv + kh) * (size_t)(hd >> 3) + (size_t)(j >> 3)) * 256 + (pos & 31) * 8 + (j & 7);
 }
 
+// f16 V cache of the trunk: tiles of 32 positions per KV head with the rows of a tile contiguous, [position tile][kv head]
+// [32 positions][head_dim], so that the V rows of 32 positions of one head are one contiguous block (one bulk copy).
+__host__ __device__ static inline size_t it_vc_index(size_t pos, int kh, int j, int nkv, int hd) {
+    return (((pos >> 5) * (size_t)nkv + kh) * 32 + (pos & 31)) * (size_t)hd + (size_t)j;
+}
+
 // Work done on the way into the Hadamard + q8k kernel.  mode 0: nothing.  mode 1: input = silu(x) * b (b is a device
 // pointer, rows b_stride apart).  mode 2: input = rmsnorm(x) over the whole row of width n with weight w and eps; when
 // xn_out is set the normed f32 row is also stored there (rows xn_stride apart).

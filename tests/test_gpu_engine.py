@@ -249,3 +249,25 @@ def test_step_kernel_and_per_op_schedule_agree(orc, monkeypatch):
     assert all(np.array_equal(x, y) for x, y in zip(a[0], b[0]))
     assert a[1] == b[1] and a[3:5] == b[3:5]
     assert all(np.array_equal(x, y) for x, y in zip(a[2], b[2]))
+
+
+def test_step_kernel_matches_the_per_op_schedule_at_long_positions(monkeypatch):
+    """Decode steps after a 330-token prompt: the attention block of the step kernel then walks more K tiles and V chunks
+    than its ring holds and crosses a 32-position tile boundary.  Picks, logits and caches equal the per-op schedule's."""
+    from irontimber_b200.engine import CudaEngine, ModelConfig
+    prompt = [int(t) for t in np.random.default_rng(77).integers(0, 1000, 330)]
+    results = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("IT_STEP_KERNEL", flag)
+        eng = CudaEngine(tiny_config(ModelConfig, ctx_len=448), seed=43, with_mtp=False)
+        try:
+            first = eng.eval_argmax(prompt)
+            hist = [first] + eng.generate([first], 40)
+            lg = bits(eng.eval([hist[-1]])).copy()
+            states = [bits(eng.state(il, k)).copy() for il in range(eng.cfg.n_layer) for k in ((0, 1) if eng.cfg.is_recurrent(il) else (2, 3))]
+            results.append((hist, lg, states))
+        finally:
+            eng.close()
+    a, b = results
+    assert a[0] == b[0] and np.array_equal(a[1], b[1])
+    assert all(np.array_equal(x, y) for x, y in zip(a[2], b[2]))
