@@ -176,7 +176,7 @@ int it_engine_build(int device, const it_model_config* cfg, uint64_t seed, int w
     const int e_ = c.n_embd, ff = c.n_ff, hd = c.head_dim, nh = c.n_head, nkv = c.n_head_kv, kvd = nkv * hd, qf = 2 * nh * hd;
     const int cd = it_cfg_conv_dim(c), inner = c.ssm_inner, nv = c.ssm_vheads, sd = c.ssm_state;
     it_engine* e = new it_engine();
-    e->ctx = nullptr; e->step = nullptr; e->cfg = c; e->seed = seed; e->has_mtp = with_mtp != 0; e->rank = rank; e->world = world; e->output = nullptr; e->tok_embd = e->m_tok_embd = nullptr; e->q8 = nullptr; e->step_graph = nullptr; e->host_pin = nullptr; e->small_pin = nullptr; e->small_next = 0;
+    e->ctx = nullptr; e->step = nullptr; e->pin_next = 0; e->cfg = c; e->seed = seed; e->has_mtp = with_mtp != 0; e->rank = rank; e->world = world; e->output = nullptr; e->tok_embd = e->m_tok_embd = nullptr; e->q8 = nullptr; e->step_graph = nullptr; e->host_pin = nullptr; e->small_pin = nullptr; e->small_next = 0;
     { const char* v = getenv("IT_PASS_GRAPHS"); e->record_passes = !v || atoi(v) != 0; }
     e->m_eh = e->m_q = e->m_k = e->m_v = e->m_o = e->m_gate = e->m_up = e->m_down = nullptr;
     e->pos = 0; e->mpos = 1; e->hp_off = 0; e->hp_n = 0; e->last_rows = 0;
@@ -244,7 +244,7 @@ int it_engine_build(int device, const it_model_config* cfg, uint64_t seed, int w
     E_TRY(it_q8_create(e->ctx, (size_t)std::max(std::max(e_, ff), std::max(inner, nh * hd)), IT_MAXT, &e->q8));
     E_TRY(dev_alloc(e, (void**)&e->toks_dev, (2 * IT_MAXT + 8) * sizeof(uint32_t), true));
     E_TRY(dev_alloc(e, (void**)&e->pos_dev, 64, true));
-    if (cudaHostAlloc((void**)&e->host_pin, (2 * IT_MAXT + 8) * sizeof(uint32_t), cudaHostAllocDefault) != cudaSuccess) return fail(it_fail(IT_ENOMEM, "engine: pinned staging allocation failed"));
+    if (cudaHostAlloc((void**)&e->host_pin, (size_t)IT_PIN_SLOTS * IT_PIN_WORDS * sizeof(uint32_t), cudaHostAllocDefault) != cudaSuccess) return fail(it_fail(IT_ENOMEM, "engine: pinned staging allocation failed"));
     if (cudaHostAlloc((void**)&e->small_pin, IT_SMALL_SLOTS * 16 * sizeof(uint32_t), cudaHostAllocDefault) != cudaSuccess) return fail(it_fail(IT_ENOMEM, "engine: pinned staging allocation failed"));
     if (cudaStreamSynchronize(e->ctx->stream) != cudaSuccess) return fail(it_fail(IT_ECUDA, "engine: weight generation failed: %s", cudaGetErrorString(cudaGetLastError())));
     E_TRY(it_step_prepare(e));

@@ -59,6 +59,7 @@ struct it_engine {
     int last_rows;                                   // rows of the last verification pass (it_engine_mtp_rollback)
     it_graph* step_graph;                            // recorded single-token greedy step
     uint32_t* host_pin;                              // pinned staging, laid out like toks_dev, plus the position at [2*IT_MAXT]
+    int pin_next;                                    // host_pin is a ring of IT_PIN_SLOTS such blocks: a block is not rewritten before the copies out of it have run
     // Recorded passes of up to IT_SMALL_ROWS rows (single tokens, verification rows, draft steps of the head), one graph
     // per shape; their token ids and positions are staged through a ring of pinned slots so that a slot is never
     // rewritten while an earlier copy out of it may still be pending.
@@ -67,6 +68,8 @@ struct it_engine {
     int small_next;
     bool record_passes;                              // environment IT_PASS_GRAPHS (default on)
 };
+#define IT_PIN_SLOTS 8
+#define IT_PIN_WORDS (2 * IT_MAXT + 8)
 #define IT_SMALL_ROWS 8
 #define IT_SMALL_SLOTS 64
 

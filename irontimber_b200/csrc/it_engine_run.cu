@@ -34,6 +34,13 @@ int logits_and_argmax(it_engine* e, size_t h_off, int rows) {
 
 }  // namespace
 
+// The next block of the pinned staging ring.  Copies out of a block are asynchronous and the host runs passes ahead of the
+// device, so a block is reused only after a synchronisation has shown that every copy out of the ring has run.
+static uint32_t* pin_block(it_engine* e) {
+    if (e->pin_next == IT_PIN_SLOTS) { cudaStreamSynchronize(e->ctx->stream); e->pin_next = 0; }
+    return e->host_pin + (size_t)IT_PIN_WORDS * (size_t)(e->pin_next++);
+}
+
 int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_rows, int nck, bool from_dev) {
     it_ctx* cx = e->ctx; const it_model_config& c = e->cfg; const it_arena_layout& L = e->lay;
     float* A = cx->arena;
@@ -45,8 +52,10 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
     if (e->step && nt == 1 && nck == 0 && from_dev) return it_step_launch(e, logit_rows ? 4 : 0);
     const int* pos_ptr = from_dev ? e->pos_dev : nullptr; const int pos0 = from_dev ? 0 : e->pos;
     if (!from_dev) {
-        for (int t = 0; t < nt; t++) { if (toks[t] >= (uint32_t)c.n_vocab) return it_fail(IT_EINVAL, "engine: token id %u outside the vocabulary", toks[t]); e->host_pin[t] = toks[t]; }
-        IT_CUDA(cudaMemcpyAsync(e->toks_dev, e->host_pin, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+        for (int t = 0; t < nt; t++) if (toks[t] >= (uint32_t)c.n_vocab) return it_fail(IT_EINVAL, "engine: token id %u outside the vocabulary", toks[t]);
+        uint32_t* pin = pin_block(e);
+        for (int t = 0; t < nt; t++) pin[t] = toks[t];
+        IT_CUDA(cudaMemcpyAsync(e->toks_dev, pin, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
     }
     IT_TRY(it_sup_embed(cx, e->toks_dev, e->tok_embd, e_, nt, A + L.x));
     // rmsnorm fused into the Hadamard + q8k kernel; the normed f32 row is kept only where a dense f32 op needs it
@@ -137,8 +146,9 @@ int mtp_pass(it_engine* e, const uint32_t* toks, int nt, int pos0, size_t hoff, 
     const int* pos_ptr = from_dev ? e->pos_dev + 1 : nullptr;
     if (from_dev) pos0 = 0;                                   // the kernels add the device-resident position
     else {
-        for (int t = 0; t < nt; t++) e->host_pin[IT_MAXT + t] = toks[t];
-        IT_CUDA(cudaMemcpyAsync(e->toks_dev + IT_MAXT, e->host_pin + IT_MAXT, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
+        uint32_t* pin = pin_block(e) + IT_MAXT;
+        for (int t = 0; t < nt; t++) pin[t] = toks[t];
+        IT_CUDA(cudaMemcpyAsync(e->toks_dev + IT_MAXT, pin, nt * sizeof(uint32_t), cudaMemcpyHostToDevice, cx->stream));
     }
     IT_TRY(it_sup_embed(cx, e->toks_dev + IT_MAXT, e->m_tok_embd, e_, nt, A + L.me));
     IT_TRY(it_sup_rmsnorm_wide(cx, A + L.me, e_, e->m_enorm, e_, c.eps, A + L.mcat, 2 * e_, nt));
@@ -267,8 +277,9 @@ namespace {
 // one pass with the position read on the device, pick -> token slot and position + 1.
 int begin_device_decode(it_engine* e) {
     it_ctx* cx = e->ctx;
-    e->host_pin[2 * IT_MAXT] = (uint32_t)e->pos;
-    IT_CUDA(cudaMemcpyAsync(e->pos_dev, e->host_pin + 2 * IT_MAXT, 4, cudaMemcpyHostToDevice, cx->stream));
+    uint32_t* pin = pin_block(e) + 2 * IT_MAXT;
+    *pin = (uint32_t)e->pos;
+    IT_CUDA(cudaMemcpyAsync(e->pos_dev, pin, 4, cudaMemcpyHostToDevice, cx->stream));
     if (e->step_graph) return IT_OK;
     IT_TRY(it_capture_begin(cx));
     int r;

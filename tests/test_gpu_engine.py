@@ -251,6 +251,31 @@ def test_step_kernel_and_per_op_schedule_agree(orc, monkeypatch):
     assert all(np.array_equal(x, y) for x, y in zip(a[2], b[2]))
 
 
+def test_prompt_of_several_full_passes_bit_exact(orc):
+    """A 330-token prompt is five 64-row passes and one of 10 rows, enqueued back to back while the device still works on
+    the first: every pass must see its own token ids (the host stages them in a ring of pinned blocks).  Logits, state and
+    the continuation (attention over more K / V tiles than the step kernel's ring holds) equal the token-by-token oracle."""
+    from irontimber_b200.engine import CudaEngine, ModelConfig
+    eng = CudaEngine(tiny_config(ModelConfig, ctx_len=448), seed=43, with_mtp=False)
+    m = oracle_model_from_engine(orc, eng, with_mtp=False)
+    try:
+        prompt = [int(t) for t in np.random.default_rng(77).integers(0, 1000, 330)]
+        st = m.new_state()
+        for i, t in enumerate(prompt):
+            want = m.forward_token(st, t, i + 1 == len(prompt), orc.DEVICE_ORDER)
+        for _ in range(3):              # the hazard is one of timing: more than one try
+            eng.reset()
+            lg = eng.eval(prompt)
+            assert np.array_equal(bits(lg), bits(want))
+            for il in range(eng.cfg.n_layer):
+                for kind in ((0, 1) if eng.cfg.is_recurrent(il) else (2, 3)):
+                    assert np.array_equal(bits(eng.state(il, kind)), bits(m.state_read(st, il, kind))), f"state {kind} of layer {il}"
+        eng.reset()
+        assert eng.generate(prompt, 12) == orc.generate_greedy(m, prompt, 12, orc.DEVICE_ORDER)
+    finally:
+        m.close(); eng.close()
+
+
 def test_step_kernel_matches_the_per_op_schedule_at_long_positions(monkeypatch):
     """Decode steps after a 330-token prompt: the attention block of the step kernel then walks more K tiles and V chunks
     than its ring holds and crosses a 32-position tile boundary.  Picks, logits and caches equal the per-op schedule's."""
