@@ -34,6 +34,7 @@ int logits_and_argmax(it_engine* e, size_t h_off, int rows) {
 
 }  // namespace
 
+static_assert(IT_MAXT <= IT_GDN_MAXROWS, "a pass must fit the delta-rule kernel's staging");
 // The next block of the pinned staging ring.  Copies out of a block are asynchronous and the host runs passes ahead of the
 // device, so a block is reused only after a synchronisation has shown that every copy out of the ring has run.
 static uint32_t* pin_block(it_engine* e) {
@@ -103,7 +104,11 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
                 IT_TRY(it_sup_rope(cx, k, hd, s_att, nkv, nt, pos0, pos_ptr, c.n_rot, e->theta_scale, c.rope_sections));
                 IT_TRY(it_sup_kv_store(cx, k, v, s_att, l.kc, l.vc, kvd, hd, pos0, pos_ptr, nt, 1));
             }
-            IT_TRY(it_sup_attention(cx, q, 2 * hd, s_att, q + hd, l.kc, l.vc, kvd, hd, nh, nkv, pos0, pos_ptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 1));
+            // prompt passes: one CTA per group of query heads and pair of rows that share their K / V reads; else one per (head, row)
+            int ar = 1;
+            static const bool grouped = []{ const char* v = getenv("IT_ATTN_GROUPED"); return !v || atoi(v) != 0; }();
+            if (grouped && nt > 8 && !pos_ptr) { ar = it_sup_attention_prefill(cx, q, 2 * hd, s_att, q + hd, l.kc, l.vc, hd, nh, nkv, pos0, A + L.o, (size_t)nh * hd, nt); if (ar < 0) return ar; }
+            if (ar == 1) IT_TRY(it_sup_attention(cx, q, 2 * hd, s_att, q + hd, l.kc, l.vc, kvd, hd, nh, nkv, pos0, pos_ptr, c.ctx_len, A + L.o, (size_t)nh * hd, nt, 1));
             IT_TRY(had_mv(e, l.o, nt, L.o, (size_t)nh * hd, L.x, e_, 1, true));
         }
         IT_TRY(norm_had(l.post_norm, nullptr));

@@ -339,114 +339,129 @@ __global__ void __launch_bounds__(256) k_conv_l2_dense(const float* mixed, size_
 }
 
 // Gated delta rule (src/cpu.rs:215-232) and the gated per-head norm that follows it (:233-237) in one launch: one CTA
-// per head.  Warps 0..SD/32-1 own one state row per thread and walk the tokens; an extra warp norms the outputs of row t
-// (squares added by one lane in index order), weights them and multiplies by silu(z) while the row owners are already
-// on row t + 1 (the outputs are double-buffered).  State layout [head][j][i] as on the CPU.
+// per head.  Warps 0..SD/32-1 own one state row per thread and walk the tokens; four extra warps take turns to norm the
+// outputs of a row (squares added by one lane in index order), weight them and multiply by silu(z) while the row owners
+// are already on the next rows (one output buffer per norm warp).  State layout [head][j][i] as on the CPU.
 // The head's SD x SD state sits in shared memory for the whole launch, rows unpadded, the 16-byte pieces of row j
 // stored at piece index ^ (j & 7): both the coalesced 16-byte moves of the tile and the 16-byte accesses of the row
 // owners are then free of bank conflicts.
+constexpr int GN_NW = 4;      // norm warps of k_gdn_norm: warp w norms the rows t with t % GN_NW == w out of its own output buffer
 template <int SD>
-__global__ void __launch_bounds__(SD + 32, 1) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
+__global__ void __launch_bounds__(SD + 32 * GN_NW, 1) k_gdn_norm(const float* co, size_t co_ts, const float* beta, const float* alpha, size_t ba_ts, const float* __restrict__ dt, const float* __restrict__ a,
                                                       float* state, float* o, size_t o_ts, int nk, int qk, int nt, float* ck, size_t ck_stride, int nck,
                                                       const float* __restrict__ nw, float eps, const float* z, size_t z_ts) {
     IT_PDL_TRIGGER(); IT_PDL_WAIT();
-    extern __shared__ __align__(16) float tile[];      // [SD][SD] swizzled rows, then q[SD], k[SD], o[2][SD]
+    extern __shared__ __align__(16) float tile[];      // [SD][SD] swizzled rows, then o[GN_NW][SD], the gates of every token, the q / k / v rows of every token
     constexpr int PPR = SD / 4;                         // 16-byte pieces per row
     const int h = blockIdx.x, tid = threadIdx.x, kh = h % nk;
-    float* qs = tile + SD * SD; float* ks = qs + SD; float* os = ks + SD;
-    // named barriers: 1 = the row owners among themselves, 2 + (t & 1) = "outputs of row t are in os[t & 1]" (owners + norm warp)
+    float* os = tile + SD * SD; float* bts = os + GN_NW * SD; float* egs = bts + IT_GDN_MAXROWS; float* rows = egs + IT_GDN_MAXROWS;      // rows: [nt][3][SD]
+    // named barriers: 1 = the row owners among themselves; 2 + w = "the outputs of a row are in buffer w" (the owners arrive,
+    // norm warp w waits); 2 + GN_NW + w = "buffer w has been read" (norm warp w arrives, the owners wait before they
+    // write the buffer again, GN_NW rows later).  One norm pass (a 128-long ordered sum by one lane, a division, a square
+    // root and four silu per lane) takes about three times as long as the owners need for a row: four warps take turns.
     auto owners_sync = [] { asm volatile("bar.sync 1, %0;" :: "n"(SD) : "memory"); };
-    auto row_done = [](int t) {
-        if (t & 1) asm volatile("bar.sync 3, %0;" :: "n"(SD + 32) : "memory"); else asm volatile("bar.sync 2, %0;" :: "n"(SD + 32) : "memory");
-    };
+    auto bar_sync = [](int id) { asm volatile("bar.sync %0, %1;" :: "r"(id), "n"(SD + 32) : "memory"); };
+    auto bar_arrive = [](int id) { asm volatile("bar.arrive %0, %1;" :: "r"(id), "n"(SD + 32) : "memory"); };
     if (tid >= SD) {
-        // ---- norm warp: row t's outputs -> o, one row behind the owners
-        const int lane = tid - SD;
-        float zr[SD / 32], wr[SD / 32];
+        // ---- norm warps: row t's outputs -> o, behind the owners
+        const int lane = (tid - SD) & 31, w = (tid - SD) >> 5;
+        float zr[SD / 32], wr[SD / 32], ov[SD / 32];
 #pragma unroll
         for (int i = 0; i < SD / 32; i++) wr[i] = nw[lane + 32 * i];
-        for (int t = 0; t < nt; t++) {
+        const float* ob = os + w * SD;
+        for (int t = w; t < nt; t += GN_NW) {
 #pragma unroll
             for (int i = 0; i < SD / 32; i++) zr[i] = z[t * z_ts + h * SD + lane + 32 * i];      // in flight while the owners compute
-            row_done(t);
-            const float* ob = os + (t & 1) * SD;
+            bar_sync(2 + w);
+#pragma unroll
+            for (int i = 0; i < SD / 32; i++) ov[i] = ob[lane + 32 * i];
             float sc = 0.f;
             if (lane == 0) {
                 float s = 0.f;
-#pragma unroll 8
+#pragma unroll 16
                 for (int i = 0; i < SD; i++) s = it_add(s, it_mul(ob[i], ob[i]));
                 sc = it_div(1.0f, it_sqrt(it_add(it_div(s, (float)SD), eps)));
             }
             sc = __shfl_sync(0xffffffffu, sc, 0);
+            bar_arrive(2 + GN_NW + w);                  // every lane has read what it needs of the buffer
 #pragma unroll
-            for (int i = 0; i < SD / 32; i++) o[t * o_ts + h * SD + lane + 32 * i] = it_mul(it_mul(it_mul(ob[lane + 32 * i], sc), wr[i]), it_silu(zr[i]));
+            for (int i = 0; i < SD / 32; i++) o[t * o_ts + h * SD + lane + 32 * i] = it_mul(it_mul(it_mul(ov[i], sc), wr[i]), it_silu(zr[i]));
         }
         return;
     }
     float* m = state + (size_t)h * SD * SD;
     auto piece = [&](int j, int c) { return reinterpret_cast<float4*>(tile + j * SD + ((c ^ (j & 7)) << 2)); };
-    auto tile_in = [&](const float* src) {   // asynchronous 16-byte copies: the whole 64 KB is in flight at once
-#pragma unroll 8
-        for (int f = tid; f < SD * PPR; f += SD)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(piece(f / PPR, f % PPR))), "l"(reinterpret_cast<const float4*>(src) + f));
-        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-    };
     auto tile_out = [&](float* dst) {
 #pragma unroll 8
         for (int f = tid; f < SD * PPR; f += SD) reinterpret_cast<float4*>(dst)[f] = *piece(f / PPR, f % PPR);
     };
-    // The inputs of row t + 1 are requested while row t is computed, so that a row never waits for L2.
-    float qn, kn, vn, bn, an;
-    auto fetch = [&](int t) {
-        const float* c = co + t * co_ts;
-        qn = c[kh * SD + tid]; kn = c[qk + kh * SD + tid]; vn = c[2 * qk + h * SD + tid];
-        bn = beta[t * ba_ts + h]; an = alpha[t * ba_ts + h];
-    };
-    fetch(0);
-    tile_in(m);
+    // Everything the pass reads is staged once: the head's state tile and the q, k, v rows of all nt tokens, as
+    // asynchronous 16-byte copies that are all in flight together; meanwhile thread t forms token t's gates
+    // (sigmoid(beta), exp(softplus(alpha + dt) * a)), which depend on no state.  The token loop then touches neither
+    // global memory nor an elementary function.
+#pragma unroll 8
+    for (int f = tid; f < SD * PPR; f += SD)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(piece(f / PPR, f % PPR))), "l"(reinterpret_cast<const float4*>(m) + f));
+    for (int f = tid; f < nt * 3 * PPR; f += SD) {
+        const int t = f / (3 * PPR), seg = (f / PPR) % 3, pc = f % PPR;
+        const float* src = co + t * co_ts + (seg == 0 ? kh * SD : seg == 1 ? qk + kh * SD : 2 * qk + h * SD) + 4 * pc;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(rows + (t * 3 + seg) * SD + 4 * pc)), "l"(src));
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int t = tid; t < nt; t += SD) {
+        bts[t] = it_sigmoid(beta[t * ba_ts + h]);
+        egs[t] = it_expf(it_mul(it_softplus(it_add(alpha[t * ba_ts + h], dt[h])), a[h]));
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     owners_sync();
     // Each owner keeps its state row in registers for the whole launch (the loops below are fully unrolled); the shared
-    // tile only stages the coalesced moves from and to global memory.
-    float st[SD];
-#pragma unroll
-    for (int cc = 0; cc < PPR; cc++) { const float4 r = *piece(tid, cc); st[4 * cc] = r.x; st[4 * cc + 1] = r.y; st[4 * cc + 2] = r.z; st[4 * cc + 3] = r.w; }
+    // tile only stages the coalesced moves from and to global memory.  x[] holds the row already multiplied by the decay
+    // of the token that is about to use it.  The two ordered sums of a token, s = sum_i x[i] * k[i] and
+    // acc = sum_i st[i] * q[i], are kept in the CPU's index order; what is interleaved is acc of token t with s of token
+    // t + 1: both read the state after token t and do not depend on each other, so the two dependent chains of additions
+    // run side by side instead of one after the other.
+    float x[SD];
     const float scale = it_div(1.0f, it_sqrt((float)SD));
-    for (int t = 0; t < nt; t++) {
-        owners_sync();                                  // the reads of q and k of row t - 1 (and of a checkpoint tile) are over
-        qs[tid] = qn; ks[tid] = kn;
-        const float v = vn;
-        const float bt = it_sigmoid(bn);
-        const float g = it_mul(it_softplus(it_add(an, dt[h])), a[h]);
-        if (t + 1 < nt) fetch(t + 1);
-        owners_sync();
-        const float eg = it_expf(g);
-        float s = 0.f;
+    float s = 0.f;
+    {
+        const float eg = egs[0]; const float* k0 = rows + SD;
 #pragma unroll
         for (int cc = 0; cc < PPR; cc++) {
-            const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc);
-            st[4 * cc] = it_mul(st[4 * cc], eg); st[4 * cc + 1] = it_mul(st[4 * cc + 1], eg); st[4 * cc + 2] = it_mul(st[4 * cc + 2], eg); st[4 * cc + 3] = it_mul(st[4 * cc + 3], eg);
-            s = it_add(s, it_mul(st[4 * cc], k4.x)); s = it_add(s, it_mul(st[4 * cc + 1], k4.y)); s = it_add(s, it_mul(st[4 * cc + 2], k4.z)); s = it_add(s, it_mul(st[4 * cc + 3], k4.w));
+            const float4 r = *piece(tid, cc); const float4 k4 = *reinterpret_cast<const float4*>(k0 + 4 * cc);
+            x[4 * cc] = it_mul(r.x, eg); x[4 * cc + 1] = it_mul(r.y, eg); x[4 * cc + 2] = it_mul(r.z, eg); x[4 * cc + 3] = it_mul(r.w, eg);
+            s = it_add(s, it_mul(x[4 * cc], k4.x)); s = it_add(s, it_mul(x[4 * cc + 1], k4.y)); s = it_add(s, it_mul(x[4 * cc + 2], k4.z)); s = it_add(s, it_mul(x[4 * cc + 3], k4.w));
         }
-        const float delta = it_mul(it_sub(v, s), bt);
-        float acc = 0.f;
-#pragma unroll
-        for (int cc = 0; cc < PPR; cc++) {
-            const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * cc), q4 = *reinterpret_cast<const float4*>(qs + 4 * cc);
-            st[4 * cc] = it_add(st[4 * cc], it_mul(k4.x, delta)); st[4 * cc + 1] = it_add(st[4 * cc + 1], it_mul(k4.y, delta));
-            st[4 * cc + 2] = it_add(st[4 * cc + 2], it_mul(k4.z, delta)); st[4 * cc + 3] = it_add(st[4 * cc + 3], it_mul(k4.w, delta));
-            acc = it_add(acc, it_mul(st[4 * cc], q4.x)); acc = it_add(acc, it_mul(st[4 * cc + 1], q4.y)); acc = it_add(acc, it_mul(st[4 * cc + 2], q4.z)); acc = it_add(acc, it_mul(st[4 * cc + 3], q4.w));
-        }
-        // os[t & 1] was last read by the norm warp for row t - 2, which it finished before it joined row_done(t - 1)
-        os[(t & 1) * SD + tid] = it_mul(acc, scale);
-        if (t < nck) {                                  // checkpoint: the state after row t, through the tile
-#pragma unroll
-            for (int cc = 0; cc < PPR; cc++) *piece(tid, cc) = make_float4(st[4 * cc], st[4 * cc + 1], st[4 * cc + 2], st[4 * cc + 3]);
-        }
-        row_done(t);
-        if (t < nck) tile_out(ck + t * ck_stride + (size_t)h * SD * SD);
     }
+    if (nck > 0) owners_sync();                         // every owner has its row in registers before a checkpoint reuses the tile
+    for (int t = 0; t < nt; t++) {
+        const float* qt = rows + (t * 3) * SD; const float* kt = qt + SD;
+        const float delta = it_mul(it_sub(qt[2 * SD + tid], s), bts[t]);
+        const bool last = t + 1 == nt, cks = t < nck;
+        const float egn = last ? 1.0f : egs[t + 1];
+        const float* kn = last ? kt : kt + 3 * SD;
+        float acc = 0.f, s2 = 0.f;
+        if (cks && t > 0) owners_sync();                // the copy of the previous checkpoint out of the tile is over
 #pragma unroll
-    for (int cc = 0; cc < PPR; cc++) *piece(tid, cc) = make_float4(st[4 * cc], st[4 * cc + 1], st[4 * cc + 2], st[4 * cc + 3]);
+        for (int cc = 0; cc < PPR; cc++) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kt + 4 * cc), q4 = *reinterpret_cast<const float4*>(qt + 4 * cc), n4 = *reinterpret_cast<const float4*>(kn + 4 * cc);
+            const float s0 = it_add(x[4 * cc], it_mul(k4.x, delta)), s1 = it_add(x[4 * cc + 1], it_mul(k4.y, delta));
+            const float s2v = it_add(x[4 * cc + 2], it_mul(k4.z, delta)), s3 = it_add(x[4 * cc + 3], it_mul(k4.w, delta));
+            acc = it_add(acc, it_mul(s0, q4.x)); acc = it_add(acc, it_mul(s1, q4.y)); acc = it_add(acc, it_mul(s2v, q4.z)); acc = it_add(acc, it_mul(s3, q4.w));
+            if (cks) *piece(tid, cc) = make_float4(s0, s1, s2v, s3);       // checkpoint: the state after row t, through the tile
+            // after the last token the factor is 1 (the product is then the state itself, bit for bit) and s2 is not used
+            x[4 * cc] = it_mul(s0, egn); x[4 * cc + 1] = it_mul(s1, egn); x[4 * cc + 2] = it_mul(s2v, egn); x[4 * cc + 3] = it_mul(s3, egn);
+            s2 = it_add(s2, it_mul(x[4 * cc], n4.x)); s2 = it_add(s2, it_mul(x[4 * cc + 1], n4.y)); s2 = it_add(s2, it_mul(x[4 * cc + 2], n4.z)); s2 = it_add(s2, it_mul(x[4 * cc + 3], n4.w));
+        }
+        const int slot = t % GN_NW;
+        if (t >= GN_NW) bar_sync(2 + GN_NW + slot);     // the norm warp has read row t - GN_NW out of this buffer
+        os[slot * SD + tid] = it_mul(acc, scale);
+        bar_arrive(2 + slot);
+        if (cks) { owners_sync(); tile_out(ck + t * ck_stride + (size_t)h * SD * SD); }
+        s = s2;
+    }
+    if (nck > 0) owners_sync();
+#pragma unroll
+    for (int cc = 0; cc < PPR; cc++) *piece(tid, cc) = make_float4(x[4 * cc], x[4 * cc + 1], x[4 * cc + 2], x[4 * cc + 3]);
     owners_sync();
     tile_out(m);
 }
@@ -659,9 +674,10 @@ int it_sup_gdn_norm(it_ctx* c, const float* co, size_t co_ts, const float* beta,
                     int nv, int nk, int sd, int qk, int nt, float* ck, size_t ck_stride, int nck, const float* nw, float eps, const float* z, size_t z_ts) {
     if (sd != 128) return it_fail(IT_EINVAL, "gdn_norm: the fused kernel is built for a state size of 128");
     it_note_op(c);
-    const size_t smem = ((size_t)sd * sd + 4 * sd) * sizeof(float);
+    if (nt > IT_GDN_MAXROWS || (reinterpret_cast<uintptr_t>(co) & 15) || co_ts % 4 || qk % 4) return it_fail(IT_EINVAL, "gdn_norm: %d rows or an unaligned conv output", nt);
+    const size_t smem = ((size_t)sd * sd + GN_NW * sd + 2 * IT_GDN_MAXROWS + (size_t)nt * 3 * sd) * sizeof(float);
     static bool set[16] = {};       // the attribute is per device
     if (!set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(k_gdn_norm<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set[c->device & 15] = true; }
-    it_pdl(k_gdn_norm<128>, dim3(dim3(nv)), dim3(128 + 32), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
+    it_pdl(k_gdn_norm<128>, dim3(dim3(nv)), dim3(128 + 32 * GN_NW), smem, c->stream, co, co_ts, beta, alpha, ba_ts, dt, a, state, o, o_ts, nk, qk, nt, ck, ck_stride, nck, nw, eps, z, z_ts);
     KCHK("gdn_norm"); return IT_OK;
 }

@@ -15,6 +15,8 @@ __host__ __device__ static inline size_t it_vc_index(size_t pos, int kh, int j, 
     return (((pos >> 5) * (size_t)nkv + kh) * 32 + (pos & 31)) * (size_t)hd + (size_t)j;
 }
 
+#define IT_GDN_MAXROWS 64    // rows of one pass the fused delta-rule kernel stages in shared memory (it_sup_gdn_norm)
+
 // Work done on the way into the Hadamard + q8k kernel.  mode 0: nothing.  mode 1: input = silu(x) * b (b is a device
 // pointer, rows b_stride apart).  mode 2: input = rmsnorm(x) over the whole row of width n with weight w and eps; when
 // xn_out is set the normed f32 row is also stored there (rows xn_stride apart).
@@ -41,6 +43,10 @@ int it_sup_attention(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const 
 
 // Longest context one attention launch can serve at this head dimension (its row of scores lives in shared memory).
 int it_sup_attention_max_positions(int hd);
+// Prompt-pass attention over the trunk's tiled f16 caches (it_attention_prefill.cu): same results as it_sup_attention.
+// Returns 1 when the shape does not fit (nothing launched), a negative code on error.
+int it_sup_attention_prefill(it_ctx* c, const float* q, size_t q_hs, size_t q_ts, const float* gate, const void* kc, const void* vc, int hd, int nh, int nkv, int slot0,
+                             float* out, size_t o_ts, int nt);
 
 // Fused forms for passes of up to 8 rows (same arithmetic and order as the separate kernels; see it_support.cu).
 int it_sup_attn_prep(it_ctx* c, float* qkv, size_t ts, int nh, int nkv, int hd, const float* q_norm, const float* k_norm, float eps, int pos0, const int* pos_ptr,
