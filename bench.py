@@ -500,6 +500,21 @@ def main():
                       "prompts": [mtp_leg(eng, cfg, rng, p, 256) for p in (128, 2048)]}               # config 3
     if world == 1:
         eng.close()
+        if not args.no_extras:
+            # the same workload on the per-op schedule (one launch per op, about 650 launches per token, replayed as a graph):
+            # the library reads the switch when an engine is built
+            os.environ["IT_STEP_KERNEL"] = "0"
+            try:
+                peng = CudaEngine(cfg, seed=7, with_mtp=False, device=local_rank)
+                psteps = min(args.steps, 64)
+                pms, _ = timed_decode(peng, prompt, psteps)
+                plaunches = peng.step_kernels()
+                pe2e, _ = timed_e2e(peng, prompt, psteps)
+                peng.close()
+                out["per_op_schedule"] = {"value": psteps / (pms / 1e3), "unit": "tok/s", "steps": psteps, "launches_per_step": plaunches, "e2e": psteps / pe2e,
+                                          "note": "the same decode as one kernel launch per op instead of the persistent step kernel (IT_STEP_KERNEL=0)"}
+            finally:
+                del os.environ["IT_STEP_KERNEL"]
     if sharded:
         out["sharded"] = sharded
         out["replicas"] = replicas
