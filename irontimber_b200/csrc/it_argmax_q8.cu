@@ -66,6 +66,12 @@ k_argmax(const float* __restrict__ v, unsigned n, unsigned per_block, unsigned l
 // reuses its 16 activations for the four rows.  HBM-bound: rows*cols*(1 + 2/32) bytes of weights (Q8_0 source: one f16
 // scale per 32 weights) or rows*cols*(1 + 4/16) (G16, Q6_K source: one f32 scale per 16 weights).
 constexpr int QROWS = 4;
+// Byte k of w (bytes already offset by 128: w = raw ^ 0x80808080) as a float, exactly: the byte becomes the low mantissa
+// bits of 2^23, and 2^23 + 128 is subtracted.  One permute and one addition on the main pipes instead of a shift and an
+// integer-to-float conversion, which shares the slow special-function pipe (72 % busy in this kernel before the change).
+__device__ __forceinline__ float q8_to_float(uint32_t w_off, int k) {
+    return __fadd_rn(__uint_as_float(__byte_perm(w_off, 0x4B000000u, 0x7650u + (unsigned)k)), -8388736.0f);
+}
 template <int NT, bool G16>
 __global__ void __launch_bounds__(256)
 k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, const float* __restrict__ ws, int rows, int cols,
@@ -80,15 +86,23 @@ k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, const 
     for (int r = 0; r < QROWS; r++)
 #pragma unroll
         for (int t = 0; t < NT; t++) acc[r][t] = 0.f;
-    for (int g = lane; g < groups; g += 32) {
-        uint4 w[QROWS]; float d[QROWS];
+    // the weights and scales of the next group are requested before this group's arithmetic starts: twice the bytes in flight
+    uint4 wn[QROWS]; float dn[QROWS];
+    auto fetch = [&](int g) {
 #pragma unroll
         for (int r = 0; r < QROWS; r++) {
             const int row = min(r0 + r, rows - 1);
-            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[r].x), "=r"(w[r].y), "=r"(w[r].z), "=r"(w[r].w)
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wn[r].x), "=r"(wn[r].y), "=r"(wn[r].z), "=r"(wn[r].w)
                          : "l"(wq + (size_t)row * cols + 16 * g));
-            d[r] = G16 ? ws[(size_t)row * (cols / 16) + g] : __half2float(wd[(size_t)row * (cols / 32) + (g >> 1)]);
+            dn[r] = G16 ? ws[(size_t)row * (cols / 16) + g] : __half2float(wd[(size_t)row * (cols / 32) + (g >> 1)]);
         }
+    };
+    if (lane < groups) fetch(lane);
+    for (int g = lane; g < groups; g += 32) {
+        uint4 w[QROWS]; float d[QROWS];
+#pragma unroll
+        for (int r = 0; r < QROWS; r++) { w[r] = wn[r]; d[r] = dn[r]; }
+        if (g + 32 < groups) fetch(g + 32);
 #pragma unroll
         for (int t = 0; t < NT; t++) {
             if (t < ntok) {
@@ -97,10 +111,10 @@ k_matvec_q8(const int8_t* __restrict__ wq, const __half* __restrict__ wd, const 
                 const float xv[16] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w, x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w };
 #pragma unroll
                 for (int r = 0; r < QROWS; r++) {
-                    const uint32_t ww[4] = { w[r].x, w[r].y, w[r].z, w[r].w };
+                    const uint32_t ww[4] = { w[r].x ^ 0x80808080u, w[r].y ^ 0x80808080u, w[r].z ^ 0x80808080u, w[r].w ^ 0x80808080u };
                     float s = 0.f;
 #pragma unroll
-                    for (int k = 0; k < 16; k++) s = fmaf((float)(int8_t)(ww[k >> 2] >> (8 * (k & 3))), xv[k], s);
+                    for (int k = 0; k < 16; k++) s = fmaf(q8_to_float(ww[k >> 2], k & 3), xv[k], s);
                     acc[r][t] = fmaf(s, d[r], acc[r][t]);
                 }
             }
