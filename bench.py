@@ -204,7 +204,7 @@ def matvec_roofline(torch, local_rank, steps):
             "traffic": NCU_DRAM_BYTES_PER_LAUNCH}
 
 
-def sweep(args, torch, np, rank, world, local_rank, base):
+def sweep(args, torch, np, rank, world, local_rank, base, emit=True, head_only=False, own_group=True):
     """Config 5 of the baseline: K = 5120, N in {17408, 34816, 69632}, M in {1, 4, 64, 512}, and the Q8_0 LM head
     (N = 248320, M = 1).  With more than one rank every matrix is split by output rows and each launch ends with the
     exchange of the result slices through peer memory; the time is the max over ranks of the device time per launch."""
@@ -213,8 +213,9 @@ def sweep(args, torch, np, rank, world, local_rank, base):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        if own_group:
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     be = CudaBackend(local_rank, arena_floats=1 << 26)
     if world > 1:
         be.attach_peers(rank, world)
@@ -248,7 +249,7 @@ def sweep(args, torch, np, rank, world, local_rank, base):
         be.graph_destroy(g)
         return us
 
-    for N in (17408, 34816, 69632):
+    for N in (() if head_only else (17408, 34816, 69632)):
         row0, n = shard_range(N, rank, world)
         nmat = max(2, min(12, int(300e6 // (n * K * 34 / 128)) + 1))        # distinct matrices: more bytes than L2
         mats = [be.mat_synth_rows(100 + i, N, K, row0, n) if world > 1 else be.mat_synth(100 + i, N, K) for i in range(nmat)]
@@ -275,11 +276,12 @@ def sweep(args, torch, np, rank, world, local_rank, base):
     if dist:
         dist.barrier()
     be.close()
-    if rank == 0:
+    if rank == 0 and emit:
         print(json.dumps(dict(base, metric="config5_sweep_us_per_launch", unit="us", higher_is_better=False, scaling="strong", value=out[0]["us"],
                               sweep=out, config={"workload": "config5: ternary product K=5120, N x M grid, and the Q8_0 LM head; rows split evenly over the ranks, result slices exchanged inside the kernels"})))
-    if dist:
+    if dist and own_group:
         dist.destroy_process_group()
+    return out
 
 
 def host_threads():
@@ -352,6 +354,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--roofline-only", action="store_true", help="only the k_matvec_t2 sweep on config 1 (the run to put under a profiler for that kernel)")
     ap.add_argument("--sweep", action="store_true", help="config 5: op-level sweep of the ternary product (N x M grid) and the q8 LM head, row-sharded over the ranks when N > 1")
+    ap.add_argument("--q8-only", action="store_true", help="only the Q8_0 LM head of config 5 (the run to put under a profiler for k_matvec_q8)")
     ap.add_argument("--decode-only", action="store_true", help="prompt + timed decode steps only (no end-to-end, speculative, roofline or CPU legs): the run to put under a profiler")
     ap.add_argument("--no-extras", action="store_true", help="skip the config 3 / 4 / 5 legs (speculative decoding, prompt lengths, op sweep)")
     args = ap.parse_args()
@@ -384,8 +387,8 @@ def main():
     from irontimber_b200 import _lib
     from irontimber_b200.engine import CudaEngine
 
-    if args.sweep:
-        sweep(args, torch, np, rank, world, local_rank, base)
+    if args.sweep or args.q8_only:
+        sweep(args, torch, np, rank, world, local_rank, base, head_only=args.q8_only)
         return
     if args.roofline_only:
         if rank == 0:
@@ -518,6 +521,9 @@ def main():
     if sharded:
         out["sharded"] = sharded
         out["replicas"] = replicas
+        if not args.no_extras:
+            # config 5 on the same ranks: every matrix split by output rows, result slices exchanged inside the kernels
+            out["sweep"] = sweep(args, torch, np, rank, world, local_rank, base, emit=False, own_group=False)
     if rank == 0:
         out["roofline"] = matvec_roofline(torch, local_rank, 200)
         out["roofline"]["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed profile summary (not measured in this run)"
