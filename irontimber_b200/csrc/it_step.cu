@@ -111,8 +111,9 @@ __device__ __forceinline__ void cons_sync() { consumer_barrier<ST_CT>(); }
 __device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) { int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
 
 // Barrier over the grid (consumer threads only; the producer warp never takes part).  Writes made by any CTA before the
-// barrier are visible to every CTA after it: thread 0 fences, announces the CTA with a release add, waits with acquire
-// loads until every CTA of this round has arrived, and fences again before the CTA goes on.  Returns false when the step
+// barrier are visible to every CTA after it: thread 0 announces the CTA with a release add and waits with acquire loads
+// until every CTA of this round has arrived (the adds form one chain on the counter, so the load that sees the last of
+// them is ordered after every CTA's writes).  Returns false when the step
 // has been given up (by this CTA's own timeout or by another CTA's).
 __device__ __forceinline__ bool grid_sync(const StepParams& P, Cta& c, int site) {
     cons_sync();
@@ -126,14 +127,13 @@ __device__ __forceinline__ bool grid_sync(const StepParams& P, Cta& c, int site)
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(P.sync) : "memory");
         const long long t0 = clock64();
         for (unsigned it = 0;; it++) {
-            unsigned v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.sync) : "memory");
+            unsigned v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.sync) : "memory");
             if ((int)(v - c.target) >= 0) break;
             if ((it & 63u) == 63u) {
                 if (*reinterpret_cast<volatile unsigned*>(P.sync + 2)) { *c.abort_flag = 1; break; }
                 if (clock64() - t0 > WAIT_CLOCKS) { atomicExch(P.error_flag, 100 + site); atomicExch(P.sync + 2, 1u); *c.abort_flag = 1; break; }
             }
         }
-        asm volatile("fence.acq_rel.gpu;" ::: "memory");             // acquire: what the other CTAs wrote before they arrived
         if (rec) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); rec[1] = t; }
         c.nsync++;
     }
