@@ -99,6 +99,7 @@ struct Cta {
     const StepLayer* lay;              // the two shared-memory copies of layer descriptions (layer il at lay[il & 1])
     unsigned target;                   // arrivals the next grid barrier waits for
     int nsync;                         // grid barriers passed so far (index into the trace)
+    float inv_sqrt_sd, inv_sqrt_hd;    // 1 / sqrt(state size), 1 / sqrt(head dimension): formed once per launch
     int evt_on, evt_base;              // diagnostics: this thread records fine-grained events into slots evt_base ..
 };
 constexpr int ST_TRACE_MAX = 1024;     // barriers recorded per traced CTA
@@ -375,8 +376,9 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
     float* tile = reinterpret_cast<float*>(c.scratch + P.gdn_off);   // [SD][SD], 16-byte pieces of row j stored at piece index ^ (j & 7); requested by gdn_prefetch
     float* vals = tile + SD * SD;                                    // [3][SD]: q, k, v runs after conv + SiLU
     float* os = vals + 3 * SD;                                       // [SD] delta-rule outputs
-    float* scs = os + SD;                                            // [2] l2norm scales, [2] beta, alpha
+    float* scs = os + SD;                                            // [2] l2norm scales, [2] beta, alpha, [2] sigmoid(beta), exp(decay)
     double* wsum = reinterpret_cast<double*>(scs + 8);               // [16] warp sums of the two dense rows
+    float* gzs = reinterpret_cast<float*>(wsum + 16);                // [SD] silu of the head's gate row
     const float* A = P.arena;
     auto piece = [&](int j, int cc) { return reinterpret_cast<float4*>(tile + j * SD + ((cc ^ (j & 7)) << 2)); };
     float* m = L.ssm_st + (size_t)h * SD * SD;
@@ -393,10 +395,16 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
 #pragma unroll
         for (int k = 0; k < 16; k++) { const int i = t8 + 256 * k; wv[k] = i < P.e ? wr[i] : 0.f; xv[k] = i < P.e ? __ldcg(xr + i) : 0.f; }
     }
+    // the gate values the norm needs at the very end: warp 0 keeps the norm weights, warp 8 (done early with its share of
+    // the dense rows) forms silu(z) while the other warps are still busy
     float zr[SD / 32], nwr[SD / 32];
     if (warp == 0) {
 #pragma unroll
-        for (int i = 0; i < SD / 32; i++) { zr[i] = __ldcg(A + P.big1 + cd + h * SD + lane + 32 * i); nwr[i] = L.ssm_norm[lane + 32 * i]; }
+        for (int i = 0; i < SD / 32; i++) nwr[i] = L.ssm_norm[lane + 32 * i];
+    }
+    if (warp == 8) {
+#pragma unroll
+        for (int i = 0; i < SD / 32; i++) zr[i] = __ldcg(A + P.big1 + cd + h * SD + lane + 32 * i);
     }
     if (tid < 3 * SD) {
         const int r = tid / SD, cc = tid % SD;
@@ -443,7 +451,13 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
         const double* ws = wsum + (warp - 2) * 8;
         double tt = ws[0];
         for (int k = 1; k < 8; k++) tt += ws[k];
-        scs[warp] = (float)tt;                                       // scs[2] = beta, scs[3] = alpha
+        const float tf = (float)tt;                                  // warp 2: beta, warp 3: alpha; the gates follow at once, off the owners' path
+        scs[warp] = tf;
+        if (warp == 2) scs[4] = it_sigmoid(tf);
+        else scs[5] = it_expf(it_mul(it_softplus(it_add(tf, L.dt[h])), L.a[h]));
+    } else if (warp == 8) {
+#pragma unroll
+        for (int i = 0; i < SD / 32; i++) gzs[lane + 32 * i] = it_silu(zr[i]);
     }
     ST_EV(P, c, c.evt_base + 7);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -456,10 +470,9 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
         asm volatile("bar.sync 3, %0;" :: "n"(SD) : "memory");
         const float* qs = vals; const float* ks = vals + SD;
         const float v = vals[2 * SD + tid];
-        const float bt = it_sigmoid(scs[2]);
-        const float gg = it_mul(it_softplus(it_add(scs[3], L.dt[h])), L.a[h]);
-        const float eg = it_expf(gg);
-        const float scale = it_div(1.0f, it_sqrt((float)SD));
+        const float bt = scs[4];
+        const float eg = scs[5];
+        const float scale = c.inv_sqrt_sd;
         // Two passes over the thread's state row, eight 16-byte pieces at a time (requested together, then used in order).
         // The first pass only reads: s = sum_i (row[i] * eg) * k[i] in index order.  The second forms row[i] * eg again (the
         // same rounded product), adds k[i] * delta, stores the new state and accumulates the output in index order.
@@ -513,7 +526,7 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
 #pragma unroll
         for (int i = 0; i < SD / 32; i++) {
             const int j = lane + 32 * i;
-            __stcg(o + j, it_mul(it_mul(it_mul(os[j], sc), nwr[i]), it_silu(zr[i])));
+            __stcg(o + j, it_mul(it_mul(it_mul(os[j], sc), nwr[i]), gzs[j]));
         }
     }
     ST_EV(P, c, c.evt_base + 11);
@@ -639,7 +652,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         }
     }
     at_sync();                                                       // q, and the new position's k and v, are in shared memory
-    const float scale = it_div(1.0f, it_sqrt((float)hd));
+    const float scale = c.inv_sqrt_hd;
     const int nvec = hd / 8;
     float mx = -INFINITY;
     if (warp < S) {
@@ -752,6 +765,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
     if (c.warp >= ST_NCONS) { sum_warps(P, c); return; }
 
     c.target = *reinterpret_cast<volatile unsigned*>(P.sync + 1);
+    c.inv_sqrt_sd = it_div(1.0f, it_sqrt((float)ST_SD)); c.inv_sqrt_hd = it_div(1.0f, it_sqrt((float)P.hd));
     if (P.trace && blockIdx.x == 0 && c.tid == 32) P.trace[4 * ST_TRACE_MAX] = 0;
     const int e = P.e, nb_e = e / 128;
     float* A = P.arena;
@@ -868,7 +882,7 @@ static size_t step_scratch_bytes(const it_model_config& c) {
     const int widest = std::max(std::max(c.n_embd, c.n_ff), std::max(c.ssm_inner, c.n_head * c.head_dim));
     size_t s = (size_t)mv_layout(widest / 128).total;
     s = std::max(s, sizeof(it_had_smem));
-    s = std::max(s, step_gdn_off(c) + (size_t)(ST_SD * ST_SD + 4 * ST_SD + 8) * 4 + 16 * 8 + 64);
+    s = std::max(s, step_gdn_off(c) + (size_t)(ST_SD * ST_SD + 5 * ST_SD + 8) * 4 + 16 * 8 + 64);
     s = std::max(s, ((size_t)c.ctx_len + 4 + 3 * c.head_dim + 48) * 4 + 128 + 3 * (size_t)c.head_dim * 64);
     return (s + 127) / 128 * 128;
 }
