@@ -78,6 +78,8 @@ struct StepParams {
     int* error_flag;
     unsigned long long* trace;         // optional: clock readings of CTA 0 and of the last CTA at every grid barrier (arrive, leave)
     int slots, scratch;                // ring slots; bytes of the phase scratch that follows the ring
+    int attn_g;                        // CTAs that share an attention head
+    float* att_sc; int att_stride; unsigned* att_cnt;   // per head: the scores its CTAs exchange [nh][att_stride], their arrival counter [nh]
     int had_base, attn_base;           // first CTA of the Hadamard blocks / of the attention heads (value heads start at CTA 0): roles on
                                        // different CTAs keep each CTA's instruction footprint small
     int gdn_off;                       // where the delta-net block keeps its state tile inside the scratch (clear of the input projection's buffers)
@@ -99,6 +101,7 @@ struct Cta {
     const StepLayer* lay;              // the two shared-memory copies of layer descriptions (layer il at lay[il & 1])
     unsigned target;                   // arrivals the next grid barrier waits for
     int nsync;                         // grid barriers passed so far (index into the trace)
+    unsigned att_seq;                  // attention blocks this CTA has run in this launch
     float inv_sqrt_sd, inv_sqrt_hd;    // 1 / sqrt(state size), 1 / sqrt(head dimension): formed once per launch
     int evt_on, evt_base;              // diagnostics: this thread records fine-grained events into slots evt_base ..
 };
@@ -544,64 +547,80 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
 // tiles, a position per lane, from shared memory; the V tiles follow through the same ring and four warps (two output
 // elements per thread) walk them in order.  Full / free mbarriers pace both; they are set up afresh by every attention
 // block.  The tiles were sent on their way into L2 while the input projection ran (attn_prefetch).
-__device__ __forceinline__ void attn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c, int h) {
-    if (c.warp != 0) return;
+__device__ __forceinline__ void attn_prefetch(const StepParams& P, const StepLayer& L, const Cta& c, int hg) {
+    if (c.warp != 0 || hg < 0 || hg >= P.nh * P.attn_g) return;
+    const int G = P.attn_g, h = hg / G, g = hg % G;
     const int kh = h / (P.nh / P.nkv), ntiles = (*P.pos + 31) / 32; const unsigned bytes = (unsigned)(P.hd * 64);
-    for (int i = c.lane; i < ntiles; i += 32) {
+    for (int i = g + G * c.lane; i < ntiles; i += G * 32)               // the K tiles this CTA will score
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(L.kc + it_kc_index((size_t)i * 32, kh, 0, P.nkv, P.hd)), "r"(bytes) : "memory");
+    for (int i = g + G * c.lane; i < ntiles; i += G * 32)               // a quarter of the V tiles each: every CTA of the head reads a slice of all of them
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(L.vc + it_vc_index((size_t)i * 32, kh, 0, P.nkv, P.hd)), "r"(bytes) : "memory");
-    }
 }
-constexpr int ST_AT_MAXS = 8, ST_AT_VWARPS = 4, ST_AT_LOADER = ST_NCONS - 1, ST_AT_T = (ST_NCONS - 1) * 32;
+constexpr int ST_AT_MAXS = 8, ST_AT_LOADER = ST_NCONS - 1, ST_AT_T = (ST_NCONS - 1) * 32;
 // the block's own barrier: every consumer warp but the loader, which runs ahead and only joins the grid barrier
 __device__ __forceinline__ void at_sync() { asm volatile("bar.sync 4, %0;" :: "n"(ST_AT_T) : "memory"); }
-__device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer& L, Cta& c, int h) {
+// G = P.attn_g CTAs share a head (hg = G h + g).  Each forms q and the new position's k and v for itself, scores the K
+// tiles i with i % G == g, publishes those scores, meets the head's other CTAs at a counter of their own, reads their
+// scores, runs the softmax for itself (one thread adds the exponentials in position order) and accumulates the
+// head_dim / G output elements [g head_dim / G, ...) over all positions from row slices of the V tiles.  A single SM can
+// keep only so many bytes in flight, so a head's cache traffic is spread over G SMs.
+__device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer& L, Cta& c, int hg) {
     const int tid = c.tid, warp = c.warp, lane = c.lane, hd = P.hd, nkv = P.nkv, kvd = nkv * hd;
+    const int G = P.attn_g, h = hg / G, g = hg % G, epc = hd / G;   // elements of the output this CTA owns
+    const int vs = it_vc_slice(hd);                                  // elements per V slice: epc is a multiple of it
     const int rep = P.nh / nkv, kh = h / rep;
-    const bool writer = h % rep == 0;
+    const bool writer = h % rep == 0 && g == 0;
     const int pos = *P.pos, n = pos + 1, nold = pos;
     const int ntiles = (nold + 31) / 32;                             // K tiles = V tiles of 32 positions
+    const int my_tiles = ntiles > g ? (ntiles - g + G - 1) / G : 0;  // tiles g, g + G, ... are scored here
     const int tile_bytes = hd * 64;                                  // 32 positions x hd halves
+    const int vslot_bytes = epc * 64;                                // 32 positions x epc halves: this CTA's slice of a V tile
     float* sc = reinterpret_cast<float*>(c.scratch);                 // [n] scores
     float* qs = sc + ((n + 3) & ~3);                                 // [hd] q head after norm + rope
     float* kl = qs + hd;                                             // [hd] k row of the new position as the cache holds it
     float* vl = kl + hd;                                             // [hd] v row of the new position as the cache holds it
     float* red = vl + hd;                                            // [32] + the sum
     unsigned char* ring = reinterpret_cast<unsigned char*>(red + 48) + ((128u - (smem_u32(red + 48) & 127u)) & 127u);
-    // slots of the ring = warps that score: as many tiles as the scratch holds behind the scores, up to eight; tile i goes
-    // to slot i % S and is scored by warp i % S, so every slot is filled and emptied by the same two warps in order
-    const int S = max(1, min(ST_AT_MAXS, (int)((c.scratch + P.scratch) - ring) / tile_bytes));
+    const int room = (int)((c.scratch + P.scratch) - ring);
+    // K: tile j of this CTA goes to slot j % S and is scored by warp j % S, so every slot is filled and emptied by the same two
+    // warps in order.  V: slice j goes to slot j % SV; the output warps walk the slices in order.
+    const int S = max(1, min(ST_AT_MAXS, room / tile_bytes)), SV = max(1, min(ST_AT_MAXS, room / vslot_bytes));
+    const int vwarps = (epc + 31) / 32;                              // output warps: one element per thread
     const unsigned kf = c.at, ke = c.at + 8 * ST_AT_MAXS, vf = c.at + 16 * ST_AT_MAXS, ve = c.at + 24 * ST_AT_MAXS;
+    c.att_seq++;
     if (tid == 0) {
         for (int k = 0; k < 4 * ST_AT_MAXS; k++) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" :: "r"(c.at + 8 * k) : "memory");
-        for (int k = 0; k < ST_AT_MAXS; k++) { mbar_init(kf + 8 * k, 1); mbar_init(ke + 8 * k, 1); mbar_init(vf + 8 * k, 1); mbar_init(ve + 8 * k, ST_AT_VWARPS); }
+        for (int k = 0; k < ST_AT_MAXS; k++) { mbar_init(kf + 8 * k, 1); mbar_init(ke + 8 * k, 1); mbar_init(vf + 8 * k, 1); mbar_init(ve + 8 * k, vwarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    ST_EV(P, c, c.evt_base + 4);
     cons_sync();                                                     // all twelve warps, the loader included
+    ST_EV(P, c, c.evt_base + 5);
     const float* row = P.arena + P.big1;
     const float* qh = row + (size_t)h * 2 * hd; const float* gate = qh + hd;
     const __half* kc = L.kc; const __half* vc = L.vc;
 
     if (warp == ST_AT_LOADER) {
-        // ---- loader: K tiles, then V tiles, as far ahead as the ring allows
-        for (int i = 0; i < ntiles; i++) {
-            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+        // ---- loader: this CTA's K tiles, then its slice of every V tile, as far ahead as the rings allow
+        for (int j = 0; j < my_tiles; j++) {
+            const unsigned sl = (unsigned)j % (unsigned)S, u = (unsigned)j / (unsigned)S;
             if (!mbar_wait(ke + 8 * sl, (u & 1u) ^ 1u, c.abort_flag, P.error_flag, 8)) break;
             if (lane == 0) {
                 mbar_expect_tx(kf + 8 * sl, (unsigned)tile_bytes);
-                bulk_load(smem_u32(ring + sl * tile_bytes), kc + it_kc_index((size_t)i * 32, kh, 0, nkv, hd), (unsigned)tile_bytes, kf + 8 * sl);
+                bulk_load(smem_u32(ring + sl * tile_bytes), kc + it_kc_index((size_t)(g + G * j) * 32, kh, 0, nkv, hd), (unsigned)tile_bytes, kf + 8 * sl);
             }
         }
-        // the V tiles go through the same slots: not before the last K tile of every slot has been scored
-        for (int i = ntiles > S ? ntiles - S : 0; i < ntiles; i++) {
-            if (!mbar_wait(ke + 8 * (i % S), (unsigned)(i / S) & 1u, c.abort_flag, P.error_flag, 8)) break;
+        // the V slices go through the same bytes: not before the last K tile of every slot has been scored
+        for (int j = my_tiles > S ? my_tiles - S : 0; j < my_tiles; j++) {
+            if (!mbar_wait(ke + 8 * (j % S), (unsigned)(j / S) & 1u, c.abort_flag, P.error_flag, 8)) break;
         }
         for (int i = 0; i < ntiles; i++) {
-            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+            const unsigned sl = (unsigned)i % (unsigned)SV, u = (unsigned)i / (unsigned)SV;
             if (!mbar_wait(ve + 8 * sl, (u & 1u) ^ 1u, c.abort_flag, P.error_flag, 9)) break;
             if (lane == 0) {
-                mbar_expect_tx(vf + 8 * sl, (unsigned)tile_bytes);
-                bulk_load(smem_u32(ring + sl * tile_bytes), vc + it_vc_index((size_t)i * 32, kh, 0, nkv, hd), (unsigned)tile_bytes, vf + 8 * sl);
+                // the slices of the tile that hold elements g epc .. (g + 1) epc - 1 are consecutive: one copy
+                mbar_expect_tx(vf + 8 * sl, (unsigned)vslot_bytes);
+                bulk_load(smem_u32(ring + sl * vslot_bytes), vc + it_vc_index((size_t)i * 32, kh, g * epc, nkv, hd), (unsigned)vslot_bytes, vf + 8 * sl);
             }
         }
         return;                                                      // the loader meets the others at the grid barrier
@@ -652,15 +671,16 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         }
     }
     at_sync();                                                       // q, and the new position's k and v, are in shared memory
+    ST_EV(P, c, c.evt_base + 6);
     const float scale = c.inv_sqrt_hd;
     const int nvec = hd / 8;
-    float mx = -INFINITY;
+    float* shared_sc = P.att_sc + (size_t)h * P.att_stride;          // the head's scores, where its CTAs leave theirs for one another
     if (warp < S) {
-        // ---- scores: tile i by warp i % S, position 32 i + lane; piece v of the tile's 32 positions is contiguous
-        for (int i = warp; i < ntiles; i += S) {
-            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+        // ---- scores: this CTA's tile j by warp j % S, position 32 (g + G j) + lane; piece v of the tile's 32 positions is contiguous
+        for (int j = warp; j < my_tiles; j += S) {
+            const unsigned sl = (unsigned)j % (unsigned)S, u = (unsigned)j / (unsigned)S;
             if (!mbar_wait(kf + 8 * sl, u & 1u, c.abort_flag, P.error_flag, 10)) break;
-            const int p = i * 32 + lane;
+            const int p = (g + G * j) * 32 + lane;
             if (p < nold) {
                 const uint4* kp = reinterpret_cast<const uint4*>(ring + sl * tile_bytes) + lane;
                 float s = 0.f;
@@ -674,17 +694,49 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
                     f = __half22float2(hh[2]); s = it_add(s, it_mul(qb.x, f.x)); s = it_add(s, it_mul(qb.y, f.y));
                     f = __half22float2(hh[3]); s = it_add(s, it_mul(qb.z, f.x)); s = it_add(s, it_mul(qb.w, f.y));
                 }
-                s = it_mul(s, scale); sc[p] = s; mx = fmaxf(mx, s);
+                s = it_mul(s, scale); sc[p] = s;
+                if (G > 1) __stcg(shared_sc + p, s);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(ke + 8 * sl);
         }
     } else if (warp == ST_AT_MAXS && lane == 0) {
-        float s = 0.f;                                               // the new position, from its row in shared memory
+        float s = 0.f;                                               // the new position, from its row in shared memory (every CTA of the head for itself)
 #pragma unroll 16
         for (int j = 0; j < hd; j++) s = it_add(s, it_mul(qs[j], kl[j]));
-        s = it_mul(s, scale); sc[nold] = s; mx = s;
+        sc[nold] = it_mul(s, scale);
     }
+    ST_EV(P, c, c.evt_base + 7);
+    if (G > 1) {
+        // ---- the head's CTAs meet: arrival counter of the head (zeroed at the start of the launch), then everyone reads the others' scores
+        at_sync();
+        if (tid == 0) {
+            unsigned* cnt = P.att_cnt + h;
+            const unsigned target = (unsigned)G * c.att_seq;
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(cnt) : "memory");
+            const long long t0 = clock64();
+            for (unsigned it = 0;; it++) {
+                unsigned v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+                if ((int)(v - target) >= 0) break;
+                if ((it & 63u) == 63u) {
+                    if (*reinterpret_cast<volatile unsigned*>(P.sync + 2)) { *c.abort_flag = 1; break; }
+                    if (clock64() - t0 > WAIT_CLOCKS) { atomicExch(P.error_flag, 112); atomicExch(P.sync + 2, 1u); *c.abort_flag = 1; break; }
+                }
+            }
+        }
+        at_sync();
+        if (!*c.abort_flag) {
+            for (int i = 0; i < ntiles; i++) {
+                if (i % G == g) continue;
+                const int p = i * 32 + (tid & 31);
+                if ((tid >> 5) == (i % (ST_NCONS - 1)) && p < nold) sc[p] = __ldcg(shared_sc + p);
+            }
+        }
+        at_sync();
+    } else at_sync();
+    ST_EV(P, c, c.evt_base + 8);
+    float mx = -INFINITY;
+    for (int p = tid; p < n; p += ST_AT_T) mx = fmaxf(mx, sc[p]);
 #pragma unroll
     for (int mm = 16; mm >= 1; mm >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, mm));
     if (lane == 0) red[warp] = mx;
@@ -704,35 +756,44 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
     const float sum = red[32];
     for (int p = tid; p < n; p += ST_AT_T) sc[p] = it_div(sc[p], sum);
     at_sync();
-    if (warp < ST_AT_VWARPS) {
-        // ---- output: element j adds w[p] * v[p][j] in ascending p; thread tid owns elements 2 tid, 2 tid + 1 (hd <= 256)
-        const bool live = 2 * tid < hd;
-        float acc0 = 0.f, acc1 = 0.f;
+    ST_EV(P, c, c.evt_base + 9);
+    if (warp < vwarps) {
+        // ---- output: element j adds w[p] * v[p][j] in ascending p; thread tid owns element g epc + tid of the head.  A whole
+        // tile's 32 values are read before the first addition, so that the chain of additions never waits for shared memory.
+        const bool live = tid < epc;
+        float acc = 0.f;
+        const int eoff = (tid / vs) * 32 * vs + tid % vs;             // [slice][32][vs]
         for (int i = 0; i < ntiles; i++) {
-            const unsigned sl = (unsigned)i % (unsigned)S, u = (unsigned)i / (unsigned)S;
+            const unsigned sl = (unsigned)i % (unsigned)SV, u = (unsigned)i / (unsigned)SV;
             if (!mbar_wait(vf + 8 * sl, u & 1u, c.abort_flag, P.error_flag, 11)) break;
             const int rows = min(32, nold - i * 32);
             if (live) {
-                const __half* src = reinterpret_cast<const __half*>(ring + sl * tile_bytes) + 2 * tid;
+                const __half* src = reinterpret_cast<const __half*>(ring + sl * vslot_bytes) + eoff;
                 const float* wp = sc + i * 32;
-#pragma unroll 8
-                for (int r = 0; r < rows; r++) {
-                    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(src + r * hd));
-                    const float w = wp[r];
-                    acc0 = it_add(acc0, it_mul(w, v.x)); acc1 = it_add(acc1, it_mul(w, v.y));
+                if (rows == 32) {
+                    float vv[32];
+#pragma unroll
+                    for (int r = 0; r < 32; r++) vv[r] = __half2float(src[r * vs]);
+#pragma unroll
+                    for (int r4 = 0; r4 < 8; r4++) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(wp + 4 * r4);
+                        acc = it_add(acc, it_mul(w4.x, vv[4 * r4])); acc = it_add(acc, it_mul(w4.y, vv[4 * r4 + 1]));
+                        acc = it_add(acc, it_mul(w4.z, vv[4 * r4 + 2])); acc = it_add(acc, it_mul(w4.w, vv[4 * r4 + 3]));
+                    }
+                } else {
+                    for (int r = 0; r < rows; r++) acc = it_add(acc, it_mul(wp[r], __half2float(src[r * vs])));
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(ve + 8 * sl);
         }
         if (live) {
-            const float w = sc[nold];
-            acc0 = it_add(acc0, it_mul(w, vl[2 * tid])); acc1 = it_add(acc1, it_mul(w, vl[2 * tid + 1]));
-            float* op = P.arena + P.o + (size_t)h * hd + 2 * tid;
-            __stcg(op, it_mul(acc0, it_sigmoid(__ldcg(gate + 2 * tid))));
-            __stcg(op + 1, it_mul(acc1, it_sigmoid(__ldcg(gate + 2 * tid + 1))));
+            const int e0 = g * epc + tid;
+            acc = it_add(acc, it_mul(sc[nold], vl[e0]));
+            __stcg(P.arena + P.o + (size_t)h * hd + e0, it_mul(acc, it_sigmoid(__ldcg(gate + e0))));
         }
     }
+    ST_EV(P, c, c.evt_base + 10);
 }
 
 // ---------------------------------------------------------------- the step
@@ -744,7 +805,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
     c.bars = smem_u32(tail);                                         // full[s] at bars + 8 s, empty[s] at bars + 8 (slots + s)
     c.abort_flag = reinterpret_cast<volatile int*>(tail + ST_BARS - 16);
     c.tid = threadIdx.x; c.warp = c.tid >> 5; c.lane = c.tid & 31;
-    c.q = 0u; c.nseq = 0u; c.mph = 0u; c.nsync = 0; c.evt_on = 0;
+    c.q = 0u; c.nseq = 0u; c.mph = 0u; c.nsync = 0; c.evt_on = 0; c.att_seq = 0u;
     c.tf = c.bars + 8 * (2 * P.slots); c.te = c.tf + 8 * ST_TB; c.pd = c.te + 8 * ST_TB; c.ps = c.pd + 8; c.at = c.bars + 704;
     c.lay = reinterpret_cast<const StepLayer*>(tail + 384);         // two layer descriptions, then the sum warps' greedy picks
     if (c.tid == 0) {
@@ -765,6 +826,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
     if (c.warp >= ST_NCONS) { sum_warps(P, c); return; }
 
     c.target = *reinterpret_cast<volatile unsigned*>(P.sync + 1);
+    if (c.tid == 0 && (int)blockIdx.x < P.nh) __stcg(P.att_cnt + blockIdx.x, 0u);       // the heads' arrival counters start every launch at zero (grid barriers precede their first use)
     c.inv_sqrt_sd = it_div(1.0f, it_sqrt((float)ST_SD)); c.inv_sqrt_hd = it_div(1.0f, it_sqrt((float)P.hd));
     if (P.trace && blockIdx.x == 0 && c.tid == 32) P.trace[4 * ST_TRACE_MAX] = 0;
     const int e = P.e, nb_e = e / 128;
@@ -834,7 +896,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
             else if (sub == 4) { nb = (L.recurrent ? P.inner : P.nh * P.hd) / 128; rows = e; }
             else if (sub == 6) { nb = nb_e; rows = 2 * P.ff; }
             else { nb = P.ff / 128; rows = e; }
-            const bool block_cta = L.recurrent ? (int)blockIdx.x < P.nv : ((int)blockIdx.x >= P.attn_base && (int)blockIdx.x < P.attn_base + P.nh);
+            const bool block_cta = L.recurrent ? (int)blockIdx.x < P.nv : ((int)blockIdx.x >= P.attn_base && (int)blockIdx.x < P.attn_base + P.nh * P.attn_g);
             matvec_phase(P, c, nb, rows, (!tail && sub == 1 && block_cta) ? &L : nullptr);
             if (tail && c.warp == 0 && c.lane == 0) {
                 // greedy pick (first index of the maximum): each sum warp has left the best of its rows behind the layer descriptions
@@ -846,7 +908,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_step(const __grid_cons
         } else if (kind == 2) {
             const int ah = (int)blockIdx.x - P.attn_base;
             if (L.recurrent) { if ((int)blockIdx.x < P.nv) gdn_phase(P, L, c, keep, (int)blockIdx.x); }
-            else if (ah >= 0 && ah < P.nh) attn_phase(P, L, c, ah);
+            else if (ah >= 0 && ah < P.nh * P.attn_g) attn_phase(P, L, c, ah);
         } else {
             if (blockIdx.x == 0 && c.warp == 0) {
                 Pick q{ -INFINITY, 0xffffffffu };
@@ -873,7 +935,8 @@ struct it_step_state {
     StepLayer* layers_dev;
     unsigned long long* trace;
     unsigned long long* partials;
-    int grid, slots, scratch, gdn_off, had_base, attn_base;
+    int grid, slots, scratch, gdn_off, had_base, attn_base, attn_g, att_stride;
+    float* att_sc; unsigned* att_cnt;
     bool cooperative;
 };
 
@@ -911,9 +974,14 @@ int it_step_prepare(it_engine* e) {
     {   // Hadamard blocks on the last CTAs, attention heads behind the value heads when they all fit side by side
         const int widest = std::max(std::max(c.n_embd, c.n_ff), std::max(c.ssm_inner, c.n_head * c.head_dim)) / 1024;
         st->had_base = st->grid - widest;
-        st->attn_base = (c.ssm_vheads + c.n_head <= st->had_base) ? c.ssm_vheads : 0;
+        // several CTAs per attention head when the grid has them: each takes a share of the K tiles and of the output elements
+        st->attn_g = 1;
+        for (int g = 4; g > 1; g /= 2) if (c.head_dim % g == 0 && (c.head_dim / g) % it_vc_slice(c.head_dim) == 0 && g * c.n_head <= st->grid) { st->attn_g = g; break; }
+        { const char* v = getenv("IT_STEP_ATTN_G"); if (v && (atoi(v) == 1 || atoi(v) == 2) && atoi(v) < st->attn_g) st->attn_g = atoi(v); }
+        st->attn_base = (c.ssm_vheads + st->attn_g * c.n_head <= st->grid) ? c.ssm_vheads : 0;
     }
-    st->layers_dev = nullptr; st->partials = nullptr; st->trace = nullptr;
+    st->layers_dev = nullptr; st->partials = nullptr; st->trace = nullptr; st->att_sc = nullptr; st->att_cnt = nullptr;
+    st->att_stride = (c.ctx_len + 32 + 3) / 4 * 4;
     { const char* v = getenv("IT_STEP_COOP"); st->cooperative = !v || atoi(v) != 0; }
     std::vector<StepLayer> hl(c.n_layer);
     for (int il = 0; il < c.n_layer; il++) {
@@ -926,6 +994,8 @@ int it_step_prepare(it_engine* e) {
     }
     int r = it_engine_dev_alloc(e, (void**)&st->layers_dev, hl.size() * sizeof(StepLayer), false);
     if (r == IT_OK) r = it_engine_dev_alloc(e, (void**)&st->partials, (size_t)st->grid * sizeof(unsigned long long), true);
+    if (r == IT_OK) r = it_engine_dev_alloc(e, (void**)&st->att_sc, (size_t)c.n_head * st->att_stride * sizeof(float), true);
+    if (r == IT_OK) r = it_engine_dev_alloc(e, (void**)&st->att_cnt, (size_t)c.n_head * sizeof(unsigned), true);
     { const char* v = getenv("IT_STEP_TRACE"); if (r == IT_OK && v && atoi(v) != 0) r = it_engine_dev_alloc(e, (void**)&st->trace, (2 * ST_TRACE_MAX * 2 + ST_EVT_MAX) * sizeof(unsigned long long), true); }
     if (r) { delete st; return r; }
     IT_CUDA(cudaMemcpyAsync(st->layers_dev, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice, cx->stream));
@@ -949,7 +1019,7 @@ int it_step_launch(it_engine* e, int flags) {
     P.tok_embd = e->tok_embd; P.output_norm = e->output_norm; P.output = e->output->tiles;
     P.toks = e->toks_dev; P.pos = e->pos_dev;
     P.sync = cx->grid_sync; P.partials = st->partials; P.error_flag = cx->error_flag_dev;
-    P.slots = st->slots; P.scratch = st->scratch; P.flags = flags; P.trace = st->trace; P.gdn_off = st->gdn_off; P.had_base = st->had_base; P.attn_base = st->attn_base;
+    P.slots = st->slots; P.scratch = st->scratch; P.flags = flags; P.trace = st->trace; P.gdn_off = st->gdn_off; P.had_base = st->had_base; P.attn_base = st->attn_base; P.attn_g = st->attn_g; P.att_sc = st->att_sc; P.att_stride = st->att_stride; P.att_cnt = st->att_cnt;
     it_note_op(cx);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)st->grid); cfg.blockDim = dim3(ST_THREADS); cfg.dynamicSmemBytes = (size_t)st->slots * ST_CHUNK + st->scratch + ST_BARS; cfg.stream = cx->stream;

@@ -9,10 +9,14 @@ __host__ __device__ static inline size_t it_kc_index(size_t pos, int kh, int j, 
     return (((pos >> 5) * (size_t)nkv + kh) * (size_t)(hd >> 3) + (size_t)(j >> 3)) * 256 + (pos & 31) * 8 + (j & 7);
 }
 
-// f16 V cache of the trunk: tiles of 32 positions per KV head with the rows of a tile contiguous, [position tile][kv head]
-// [32 positions][head_dim], so that the V rows of 32 positions of one head are one contiguous block (one bulk copy).
+// f16 V cache of the trunk: tiles of 32 positions per KV head, [position tile][kv head][slice][32 positions][64 elements]
+// (slices of 64 elements; one slice of head_dim elements when head_dim is not a multiple of 64).  The V rows of 32
+// positions of one head are one contiguous block (one bulk copy), and so is any run of slices of it: a CTA that owns a
+// quarter of a head's output elements fetches its quarter of a tile with one copy.
+__host__ __device__ static inline int it_vc_slice(int hd) { return (hd & 63) ? hd : 64; }
 __host__ __device__ static inline size_t it_vc_index(size_t pos, int kh, int j, int nkv, int hd) {
-    return (((pos >> 5) * (size_t)nkv + kh) * 32 + (pos & 31)) * (size_t)hd + (size_t)j;
+    const int vs = it_vc_slice(hd), ns = hd / vs;
+    return ((((pos >> 5) * (size_t)nkv + kh) * ns + (size_t)(j / vs)) * 32 + (pos & 31)) * (size_t)vs + (size_t)(j % vs);
 }
 
 #define IT_GDN_MAXROWS 64    // rows of one pass the fused delta-rule kernel stages in shared memory (it_sup_gdn_norm)
