@@ -34,15 +34,25 @@ __device__ __forceinline__ bool mbar_poll(unsigned bar, unsigned parity) {
 #ifndef IT_MBAR_SLEEP_NS
 #define IT_MBAR_SLEEP_NS 20000u
 #endif
-// Bounded wait: gives up after WAIT_CLOCKS, or as soon as another thread of the CTA has given up.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag, int site = 1) {
-    if (mbar_test(bar, parity)) return true;
+// Bounded wait: gives up after WAIT_CLOCKS, or as soon as another thread of the CTA has given up.  The retry loop is one
+// function when IT_PIPE_OUTLINE_WAIT is defined (a kernel whose speed is its code size calls it from dozens of places);
+// it takes values only, so the caller's state stays in registers.
+#ifdef IT_PIPE_OUTLINE_WAIT
+#define IT_WAIT_SLOW static __device__ __noinline__
+#else
+#define IT_WAIT_SLOW __device__ __forceinline__
+#endif
+IT_WAIT_SLOW bool mbar_wait_retry(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag, int site) {
     const long long t0 = clock64();
     for (;;) {
         for (int i = 0; i < 8; i++) if (mbar_test_hint(bar, parity, IT_MBAR_SLEEP_NS)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_CLOCKS) { if (!*abort_flag) atomicExch(error_flag, site); *abort_flag = 1; return false; }
     }
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_flag, int site = 1) {
+    if (mbar_test(bar, parity)) return true;
+    return mbar_wait_retry(bar, parity, abort_flag, error_flag, site);
 }
 __device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

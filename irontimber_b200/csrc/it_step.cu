@@ -29,6 +29,7 @@
 //
 // Every wait (mbarrier, grid barrier) is bounded; when one runs out the CTA raises the context's error flag and an abort
 // word that makes every other CTA leave at its next barrier, drains its copies and returns (IT_ETIMEOUT on the host).
+#define IT_PIPE_OUTLINE_WAIT  // one copy of the retry loop of bounded waits
 #define IT_MATH_OUTLINE      // one copy of division, square root and the elementary functions: this kernel's code size is its speed
 #include "it_math.h"
 #include "it_engine.h"
@@ -108,7 +109,12 @@ struct Cta {
 constexpr int ST_TRACE_MAX = 1024;     // barriers recorded per traced CTA
 constexpr int ST_EVT_MAX = 2048;       // fine-grained events (diagnostics)
 // Diagnostics: slot `id` of the event area receives the nanosecond clock when the chosen thread passes (one store, no read).
+// fine-grained events are compiled in only with -DIT_STEP_EVENTS: their two dozen sites cost 2.8 KB of code, about 1 % of a step
+#ifndef IT_STEP_EVENTS
+#define ST_EV(P, c, id) do { } while (0)
+#else
 #define ST_EV(P, c, id) do { if ((P).trace && (c).evt_on && (c).lane == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); (P).trace[4 * ST_TRACE_MAX + (id)] = t_; } } while (0)
+#endif
 
 __device__ __forceinline__ void cons_sync() { consumer_barrier<ST_CT>(); }
 // four u8 x s8 products added to c
