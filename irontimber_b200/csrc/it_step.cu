@@ -431,16 +431,13 @@ __device__ __forceinline__ void gdn_phase(const StepParams& P, const StepLayer& 
     ST_EV(P, c, c.evt_base + 5);
     for (int vw = warp; vw < 16; vw += ST_NCONS) {
         const int t8 = (vw & 7) * 32 + lane; const float* wr = (vw >= 8 ? L.alpha : L.beta) + (size_t)h * P.e;
-        if (vw != warp) {
-#pragma unroll
-            for (int k = 0; k < 16; k++) { const int i = t8 + 256 * k; wv[k] = i < P.e ? wr[i] : 0.f; xv[k] = i < P.e ? __ldcg(xr + i) : 0.f; }
-        }
         double s = 0.0;
+#pragma unroll 1
+        for (int base = 0; base < P.e; base += 16 * 256) {            // one copy of the load and of the add block: the first block of the warp's own row is already in registers
+            if (vw != warp || base) {
 #pragma unroll
-        for (int k = 0; k < 16; k++) if (t8 + 256 * k < P.e) s += (double)it_mul(wv[k], xv[k]);
-        for (int base = 16 * 256; base < P.e; base += 16 * 256) {
-#pragma unroll
-            for (int k = 0; k < 16; k++) { const int i = base + t8 + 256 * k; wv[k] = i < P.e ? wr[i] : 0.f; xv[k] = i < P.e ? __ldcg(xr + i) : 0.f; }
+                for (int k = 0; k < 16; k++) { const int i = base + t8 + 256 * k; wv[k] = i < P.e ? wr[i] : 0.f; xv[k] = i < P.e ? __ldcg(xr + i) : 0.f; }
+            }
 #pragma unroll
             for (int k = 0; k < 16; k++) if (base + t8 + 256 * k < P.e) s += (double)it_mul(wv[k], xv[k]);
         }
@@ -595,7 +592,9 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
     const unsigned kf = c.at, ke = c.at + 8 * ST_AT_MAXS, vf = c.at + 16 * ST_AT_MAXS, ve = c.at + 24 * ST_AT_MAXS;
     c.att_seq++;
     if (tid == 0) {
+#pragma unroll 1
         for (int k = 0; k < 4 * ST_AT_MAXS; k++) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" :: "r"(c.at + 8 * k) : "memory");
+#pragma unroll 1
         for (int k = 0; k < ST_AT_MAXS; k++) { mbar_init(kf + 8 * k, 1); mbar_init(ke + 8 * k, 1); mbar_init(vf + 8 * k, 1); mbar_init(ve + 8 * k, vwarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -608,6 +607,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
 
     if (warp == ST_AT_LOADER) {
         // ---- loader: this CTA's K tiles, then its slice of every V tile, as far ahead as the rings allow
+#pragma unroll 1
         for (int j = 0; j < my_tiles; j++) {
             const unsigned sl = (unsigned)j % (unsigned)S, u = (unsigned)j / (unsigned)S;
             if (!mbar_wait(ke + 8 * sl, (u & 1u) ^ 1u, c.abort_flag, P.error_flag, 8)) break;
@@ -620,6 +620,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         for (int j = my_tiles > S ? my_tiles - S : 0; j < my_tiles; j++) {
             if (!mbar_wait(ke + 8 * (j % S), (unsigned)(j / S) & 1u, c.abort_flag, P.error_flag, 8)) break;
         }
+#pragma unroll 1
         for (int i = 0; i < ntiles; i++) {
             const unsigned sl = (unsigned)i % (unsigned)SV, u = (unsigned)i / (unsigned)SV;
             if (!mbar_wait(ve + 8 * sl, (u & 1u) ^ 1u, c.abort_flag, P.error_flag, 9)) break;
@@ -652,6 +653,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         for (int k = 0; k < 8; k++) if (lane + 32 * k < hd) buf[lane + 32 * k] = it_mul(it_mul(buf[lane + 32 * k], scl), wr[k]);
         __syncwarp();
         const int half = P.n_rot / 2, sect = P.sec[0] + P.sec[1] + P.sec[2] + P.sec[3];
+#pragma unroll 1
         for (int i = lane; i < half; i += 32) {
             float theta = (float)pos;
             for (int k = 0; k < i; k++) theta = it_mul(theta, P.theta_scale);
@@ -732,6 +734,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
         }
         at_sync();
         if (!*c.abort_flag) {
+#pragma unroll 1
             for (int i = 0; i < ntiles; i++) {
                 if (i % G == g) continue;
                 const int p = i * 32 + (tid & 31);
@@ -742,6 +745,7 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
     } else at_sync();
     ST_EV(P, c, c.evt_base + 8);
     float mx = -INFINITY;
+#pragma unroll 1
     for (int p = tid; p < n; p += ST_AT_T) mx = fmaxf(mx, sc[p]);
 #pragma unroll
     for (int mm = 16; mm >= 1; mm >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, mm));
@@ -750,16 +754,18 @@ __device__ __forceinline__ void attn_phase(const StepParams& P, const StepLayer&
     mx = red[0];
 #pragma unroll
     for (int k = 1; k < ST_NCONS - 1; k++) mx = fmaxf(mx, red[k]);
+#pragma unroll 1
     for (int p = tid; p < n; p += ST_AT_T) sc[p] = it_expf(it_sub(sc[p], mx));
     at_sync();
     if (tid == 0) {
         float s = 0.f;
-#pragma unroll 32
+#pragma unroll 8
         for (int p = 0; p < n; p++) s = it_add(s, sc[p]);
         red[32] = s;
     }
     at_sync();
     const float sum = red[32];
+#pragma unroll 1
     for (int p = tid; p < n; p += ST_AT_T) sc[p] = it_div(sc[p], sum);
     at_sync();
     ST_EV(P, c, c.evt_base + 9);
