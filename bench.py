@@ -491,7 +491,7 @@ def main():
             print(json.dumps(dict(base, value=args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * launches,
                                   prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64}, decode_only=True)))
             return
-        e2e_s, _ = timed_e2e(eng, prompt, args.steps)
+        e2e_s, step_hist = timed_e2e(eng, prompt, args.steps)
     out = dict(base, value=args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * launches, launches_per_step=launches,
                e2e={"value": args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "ms_per_token": e2e_s / args.steps * 1e3},
                prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64},
@@ -512,9 +512,10 @@ def main():
                 psteps = min(args.steps, 64)
                 pms, _ = timed_decode(peng, prompt, psteps)
                 plaunches = peng.step_kernels()
-                pe2e, _ = timed_e2e(peng, prompt, psteps)
+                pe2e, phist = timed_e2e(peng, prompt, psteps)
                 peng.close()
                 out["per_op_schedule"] = {"value": psteps / (pms / 1e3), "unit": "tok/s", "steps": psteps, "launches_per_step": plaunches, "e2e": psteps / pe2e,
+                                          "same_picks_as_step_kernel": phist == step_hist[:len(phist)], "picks_compared": len(phist),
                                           "note": "the same decode as one kernel launch per op instead of the persistent step kernel (IT_STEP_KERNEL=0)"}
             finally:
                 del os.environ["IT_STEP_KERNEL"]
