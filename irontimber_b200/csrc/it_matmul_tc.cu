@@ -3,7 +3,8 @@
 // (src/cpu.rs:48-63); it takes the place of the 64x64 tile kernels VkEngine::mv selects for prompt chunks
 // (src/vk/mod.rs:655-677).
 //
-// A CTA owns 128 matrix rows (four 32-row groups) x 64 activation rows and walks the 128-column blocks in order.
+// A CTA owns 128 matrix rows (four 32-row groups) x 64 activation rows (x 128 when the launch has more than 64: one
+// expanded tile and one issue sequence then feed twice the columns) and walks the 128-column blocks in order.
 //   warp 24  producer: per block one stage = four weight tiles (bulk copies) + the 64 x 128 int8 activations as one
 //            box of a tiled tensor map with the 128-byte swizzle, i.e. already in the K-major layout the MMA reads
 //   warps 16-23 expanders (two sets of four, alternating blocks): turn the packed 2-bit codes of a stage into a 128 x 128 tile of unsigned bytes (codes 0..3)
@@ -26,28 +27,37 @@
 
 namespace {
 
-constexpr int TC_TOK = 64;                       // activation rows per CTA (N of the MMA)
 constexpr int TC_ROWS = 128;                     // matrix rows per CTA (M of the MMA)
-constexpr int TC_X_BYTES = TC_TOK * 128;         // one box of the activation tensor map
 constexpr int TC_A_BYTES = TC_ROWS * 128;        // one expanded weight tile
 constexpr int TC_KB = 4;                         // blocks per weight stage: one bulk copy per row group and stage (issuing a bulk copy costs a
                                                  // thread some 250 cycles, so four small copies per block made the producer the bottleneck)
 constexpr int TC_W_BYTES = 4 * TC_KB * IT_TILE_BYTES;   // four row groups x TC_KB consecutive tiles
-constexpr int TC_XS = 6;                         // activation boxes in flight (they come from L2)
 constexpr int TC_NA = 2;                         // expanded tiles in flight
-constexpr int TC_ND = 8;                         // accumulators in tensor memory: the MMA -> read-out -> release loop is long, so many are in flight
-constexpr int TC_NDW = 16;                       // ring of per-block row scales (expanders run at most TC_NA + TC_ND blocks ahead of the epilogue)
+constexpr int TC_NDW = 16;                       // ring of per-block row scales (expanders run at most TC_NA + ND blocks ahead of the epilogue)
 constexpr int TC_SMEM_MAX = 226 * 1024;
-constexpr unsigned TC_TMEM_COLS = TC_ND * TC_TOK; // all 512 columns: 8 accumulators x 64 columns
-constexpr int TC_EPI_GROUPS = 4, TC_EPI_TOK = TC_TOK / TC_EPI_GROUPS, TC_EPI_WARPS = 4 * TC_EPI_GROUPS;   // epilogue warps 0..15
-constexpr int TC_ESETS = 2;                      // sets of four expander warps; set e expands the blocks b with b % TC_ESETS == e
-constexpr int TC_EXP_WARPS = 4 * TC_ESETS;
-constexpr int TC_THREADS = (TC_EPI_WARPS + TC_EXP_WARPS + 3) * 32;   // + weight producer, MMA issuer, activation producer
+constexpr unsigned TC_TMEM_COLS = 512;           // all of it: ND accumulators x TOK columns
+constexpr int TC_EPI_GROUPS = 4, TC_EPI_WARPS = 4 * TC_EPI_GROUPS;   // epilogue warps 0..15
+// NH: 64-row halves of the CTA's activation tile.  NH = 1: 64 activation rows per CTA (prompt passes of up to 64 rows).
+// NH = 2: 128 rows: one expanded weight tile and one issue sequence feed twice the columns, which is what the kernel is
+// bound by (the tensor pipe is 8 % busy at 64 rows); the epilogue then folds 32 values per thread and block.
+template <int NH> struct Tc {
+    static constexpr int TOK = 64 * NH;                  // activation rows per CTA (N of the MMA)
+    static constexpr int X_BYTES = TOK * 128;            // the activation tile of one block: NH boxes of the tensor map, one under the other
+    static constexpr int XS = NH == 1 ? 6 : 3;           // activation tiles in flight (they come from L2)
+    static constexpr int ND = 512 / TOK;                 // accumulators in tensor memory: the MMA -> read-out -> release loop is long, so many are in flight
+    static constexpr int EPI_TOK = TOK / TC_EPI_GROUPS;  // activation rows per epilogue thread
+    static constexpr int ESETS = NH == 1 ? 2 : 1;        // sets of four expander warps; set e expands the blocks b with b % ESETS == e
+    static constexpr int EXP_WARPS = 4 * ESETS;
+    static constexpr int THREADS = (TC_EPI_WARPS + EXP_WARPS + 3) * 32;   // + weight producer, MMA issuer, activation producer
+    // kind::i8 instruction descriptor: D s32, A unsigned 8 bit, B signed 8 bit, both K-major, N = TOK, M = 128
+    static constexpr unsigned IDESC = (2u << 4) | (0u << 7) | (1u << 10) | ((unsigned)(TOK >> 3) << 17) | ((unsigned)(TC_ROWS >> 4) << 24);
+};
 
 // Weight stages and activation boxes have rings of their own: the weights come from HBM (a deep ring, about 70 KB in
 // flight per SM, hides its latency), the boxes from L2.
 struct TcSmem { int x, a, w, dx, s128, dw, bars, tmem, flag, total; };
-__host__ __device__ inline TcSmem tc_layout(int nb, int wstages) {
+template <int NH> __host__ __device__ inline TcSmem tc_layout(int nb, int wstages) {
+    constexpr int TC_XS = Tc<NH>::XS, TC_X_BYTES = Tc<NH>::X_BYTES, TC_TOK = Tc<NH>::TOK, TC_ND = Tc<NH>::ND;
     TcSmem L; int o = 0;
     L.x = o; o += TC_XS * TC_X_BYTES;              // 1024-byte aligned (128-byte swizzle)
     L.a = o; o += TC_NA * TC_A_BYTES;              // 1024-byte aligned
@@ -68,14 +78,11 @@ __host__ __device__ inline TcSmem tc_layout(int nb, int wstages) {
 __device__ __forceinline__ unsigned long long tc_smem_desc(unsigned addr) {
     return (unsigned long long)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-// kind::i8 instruction descriptor: D s32, A unsigned 8 bit, B signed 8 bit, both K-major, N = 64, M = 128
-constexpr unsigned TC_IDESC = (2u << 4) | (0u << 7) | (1u << 10) | ((unsigned)(TC_TOK >> 3) << 17) | ((unsigned)(TC_ROWS >> 4) << 24);
-
 template <bool ACC>
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc) {
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc, unsigned idesc) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "n"(ACC ? 1 : 0), "r"(0u) : "memory");
+                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void tc_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
@@ -87,15 +94,20 @@ __device__ __forceinline__ void tc_ld16(unsigned taddr, int (&v)[16]) {
                  : "r"(taddr) : "memory");
 }
 
-__device__ __forceinline__ float tc_int_to_float(int v) { return __fsub_rn(__int_as_float(0x4B400000 + v), 12582912.0f); }   // exact below 2^22
+// v + 0x4B400000 (the bit pattern of 1.5 * 2^23 plus an integer of magnitude below 2^22) as the float v, exactly; the block's
+// -sum128 and the constant are one shared-memory word, so the conversion costs one integer and one float addition
+__device__ __forceinline__ float tc_biased_to_float(int biased) { return __fsub_rn(__int_as_float(biased), 12582912.0f); }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int NH>
+__global__ void __launch_bounds__(Tc<NH>::THREADS, 1)
 k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict__ tiles, int nb, int rows, int row_groups, int wstages,
             const float* __restrict__ xd, const int32_t* __restrict__ xs128, int x_stride, int ntok,
             float* arena, size_t y_off, size_t y_stride, int accum, int* error_flag, const it_peers* peers, const it_rowmap map) {
+    constexpr int TC_TOK = Tc<NH>::TOK, TC_X_BYTES = Tc<NH>::X_BYTES, TC_XS = Tc<NH>::XS, TC_ND = Tc<NH>::ND, TC_EPI_TOK = Tc<NH>::EPI_TOK,
+                  TC_ESETS = Tc<NH>::ESETS, TC_EXP_WARPS = Tc<NH>::EXP_WARPS;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const TcSmem L = tc_layout(nb, wstages);
+    const TcSmem L = tc_layout<NH>(nb, wstages);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.flag);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + L.tmem);
@@ -160,7 +172,9 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                 // the box slot was last read by block b - TC_XS: wait for that block's commit
                 if (b >= TC_XS && !mbar_wait(dfull0 + 8 * ((b - TC_XS) % TC_ND), (unsigned)((b - TC_XS) / TC_ND) & 1u, abort_flag, error_flag, 19)) break;
                 mbar_expect_tx(xfull0 + 8 * s, (unsigned)TC_X_BYTES);
-                tma_load_2d(smem_u32(smem + L.x + s * TC_X_BYTES), &xmap, b * 128, tok0, xfull0 + 8 * s);
+#pragma unroll
+                for (int hh = 0; hh < NH; hh++)     // 64 rows per box; the boxes of a block lie one under the other like one box of TOK rows
+                    tma_load_2d(smem_u32(smem + L.x + s * TC_X_BYTES + hh * 64 * 128), &xmap, b * 128, tok0 + 64 * hh, xfull0 + 8 * s);
                 issued++;
                 if (++s == TC_XS) s = 0;
             }
@@ -186,10 +200,10 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
                 // descriptors differ from the first tile's only in the start-address field (16-byte units): + tile index, + 2 per K step of 32
                 const unsigned long long ad = adesc0 + (unsigned)(a * (TC_A_BYTES >> 4)), bd = bdesc0 + (unsigned)(s * (TC_X_BYTES >> 4));
                 const unsigned dt = tmem_base + (unsigned)(d * TC_TOK);
-                tc_mma<false>(dt, ad, bd);
-                tc_mma<true>(dt, ad + 2, bd + 2);
-                tc_mma<true>(dt, ad + 4, bd + 4);
-                tc_mma<true>(dt, ad + 6, bd + 6);
+                tc_mma<false>(dt, ad, bd, Tc<NH>::IDESC);
+                tc_mma<true>(dt, ad + 2, bd + 2, Tc<NH>::IDESC);
+                tc_mma<true>(dt, ad + 4, bd + 4, Tc<NH>::IDESC);
+                tc_mma<true>(dt, ad + 6, bd + 6, Tc<NH>::IDESC);
                 tc_commit(dfull0 + 8 * d);        // accumulator complete; tile and box of this block may be reused
                 if (++s == TC_XS) s = 0;
                 if (++a == TC_NA) { a = 0; aph ^= 1u; }
@@ -242,7 +256,7 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
         asm volatile("griddepcontrol.wait;" ::: "memory");            // q8 scales, block sums and (when accumulating) y come from earlier kernels
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         for (int i = tid; i < (nb / 2) * TC_TOK; i += NEPI) { const int m = i % TC_TOK, bb = i / TC_TOK; dxs[i] = m < ntv ? xd[(size_t)(tok0 + m) * (x_stride / 256) + bb] : 0.f; }
-        for (int i = tid; i < nb * TC_TOK; i += NEPI) { const int m = i % TC_TOK, bb = i / TC_TOK; sss[i] = m < ntv ? xs128[(size_t)(tok0 + m) * (x_stride / 128) + bb] : 0; }
+        for (int i = tid; i < nb * TC_TOK; i += NEPI) { const int m = i % TC_TOK, bb = i / TC_TOK; sss[i] = 0x4B400000 - (m < ntv ? xs128[(size_t)(tok0 + m) * (x_stride / 128) + bb] : 0); }   // ready to be added to the integer block sum: see tc_int_to_float
         asm volatile("bar.sync 1, %0;" :: "n"(NEPI) : "memory");
         const int grp = warp >> 2, r = 32 * (warp & 3) + lane, m0 = grp * TC_EPI_TOK;
         const bool active = m0 < ntv;              // groups past the last activation row only release the accumulators
@@ -256,7 +270,9 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
             int S[TC_EPI_TOK];
             if (active) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tc_ld16(tmem_base + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)(d * TC_TOK + m0), S);
+#pragma unroll
+                for (int cch = 0; cch < TC_EPI_TOK / 16; cch++)
+                    tc_ld16(tmem_base + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)(d * TC_TOK + m0 + 16 * cch), *reinterpret_cast<int (*)[16]>(&S[16 * cch]));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
@@ -269,10 +285,10 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
 #pragma unroll
                 for (int q = 0; q < TC_EPI_TOK / 4; q++) {
                     const float4 dx = dx4[q]; const int4 sb = s4[q];
-                    acc[4 * q + 0] = __fadd_rn(acc[4 * q + 0], __fmul_rn(__fmul_rn(dw, dx.x), tc_int_to_float(S[4 * q + 0] - sb.x)));
-                    acc[4 * q + 1] = __fadd_rn(acc[4 * q + 1], __fmul_rn(__fmul_rn(dw, dx.y), tc_int_to_float(S[4 * q + 1] - sb.y)));
-                    acc[4 * q + 2] = __fadd_rn(acc[4 * q + 2], __fmul_rn(__fmul_rn(dw, dx.z), tc_int_to_float(S[4 * q + 2] - sb.z)));
-                    acc[4 * q + 3] = __fadd_rn(acc[4 * q + 3], __fmul_rn(__fmul_rn(dw, dx.w), tc_int_to_float(S[4 * q + 3] - sb.w)));
+                    acc[4 * q + 0] = __fadd_rn(acc[4 * q + 0], __fmul_rn(__fmul_rn(dw, dx.x), tc_biased_to_float(S[4 * q + 0] + sb.x)));
+                    acc[4 * q + 1] = __fadd_rn(acc[4 * q + 1], __fmul_rn(__fmul_rn(dw, dx.y), tc_biased_to_float(S[4 * q + 1] + sb.y)));
+                    acc[4 * q + 2] = __fadd_rn(acc[4 * q + 2], __fmul_rn(__fmul_rn(dw, dx.z), tc_biased_to_float(S[4 * q + 2] + sb.z)));
+                    acc[4 * q + 3] = __fadd_rn(acc[4 * q + 3], __fmul_rn(__fmul_rn(dw, dx.w), tc_biased_to_float(S[4 * q + 3] + sb.w)));
                 }
             }
             if (++d == TC_ND) { d = 0; dph ^= 1u; }
@@ -298,24 +314,32 @@ k_matmul_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t* __restrict_
 
 }  // namespace
 
-// Returns IT_OK after launching, or a positive value when the shape does not suit this kernel (the caller then uses k_matmul_t2).
-int it_matmul_tc_launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum) {
+template <int NH>
+static int tc_launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum) {
     const int nb = (int)(w->cols / 128);
     int stages = 5;                        // weight stages of TC_KB blocks: as deep as shared memory allows (about 70 KB in flight)
-    while (stages > 2 && tc_layout(nb, stages).total + 1024 > TC_SMEM_MAX) stages--;
-    const TcSmem L = tc_layout(nb, stages);
+    while (stages > 2 && tc_layout<NH>(nb, stages).total + 1024 > TC_SMEM_MAX) stages--;
+    const TcSmem L = tc_layout<NH>(nb, stages);
     if (L.total + 1024 > TC_SMEM_MAX) return 1;
     static bool attr_set[16] = {};
-    if (!attr_set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(k_matmul_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_MAX)); attr_set[c->device & 15] = true; }
+    if (!attr_set[c->device & 15]) { IT_CUDA(cudaFuncSetAttribute(k_matmul_tc<NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_MAX)); attr_set[c->device & 15] = true; }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((w->row_groups + 3) / 4), (unsigned)((ntok + TC_TOK - 1) / TC_TOK));
-    cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = (size_t)L.total + 1024; cfg.stream = c->stream;
+    cfg.gridDim = dim3((unsigned)((w->row_groups + 3) / 4), (unsigned)((ntok + Tc<NH>::TOK - 1) / Tc<NH>::TOK));
+    cfg.blockDim = dim3(Tc<NH>::THREADS); cfg.dynamicSmemBytes = (size_t)L.total + 1024; cfg.stream = c->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    IT_CUDA(cudaLaunchKernelEx(&cfg, k_matmul_tc, x->tmap, (const uint8_t*)w->tiles, nb, (int)w->rows, (int)w->row_groups, stages,
+    IT_CUDA(cudaLaunchKernelEx(&cfg, k_matmul_tc<NH>, x->tmap, (const uint8_t*)w->tiles, nb, (int)w->rows, (int)w->row_groups, stages,
         (const float*)x->d, (const int32_t*)x->sum128, (int)x->max_n, ntok, c->arena, (size_t)(y - c->arena), y_stride, accum, c->error_flag_dev,
         (const it_peers*)(w->sharded ? c->peers_dev : nullptr), w->map));
     c->pdl_safe_q8 = x;
     return IT_OK;
+}
+
+// Returns IT_OK after launching, or a positive value when the shape does not suit this kernel (the caller then uses k_matmul_t2).
+// More than 64 activation rows go to the 128-row variant when its buffers fit (rows of up to about 12,000 columns).
+int it_matmul_tc_launch(it_ctx* c, const it_mat* w, int ntok, const it_q8* x, float* y, size_t y_stride, int accum) {
+    static const bool wide = []{ const char* v = getenv("IT_MATMUL_WIDE"); return !v || atoi(v) != 0; }();
+    if (wide && ntok > 64) { const int r = tc_launch<2>(c, w, ntok, x, y, y_stride, accum); if (r != 1) return r; }
+    return tc_launch<1>(c, w, ntok, x, y, y_stride, accum);
 }

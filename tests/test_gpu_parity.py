@@ -156,12 +156,14 @@ def test_matvec_t2_model_shapes_bit_exact(be, orc, rows, cols):
 
 
 @pytest.mark.parametrize("rows,cols,ntok,acc", [(1001, 1024, 22, False), (999, 1024, 64, True), (1000, 2048, 65, False), (96, 1024, 130, True),
-                                               (17408, 5120, 64, False), (5120, 17408, 64, True), (10240, 5120, 40, False), (1024, 5120, 64, False)])
+                                               (17408, 5120, 64, False), (5120, 17408, 64, True), (10240, 5120, 40, False), (1024, 5120, 64, False),
+                                               (17408, 5120, 128, False), (2048, 5120, 200, True), (1024, 2048, 512, False), (640, 6144, 129, True)])
 @pytest.mark.parametrize("kernel", ["tc", "legacy"])
 def test_matmul_t2_tile_kernel_bit_exact(be, orc, rows, cols, ntok, acc, kernel, monkeypatch):
     """More than eight activation rows go through the tile kernel (the role of matmul_t2, src/vk/mod.rs:655-677): every
     row tile width of its policy, ragged row groups and ragged activation tiles, same bits as the CPU's row-by-row matvec.
-    Both implementations are forced in turn: "tc" = tcgen05.mma with accumulators in tensor memory, "legacy" = mma.sync."""
+    Both implementations are forced in turn: "tc" = tcgen05.mma with accumulators in tensor memory (64 activation rows per
+    CTA, 128 when there are more than 64), "legacy" = mma.sync."""
     monkeypatch.setenv("IT_MATMUL", kernel)
     rng = np.random.default_rng(rows + cols + ntok)
     raw = synth_pq2(rows * 3 + cols, rows, cols) if rows >= 1024 else make_pq2(rng, rows, cols, ncodes=4)[0]
