@@ -489,12 +489,12 @@ def main():
         if args.decode_only:
             eng.close()
             print(json.dumps(dict(base, value=args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * launches,
-                                  prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64}, decode_only=True)))
+                                  prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 256}, decode_only=True)))
             return
         e2e_s, step_hist = timed_e2e(eng, prompt, args.steps)
     out = dict(base, value=args.steps / (ms / 1e3), ms_per_step=ms / args.steps, clocks=clocks.summary(), gpu_launches=args.steps * launches, launches_per_step=launches,
                e2e={"value": args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4, "ms_per_token": e2e_s / args.steps * 1e3},
-               prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 64},
+               prefill={"tokens": args.prompt, "seconds": prefill_s, "tok_s": args.prompt / prefill_s, "rows_per_pass": 256},
                step_weight_gbs=step_weight_bytes(cfg) * args.steps / (ms / 1e3) / 1e9)
     if world == 1 and not args.no_extras:
         rng = np.random.default_rng(300)

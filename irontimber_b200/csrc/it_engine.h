@@ -5,7 +5,8 @@
 #include <map>
 #include <vector>
 
-#define IT_MAXT 64    // activation rows per pass: the prompt chunk of prefill_chunks (src/vk/mod.rs:130-134)
+#define IT_MAXT 256   // activation rows per pass: the prompt chunk of prefill_chunks (src/vk/mod.rs:130-134 uses 64; the chunk size changes no result,
+                      // and with 256 rows the tile kernels pay their per-block cost once per 128 rows and the row-parallel kernels fill the GPU)
 #define IT_MAXLOGIT 8 // rows of a pass that can get logits and a greedy pick (verification passes)
 #define IT_MAXCK 3    // recurrent-state checkpoints per pass (rows 0..2 of a verification pass)
 

@@ -3,8 +3,9 @@
 // The schedule of one pass is the reference's run_chunk_v (src/vk/mod.rs:763-892): per layer norm -> Hadamard ->
 // grouped ternary matvecs -> delta-rule or attention block -> Hadamard -> output matvec (accumulating into the residual)
 // -> norm -> Hadamard -> gate / up -> silu*mul -> Hadamard -> down (accumulating).  Differences: the Hadamard is fused
-// with q8k quantisation (the CPU numerics), embeddings are gathered on the device, and a pass takes up to 64 rows (the
-// reference's prompt chunk): passes of more than eight rows run their ternary products on the tile kernel.
+// with q8k quantisation (the CPU numerics), embeddings are gathered on the device, and a pass takes up to IT_MAXT rows (four
+// times the reference's prompt chunk; the chunk size changes no result): passes of more than eight rows run their ternary
+// products on the tile kernels.
 #include "it_engine.h"
 #include "it_support.h"
 #include <algorithm>
@@ -34,7 +35,6 @@ int logits_and_argmax(it_engine* e, size_t h_off, int rows) {
 
 }  // namespace
 
-static_assert(IT_MAXT <= IT_GDN_MAXROWS, "a pass must fit the delta-rule kernel's staging");
 // The next block of the pinned staging ring.  Copies out of a block are asynchronous and the host runs passes ahead of the
 // device, so a block is reused only after a synchronisation has shown that every copy out of the ring has run.
 static uint32_t* pin_block(it_engine* e) {
@@ -83,8 +83,13 @@ int it_engine_run_chunk(it_engine* e, const uint32_t* toks, int nt, int logit_ro
             }
             if (sd == 128) {
                 // [delta rule | gated norm] in one launch, for any number of rows (the state stays in shared memory across the rows)
-                IT_TRY(it_sup_gdn_norm(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck,
-                                       l.ssm_norm, c.eps, A + L.big1 + cd, s_gdn));
+                // (the kernel stages up to IT_GDN_MAXROWS rows at a time; the state carries over from one launch to the next)
+                for (int t0 = 0; t0 < nt; t0 += IT_GDN_MAXROWS) {
+                    const int n0 = std::min(IT_GDN_MAXROWS, nt - t0);
+                    IT_TRY(it_sup_gdn_norm(cx, A + L.conv + (size_t)t0 * cd, cd, A + L.beta + (size_t)t0 * nv, A + L.alpha + (size_t)t0 * nv, nv, l.dt, l.a, l.ssm_st,
+                                           A + L.o + (size_t)t0 * inner, inner, nv, nk, sd, qk, n0, l.ck_ssm, ssz, t0 ? 0 : nck,
+                                           l.ssm_norm, c.eps, A + L.big1 + cd + (size_t)t0 * s_gdn, s_gdn));
+                }
             } else {
                 IT_TRY(it_sup_gdn(cx, A + L.conv, cd, A + L.beta, A + L.alpha, nv, l.dt, l.a, l.ssm_st, A + L.o, inner, nv, nk, sd, qk, nt, l.ck_ssm, ssz, nck));
                 IT_TRY(it_sup_norm_head(cx, A + L.o, sd, inner, A + L.o, sd, inner, sd, nv, l.ssm_norm, 1, c.eps, A + L.big1 + cd, sd, s_gdn, nt));

@@ -105,14 +105,15 @@ def test_speculative_decode_equals_plain_greedy_with_oracle_counts(orc, pair):
     assert out == plain[:12] and st["rejected"] == 0 and st["accepted"] == st["drafted"] > 0
 
 
-def test_long_prompt_in_64_row_passes_bit_exact(orc):
-    """A 75-token prompt runs as one pass of 64 rows and one of 11 (prefill_chunks, src/vk/mod.rs:130-134): logits, the
-    greedy continuation and the speculative loop with its head catch-up across passes equal the token-by-token oracle."""
+def test_long_prompt_in_several_passes_bit_exact(orc):
+    """A 300-token prompt runs as one pass of 256 rows and one of 44 (prefill_chunks, src/vk/mod.rs:130-134, with a larger
+    chunk): logits, the greedy continuation and the speculative loop with its head catch-up across passes equal the
+    token-by-token oracle."""
     from irontimber_b200.engine import CudaEngine, ModelConfig
-    eng = CudaEngine(tiny_config(ModelConfig, ctx_len=128), seed=23, with_mtp=True)
+    eng = CudaEngine(tiny_config(ModelConfig, ctx_len=352), seed=23, with_mtp=True)
     m = oracle_model_from_engine(orc, eng, with_mtp=True)
     try:
-        prompt = [int(t) for t in np.random.default_rng(9).integers(0, eng.cfg.n_vocab, 75)]
+        prompt = [int(t) for t in np.random.default_rng(9).integers(0, eng.cfg.n_vocab, 300)]
         lg = eng.eval(prompt)
         st = m.new_state()
         for i, t in enumerate(prompt):
@@ -252,14 +253,14 @@ def test_step_kernel_and_per_op_schedule_agree(orc, monkeypatch):
 
 
 def test_prompt_of_several_full_passes_bit_exact(orc):
-    """A 330-token prompt is five 64-row passes and one of 10 rows, enqueued back to back while the device still works on
+    """A 1100-token prompt is four 256-row passes and one of 76 rows, enqueued back to back while the device still works on
     the first: every pass must see its own token ids (the host stages them in a ring of pinned blocks).  Logits, state and
     the continuation (attention over more K / V tiles than the step kernel's ring holds) equal the token-by-token oracle."""
     from irontimber_b200.engine import CudaEngine, ModelConfig
-    eng = CudaEngine(tiny_config(ModelConfig, ctx_len=448), seed=43, with_mtp=False)
+    eng = CudaEngine(tiny_config(ModelConfig, ctx_len=1152), seed=43, with_mtp=False)
     m = oracle_model_from_engine(orc, eng, with_mtp=False)
     try:
-        prompt = [int(t) for t in np.random.default_rng(77).integers(0, 1000, 330)]
+        prompt = [int(t) for t in np.random.default_rng(77).integers(0, 1000, 1100)]
         st = m.new_state()
         for i, t in enumerate(prompt):
             want = m.forward_token(st, t, i + 1 == len(prompt), orc.DEVICE_ORDER)

@@ -20,13 +20,15 @@ N_VOCAB = 2048
 @pytest.fixture(scope="module")
 def pair(orc):
     from irontimber_b200.engine import CudaEngine, config_27b
-    eng = CudaEngine(config_27b(n_layer=4, ctx_len=128, n_vocab=N_VOCAB), seed=17, with_mtp=True)
+    eng = CudaEngine(config_27b(n_layer=4, ctx_len=320, n_vocab=N_VOCAB), seed=17, with_mtp=True)
     model = oracle_model_from_engine(orc, eng, with_mtp=True)
     yield eng, model
     model.close(); eng.close()
 
 
-PROMPT = [int(t) for t in np.random.default_rng(27).integers(0, N_VOCAB, 70)]     # one pass of 64 rows + a ragged one of 6
+PROMPT = [int(t) for t in np.random.default_rng(27).integers(0, N_VOCAB, 70)]     # one ragged pass of 70 rows
+LONG_PROMPT = [int(t) for t in np.random.default_rng(28).integers(0, N_VOCAB, 262)]  # one pass of 256 rows + a ragged one of 6
+ROWS_PER_PASS = 256
 
 
 def test_prompt_passes_logits_state_and_hidden_bit_exact(orc, pair):
@@ -38,7 +40,7 @@ def test_prompt_passes_logits_state_and_hidden_bit_exact(orc, pair):
         want = m.forward_token(st, t, i + 1 == len(PROMPT), orc.DEVICE_ORDER)
     assert np.array_equal(bits(lg), bits(want))
     assert eng.pos == m.state_pos(st) == len(PROMPT)
-    assert np.array_equal(bits(eng.hidden(len(PROMPT) - 64 - 1)), bits(m.state_h(st)))     # last row of the ragged pass
+    assert np.array_equal(bits(eng.hidden((len(PROMPT) - 1) % ROWS_PER_PASS)), bits(m.state_h(st)))     # last row of the last pass
     for il in range(eng.cfg.n_layer):
         kinds = (0, 1) if eng.cfg.is_recurrent(il) else (2, 3)
         for kind in kinds:
@@ -47,6 +49,23 @@ def test_prompt_passes_logits_state_and_hidden_bit_exact(orc, pair):
     for t in (3, 1999):
         lg = eng.eval([t]); want = m.forward_token(st, t, True, orc.DEVICE_ORDER)
         assert np.array_equal(bits(lg), bits(want))
+    m.free_state(st)
+
+
+def test_two_prompt_passes_logits_and_state_bit_exact(orc, pair):
+    """262 tokens: a full pass of 256 rows (the tile kernels' 128-row CTAs, four launches of the delta-rule kernel) and a
+    ragged pass of 6 rows that continues from its state."""
+    eng, m = pair
+    eng.reset()
+    lg = eng.eval(LONG_PROMPT)
+    st = m.new_state()
+    for i, t in enumerate(LONG_PROMPT):
+        want = m.forward_token(st, t, i + 1 == len(LONG_PROMPT), orc.DEVICE_ORDER)
+    assert np.array_equal(bits(lg), bits(want))
+    assert np.array_equal(bits(eng.hidden((len(LONG_PROMPT) - 1) % ROWS_PER_PASS)), bits(m.state_h(st)))
+    for il in range(eng.cfg.n_layer):
+        for kind in ((0, 1) if eng.cfg.is_recurrent(il) else (2, 3)):
+            assert np.array_equal(bits(eng.state(il, kind)), bits(m.state_read(st, il, kind))), f"state {kind} of layer {il}"
     m.free_state(st)
 
 
